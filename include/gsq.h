@@ -1,0 +1,166 @@
+/*
+ * gsq.h -- C ABI of the B200 (sm_100a) GGUF quantised-linear kernels.
+ *
+ * This is the drop-in boundary for the "Route L" path of vllm_gguf_plugin: each
+ * entry point below replaces one piece of plugin/vllm_gguf_plugin/csrc/lcpp_shim.cu
+ * (and the kernels it launches) of the reference. All pointers are raw device
+ * pointers unless stated otherwise; sizes are plain integers; `stream` is a
+ * cudaStream_t passed as void*. No function allocates device memory, synchronises
+ * the device or throws: every one returns GSQ_OK (0) or a negative status, and
+ * gsq_strerror() names it. The caller (the Python registration layer, which mirrors
+ * the reference's torch ops `_C_gguf::lcpp_*`) owns every buffer.
+ *
+ * ggml type ids are those of gguf.GGMLQuantizationType: Q4_K 12, Q6_K 14,
+ * IQ3_S 21, IQ4_XS 23.
+ */
+#ifndef GSQ_H
+#define GSQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GSQ_TYPE_Q4_K 12
+#define GSQ_TYPE_Q6_K 14
+#define GSQ_TYPE_IQ3_S 21
+#define GSQ_TYPE_IQ4_XS 23
+
+/* element types of X / Y */
+#define GSQ_F32 0
+#define GSQ_F16 1
+#define GSQ_BF16 2
+/* anything else the caller could not map (guards reject it) */
+#define GSQ_DTYPE_OTHER 99
+
+/* q8_1 scale layouts of the 128-value activation blocks (mmq.cuh:60-101 of the vendored llama.cpp) */
+#define GSQ_Q8_LAYOUT_D4 0  /* 4 x fp32 d            : IQ3_S, IQ4_XS, Q6_K */
+#define GSQ_Q8_LAYOUT_DS4 1 /* 4 x half2 (d, sum x)  : Q4_K */
+
+/* status codes */
+#define GSQ_OK 0
+#define GSQ_ERR_GUARD -1     /* an input guard fired; message written to the caller's buffer */
+#define GSQ_ERR_CUDA -2      /* a CUDA runtime call failed (see gsq_last_cuda_error) */
+#define GSQ_ERR_UNSUPPORTED -3
+#define GSQ_ERR_SCRATCH -4   /* scratch buffer missing or too small */
+#define GSQ_ERR_TOO_LARGE -5 /* shape exceeds what the kernel (or the static buffer) can hold */
+#define GSQ_ERR_DEVICE -6    /* kernel reported an internal error flag (bounded wait gave up) */
+
+/* kernel selectors returned by gsq_route / accepted by gsq_mul_mat */
+#define GSQ_KERNEL_NONE 0
+#define GSQ_KERNEL_GEMV 1 /* dp4a streaming GEMV, 1..8 activation rows, reads block_q8_1 */
+#define GSQ_KERNEL_GEMM 2 /* tcgen05 kind::i8 GEMM, any rows, reads 128-value q8_1 blocks */
+
+const char* gsq_strerror(int status);
+/* cudaError_t of the last failing CUDA call made by this library on this thread (0 if none). */
+int gsq_last_cuda_error(void);
+
+/* ABI version of this header; bumped when a signature changes. */
+int gsq_abi_version(void);
+
+/* Bytes per 256-value superblock of a ggml type, 0 if the type is not supported. */
+int gsq_type_block_bytes(int ggml_type);
+
+/*
+ * Input guards of every product op: replaces check_inputs() and the per-kernel
+ * checks at the top of run() (lcpp_shim.cu:690-732, 767-791). Nothing here touches
+ * CUDA, so it also runs for CPU tensors (the reference registers its ops for the
+ * CPU dispatch key for the same reason, lcpp_shim.cu:997-1008).
+ *   op           name used as the message prefix ("lcpp_mul_mat_vec_q", ...)
+ *   w_*          W: dim count, dtype is uint8?, sizes, strides (elements), data address
+ *   x_*          X likewise; x_dtype one of GSQ_F32/F16/BF16 or GSQ_DTYPE_OTHER
+ *   row          number of weight rows to use
+ *   max_rows     limit on X rows (0 = none)
+ *   need_iq3 / need_q4k_own / need_mma_k / is_mmq / packed : which op-specific type checks apply
+ *   k_multiple   512 for the reference-compatible ops, 256 for the tensor-parallel entry points
+ *   w_is_cuda, x_is_cuda, same_device : device facts, checked last
+ * On failure writes a NUL-terminated message into msg[0..msg_len) and returns GSQ_ERR_GUARD.
+ * On success stores the logical column count in *k_out.
+ */
+typedef struct gsq_guard_args {
+  const char* op;
+  int w_dim, w_is_uint8;
+  int64_t w_size0, w_size1, w_stride0, w_stride1;
+  uint64_t w_addr;
+  int x_dim, x_dtype;
+  int64_t x_size0, x_size1, x_stride0, x_stride1;
+  int64_t row, max_rows;
+  int ggml_type;
+  int need_iq3, need_q4k_own, need_mma_k, is_mmq, packed;
+  int k_multiple;
+  int w_is_cuda, x_is_cuda, same_device;
+} gsq_guard_args;
+int gsq_check_inputs(const gsq_guard_args* a, int64_t* k_out, char* msg, size_t msg_len);
+
+/*
+ * One-time per-device set-up (shared-memory opt-in of the kernels, SM count cache). Call once per
+ * device before the first launch and outside any stream capture; the reference needed a
+ * dedicated test because its occupancy caches could be filled inside a capture
+ * (tests/gpu/test_kernel_parity.py:655-698). Every launch entry point calls it lazily too.
+ */
+int gsq_device_init(int device);
+
+/*
+ * q8_1 quantisation, MMVQ layout: replaces quantize_q8_1_x (lcpp_shim.cu:274-294, launch 361-368).
+ * x [m, k] with row stride x_row_stride elements -> out: m * k/32 blocks of 36 bytes
+ * (32 x int8, half d, half sum), rows contiguous. k % 32 == 0.
+ */
+int gsq_quantize_q8_1(const void* x, int x_dtype, int64_t m, int64_t k, int64_t x_row_stride, void* out,
+                      void* stream);
+
+/*
+ * q8_1 quantisation, 128-value blocks: replaces quantize_mmq_q8_1_x (lcpp_shim.cu:298-355).
+ * out: k/128 * m blocks of 144 bytes (16 scale bytes in `layout`, then 128 x int8); block (kb, row)
+ * sits at (kb * m + row) * 144. k % 128 == 0.
+ */
+int gsq_quantize_q8_1_mmq(const void* x, int x_dtype, int64_t m, int64_t k, int64_t x_row_stride, int layout,
+                          void* out, void* stream);
+
+/*
+ * Streaming GEMV, 1..8 activation rows: replaces the vendored MMVQ (ggml_cuda_op_mul_mat_vec_q,
+ * mmvq.cu:1538) and the owned 1..8-row kernels iq3_mul_mat_vec (lcpp_shim.cu:498-572),
+ * own_mul_mat_vec (lcpp_owned_k4.cu:116-234), iq3_mma / iq3_mma_packed
+ * (lcpp_owned_iq3_mma.cu:179-328, 483-600).
+ *   w            uint8 [rows, row_bytes] GGUF blocks (packed != 0: IQ3_S in gsq_iq3s_repack's layout)
+ *   x_q8         m * k/32 block_q8_1 (36 bytes each)
+ *   y            [m, rows] in y_dtype, row stride y_row_stride elements
+ */
+int gsq_mul_mat_vec_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,
+                       const void* x_q8, int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride,
+                       void* stream);
+
+/*
+ * Tensor-core GEMM (tcgen05 kind::i8, TMEM accumulators), any number of activation rows: replaces
+ * the vendored MMQ (mul_mat_q, mmq.cuh:961-1385 + shim host side lcpp_shim.cu:626-671) and the owned
+ * mma_k (lcpp_owned_mma_k.cu:353-539) and iq3_packed_mmq (lcpp_owned_iq3_mma.cu:768-970).
+ *   x_q8_mmq     k/128 * m blocks of 144 bytes in the type's layout (gsq_q8_layout_for_type)
+ *   scratch      gsq_mul_mat_scratch_bytes(...) bytes, 256-byte aligned; contents need not be
+ *                initialised and are not preserved
+ */
+int gsq_q8_layout_for_type(int ggml_type);
+size_t gsq_mul_mat_scratch_bytes(int64_t rows, int64_t m, int64_t k, int ggml_type);
+int gsq_mul_mat_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,
+                   const void* x_q8_mmq, int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride,
+                   void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * IQ3_S load-time repack, in place, bijective: replaces iq3_pack.pack_ / unpack
+ * (plugin/vllm_gguf_plugin/quantization/iq3_pack.py:73-181). w uint8 [rows, row_bytes], rows % 16 == 0,
+ * 16-byte aligned. direction 0: GGUF blocks -> streaming layout; 1: back. One thread block stages one
+ * 16-row tile in shared memory, so 16 * row_bytes must fit (GSQ_ERR_TOO_LARGE otherwise).
+ */
+int gsq_iq3s_repack(void* w, int64_t rows, int64_t row_bytes, int direction, void* stream);
+
+/*
+ * Kernel choice on B200 for (activation rows m, type, weight rows, k, packed): GSQ_KERNEL_*.
+ * The op-level routing table of the reference (_lcpp_op, quantization/linear.py:85-114) stays in the
+ * Python layer because its op names are API; this is the choice made underneath those names.
+ */
+int gsq_route(int64_t m, int ggml_type, int64_t rows, int64_t k, int packed);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GSQ_H */

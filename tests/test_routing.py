@@ -1,0 +1,100 @@
+"""Routing: `_lcpp_op` against the reference's own function (golden table made by importing it,
+tests/golden/make_golden.py) and against the cases its test pins (tests/cpu/test_lcpp_routing.py:14-116)."""
+
+import json
+import os
+
+import pytest
+import torch
+
+from gsq_b200.quantization import linear
+
+IQ3, MMA, OWN = "lcpp_mul_mat_vec_iq3", "lcpp_mul_mat_vec_iq3_mma", "lcpp_mul_mat_vec_own"
+MMVQ, MMQ, MMA_K = "lcpp_mul_mat_vec_q", "lcpp_mul_mat_q", "lcpp_mul_mat_mma_k"
+PACKED_VEC, PACKED_TILED = "lcpp_mul_mat_vec_iq3_mma_packed", "lcpp_mul_mat_iq3_packed"
+Q4_K, Q6_K, IQ3_S, IQ4_XS, IQ1_M, IQ2_S, IQ2_XS = 12, 14, 21, 23, 29, 22, 17
+BIG, K = 17408, 5120
+
+
+def test_matches_reference_function_on_golden_grid(golden_dir):
+    g = json.load(open(os.path.join(golden_dir, "routing.json")))
+    assert len(g["cases"]) == 3800
+    bad = [(n, t, rows, k, p, want, linear._lcpp_op(n, t, rows, k, p))
+           for n, t, rows, k, p, want in g["cases"] if linear._lcpp_op(n, t, rows, k, p) != want]
+    assert not bad, bad[:5]
+    c = g["constants"]
+    assert list(linear._OWN_QUANTIZE_OPS) == c["_OWN_QUANTIZE_OPS"]
+    assert list(linear._X_DTYPE_OPS) == c["_X_DTYPE_OPS"]
+    assert linear.PACKED_VEC_MAX_ROWS == c["PACKED_VEC_MAX_ROWS"]
+
+
+@pytest.mark.parametrize("t,n,rows,want", [
+    (IQ3_S, 1, 1024, IQ3), (IQ3_S, 5, BIG, IQ3), (IQ3_S, 6, BIG, MMA), (IQ3_S, 8, 1024, MMA), (IQ3_S, 9, BIG, MMQ),
+    (Q4_K, 1, BIG, MMVQ), (Q4_K, 2, BIG, MMVQ), (Q4_K, 3, BIG, OWN), (Q4_K, 8, BIG, OWN), (Q4_K, 9, BIG, MMA_K),
+    (Q4_K, 32, BIG, MMA_K), (Q4_K, 33, BIG, MMQ), (Q4_K, 3, 2049, OWN), (Q4_K, 4, 2048, MMVQ), (Q4_K, 8, 2048, MMQ),
+    (IQ4_XS, 7, BIG, MMVQ), (IQ4_XS, 8, BIG, MMQ), (IQ4_XS, 16, 2049, MMA_K), (IQ4_XS, 17, 2049, MMQ),
+    (IQ4_XS, 17, 12288, MMA_K), (IQ4_XS, 17, 12032, MMQ), (IQ4_XS, 33, BIG, MMQ),
+    (Q6_K, 1, BIG, MMVQ), (Q6_K, 7, BIG, MMVQ), (Q6_K, 8, BIG, MMQ), (Q6_K, 32, BIG, MMQ),
+    (IQ1_M, 9, BIG, MMVQ), (IQ1_M, 33, BIG, None),
+])
+def test_boundaries(t, n, rows, want):
+    assert linear._lcpp_op(n, t, rows, K) == want
+    assert linear._lcpp_op(n, t, rows, K, False) == want
+
+
+@pytest.mark.parametrize("n,want", [(1, PACKED_VEC), (8, PACKED_VEC), (9, PACKED_TILED), (2048, PACKED_TILED)])
+def test_packed(n, want):
+    assert linear._lcpp_op(n, IQ3_S, BIG, K, True) == want
+    assert linear._lcpp_op(3, Q4_K, BIG, K, True) == OWN      # a packed layer's other runs route as unpacked
+
+
+class _Quantizer:
+    """Stands in for torch.ops._C_gguf: records which type the shared quantise runs with."""
+
+    def __init__(self):
+        self.calls = []
+
+    def lcpp_quantize_q8_1(self, x, qt, mmq, vendored):
+        self.calls.append((qt, mmq, vendored))
+        return "filled"
+
+
+@pytest.mark.parametrize("n,types,rows,want,packed", [
+    (4, [Q4_K, IQ2_XS], [2048, BIG], Q4_K, False),
+    (8, [Q4_K], [BIG], Q4_K, False),
+    (8, [Q4_K], [2048], None, False),
+    (8, [IQ4_XS, Q4_K], [BIG, BIG], Q4_K, False),
+    (8, [Q4_K, IQ3_S], [2048, BIG], IQ3_S, False),
+    (9, [IQ3_S, Q4_K], [BIG, BIG], None, False),
+    (16, [Q4_K, IQ1_M], [BIG, BIG], IQ1_M, False),
+    (33, [IQ1_M, Q4_K], [BIG, BIG], None, False),
+    (0, [IQ3_S], [BIG], None, False),
+    (4, [IQ3_S, Q4_K], [BIG, BIG], IQ3_S, True),
+    (9, [IQ3_S, IQ1_M], [BIG, BIG], IQ1_M, True),
+])
+def test_quantize_x_q8_1_fills(monkeypatch, n, types, rows, want, packed):
+    """The shared quantise runs (once, block_q8_1 layout) iff some run's op reads q8_1; otherwise an
+    unfilled buffer of the q8_1 size comes back."""
+    q = _Quantizer()
+    monkeypatch.setattr(torch.ops, "_C_gguf", q, raising=False)
+    x = torch.zeros(n, 512, dtype=torch.bfloat16)
+    out = linear._quantize_x_q8_1(x, [int(t) for t in types], rows, packed)
+    if want is None:
+        assert q.calls == [] and out.dtype == torch.uint8 and out.numel() == n * 512 // 32 * 36
+    else:
+        assert q.calls == [(int(want), False, False)] and out == "filled"
+
+
+def test_zero_rows_return_before_routing():
+    y = linear._fused_mul_mat_gguf(torch.zeros(0, 512, dtype=torch.bfloat16),
+                                   torch.zeros(BIG, 512 // 256 * 110, dtype=torch.uint8), IQ3_S)
+    assert y.shape == (0, BIG) and y.dtype == torch.bfloat16
+
+
+def test_c_route():
+    from gsq_b200 import _cabi
+
+    assert _cabi.lib.gsq_route(1, IQ3_S, BIG, K, 1) == _cabi.KERNEL_GEMV
+    assert _cabi.lib.gsq_route(8, Q4_K, BIG, K, 0) == _cabi.KERNEL_GEMV
+    assert _cabi.lib.gsq_route(9, Q4_K, BIG, K, 0) == _cabi.KERNEL_GEMM
+    assert _cabi.lib.gsq_route(4, IQ2_S, BIG, K, 0) == _cabi.KERNEL_NONE

@@ -1,0 +1,173 @@
+// Host-only pieces of the C ABI: status strings, input guards, device set-up, kernel routing.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "gsq_common.cuh"
+
+namespace gsq {
+
+static thread_local int t_last_cuda_error = 0;
+
+int record_cuda_error(cudaError_t e) {
+  t_last_cuda_error = (int)e;
+  return GSQ_ERR_CUDA;
+}
+
+int gemv_device_init(int device);  // gsq_gemv.cu
+
+static DeviceInfo g_info[64];
+
+int device_info(DeviceInfo* out) {
+  int dev = 0;
+  GSQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return GSQ_ERR_UNSUPPORTED;
+  if (!g_info[dev].ready) {
+    int rc = gsq_device_init(dev);
+    if (rc != GSQ_OK) return rc;
+  }
+  *out = g_info[dev];
+  return GSQ_OK;
+}
+
+}  // namespace gsq
+
+extern "C" const char* gsq_strerror(int status) {
+  switch (status) {
+    case GSQ_OK: return "ok";
+    case GSQ_ERR_GUARD: return "input guard failed";
+    case GSQ_ERR_CUDA: return "CUDA runtime error";
+    case GSQ_ERR_UNSUPPORTED: return "unsupported arguments";
+    case GSQ_ERR_SCRATCH: return "scratch buffer missing or too small";
+    case GSQ_ERR_TOO_LARGE: return "shape too large for this kernel";
+    case GSQ_ERR_DEVICE: return "kernel reported an internal error";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int gsq_last_cuda_error(void) { return gsq::t_last_cuda_error; }
+
+extern "C" int gsq_abi_version(void) { return 1; }
+
+extern "C" int gsq_type_block_bytes(int ggml_type) { return gsq::block_bytes(ggml_type); }
+
+extern "C" int gsq_device_init(int device) {
+  using namespace gsq;
+  if (device < 0 || device >= 64) return GSQ_ERR_UNSUPPORTED;
+  if (g_info[device].ready) return GSQ_OK;
+  int prev = 0;
+  GSQ_CUDA_TRY(cudaGetDevice(&prev));
+  if (prev != device) GSQ_CUDA_TRY(cudaSetDevice(device));
+  int sm = 0, smem = 0;
+  GSQ_CUDA_TRY(cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, device));
+  GSQ_CUDA_TRY(cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+  int rc = gemv_device_init(device);
+  if (prev != device) cudaSetDevice(prev);
+  if (rc != GSQ_OK) return rc;
+  g_info[device].sm_count = sm;
+  g_info[device].max_smem_optin = smem;
+  g_info[device].ready = true;
+  return GSQ_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Guards. Same checks, same order and the same message fragments as check_inputs() and the top of run()
+// in the reference's lcpp_shim.cu:690-732, 767-777 (the fragments are what its guard test greps for).
+
+static int guard_fail(char* msg, size_t n, const char* fmt, ...) {
+  if (msg && n) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(msg, n, fmt, ap);
+    va_end(ap);
+  }
+  return GSQ_ERR_GUARD;
+}
+
+// every type the reference's Route L accepts (its lcpp_type_supported); the kernels here cover four
+static bool route_l_type(int t) {
+  switch (t) {
+    case 10: case 12: case 14: case 16: case 17: case 22: case 18: case 21: case 23: case 29: return true;
+    default: return false;
+  }
+}
+static int any_type_block_bytes(int t) {
+  switch (t) {
+    case 10: return 84;   // Q2_K
+    case 12: return 144;  // Q4_K
+    case 14: return 210;  // Q6_K
+    case 16: return 66;   // IQ2_XXS
+    case 17: return 74;   // IQ2_XS
+    case 22: return 82;   // IQ2_S
+    case 18: return 98;   // IQ3_XXS
+    case 21: return 110;  // IQ3_S
+    case 23: return 136;  // IQ4_XS
+    case 29: return 56;   // IQ1_M
+    default: return 0;
+  }
+}
+
+extern "C" int gsq_check_inputs(const gsq_guard_args* a, int64_t* k_out, char* msg, size_t n) {
+  const char* op = a->op ? a->op : "gsq";
+  const long long type = a->ggml_type;
+  if (a->need_iq3 && !(type == 21 || type == 18))
+    return guard_fail(msg, n, "%s: IQ3_S or IQ3_XXS only, got type %lld", op, type);
+  if (a->need_q4k_own && !(type == 12 || type == 22))
+    return guard_fail(msg, n, "%s: Q4_K or IQ2_S only, got type %lld", op, type);
+  if (a->need_mma_k && !(type == 12 || type == 23 || type == 22))
+    return guard_fail(msg, n, "%s: Q4_K, IQ4_XS or IQ2_S only, got type %lld", op, type);
+  if (a->is_mmq && type == 29) return guard_fail(msg, n, "%s: no MMQ for IQ1_M", op);
+  if (a->packed && a->row % 16 != 0)
+    return guard_fail(msg, n, "%s: row=%lld must be a multiple of 16 (packed 16-row tiles)", op, (long long)a->row);
+
+  if (!route_l_type((int)type)) return guard_fail(msg, n, "%s: unsupported ggml type %lld", op, type);
+  if (!(a->w_dim == 2 && a->x_dim == 2)) return guard_fail(msg, n, "%s: W and X must be 2-D", op);
+  if (!a->w_is_uint8) return guard_fail(msg, n, "%s: W must be uint8", op);
+  if (!(a->x_dtype == GSQ_F32 || a->x_dtype == GSQ_F16 || a->x_dtype == GSQ_BF16))
+    return guard_fail(msg, n, "%s: X must be fp32, fp16 or bf16", op);
+  const int64_t ts = any_type_block_bytes((int)type);
+  const int64_t row_bytes = a->w_size1;
+  if (!(row_bytes > 0 && row_bytes % ts == 0))
+    return guard_fail(msg, n, "%s: W row bytes %lld not a multiple of the block size %lld", op, (long long)row_bytes,
+                      (long long)ts);
+  const int64_t k = row_bytes / ts * 256;
+  const int km = a->k_multiple > 0 ? a->k_multiple : 512;
+  if (k % km != 0)
+    return guard_fail(msg, n, "%s: K=%lld must be a multiple of %d (no weight tail padding)", op, (long long)k, km);
+  if (!(k <= INT32_MAX && a->w_size0 <= INT32_MAX)) return guard_fail(msg, n, "%s: W too large", op);
+  if (!(a->row > 0 && a->row <= a->w_size0))
+    return guard_fail(msg, n, "%s: row=%lld out of range (W has %lld rows)", op, (long long)a->row,
+                      (long long)a->w_size0);
+  if (a->w_stride1 != 1) return guard_fail(msg, n, "%s: W inner stride must be 1", op);
+  if (!(a->w_size0 == 1 || a->w_stride0 == row_bytes))
+    return guard_fail(msg, n, "%s: W rows must be contiguous (row stride %lld, row bytes %lld)", op,
+                      (long long)a->w_stride0, (long long)row_bytes);
+  if (a->w_addr % 16 != 0) return guard_fail(msg, n, "%s: W data must be 16-byte aligned", op);
+  if (a->x_size1 != k)
+    return guard_fail(msg, n, "%s: X has %lld columns, W rows hold K=%lld", op, (long long)a->x_size1, (long long)k);
+  if (!(a->x_stride1 == 1 && (a->x_size0 <= 1 || a->x_stride0 >= k)))
+    return guard_fail(msg, n, "%s: X inner stride must be 1", op);
+  if (a->max_rows > 0 && a->x_size0 > a->max_rows)
+    return guard_fail(msg, n, "%s: at most %lld rows, got %lld", op, (long long)a->max_rows, (long long)a->x_size0);
+  if (a->x_size0 > INT32_MAX) return guard_fail(msg, n, "%s: X too large", op);
+  // device checks last, so that a CPU call exercises every guard above and then ends here
+  if (!(a->w_is_cuda && a->x_is_cuda)) return guard_fail(msg, n, "%s: W and X must be CUDA tensors", op);
+  if (!a->same_device) return guard_fail(msg, n, "%s: W and X must be on the same device", op);
+  if (gsq::block_bytes((int)type) == 0)
+    return guard_fail(msg, n, "%s: ggml type %lld has no sm_100a kernel in this build (IQ3_S, IQ4_XS, Q4_K, Q6_K)", op,
+                      type);
+  if (k_out) *k_out = k;
+  return GSQ_OK;
+}
+
+extern "C" int gsq_route(int64_t m, int ggml_type, int64_t rows, int64_t k, int packed) {
+  (void)rows;
+  (void)k;
+  (void)packed;
+  if (gsq::block_bytes(ggml_type) == 0 || m <= 0) return GSQ_KERNEL_NONE;
+  return m <= 8 ? GSQ_KERNEL_GEMV : GSQ_KERNEL_GEMM;
+}
+
+extern "C" int gsq_q8_layout_for_type(int ggml_type) {
+  return ggml_type == GSQ_TYPE_Q4_K ? GSQ_Q8_LAYOUT_DS4 : GSQ_Q8_LAYOUT_D4;
+}

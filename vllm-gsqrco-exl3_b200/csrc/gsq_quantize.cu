@@ -1,0 +1,215 @@
+// q8_1 activation quantisers for fp32 / fp16 / bf16 X (sm_100a).
+//
+// Same arithmetic, bit for bit, as the reference's quantize_q8_1_x and quantize_mmq_q8_1_x
+// (plugin/vllm_gguf_plugin/csrc/lcpp_shim.cu:274-294, 298-355), which are built with
+// --use_fast_math (plugin/setup.py:42): divisions are the approximate div.approx.ftz / rcp.approx.ftz
+// forms, written out explicitly here so this file needs no global fast-math flag. The launch shape
+// differs: each thread owns 8 consecutive values (one 128-bit load of 16-bit X), 4 threads share a
+// 32-value block. The block sum is formed in the same order as the reference's 16,8,4,2,1
+// xor-shuffle tree over one value per lane (common.cuh:468-475): lane offsets 16 and 8 become
+// thread offsets 2 and 1, offsets 4,2,1 become a tree inside the thread.
+#include "gsq_common.cuh"
+
+namespace gsq {
+
+__device__ __forceinline__ float div_approx(float a, float b) {
+  float r;
+  asm("div.approx.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float rcp_approx(float a) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));
+  return r;
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// 8 consecutive values of row `row` starting at column c (c % 8 == 0). VEC: 16-byte aligned rows.
+template <typename T, bool VEC>
+__device__ __forceinline__ void load8(const T* __restrict__ x, int64_t off, float (&v)[8]) {
+  if constexpr (VEC && sizeof(T) == 2) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + off);
+    const T* p = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = to_f32<T>(p[e]);
+  } else if constexpr (VEC && sizeof(T) == 4) {
+    const float4 a = *reinterpret_cast<const float4*>(x + off);
+    const float4 b = *reinterpret_cast<const float4*>(x + off + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = to_f32<T>(x[off + e]);
+  }
+}
+
+__device__ __forceinline__ uint32_t pack4(float a, float b, float c, float d) {
+  // float -> int8 as the C conversion in the reference (round toward zero of an already rounded value)
+  const int ia = (int)a, ib = (int)b, ic = (int)c, id = (int)d;
+  return (uint32_t)(ia & 0xFF) | ((uint32_t)(ib & 0xFF) << 8) | ((uint32_t)(ic & 0xFF) << 16) | ((uint32_t)(id & 0xFF) << 24);
+}
+
+// MMVQ layout: block_q8_1 = 32 x int8, half d, half sum (36 bytes).
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict__ x, uint8_t* __restrict__ out,
+                                                           int64_t m, int64_t k, int64_t stride) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 8 values
+  const int64_t per_row = k >> 3;
+  // whole warps stay together: k % 32 == 0 makes per_row a multiple of 4, so a 4-thread group never
+  // straddles the end of the work
+  const bool live = t < m * per_row;
+  const int64_t row = live ? t / per_row : 0;
+  const int64_t c8 = live ? t - row * per_row : 0;
+  float v[8];
+  if (live) {
+    load8<T, VEC>(x, row * stride + c8 * 8, v);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+  float s[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) s[e] = v[e] + __shfl_xor_sync(0xFFFFFFFFu, v[e], 2);  // lane offset 16
+#pragma unroll
+  for (int e = 0; e < 8; ++e) s[e] = s[e] + __shfl_xor_sync(0xFFFFFFFFu, s[e], 1);  // lane offset 8
+  const float s0 = s[0] + s[4], s1 = s[1] + s[5], s2 = s[2] + s[6], s3 = s[3] + s[7];  // offset 4
+  const float sum = (s0 + s2) + (s1 + s3);                                              // offsets 2, 1
+  if (!live) return;
+  const float d = div_approx(amax, 127.0f);
+  float q[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) q[e] = amax == 0.0f ? 0.0f : roundf(div_approx(v[e], d));
+  const int64_t blk = row * (k >> 5) + (c8 >> 2);
+  uint8_t* b = out + blk * 36;
+  uint32_t* q32 = reinterpret_cast<uint32_t*>(b + (c8 & 3) * 8);
+  q32[0] = pack4(q[0], q[1], q[2], q[3]);
+  q32[1] = pack4(q[4], q[5], q[6], q[7]);
+  if ((c8 & 3) == 0) {
+    *reinterpret_cast<__half2*>(b + 32) = __floats2half2_rn(d, sum);
+  }
+}
+
+// 128-value blocks: 16 scale bytes + 128 x int8, block (kb, row) at (kb * m + row) * 144.
+template <typename T, bool VEC, int LAYOUT>
+__global__ void __launch_bounds__(256) quantize_q8_1_mmq_kernel(const T* __restrict__ x, uint8_t* __restrict__ out,
+                                                               int64_t m, int64_t k, int64_t stride) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t per_row = k >> 3;
+  const bool live = t < m * per_row;
+  const int64_t row = live ? t / per_row : 0;
+  const int64_t c8 = live ? t - row * per_row : 0;
+  float v[8];
+  if (live) {
+    load8<T, VEC>(x, row * stride + c8 * 8, v);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+  float sum = 0.0f;
+  if constexpr (LAYOUT == GSQ_Q8_LAYOUT_DS4) {
+    // the reference sums 4 values per thread, then lane offsets 4, 2, 1 over 8 threads
+    float pa = ((v[0] + v[1]) + v[2]) + v[3];
+    float pb = ((v[4] + v[5]) + v[6]) + v[7];
+    pa += __shfl_xor_sync(0xFFFFFFFFu, pa, 2);
+    pb += __shfl_xor_sync(0xFFFFFFFFu, pb, 2);
+    pa += __shfl_xor_sync(0xFFFFFFFFu, pa, 1);
+    pb += __shfl_xor_sync(0xFFFFFFFFu, pb, 1);
+    sum = pa + pb;
+  }
+  if (!live) return;
+  const float d_inv = div_approx(127.0f, amax);
+  float q[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) q[e] = roundf(v[e] * d_inv);
+  const float d = rcp_approx(d_inv);
+  const int64_t kb = c8 >> 4;             // 128-value block along k
+  const int iqs = (int)(c8 & 15) * 8;     // value offset inside the block
+  uint8_t* b = out + (kb * m + row) * 144;
+  *reinterpret_cast<uint2*>(b + 16 + iqs) = make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
+  if ((iqs & 31) == 0) {
+    if constexpr (LAYOUT == GSQ_Q8_LAYOUT_DS4) {
+      reinterpret_cast<__half2*>(b)[iqs >> 5] = __floats2half2_rn(d, sum);
+    } else {
+      reinterpret_cast<float*>(b)[iqs >> 5] = d;
+    }
+  }
+}
+
+template <typename T>
+static int launch_q8_1(const void* x, int64_t m, int64_t k, int64_t stride, void* out, cudaStream_t st) {
+  const int64_t threads = m * (k >> 3);
+  if (threads == 0) return GSQ_OK;
+  const unsigned grid = (unsigned)((threads + 255) / 256);
+  const bool vec = ((uintptr_t)x % 16 == 0) && ((stride * (int64_t)sizeof(T)) % 16 == 0);
+  if (vec) {
+    quantize_q8_1_kernel<T, true><<<grid, 256, 0, st>>>((const T*)x, (uint8_t*)out, m, k, stride);
+  } else {
+    quantize_q8_1_kernel<T, false><<<grid, 256, 0, st>>>((const T*)x, (uint8_t*)out, m, k, stride);
+  }
+  GSQ_CUDA_TRY(cudaGetLastError());
+  return GSQ_OK;
+}
+
+template <typename T, int LAYOUT>
+static int launch_q8_1_mmq(const void* x, int64_t m, int64_t k, int64_t stride, void* out, cudaStream_t st) {
+  const int64_t threads = m * (k >> 3);
+  if (threads == 0) return GSQ_OK;
+  const unsigned grid = (unsigned)((threads + 255) / 256);
+  const bool vec = ((uintptr_t)x % 16 == 0) && ((stride * (int64_t)sizeof(T)) % 16 == 0);
+  if (vec) {
+    quantize_q8_1_mmq_kernel<T, true, LAYOUT><<<grid, 256, 0, st>>>((const T*)x, (uint8_t*)out, m, k, stride);
+  } else {
+    quantize_q8_1_mmq_kernel<T, false, LAYOUT><<<grid, 256, 0, st>>>((const T*)x, (uint8_t*)out, m, k, stride);
+  }
+  GSQ_CUDA_TRY(cudaGetLastError());
+  return GSQ_OK;
+}
+
+}  // namespace gsq
+
+extern "C" int gsq_quantize_q8_1(const void* x, int x_dtype, int64_t m, int64_t k, int64_t x_row_stride, void* out,
+                                 void* stream) {
+  if (m < 0 || k <= 0 || k % 32 != 0 || (m > 0 && (!x || !out))) return GSQ_ERR_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (x_dtype) {
+    case GSQ_F32: return gsq::launch_q8_1<float>(x, m, k, x_row_stride, out, st);
+    case GSQ_F16: return gsq::launch_q8_1<__half>(x, m, k, x_row_stride, out, st);
+    case GSQ_BF16: return gsq::launch_q8_1<__nv_bfloat16>(x, m, k, x_row_stride, out, st);
+    default: return GSQ_ERR_UNSUPPORTED;
+  }
+}
+
+extern "C" int gsq_quantize_q8_1_mmq(const void* x, int x_dtype, int64_t m, int64_t k, int64_t x_row_stride,
+                                     int layout, void* out, void* stream) {
+  if (m < 0 || k <= 0 || k % 128 != 0 || (m > 0 && (!x || !out))) return GSQ_ERR_UNSUPPORTED;
+  if (layout != GSQ_Q8_LAYOUT_D4 && layout != GSQ_Q8_LAYOUT_DS4) return GSQ_ERR_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+#define GSQ_MMQ_CASE(T)                                                                                   \
+  return layout == GSQ_Q8_LAYOUT_D4 ? gsq::launch_q8_1_mmq<T, GSQ_Q8_LAYOUT_D4>(x, m, k, x_row_stride, out, st) \
+                                    : gsq::launch_q8_1_mmq<T, GSQ_Q8_LAYOUT_DS4>(x, m, k, x_row_stride, out, st)
+  switch (x_dtype) {
+    case GSQ_F32: GSQ_MMQ_CASE(float);
+    case GSQ_F16: GSQ_MMQ_CASE(__half);
+    case GSQ_BF16: GSQ_MMQ_CASE(__nv_bfloat16);
+    default: return GSQ_ERR_UNSUPPORTED;
+  }
+#undef GSQ_MMQ_CASE
+}

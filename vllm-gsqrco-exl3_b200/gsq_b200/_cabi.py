@@ -1,0 +1,91 @@
+"""ctypes binding of the C ABI declared in include/gsq.h (libgsq.so, built by build.py).
+
+There is no fallback: if the library is missing, importing this module raises, and every op of
+this package fails loudly instead of computing something elsewhere.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libgsq.so")
+
+OK, ERR_GUARD, ERR_CUDA, ERR_UNSUPPORTED, ERR_SCRATCH, ERR_TOO_LARGE, ERR_DEVICE = 0, -1, -2, -3, -4, -5, -6
+F32, F16, BF16, DTYPE_OTHER = 0, 1, 2, 99
+LAYOUT_D4, LAYOUT_DS4 = 0, 1
+KERNEL_NONE, KERNEL_GEMV, KERNEL_GEMM = 0, 1, 2
+
+EXPORTS = (
+    "gsq_strerror", "gsq_last_cuda_error", "gsq_abi_version", "gsq_type_block_bytes", "gsq_check_inputs",
+    "gsq_device_init", "gsq_quantize_q8_1", "gsq_quantize_q8_1_mmq", "gsq_mul_mat_vec_q8",
+    "gsq_q8_layout_for_type", "gsq_mul_mat_scratch_bytes", "gsq_mul_mat_q8", "gsq_iq3s_repack", "gsq_route",
+)
+
+
+class GuardArgs(C.Structure):
+    _fields_ = [
+        ("op", C.c_char_p),
+        ("w_dim", C.c_int), ("w_is_uint8", C.c_int),
+        ("w_size0", C.c_int64), ("w_size1", C.c_int64), ("w_stride0", C.c_int64), ("w_stride1", C.c_int64),
+        ("w_addr", C.c_uint64),
+        ("x_dim", C.c_int), ("x_dtype", C.c_int),
+        ("x_size0", C.c_int64), ("x_size1", C.c_int64), ("x_stride0", C.c_int64), ("x_stride1", C.c_int64),
+        ("row", C.c_int64), ("max_rows", C.c_int64),
+        ("ggml_type", C.c_int),
+        ("need_iq3", C.c_int), ("need_q4k_own", C.c_int), ("need_mma_k", C.c_int), ("is_mmq", C.c_int),
+        ("packed", C.c_int),
+        ("k_multiple", C.c_int),
+        ("w_is_cuda", C.c_int), ("x_is_cuda", C.c_int), ("same_device", C.c_int),
+    ]
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python vllm-gsqrco-exl3_b200/build.py` "
+            "(nvcc, sm_100a). This package has no other compute path."
+        )
+    lib = C.CDLL(LIB_PATH)
+    i64, vp, ci, sz = C.c_int64, C.c_void_p, C.c_int, C.c_size_t
+    lib.gsq_strerror.restype = C.c_char_p
+    lib.gsq_strerror.argtypes = [ci]
+    lib.gsq_last_cuda_error.restype = ci
+    lib.gsq_abi_version.restype = ci
+    lib.gsq_type_block_bytes.restype = ci
+    lib.gsq_type_block_bytes.argtypes = [ci]
+    lib.gsq_check_inputs.restype = ci
+    lib.gsq_check_inputs.argtypes = [C.POINTER(GuardArgs), C.POINTER(i64), C.c_char_p, sz]
+    lib.gsq_device_init.restype = ci
+    lib.gsq_device_init.argtypes = [ci]
+    lib.gsq_quantize_q8_1.restype = ci
+    lib.gsq_quantize_q8_1.argtypes = [vp, ci, i64, i64, i64, vp, vp]
+    lib.gsq_quantize_q8_1_mmq.restype = ci
+    lib.gsq_quantize_q8_1_mmq.argtypes = [vp, ci, i64, i64, i64, ci, vp, vp]
+    lib.gsq_mul_mat_vec_q8.restype = ci
+    lib.gsq_mul_mat_vec_q8.argtypes = [vp, i64, i64, ci, ci, vp, i64, i64, vp, ci, i64, vp]
+    lib.gsq_q8_layout_for_type.restype = ci
+    lib.gsq_q8_layout_for_type.argtypes = [ci]
+    lib.gsq_mul_mat_scratch_bytes.restype = sz
+    lib.gsq_mul_mat_scratch_bytes.argtypes = [i64, i64, i64, ci]
+    lib.gsq_mul_mat_q8.restype = ci
+    lib.gsq_mul_mat_q8.argtypes = [vp, i64, i64, ci, ci, vp, i64, i64, vp, ci, i64, vp, sz, vp]
+    lib.gsq_iq3s_repack.restype = ci
+    lib.gsq_iq3s_repack.argtypes = [vp, i64, i64, ci, vp]
+    lib.gsq_route.restype = ci
+    lib.gsq_route.argtypes = [i64, ci, i64, i64, ci]
+    return lib
+
+
+lib = _load()
+
+
+def check(status: int, what: str) -> None:
+    """Raise RuntimeError for a non-zero status of a launch entry point."""
+    if status == OK:
+        return
+    msg = lib.gsq_strerror(status).decode()
+    if status == ERR_CUDA:
+        msg += f" (cudaError {lib.gsq_last_cuda_error()})"
+    raise RuntimeError(f"{what}: {msg}")
