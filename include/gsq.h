@@ -132,6 +132,17 @@ int gsq_mul_mat_vec_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_
                        void* stream);
 
 /*
+ * Test hook: the raw int32 dot product of every weight group with the matching activation quants, taken
+ * from inside the GEMV kernel itself (a debug instantiation of the same code, one activation row per
+ * launch). These are the `sumi` of the reference's vec_dot_*_q8_1 (vecdotq.cuh:1233-1243 and siblings)
+ * before any scale is applied; no reference op exposes them.
+ *   sums       int32 [m, rows, k/g], g = 32 (16 for Q6_K); MUST be zeroed by the caller (lanes add into it)
+ *   y_scratch  rows floats, overwritten
+ */
+int gsq_debug_block_sums(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,
+                         const void* x_q8, int64_t m, int64_t k, int32_t* sums, float* y_scratch, void* stream);
+
+/*
  * Tensor-core GEMM (tcgen05 kind::i8, TMEM accumulators), any number of activation rows: replaces
  * the vendored MMQ (mul_mat_q, mmq.cuh:961-1385 + shim host side lcpp_shim.cu:626-671) and the owned
  * mma_k (lcpp_owned_mma_k.cu:353-539) and iq3_packed_mmq (lcpp_owned_iq3_mma.cu:768-970).

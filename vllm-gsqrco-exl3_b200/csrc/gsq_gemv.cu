@@ -46,6 +46,8 @@ struct GemvArgs {
   int n_units;       // CTA steps in total
   int nrec;          // records per row tile
   int rec_per_part;  // ceil(nrec / parts)
+  int* dump;         // debug only: integer slice sums
+  int dump_m0;
 };
 
 template <int KIND>
@@ -185,7 +187,16 @@ struct Planes {
   const float* xs;    // [m][k/32] d * sum(q) of the block (Q4_K only)
   const uint32_t* grid;  // replicated IQ3_S codebook
   int k;
+  // debug dump of the raw integer slice sums (gsq_debug_block_sums): out[(m * nrows + row) * (k / g) + group]
+  int* dump;
+  int dump_row0, dump_rows, dump_m0;
 };
+
+template <int M>
+__device__ __forceinline__ void dump_add(const Planes& pl, int m, int row_in_tile, int group, int groups, int v) {
+  const int row = pl.dump_row0 + row_in_tile;
+  if (row < pl.dump_rows) atomicAdd(pl.dump + ((int64_t)(pl.dump_m0 + m) * pl.dump_rows + row) * groups + group, v);
+}
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t r;
@@ -195,9 +206,9 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 
 // wv[i][e] = 4 signed int8 of group e (values 4e..4e+3 of the lane's slice) of row i; common dot loop of
 // the kinds whose lane owns one whole 32-value slice with a single integer sub-scale.
-template <int M>
+template <int M, bool DUMP>
 __device__ __forceinline__ void dot_slice(const int (&wv)[4][8], const int (&isc)[4], const float (&dw)[4],
-                                          const Planes& pl, int blk, float (&acc)[4][M]) {
+                                          const Planes& pl, int blk, int row_base, int row_step, float (&acc)[4][M]) {
   const int nb32 = pl.k >> 5;
 #pragma unroll
   for (int m = 0; m < M; ++m) {
@@ -210,6 +221,7 @@ __device__ __forceinline__ void dot_slice(const int (&wv)[4][8], const int (&isc
       int sumi = 0;
 #pragma unroll
       for (int e = 0; e < 8; ++e) sumi = dp4a(wv[i][e], u[e], sumi);
+      if constexpr (DUMP) dump_add<M>(pl, m, row_base + row_step * i, blk, nb32, sumi);
       acc[i][m] = fmaf(dw[i] * d8, (float)(sumi * isc[i]), acc[i][m]);
     }
   }
@@ -217,7 +229,7 @@ __device__ __forceinline__ void dot_slice(const int (&wv)[4][8], const int (&isc
 
 // RS: log2 of the byte stride between codebook entries in the replicated table (7: one copy per lane,
 // 5: one copy per 8 lanes, used when the activations leave less shared memory).
-template <int M, int RS>
+template <int M, int RS, bool DUMP>
 __device__ __forceinline__ void accumulate(const Rec<KIND_IQ3S_PACKED>& r, int rec, int lane, bool ok,
                                            const Planes& pl, float (&acc)[4][M]) {
   (void)ok;
@@ -245,10 +257,10 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_IQ3S_PACKED>& r, int r
     isc[i] = 1 + 2 * (int)((r.sc >> (4 * i)) & 15u);
     dw[i] = h2f((i < 2 ? r.dd.x : r.dd.y) >> (16 * (i & 1)));
   }
-  dot_slice<M>(wv, isc, dw, pl, rec * 8 + (lane & 7), acc);
+  dot_slice<M, DUMP>(wv, isc, dw, pl, rec * 8 + (lane & 7), lane >> 3, 4, acc);
 }
 
-template <int M, int RS>
+template <int M, int RS, bool DUMP>
 __device__ __forceinline__ void accumulate(const Rec<KIND_IQ3S_RAW>& r, int rec, int lane, bool ok,
                                            const Planes& pl, float (&acc)[4][M]) {
   if (!ok) return;
@@ -271,7 +283,7 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_IQ3S_RAW>& r, int rec,
     isc[i] = 1 + 2 * (int)r.ls[i];
     dw[i] = h2f(r.d[i]);
   }
-  dot_slice<M>(wv, isc, dw, pl, (rec * 4 + (lane >> 3)) * 8 + (lane & 7), acc);
+  dot_slice<M, DUMP>(wv, isc, dw, pl, (rec * 4 + (lane >> 3)) * 8 + (lane & 7), 0, 1, acc);
 }
 
 // 8 four-bit indices of v -> the table bytes: lo = entries of the 4 low nibbles, hi = of the 4 high nibbles.
@@ -285,7 +297,7 @@ __device__ __forceinline__ void iq4_lookup(uint32_t v, uint32_t& lo, uint32_t& h
   hi = prmt(r01, r23, 0x7531u);
 }
 
-template <int M, int RS>
+template <int M, int RS, bool DUMP>
 __device__ __forceinline__ void accumulate(const Rec<KIND_IQ4XS>& r, int rec, int lane, bool ok, const Planes& pl,
                                            float (&acc)[4][M]) {
   if (!ok) return;
@@ -307,10 +319,10 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_IQ4XS>& r, int rec, in
     isc[i] = (int)ls - 32;
     dw[i] = h2f(r.hdr[i].x);
   }
-  dot_slice<M>(wv, isc, dw, pl, (rec * 4 + (lane >> 3)) * 8 + p, acc);
+  dot_slice<M, DUMP>(wv, isc, dw, pl, (rec * 4 + (lane >> 3)) * 8 + p, 0, 1, acc);
 }
 
-template <int M, int RS>
+template <int M, int RS, bool DUMP>
 __device__ __forceinline__ void accumulate(const Rec<KIND_Q4K>& r, int rec, int lane, bool ok, const Planes& pl,
                                            float (&acc)[4][M]) {
   if (!ok) return;
@@ -358,6 +370,10 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_Q4K>& r, int rec, int 
         dl = dp4a(lo[i][e], u0[e], dl);
         dh = dp4a(hi[i][e], u1[e], dh);
       }
+      if constexpr (DUMP) {
+        dump_add<M>(pl, m, i, blk, nb32, dl);
+        dump_add<M>(pl, m, i, blk + 1, nb32, dh);
+      }
       const float sd = d80 * (float)(dl * sc0[i]) + d81 * (float)(dh * sc1[i]);
       const float sm = xs0 * dmn0[i] + xs1 * dmn1[i];
       acc[i][m] += dd[i] * sd - sm;
@@ -365,7 +381,7 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_Q4K>& r, int rec, int 
   }
 }
 
-template <int M, int RS>
+template <int M, int RS, bool DUMP>
 __device__ __forceinline__ void accumulate(const Rec<KIND_Q6K>& r, int rec, int lane, bool ok, const Planes& pl,
                                            float (&acc)[4][M]) {
   (void)ok;
@@ -392,7 +408,13 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_Q6K>& r, int rec, int 
     const float d80 = pl.xd[m * nb32 + blk], d81 = pl.xd[m * nb32 + blk + 2];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float sf = d80 * (float)(dp4a(v0[i], u0, 0) * s0[i]) + d81 * (float)(dp4a(v1[i], u1, 0) * s1[i]);
+      const int p0 = dp4a(v0[i], u0, 0), p1 = dp4a(v1[i], u1, 0);
+      if constexpr (DUMP) {
+        const int g16 = rec * 16 + 8 * n + (w16 >> 2);
+        dump_add<M>(pl, m, i, g16, pl.k >> 4, p0);
+        dump_add<M>(pl, m, i, g16 + 4, pl.k >> 4, p1);
+      }
+      const float sf = d80 * (float)(p0 * s0[i]) + d81 * (float)(p1 * s1[i]);
       acc[i][m] = fmaf(dd[i], sf, acc[i][m]);
     }
   }
@@ -414,7 +436,7 @@ __host__ __device__ inline size_t gemv_smem_bytes(int kind, int rs, int m, int k
   return s;
 }
 
-template <int KIND, int M, int RS>
+template <int KIND, int M, int RS, bool DUMP>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   constexpr int TR = KindTraits<KIND>::tile_rows;
@@ -460,6 +482,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
 
   Planes pl;
   pl.xq = xq; pl.xd = xd; pl.xs = xs; pl.grid = grid_s; pl.k = a.k;
+  pl.dump = a.dump; pl.dump_rows = a.nrows; pl.dump_m0 = a.dump_m0; pl.dump_row0 = 0;
 
   const int parts = a.parts;
   const int tiles = GEMV_WARPS / parts;
@@ -470,6 +493,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
 
   for (int unit = blockIdx.x; unit < a.n_units; unit += gridDim.x) {
     const int row0 = (unit * tiles + tile_l) * TR;
+    pl.dump_row0 = row0;
     float acc[4][M];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -486,7 +510,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
         const bool has_next = rec + 1 < r_end;
         const bool ok_nxt = has_next && (RSB == 1 || ((rec + 1) * 4 + (lane >> 3)) < nsb);
         nxt.load(a, row0, rec + 1, lane, ok_nxt);
-        accumulate<M, RS>(cur, rec, lane, ok_cur, pl, acc);
+        accumulate<M, RS, DUMP>(cur, rec, lane, ok_cur, pl, acc);
         cur = nxt;
         ok_cur = ok_nxt;
       }
@@ -561,9 +585,9 @@ int gemv_device_init(int device) {
   return GSQ_OK;
 }
 
-template <int KIND, int M, int RS>
+template <int KIND, int M, int RS, bool DUMP = false>
 static int launch_gemv(const GemvArgs& a, int grid, size_t smem, cudaStream_t st) {
-  auto kern = gemv_kernel<KIND, M, RS>;
+  auto kern = gemv_kernel<KIND, M, RS, DUMP>;
   static int configured_mask = 0;  // per instantiation: devices whose smem attribute is set
   int dev = 0;
   GSQ_CUDA_TRY(cudaGetDevice(&dev));
@@ -593,10 +617,10 @@ static int launch_gemv_m(int m, const GemvArgs& a, int grid, size_t smem, cudaSt
 
 }  // namespace gsq
 
-extern "C" int gsq_mul_mat_vec_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,
-                                  const void* x_q8, int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride,
-                                  void* stream) {
-  using namespace gsq;
+namespace gsq {
+static int gemv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_q8,
+                     int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump,
+                     int dump_m0) {
   if (m == 0 || rows == 0) return GSQ_OK;
   if (m < 0 || m > 8 || rows < 0 || k <= 0 || k % 256 != 0 || !w || !x_q8 || !y) return GSQ_ERR_UNSUPPORTED;
   if (rows > INT32_MAX || k > INT32_MAX) return GSQ_ERR_TOO_LARGE;
@@ -642,6 +666,8 @@ extern "C" int gsq_mul_mat_vec_q8(const void* w, int64_t row_bytes, int64_t rows
   a.n_units = (ntiles + tiles - 1) / tiles;
   a.nrec = nrec;
   a.rec_per_part = (nrec + parts - 1) / parts;
+  a.dump = dump;
+  a.dump_m0 = dump_m0;
   const int grid = a.n_units < di.sm_count ? a.n_units : di.sm_count;
   cudaStream_t st = (cudaStream_t)stream;
 
@@ -654,6 +680,20 @@ extern "C" int gsq_mul_mat_vec_q8(const void* w, int64_t row_bytes, int64_t rows
   }
   if (smem > (size_t)di.max_smem_optin) return GSQ_ERR_TOO_LARGE;
 
+  if (dump) {  // debug build of the same kernel, one activation row per launch
+    if (m != 1) return GSQ_ERR_UNSUPPORTED;
+    switch (kind) {
+      case KIND_IQ3S_PACKED:
+        return rs == 7 ? launch_gemv<KIND_IQ3S_PACKED, 1, 7, true>(a, grid, smem, st)
+                       : launch_gemv<KIND_IQ3S_PACKED, 1, 5, true>(a, grid, smem, st);
+      case KIND_IQ3S_RAW:
+        return rs == 7 ? launch_gemv<KIND_IQ3S_RAW, 1, 7, true>(a, grid, smem, st)
+                       : launch_gemv<KIND_IQ3S_RAW, 1, 5, true>(a, grid, smem, st);
+      case KIND_Q4K: return launch_gemv<KIND_Q4K, 1, 7, true>(a, grid, smem, st);
+      case KIND_IQ4XS: return launch_gemv<KIND_IQ4XS, 1, 7, true>(a, grid, smem, st);
+      default: return launch_gemv<KIND_Q6K, 1, 7, true>(a, grid, smem, st);
+    }
+  }
   switch (kind) {
     case KIND_IQ3S_PACKED:
       return rs == 7 ? launch_gemv_m<KIND_IQ3S_PACKED, 7>((int)m, a, grid, smem, st)
@@ -665,4 +705,23 @@ extern "C" int gsq_mul_mat_vec_q8(const void* w, int64_t row_bytes, int64_t rows
     case KIND_IQ4XS: return launch_gemv_m<KIND_IQ4XS, 7>((int)m, a, grid, smem, st);
     default: return launch_gemv_m<KIND_Q6K, 7>((int)m, a, grid, smem, st);
   }
+}
+}  // namespace gsq
+
+extern "C" int gsq_mul_mat_vec_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,
+                                  const void* x_q8, int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride,
+                                  void* stream) {
+  return gsq::gemv_host(w, row_bytes, rows, ggml_type, packed, x_q8, m, k, y, y_dtype, y_row_stride, stream, nullptr, 0);
+}
+
+extern "C" int gsq_debug_block_sums(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,
+                                    const void* x_q8, int64_t m, int64_t k, int32_t* sums, float* y_scratch,
+                                    void* stream) {
+  if (!sums || !y_scratch) return GSQ_ERR_UNSUPPORTED;
+  for (int64_t i = 0; i < m; ++i) {
+    const int rc = gsq::gemv_host(w, row_bytes, rows, ggml_type, packed, (const uint8_t*)x_q8 + i * (k / 32) * 36, 1, k,
+                                  y_scratch, GSQ_F32, rows, stream, sums, (int)i);
+    if (rc != GSQ_OK) return rc;
+  }
+  return GSQ_OK;
 }
