@@ -132,6 +132,19 @@ int gsq_mul_mat_vec_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_
                        void* stream);
 
 /*
+ * The GEMV has two weight-streaming variants: bulk copies (cp.async.bulk + mbarrier) into a per-warp
+ * shared-memory ring, used wherever row segments are 16-byte aligned, and direct 128-bit loads otherwise.
+ * Test hook: on != 0 forces the direct variant everywhere; returns the previous setting.
+ */
+int gsq_debug_force_direct_loads(int on);
+
+/*
+ * Every wait on a bulk copy inside a kernel is bounded; a wait that gave up sets a sticky per-device flag
+ * instead of hanging. Copies the flag (0 = never happened) to *flag. Synchronises the device.
+ */
+int gsq_device_error_flag(int* flag);
+
+/*
  * Test hook: the raw int32 dot product of every weight group with the matching activation quants, taken
  * from inside the GEMV kernel itself (a debug instantiation of the same code, one activation row per
  * launch). These are the `sumi` of the reference's vec_dot_*_q8_1 (vecdotq.cuh:1233-1243 and siblings)

@@ -38,7 +38,7 @@ def pack_ref(w: np.ndarray) -> np.ndarray:
                     o = 0
                     for e in range(8):
                         for p in range(4):
-                            o |= ((g >> (4 * e + p)) & 1) << (8 * p + e)
+                            o |= ((g >> (4 * e + p)) & 1) << (16 * (e >> 2) + 4 * p + (e & 3))
                     rec[1152 + 16 * lane + 4 * i: 1156 + 16 * lane + 4 * i] = np.frombuffer(o.to_bytes(4, "little"), np.uint8)
                     sc |= ((int(b[106 + (s >> 1)]) >> (4 * (s & 1))) & 15) << (4 * i)
                     if s == 0:

@@ -115,9 +115,25 @@ CASES = [
 ]
 
 
+@pytest.fixture(params=["staged", "direct"])
+def load_variant(request):
+    """Both weight-streaming variants of the GEMV: bulk copies into a shared-memory ring, direct loads."""
+    old = _cabi.lib.gsq_debug_force_direct_loads(int(request.param == "direct"))
+    yield request.param
+    _cabi.lib.gsq_debug_force_direct_loads(old)
+
+
+def test_no_bounded_wait_gave_up():
+    import ctypes
+
+    flag = ctypes.c_int(-1)
+    assert _cabi.lib.gsq_device_error_flag(ctypes.byref(flag)) == 0
+    assert flag.value == 0
+
+
 @pytest.mark.parametrize("name,rows,k,packed", CASES)
 @pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8])
-def test_gemv_fp32_vs_oracle(name, rows, k, packed, m):
+def test_gemv_fp32_vs_oracle(name, rows, k, packed, m, load_variant):
     raw, w = _weights(name, rows, k, 1000 + rows, packed)
     x = _x(m, k, torch.float32, 1200 + m)
     y = getattr(torch.ops._C_gguf, _op_for(name, packed))(w, x.to(DEV), TYPES[name], rows)
@@ -275,6 +291,10 @@ def test_apply_mixed_type_fused_layer(m):
         refs.append(product.product_q81(dec, q, d.astype(np.float32)))
     ref = np.concatenate(refs, axis=1) + bias.float().cpu().numpy()
     assert product.rel_err(_to_np(y), ref) <= 5e-3
+
+
+def test_zz_no_bounded_wait_gave_up_after_all_tests():
+    test_no_bounded_wait_gave_up()
 
 
 def test_apply_single_type_and_unfused():

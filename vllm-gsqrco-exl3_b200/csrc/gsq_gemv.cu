@@ -6,22 +6,31 @@
 // sums and the slice terms d_w * d_q8 * scale * sumi are the reference's; only the fp32 order in which
 // a row's slice terms are added differs (fixed, so results are run-to-run and graph-replay identical).
 //
-// Shape of the kernel (one persistent CTA of 16 warps per SM):
-//   * the q8_1 activations of all rows are staged once per CTA into shared memory as planes
-//     (int8 values, fp32 scales, and for Q4_K the fp32 d * sum(q) of every block);
-//   * weights stream straight from HBM into registers with 128-bit no-allocate loads, one
-//     "record" ahead of the arithmetic; a record is what one warp consumes per step:
+// Shape of the kernel: one CTA of 16 warps per SM, CTAs grouped in thread-block clusters of 4.
+//   * A "record" is what one warp consumes per step, every lane decoding its 32 values of 4 weight rows
+//     once and dotting them with each activation row:
 //        IQ3_S packed : one 16-row x 256-column tile record of gsq_iq3s_repack (1760 bytes);
 //                       lane = (row group a = lane / 8, slice s = lane % 8), rows a, a+4, a+8, a+12
 //        Q4_K, IQ4_XS, IQ3_S in GGUF order : 4 rows x 4 superblocks; lane = (superblock, 32-value chunk)
 //        Q6_K         : 4 rows x 1 superblock; lane = 4-byte word of ql
-//     so every lane decodes its 32 values of 4 weight rows once and dots them with each activation row;
-//   * IQ3_S reads its 512-entry codebook from a copy replicated per lane (entry i of lane l at word
-//     32 i + l), so the data-dependent lookups never collide on a shared-memory bank;
-//   * a CTA step covers `tiles` row tiles x `parts` column parts (tiles * parts = 16 warps); partial
-//     sums meet in shared memory and are added in part order.
+//   * Each cluster owns a contiguous range of row tiles, i.e. a contiguous byte range of W. The records of
+//     that range, in memory order, are cut into equal contiguous chunks, one per warp of the cluster, so
+//     every warp streams the same number of bytes whatever the shape. A warp reads its chunk with 128-bit
+//     no-allocate loads straight into registers, one record ahead of the arithmetic, across tile
+//     boundaries, with no block-wide barrier in the loop.
+//   * Chunks do not respect tile boundaries: when a warp leaves a tile it parks that tile's partial sums
+//     in its CTA's shared memory. After one cluster barrier the threads of the cluster add, for every row,
+//     the partial sums of the warps that touched it, in warp order, reading the other CTAs' shared memory
+//     (distributed shared memory), and write Y in its final dtype. No atomics, no global scratch.
+//   * The q8_1 activations are read where they lie (36-byte blocks) through L1; every SM pulls them from
+//     L2 once. IQ3_S reads its 512-entry codebook from a shared-memory copy replicated per lane (entry i of
+//     lane l at word 32 i + l), so the data-dependent lookups never collide on a bank.
+#include <cooperative_groups.h>
+
 #include "gsq_common.cuh"
 #include "gsq_tables.h"
+
+namespace cg = cooperative_groups;
 
 namespace gsq {
 
@@ -33,6 +42,8 @@ constexpr int GEMV_THREADS = GEMV_WARPS * 32;
 __device__ const uint32_t g_iq3s_grid[512] = GSQ_IQ3S_GRID_INIT;
 __constant__ uint32_t c_iq4nl_words[4] = {0, 0, 0, 0};  // filled at device init from GSQ_IQ4NL_VALUES_INIT
 
+constexpr int SEG_CAP = 4;  // most tiles one warp's chunk may touch in a round
+
 struct GemvArgs {
   const uint8_t* w;
   int64_t row_bytes;
@@ -42,10 +53,13 @@ struct GemvArgs {
   void* y;
   int y_dtype;
   int64_t ldy;
-  int parts;         // column parts per tile (power of two, <= 16)
-  int n_units;       // CTA steps in total
+  int ntiles;        // row tiles in W
   int nrec;          // records per row tile
-  int rec_per_part;  // ceil(nrec / parts)
+  int tiles_base;    // tiles per cluster: the first tiles_extra clusters own tiles_base + 1
+  int tiles_extra;
+  int tiles_round;   // tiles a cluster takes per round (<= (SEG_CAP - 2) * warps per cluster)
+  int stage_shift;   // log2 of the bulk-copy ring depth per warp (staged variant only)
+  int force_direct;  // tests: use the direct-load variant even where the staged one applies
   int* dump;         // debug only: integer slice sums
   int dump_m0;
 };
@@ -91,6 +105,19 @@ struct Rec<KIND_IQ3S_PACKED> {
     sc = ldg_stream_u16(p + 1664 + 2 * lane);
     dd = ldg_stream_v2(p + 1728 + 8 * (lane >> 3));
   }
+  // the same record already staged in shared memory by a bulk copy
+  __device__ __forceinline__ void load_smem(const uint8_t* p, int lane, bool ok, int = 0) {
+    (void)ok;
+    const uint4 ia = *reinterpret_cast<const uint4*>(p + 16 * lane);
+    const uint4 ib = *reinterpret_cast<const uint4*>(p + 512 + 16 * lane);
+    idx[0] = ia.x; idx[1] = ia.y; idx[2] = ia.z; idx[3] = ia.w;
+    idx[4] = ib.x; idx[5] = ib.y; idx[6] = ib.z; idx[7] = ib.w;
+    idx[8] = *reinterpret_cast<const uint32_t*>(p + 1024 + 4 * lane);
+    const uint4 s = *reinterpret_cast<const uint4*>(p + 1152 + 16 * lane);
+    sg[0] = s.x; sg[1] = s.y; sg[2] = s.z; sg[3] = s.w;
+    sc = *reinterpret_cast<const uint16_t*>(p + 1664 + 2 * lane);
+    dd = *reinterpret_cast<const uint2*>(p + 1728 + 8 * (lane >> 3));
+  }
 };
 
 // IQ3_S in GGUF order: 110-byte blocks are only 2-byte aligned, so everything comes in as halfwords.
@@ -118,6 +145,7 @@ struct Rec<KIND_IQ3S_RAW> {
       ls[i] = (ldg_stream_u8(b + 106 + (s >> 1)) >> (4 * (s & 1))) & 0x0F;
     }
   }
+  __device__ __forceinline__ void load_smem(const uint8_t*, int, bool, int = 0) {}
 };
 
 // Q4_K: 144-byte blocks, 16-byte aligned: header (d, dmin, 12 scale bytes) and the lane's 16-byte chunk.
@@ -134,6 +162,16 @@ struct Rec<KIND_Q4K> {
       const uint8_t* b = a.w + (int64_t)r * a.row_bytes + (int64_t)sb * 144;
       hdr[i] = ldg_stream_v4(b);
       qs[i] = ldg_stream_v4(b + 16 + 16 * p);
+    }
+  }
+  // staged record: row i's superblocks at p + i * row_stride
+  __device__ __forceinline__ void load_smem(const uint8_t* p, int lane, bool ok, int row_stride = 576) {
+    if (!ok) return;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint8_t* b = p + i * row_stride + (lane >> 3) * 144;
+      hdr[i] = *reinterpret_cast<const uint4*>(b);
+      qs[i] = *reinterpret_cast<const uint4*>(b + 16 + 16 * (lane & 7));
     }
   }
 };
@@ -153,6 +191,17 @@ struct Rec<KIND_IQ4XS> {
       hdr[i] = ldg_stream_v2(b);
       qa[i] = ldg_stream_v2(b + 8 + 16 * p);
       qb[i] = ldg_stream_v2(b + 16 + 16 * p);
+    }
+  }
+  // staged record: row i's superblocks at p + i * row_stride
+  __device__ __forceinline__ void load_smem(const uint8_t* p, int lane, bool ok, int row_stride = 544) {
+    if (!ok) return;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint8_t* b = p + i * row_stride + (lane >> 3) * 136;
+      hdr[i] = *reinterpret_cast<const uint2*>(b);
+      qa[i] = *reinterpret_cast<const uint2*>(b + 8 + 16 * (lane & 7));
+      qb[i] = *reinterpret_cast<const uint2*>(b + 16 + 16 * (lane & 7));
     }
   }
 };
@@ -176,26 +225,24 @@ struct Rec<KIND_Q6K> {
       d[i] = ldg_stream_u16(b + 208);
     }
   }
+  __device__ __forceinline__ void load_smem(const uint8_t*, int, bool, int = 0) {}
 };
 
 // ---------------------------------------------------------------------------------------------
-// Decode + dot. `Planes` are the staged activations in shared memory.
+// Decode + dot. Activations are block_q8_1 in global memory (L1-cached reads).
 
-struct Planes {
-  const int8_t* xq;   // [m][k] int8, 16-byte aligned rows
-  const float* xd;    // [m][k/32] block scale d
-  const float* xs;    // [m][k/32] d * sum(q) of the block (Q4_K only)
-  const uint32_t* grid;  // replicated IQ3_S codebook
+struct Ctx {
+  const uint8_t* xq8;    // [m][k/32] blocks of 36 bytes
+  const uint32_t* grid;  // replicated IQ3_S codebook (shared memory)
   int k;
+  int nb32;
   // debug dump of the raw integer slice sums (gsq_debug_block_sums): out[(m * nrows + row) * (k / g) + group]
   int* dump;
-  int dump_row0, dump_rows, dump_m0;
+  int dump_rows, dump_m0;
 };
 
-template <int M>
-__device__ __forceinline__ void dump_add(const Planes& pl, int m, int row_in_tile, int group, int groups, int v) {
-  const int row = pl.dump_row0 + row_in_tile;
-  if (row < pl.dump_rows) atomicAdd(pl.dump + ((int64_t)(pl.dump_m0 + m) * pl.dump_rows + row) * groups + group, v);
+__device__ __forceinline__ void dump_add(const Ctx& cx, int m, int row, int group, int groups, int v) {
+  if (row < cx.dump_rows) atomicAdd(cx.dump + ((int64_t)(cx.dump_m0 + m) * cx.dump_rows + row) * groups + group, v);
 }
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -204,38 +251,47 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   return r;
 }
 
+__device__ __forceinline__ const uint32_t* q8_block(const Ctx& cx, int m, int blk) {
+  return reinterpret_cast<const uint32_t*>(cx.xq8 + ((int64_t)m * cx.nb32 + blk) * 36);
+}
+
 // wv[i][e] = 4 signed int8 of group e (values 4e..4e+3 of the lane's slice) of row i; common dot loop of
 // the kinds whose lane owns one whole 32-value slice with a single integer sub-scale.
 template <int M, bool DUMP>
 __device__ __forceinline__ void dot_slice(const int (&wv)[4][8], const int (&isc)[4], const float (&dw)[4],
-                                          const Planes& pl, int blk, int row_base, int row_step, float (&acc)[4][M]) {
-  const int nb32 = pl.k >> 5;
+                                          const Ctx& cx, int blk, int row_base, int row_step, float (&acc)[4][M]) {
+  float dws[4];  // d_w times the integer sub-scale: exact in fp32 (11-bit by 6-bit significands)
+#pragma unroll
+  for (int i = 0; i < 4; ++i) dws[i] = dw[i] * (float)isc[i];
 #pragma unroll
   for (int m = 0; m < M; ++m) {
-    const uint4* up = reinterpret_cast<const uint4*>(pl.xq + (int64_t)m * pl.k + (int64_t)blk * 32);
-    const uint4 ua = up[0], ub = up[1];
-    const int u[8] = {(int)ua.x, (int)ua.y, (int)ua.z, (int)ua.w, (int)ub.x, (int)ub.y, (int)ub.z, (int)ub.w};
-    const float d8 = pl.xd[m * nb32 + blk];
+    const uint32_t* b = q8_block(cx, m, blk);
+    int u[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) u[e] = (int)__ldg(b + e);
+    const float d8 = h2f(__ldg(b + 8));
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       int sumi = 0;
 #pragma unroll
       for (int e = 0; e < 8; ++e) sumi = dp4a(wv[i][e], u[e], sumi);
-      if constexpr (DUMP) dump_add<M>(pl, m, row_base + row_step * i, blk, nb32, sumi);
-      acc[i][m] = fmaf(dw[i] * d8, (float)(sumi * isc[i]), acc[i][m]);
+      if constexpr (DUMP) dump_add(cx, m, row_base + row_step * i, blk, cx.nb32, sumi);
+      // |sumi| <= 32 * 127 * 127 < 2^22: adding the bit pattern of 1.5 * 2^23 makes it a float without a conversion
+      const float sf = __int_as_float(sumi + 0x4B400000) - 12582912.0f;
+      acc[i][m] = fmaf(dws[i] * d8, sf, acc[i][m]);
     }
   }
 }
 
-// RS: log2 of the byte stride between codebook entries in the replicated table (7: one copy per lane,
-// 5: one copy per 8 lanes, used when the activations leave less shared memory).
+// The codebook copy in shared memory holds, per entry and per lane-mod-16 replica, the pair (g, -g) of packed
+// int8x4 words (entry i of replica r at byte 128 i + 8 r): a 64-bit load per half-warp touches every bank once.
+// A group's signed word is then one byte permute of the pair, the selector built from the record's sign bits.
 template <int M, int RS, bool DUMP>
-__device__ __forceinline__ void accumulate(const Rec<KIND_IQ3S_PACKED>& r, int rec, int lane, bool ok,
-                                           const Planes& pl, float (&acc)[4][M]) {
+__device__ __forceinline__ void accumulate(const Rec<KIND_IQ3S_PACKED>& r, int row0, int rec, int lane, bool ok,
+                                           const Ctx& cx, float (&acc)[4][M]) {
   (void)ok;
-  constexpr uint32_t mask = RS == 7 ? 0xFF80u : 0x3FE0u;
-  const uint32_t lane_off = RS == 7 ? (uint32_t)lane << 2 : (uint32_t)(lane & 7) << 2;
-  const char* gbase = reinterpret_cast<const char*>(pl.grid);
+  const uint32_t lane_off = (uint32_t)(lane & 15) << 3;
+  const char* gbase = reinterpret_cast<const char*>(cx.grid);
   int wv[4][8];
   int isc[4];
   float dw[4];
@@ -246,27 +302,28 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_IQ3S_PACKED>& r, int r
       const int bit = 9 * (8 * i + e), word = bit >> 5, off = bit & 31;
       uint32_t t;
       if (off + 9 <= 32) {
-        t = off >= RS ? r.idx[word] >> (off - RS) : r.idx[word] << (RS - off);
+        t = off >= 7 ? r.idx[word] >> (off - 7) : r.idx[word] << (7 - off);
       } else {
-        t = __funnelshift_r(r.idx[word], r.idx[word + 1], off - RS);
+        t = __funnelshift_r(r.idx[word], r.idx[word + 1], off - 7);
       }
-      const uint32_t g = *reinterpret_cast<const uint32_t*>(gbase + ((t & mask) | lane_off));
-      const uint32_t msk = prmt(r.sg[i] << (7 - e), 0u, 0xBA98u);  // 0xFF where the value is negative
-      wv[i][e] = (int)((g ^ msk) + (msk & 0x01010101u));
+      const uint2 g = *reinterpret_cast<const uint2*>(gbase + ((t & 0xFF80u) | lane_off));
+      // sign of value p of group e sits at bit 16 (e / 4) + 4 p + e % 4: move it to bit 4 p + 2 of the selector
+      const int sh = 16 * (e >> 2) + (e & 3) - 2;
+      const uint32_t sgs = sh >= 0 ? r.sg[i] >> sh : r.sg[i] << (-sh);
+      wv[i][e] = (int)prmt(g.x, g.y, (sgs & 0x4444u) | 0x3210u);
     }
     isc[i] = 1 + 2 * (int)((r.sc >> (4 * i)) & 15u);
     dw[i] = h2f((i < 2 ? r.dd.x : r.dd.y) >> (16 * (i & 1)));
   }
-  dot_slice<M, DUMP>(wv, isc, dw, pl, rec * 8 + (lane & 7), lane >> 3, 4, acc);
+  dot_slice<M, DUMP>(wv, isc, dw, cx, rec * 8 + (lane & 7), row0 + (lane >> 3), 4, acc);
 }
 
 template <int M, int RS, bool DUMP>
-__device__ __forceinline__ void accumulate(const Rec<KIND_IQ3S_RAW>& r, int rec, int lane, bool ok,
-                                           const Planes& pl, float (&acc)[4][M]) {
+__device__ __forceinline__ void accumulate(const Rec<KIND_IQ3S_RAW>& r, int row0, int rec, int lane, bool ok,
+                                           const Ctx& cx, float (&acc)[4][M]) {
   if (!ok) return;
-  constexpr uint32_t mask = RS == 7 ? 0xFF80u : 0x3FE0u;
-  const uint32_t lane_off = RS == 7 ? (uint32_t)lane << 2 : (uint32_t)(lane & 7) << 2;
-  const char* gbase = reinterpret_cast<const char*>(pl.grid);
+  const uint32_t lane_off = (uint32_t)(lane & 15) << 3;
+  const char* gbase = reinterpret_cast<const char*>(cx.grid);
   int wv[4][8];
   int isc[4];
   float dw[4];
@@ -276,14 +333,14 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_IQ3S_RAW>& r, int rec,
     for (int e = 0; e < 8; ++e) {
       const uint32_t byte = (r.qs[i][e >> 2] >> (8 * (e & 3))) & 0xFFu;
       const uint32_t idx = byte | ((r.qh[i] << (8 - e)) & 0x100u);
-      const uint32_t g = *reinterpret_cast<const uint32_t*>(gbase + (((idx << RS) & mask) | lane_off));
+      const uint32_t g = *reinterpret_cast<const uint32_t*>(gbase + ((idx << 7) | lane_off));
       const uint32_t ones = (((r.sg[i] >> (4 * e)) & 0xFu) * 0x00204081u) & 0x01010101u;
       wv[i][e] = (int)((g ^ (ones * 0xFFu)) + ones);
     }
     isc[i] = 1 + 2 * (int)r.ls[i];
     dw[i] = h2f(r.d[i]);
   }
-  dot_slice<M, DUMP>(wv, isc, dw, pl, (rec * 4 + (lane >> 3)) * 8 + (lane & 7), 0, 1, acc);
+  dot_slice<M, DUMP>(wv, isc, dw, cx, (rec * 4 + (lane >> 3)) * 8 + (lane & 7), row0, 1, acc);
 }
 
 // 8 four-bit indices of v -> the table bytes: lo = entries of the 4 low nibbles, hi = of the 4 high nibbles.
@@ -298,8 +355,8 @@ __device__ __forceinline__ void iq4_lookup(uint32_t v, uint32_t& lo, uint32_t& h
 }
 
 template <int M, int RS, bool DUMP>
-__device__ __forceinline__ void accumulate(const Rec<KIND_IQ4XS>& r, int rec, int lane, bool ok, const Planes& pl,
-                                           float (&acc)[4][M]) {
+__device__ __forceinline__ void accumulate(const Rec<KIND_IQ4XS>& r, int row0, int rec, int lane, bool ok,
+                                           const Ctx& cx, float (&acc)[4][M]) {
   if (!ok) return;
   const int p = lane & 7;
   int wv[4][8];
@@ -319,19 +376,31 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_IQ4XS>& r, int rec, in
     isc[i] = (int)ls - 32;
     dw[i] = h2f(r.hdr[i].x);
   }
-  dot_slice<M, DUMP>(wv, isc, dw, pl, (rec * 4 + (lane >> 3)) * 8 + p, 0, 1, acc);
+  dot_slice<M, DUMP>(wv, isc, dw, cx, (rec * 4 + (lane >> 3)) * 8 + p, row0, 1, acc);
 }
 
+// Q4_K. Lane (superblock b, chunk p) holds 16 bytes of 4 rows: low nibbles = 16 values of sub-block 2 jj,
+// high nibbles = 16 values of sub-block 2 jj + 1 (jj = p / 2). The 6-bit scale / min pair of those two
+// sub-blocks comes out of the 12 packed bytes with lane-constant byte permutes and masks (no branches):
+//   jj < 2 : sc = q16[jj] & 0x3f3f,                                   m = q16[2 + jj] & 0x3f3f
+//   jj >= 2: sc = (q16[jj + 2] & 0x0f0f) | ((q16[jj - 2] & 0xc0c0) >> 2), m = ((q16[jj + 2] >> 4) & 0x0f0f) | ((q16[jj] & 0xc0c0) >> 2)
+// with q16[] the bytes taken as six halfwords. Integer sums become floats by adding the bit pattern of
+// 1.5 * 2^23 inside the integer multiply-add and subtracting it again as a float (exact below 2^22), which
+// keeps the conversions off the slow conversion pipe.
 template <int M, int RS, bool DUMP>
-__device__ __forceinline__ void accumulate(const Rec<KIND_Q4K>& r, int rec, int lane, bool ok, const Planes& pl,
-                                           float (&acc)[4][M]) {
+__device__ __forceinline__ void accumulate(const Rec<KIND_Q4K>& r, int row0, int rec, int lane, bool ok,
+                                           const Ctx& cx, float (&acc)[4][M]) {
   if (!ok) return;
-  const int p = lane & 7, jj = p >> 1, half = p & 1, jm = jj & 1;
-  const int nb32 = pl.k >> 5;
-  const int blk = (rec * 4 + (lane >> 3)) * 8 + 2 * jj;  // q8 block of the low nibbles; high nibbles: blk + 1
+  const int p = lane & 7, jj = p >> 1, half = p & 1;
+  const bool lo4 = jj < 2;
+  const uint32_t selh = (jj & 1) ? 0x4432u : 0x4410u;          // halfword jj % 2 of a word, zero-extended
+  const uint32_t m_low = lo4 ? 0x3F3Fu : 0u, m_top = lo4 ? 0u : 0xC0C0u, m_nib = lo4 ? 0u : 0x0F0Fu;
+  const int blk = (rec * 4 + (lane >> 3)) * 8 + 2 * jj;        // q8 block of the low nibbles; high nibbles: blk + 1
+  constexpr int MAGIC = 0x4B400000;
+  constexpr float MAGIC_F = 12582912.0f;
   int lo[4][4], hi[4][4];
   int sc0[4], sc1[4];
-  float dd[4], dmn0[4], dmn1[4];
+  float dd[4], dmn0[4], dmn1[4];  // d, and -dmin times each sub-block's 6-bit min
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const uint32_t q[4] = {r.qs[i].x, r.qs[i].y, r.qs[i].z, r.qs[i].w};
@@ -340,28 +409,36 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_Q4K>& r, int rec, int 
       lo[i][e] = (int)(q[e] & 0x0F0F0F0Fu);
       hi[i][e] = (int)((q[e] >> 4) & 0x0F0F0F0Fu);
     }
-    const uint32_t s0 = (r.hdr[i].y >> (16 * jm)) & 0xFFFFu;
-    const uint32_t s2 = (r.hdr[i].z >> (16 * jm)) & 0xFFFFu;
-    const uint32_t s4 = (r.hdr[i].w >> (16 * jm)) & 0xFFFFu;
-    const uint32_t a0 = jj < 2 ? (s0 & 0x3F3Fu) : ((s4 & 0x0F0Fu) | ((s0 & 0xC0C0u) >> 2));
-    const uint32_t a1 = jj < 2 ? (s2 & 0x3F3Fu) : (((s4 >> 4) & 0x0F0Fu) | ((s2 & 0xC0C0u) >> 2));
-    sc0[i] = (int)(a0 & 0xFFu);
-    sc1[i] = (int)(a0 >> 8);
+    const uint32_t A = prmt(r.hdr[i].y, 0u, selh), B = prmt(r.hdr[i].z, 0u, selh), C = prmt(r.hdr[i].w, 0u, selh);
+    const uint32_t sc = (A & m_low) | ((A & m_top) >> 2) | (C & m_nib);
+    const uint32_t mn = (B & m_low) | ((B & m_top) >> 2) | ((C >> 4) & m_nib);
+    sc0[i] = (int)(sc & 0xFFu);
+    sc1[i] = (int)(sc >> 8);
     dd[i] = h2f(r.hdr[i].x);
-    // the min term of a whole 32-value sub-block is added by the lane holding its first half
-    const float dmin = half == 0 ? h2f(r.hdr[i].x >> 16) : 0.0f;
-    dmn0[i] = dmin * (float)(a1 & 0xFFu);
-    dmn1[i] = dmin * (float)(a1 >> 8);
+    const float ndm = -h2f(r.hdr[i].x >> 16);
+    dmn0[i] = ndm * (__int_as_float((int)(mn & 0xFFu) + MAGIC) - MAGIC_F);
+    dmn1[i] = ndm * (__int_as_float((int)(mn >> 8) + MAGIC) - MAGIC_F);
   }
+  const uint32_t* b0 = q8_block(cx, 0, blk) + 4 * half;
+  const int64_t mstride = (int64_t)cx.nb32 * 9;
 #pragma unroll
   for (int m = 0; m < M; ++m) {
-    const int8_t* xr = pl.xq + (int64_t)m * pl.k + (int64_t)blk * 32 + 16 * half;
-    const uint4 ul = *reinterpret_cast<const uint4*>(xr);
-    const uint4 uh = *reinterpret_cast<const uint4*>(xr + 32);
-    const int u0[4] = {(int)ul.x, (int)ul.y, (int)ul.z, (int)ul.w};
-    const int u1[4] = {(int)uh.x, (int)uh.y, (int)uh.z, (int)uh.w};
-    const float d80 = pl.xd[m * nb32 + blk], d81 = pl.xd[m * nb32 + blk + 1];
-    const float xs0 = pl.xs[m * nb32 + blk], xs1 = pl.xs[m * nb32 + blk + 1];
+    const uint32_t* bm = b0 + m * mstride;
+    int u0[4], u1[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      u0[e] = (int)__ldg(bm + e);
+      u1[e] = (int)__ldg(bm + 9 + e);
+    }
+    const float d80 = h2f(__ldg(bm + 8 - 4 * half)), d81 = h2f(__ldg(bm + 17 - 4 * half));
+    // sum of the activation quants this lane pairs with its 16 + 16 weights (the min term's factor)
+    int q0 = 0, q1 = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      q0 = dp4a(0x01010101, u0[e], q0);
+      q1 = dp4a(0x01010101, u1[e], q1);
+    }
+    const float xs0 = d80 * (__int_as_float(q0 + MAGIC) - MAGIC_F), xs1 = d81 * (__int_as_float(q1 + MAGIC) - MAGIC_F);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       int dl = 0, dh = 0;
@@ -371,22 +448,22 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_Q4K>& r, int rec, int 
         dh = dp4a(hi[i][e], u1[e], dh);
       }
       if constexpr (DUMP) {
-        dump_add<M>(pl, m, i, blk, nb32, dl);
-        dump_add<M>(pl, m, i, blk + 1, nb32, dh);
+        dump_add(cx, m, row0 + i, blk, cx.nb32, dl);
+        dump_add(cx, m, row0 + i, blk + 1, cx.nb32, dh);
       }
-      const float sd = d80 * (float)(dl * sc0[i]) + d81 * (float)(dh * sc1[i]);
-      const float sm = xs0 * dmn0[i] + xs1 * dmn1[i];
-      acc[i][m] += dd[i] * sd - sm;
+      const float fi0 = __int_as_float(dl * sc0[i] + MAGIC) - MAGIC_F;
+      const float fi1 = __int_as_float(dh * sc1[i] + MAGIC) - MAGIC_F;
+      const float t = fmaf(fi1, d81, fi0 * d80);
+      acc[i][m] = fmaf(xs1, dmn1[i], fmaf(xs0, dmn0[i], fmaf(t, dd[i], acc[i][m])));
     }
   }
 }
 
 template <int M, int RS, bool DUMP>
-__device__ __forceinline__ void accumulate(const Rec<KIND_Q6K>& r, int rec, int lane, bool ok, const Planes& pl,
-                                           float (&acc)[4][M]) {
+__device__ __forceinline__ void accumulate(const Rec<KIND_Q6K>& r, int row0, int rec, int lane, bool ok,
+                                           const Ctx& cx, float (&acc)[4][M]) {
   (void)ok;
   const int n = lane >> 4, w16 = lane & 15;
-  const int nb32 = pl.k >> 5;
   const int blk = rec * 8 + 4 * n + (w16 >> 3);
   int v0[4], v1[4], s0[4], s1[4];
   float dd[4];
@@ -403,16 +480,17 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_Q6K>& r, int rec, int 
   }
 #pragma unroll
   for (int m = 0; m < M; ++m) {
-    const int* xr = reinterpret_cast<const int*>(pl.xq + (int64_t)m * pl.k + (int64_t)blk * 32) + (w16 & 7);
-    const int u0 = xr[0], u1 = xr[16];  // 64 values further: q8 block blk + 2
-    const float d80 = pl.xd[m * nb32 + blk], d81 = pl.xd[m * nb32 + blk + 2];
+    const uint32_t* b0 = q8_block(cx, m, blk);
+    const uint32_t* b1 = q8_block(cx, m, blk + 2);  // 64 values further
+    const int u0 = (int)__ldg(b0 + (w16 & 7)), u1 = (int)__ldg(b1 + (w16 & 7));
+    const float d80 = h2f(__ldg(b0 + 8)), d81 = h2f(__ldg(b1 + 8));
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int p0 = dp4a(v0[i], u0, 0), p1 = dp4a(v1[i], u1, 0);
       if constexpr (DUMP) {
         const int g16 = rec * 16 + 8 * n + (w16 >> 2);
-        dump_add<M>(pl, m, i, g16, pl.k >> 4, p0);
-        dump_add<M>(pl, m, i, g16 + 4, pl.k >> 4, p1);
+        dump_add(cx, m, row0 + i, g16, cx.k >> 4, p0);
+        dump_add(cx, m, row0 + i, g16 + 4, cx.k >> 4, p1);
       }
       const float sf = d80 * (float)(p0 * s0[i]) + d81 * (float)(p1 * s1[i]);
       acc[i][m] = fmaf(dd[i], sf, acc[i][m]);
@@ -425,151 +503,292 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_Q6K>& r, int rec, int 
 
 template <int KIND>
 __host__ __device__ constexpr bool kind_uses_grid() { return KIND == KIND_IQ3S_PACKED || KIND == KIND_IQ3S_RAW; }
+// The staged variant moves SUB records per ring stage (one wait, one refill and one round of loop
+// bookkeeping per 3.5 - 4.6 KB instead of per 1.8 - 2.3 KB).
+constexpr int SUB = 2;
+template <int KIND>
+__host__ __device__ constexpr int rec_bytes() {
+  return KIND == KIND_IQ3S_PACKED ? 1760 : KindTraits<KIND>::rec_sb * KindTraits<KIND>::bs * 4;
+}
+template <int KIND>
+__host__ __device__ constexpr int stage_bytes() { return SUB * rec_bytes<KIND>(); }
 
-__host__ __device__ inline size_t gemv_smem_bytes(int kind, int rs, int m, int k) {
+// Set (sticky) when a bounded wait on a bulk copy gave up; read through gsq_device_error_flag.
+__device__ int g_gemv_error = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// Wait for the phase with the given parity; gives up after about a second and raises the error flag.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done = 0;
+  for (int spin = 0; spin < (1 << 22); ++spin) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return;
+  }
+  atomicExch(&g_gemv_error, 1);
+}
+
+// Lane 0 of a warp: start the bulk copies of one stage (SUB records) into the ring. Row-major kinds copy 4
+// row segments (rows past the end of W are replaced by the last row; their results are never stored).
+template <int KIND>
+__device__ __forceinline__ void issue_record(const GemvArgs& a, uint32_t stage, uint32_t bar, int row0, int rec) {
+  const int nsb = a.k >> 8;
+  if (KIND == KIND_IQ3S_PACKED) {
+    const uint32_t bytes = (uint32_t)min(SUB, nsb - rec * SUB) * 1760u;
+    mbar_expect_tx(bar, bytes);
+    bulk_g2s(stage, a.w + (int64_t)row0 * a.row_bytes + (int64_t)rec * (SUB * 1760), bytes, bar);
+  } else {
+    constexpr int BS = KindTraits<KIND>::bs;
+    const int here = min(4 * SUB, nsb - rec * (4 * SUB));
+    const uint32_t bytes = (uint32_t)(here * BS);
+    mbar_expect_tx(bar, 4 * bytes);
+    const uint8_t* src = a.w + (int64_t)row0 * a.row_bytes + (int64_t)rec * (4 * SUB * BS);
+    const int last = a.nrows - 1 - row0;  // rows of this tile that exist, minus one
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      bulk_g2s(stage + i * (4 * SUB * BS), src + (int64_t)min(i, last) * a.row_bytes, bytes, bar);
+    }
+  }
+}
+
+__host__ __device__ inline size_t gemv_smem_bytes(int kind, int rs, int m, int stages) {
+  const int tr = kind == KIND_IQ3S_PACKED ? 16 : 4;
+  const int rb = kind == KIND_IQ3S_PACKED ? 1760 : kind == KIND_Q4K ? 2304 : kind == KIND_IQ4XS ? 2176 : 0;
   size_t s = 0;
   if (kind == KIND_IQ3S_PACKED || kind == KIND_IQ3S_RAW) s += (size_t)512 << rs;  // replicated codebook
-  s += (size_t)m * k;                                   // int8 plane
-  s += (size_t)m * (k / 32) * 4;                        // d plane
-  if (kind == KIND_Q4K) s += (size_t)m * (k / 32) * 4;  // d * sum(q) plane
-  s += (size_t)GEMV_WARPS * 16 * m * 4;                 // partial sums
+  s += (size_t)GEMV_WARPS * SEG_CAP * tr * m * 4;                                  // partial sums of a round
+  if (stages > 0) s += (size_t)GEMV_WARPS * stages * (SUB * rb + 8);               // ring + its barriers
   return s;
 }
 
-template <int KIND, int M, int RS, bool DUMP>
+// TMA: weights come through a per-warp ring of bulk copies (cp.async.bulk + mbarrier) instead of direct loads.
+template <int KIND, int M, int RS, bool DUMP, bool TMA>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a) {
-  extern __shared__ __align__(16) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];
   constexpr int TR = KindTraits<KIND>::tile_rows;
   constexpr int RSB = KindTraits<KIND>::rec_sb;
+  constexpr int PBUF = GEMV_WARPS * SEG_CAP * TR * M;  // floats per partial buffer
+  constexpr int RECB = TMA ? stage_bytes<KIND>() : rec_bytes<KIND>();
+  cg::cluster_group cluster = cg::this_cluster();
+  const int cs = (int)cluster.num_blocks();
+  const int crank = (int)cluster.block_rank();
+  const int cluster_id = (int)blockIdx.x / cs;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int nb32 = a.k >> 5;
+  const int nsb = a.k >> 8;
+  const int nrec = a.nrec;
 
   uint8_t* sp = smem;
   uint32_t* grid_s = reinterpret_cast<uint32_t*>(sp);
   if (kind_uses_grid<KIND>()) sp += (size_t)512 << RS;
-  int8_t* xq = reinterpret_cast<int8_t*>(sp);
-  sp += (size_t)M * a.k;
-  float* xd = reinterpret_cast<float*>(sp);
-  sp += (size_t)M * nb32 * 4;
-  float* xs = reinterpret_cast<float*>(sp);
-  if (KIND == KIND_Q4K) sp += (size_t)M * nb32 * 4;
-  float* partial = reinterpret_cast<float*>(sp);  // [warp][16][M]
+  float* partial = reinterpret_cast<float*>(sp);
+  sp += (size_t)PBUF * 4;
+  const int stages = 1 << a.stage_shift;
+  const uint32_t smask = (uint32_t)stages - 1;
+  // ring of this warp (16-byte aligned: every size above is a multiple of 16), then all the barriers
+  const uint8_t* ring = sp + (size_t)warp * stages * RECB;
+  const uint32_t ring_u32 = smem_u32(ring);
+  const uint32_t bars_u32 = smem_u32(sp + (size_t)GEMV_WARPS * stages * RECB) + (uint32_t)(warp * stages * 8);
 
-  // stage the codebook copies and the activation planes
+  Ctx cx;
+  cx.xq8 = a.xq8; cx.grid = grid_s; cx.k = a.k; cx.nb32 = a.k >> 5;
+  cx.dump = a.dump; cx.dump_rows = a.nrows; cx.dump_m0 = a.dump_m0;
+
+  const int tile_begin = cluster_id * a.tiles_base + min(cluster_id, a.tiles_extra);
+  const int tile_cnt = a.tiles_base + (cluster_id < a.tiles_extra ? 1 : 0);
+  const int wc = cs * GEMV_WARPS;
+  const int gw = crank * GEMV_WARPS + warp;
+
+  if (TMA) {
+    if (lane == 0) {
+      for (int s = 0; s < stages; ++s) mbar_init(bars_u32 + 8 * s, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+  }
+
+  // the first loads go out before anything else, so the codebook staging below hides behind them
+  Rec<KIND> cur;
+  bool ok_cur = false;
+  uint32_t cnt = 0;       // records this warp has consumed (ring position and barrier phase)
+  int pre_issued = 0;     // records of round 0 already in flight
+  {
+    const int tiles_r = min(a.tiles_round, tile_cnt);
+    const int rr = tiles_r * nrec, c = (rr + wc - 1) / wc;
+    const int idx0 = gw * c, idx1 = min(rr, idx0 + c);
+    if (idx0 < idx1) {
+      int tl = idx0 / nrec, rec = idx0 - tl * nrec;
+      if (TMA) {
+        for (; pre_issued < stages && idx0 + pre_issued < idx1; ++pre_issued) {
+          if (lane == 0)
+            issue_record<KIND>(a, ring_u32 + pre_issued * RECB, bars_u32 + 8 * pre_issued, (tile_begin + tl) * TR, rec);
+          if (++rec == nrec) { rec = 0; ++tl; }
+        }
+      } else {
+        ok_cur = RSB == 1 || (rec * 4 + (lane >> 3)) < nsb;
+        cur.load(a, (tile_begin + tl) * TR, rec, lane, ok_cur);
+      }
+    }
+  }
   if (kind_uses_grid<KIND>()) {
-    constexpr int REP = 1 << (RS - 2);
-    for (int i = tid; i < 512 * REP; i += GEMV_THREADS) grid_s[i] = g_iq3s_grid[i >> (RS - 2)];
-  }
-  for (int b = tid; b < M * nb32; b += GEMV_THREADS) {
-    const uint32_t* src = reinterpret_cast<const uint32_t*>(a.xq8 + (int64_t)b * 36);
-    uint32_t q[8];
+    // one global load per thread (512 threads, 512 entries), then the 16 replicas of its entry
+    const uint32_t g = g_iq3s_grid[tid & 511];
+    // per-byte negation: no byte of the codebook is zero, so ~g + 1 per byte never carries
+    const uint2 pair = make_uint2(g, ~g + 0x01010101u);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint2*>(grid_s) + (tid & 511) * 16);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) q[e] = __ldg(src + e);
-    const uint32_t ds = __ldg(src + 8);
-    uint4* dst = reinterpret_cast<uint4*>(xq + (int64_t)b * 32);
-    dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
-    dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
-    const float d = h2f(ds);
-    xd[b] = d;
-    if (KIND == KIND_Q4K) {
-      int s = 0;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) s = dp4a(0x01010101, (int)q[e], s);
-      xs[b] = d * (float)s;
-    }
-  }
-  __syncthreads();
-
-  Planes pl;
-  pl.xq = xq; pl.xd = xd; pl.xs = xs; pl.grid = grid_s; pl.k = a.k;
-  pl.dump = a.dump; pl.dump_rows = a.nrows; pl.dump_m0 = a.dump_m0; pl.dump_row0 = 0;
-
-  const int parts = a.parts;
-  const int tiles = GEMV_WARPS / parts;
-  const int tile_l = warp / parts, part = warp - tile_l * parts;
-  const int nsb = a.k >> 8;
-  const int r_begin = part * a.rec_per_part;
-  const int r_end = min(a.nrec, r_begin + a.rec_per_part);
-
-  for (int unit = blockIdx.x; unit < a.n_units; unit += gridDim.x) {
-    const int row0 = (unit * tiles + tile_l) * TR;
-    pl.dump_row0 = row0;
-    float acc[4][M];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int m = 0; m < M; ++m) acc[i][m] = 0.0f;
-
-    if (row0 < a.nrows && r_begin < r_end) {
-      Rec<KIND> cur;
-      bool ok_cur = RSB == 1 || (r_begin * 4 + (lane >> 3)) < nsb;
-      cur.load(a, row0, r_begin, lane, ok_cur);
-#pragma unroll 1
-      for (int rec = r_begin; rec < r_end; ++rec) {
-        Rec<KIND> nxt;
-        const bool has_next = rec + 1 < r_end;
-        const bool ok_nxt = has_next && (RSB == 1 || ((rec + 1) * 4 + (lane >> 3)) < nsb);
-        nxt.load(a, row0, rec + 1, lane, ok_nxt);
-        accumulate<M, RS, DUMP>(cur, rec, lane, ok_cur, pl, acc);
-        cur = nxt;
-        ok_cur = ok_nxt;
-      }
-    }
-
-    // lanes that share weight rows add up; then one lane per row group parks the sums in shared memory
-    if (KIND == KIND_IQ3S_PACKED) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-          float v = acc[i][m];
-          v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
-          v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
-          v += __shfl_xor_sync(0xFFFFFFFFu, v, 4);
-          acc[i][m] = v;
-        }
-      if ((lane & 7) == 0) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-          for (int m = 0; m < M; ++m) partial[(warp * 16 + (lane >> 3) + 4 * i) * M + m] = acc[i][m];
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-          float v = acc[i][m];
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
-          acc[i][m] = v;
-        }
-      if (lane == 0) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-          for (int m = 0; m < M; ++m) partial[(warp * 16 + i) * M + m] = acc[i][m];
-      }
-    }
+    for (int r2 = 0; r2 < 8; ++r2) dst[r2] = make_uint4(pair.x, pair.y, pair.x, pair.y);
     __syncthreads();
-    const int rows_step = tiles * TR;
-    for (int o = tid; o < rows_step * M; o += GEMV_THREADS) {
-      const int m = o / rows_step, rr = o - m * rows_step;
-      const int tl = rr / TR, ri = rr - tl * TR;
-      const int row = (unit * tiles + tl) * TR + ri;
+  }
+
+  for (int t0 = 0; t0 < tile_cnt; t0 += a.tiles_round) {
+    const int tiles_r = min(a.tiles_round, tile_cnt - t0);
+    const int rr = tiles_r * nrec;
+    const int c = (rr + wc - 1) / wc;  // records per warp this round
+    const int idx0 = gw * c, idx1 = min(rr, idx0 + c);
+    float* mypart = partial + warp * (SEG_CAP * TR * M);
+    if (idx0 < idx1) {
+      int tl = idx0 / nrec, rec = idx0 - tl * nrec;
+      const int first_tl = tl;
+      // issue cursor of the staged variant: the record `stages` ahead of the one being consumed
+      int itl = tl, irec = rec, iidx = idx0;
+      if (TMA) {
+        int ahead = t0 == 0 ? pre_issued : 0;
+        for (int j = 0; j < ahead; ++j) { if (++irec == nrec) { irec = 0; ++itl; } }
+        iidx = idx0 + ahead;
+        for (; ahead < stages && iidx < idx1; ++ahead, ++iidx) {
+          const uint32_t st = (cnt + ahead) & smask;
+          if (lane == 0) issue_record<KIND>(a, ring_u32 + st * RECB, bars_u32 + 8 * st, (tile_begin + t0 + itl) * TR, irec);
+          if (++irec == nrec) { irec = 0; ++itl; }
+        }
+      } else if (t0 != 0) {
+        ok_cur = RSB == 1 || (rec * 4 + (lane >> 3)) < nsb;
+        cur.load(a, (tile_begin + t0 + tl) * TR, rec, lane, ok_cur);
+      }
+      float acc[4][M];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[i][m] = 0.0f;
+#pragma unroll 1
+      for (int idx = idx0; idx < idx1; ++idx) {
+        const bool has_next = idx + 1 < idx1;
+        const bool wrap = rec + 1 == nrec;
+        const int ntl = wrap ? tl + 1 : tl, nrc = wrap ? 0 : rec + 1;
+        Rec<KIND> nxt;
+        bool ok_nxt = false;
+        if (TMA) {
+          const uint32_t st = cnt & smask;
+          mbar_wait(bars_u32 + 8 * st, (cnt >> a.stage_shift) & 1u);
+#pragma unroll
+          for (int h = 0; h < SUB; ++h) {
+            const int srec = rec * SUB + h;
+            const bool okh = RSB == 1 ? srec < nsb : (srec * 4 + (lane >> 3)) < nsb;
+            if (RSB == 1 && !okh) break;  // warp-uniform: the last stage of an odd superblock count is half full
+            cur.load_smem(ring + st * RECB + h * (RSB == 1 ? rec_bytes<KIND>() : rec_bytes<KIND>() / 4), lane, okh,
+                          RECB / 4);
+            accumulate<M, RS, DUMP>(cur, (tile_begin + t0 + tl) * TR, srec, lane, okh, cx, acc);
+          }
+        } else {
+          ok_nxt = has_next && (RSB == 1 || (nrc * 4 + (lane >> 3)) < nsb);
+          nxt.load(a, (tile_begin + t0 + ntl) * TR, nrc, lane, ok_nxt);
+          accumulate<M, RS, DUMP>(cur, (tile_begin + t0 + tl) * TR, rec, lane, ok_cur, cx, acc);
+        }
+        if (TMA) {
+          // the stage has been read into registers and used: refill it with the record `stages` ahead
+          __syncwarp();
+          if (iidx < idx1) {
+            const uint32_t st = cnt & smask;
+            if (lane == 0) issue_record<KIND>(a, ring_u32 + st * RECB, bars_u32 + 8 * st, (tile_begin + t0 + itl) * TR, irec);
+            if (++irec == nrec) { irec = 0; ++itl; }
+            ++iidx;
+          }
+          ++cnt;
+        }
+        if (!has_next || wrap) {
+          // leaving tile tl: lanes that share weight rows add up, one lane per row parks the sums
+          float* seg = mypart + (tl - first_tl) * (TR * M);
+          if (KIND == KIND_IQ3S_PACKED) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int m = 0; m < M; ++m) {
+                float v = acc[i][m];
+                v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+                v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
+                v += __shfl_xor_sync(0xFFFFFFFFu, v, 4);
+                if ((lane & 7) == 0) seg[((lane >> 3) + 4 * i) * M + m] = v;
+                acc[i][m] = 0.0f;
+              }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int m = 0; m < M; ++m) {
+                float v = acc[i][m];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+                if (lane == 0) seg[i * M + m] = v;
+                acc[i][m] = 0.0f;
+              }
+          }
+        }
+        if (!TMA) {
+          cur = nxt;
+          ok_cur = ok_nxt;
+        }
+        tl = ntl;
+        rec = nrc;
+      }
+    }
+    cluster.sync();
+    // every row of the round: add the partial sums of the warps that touched its tile, in warp order
+    const int rows_r = tiles_r * TR;
+    for (int e = crank * GEMV_THREADS + tid; e < rows_r * M; e += cs * GEMV_THREADS) {
+      const int m = e / rows_r, r2 = e - m * rows_r;
+      const int tl = r2 / TR, ri = r2 - tl * TR;
+      const int row = (tile_begin + t0 + tl) * TR + ri;
       if (row < a.nrows) {
+        const int w0 = (tl * nrec) / c, w1 = ((tl + 1) * nrec - 1) / c;
         float v = 0.0f;
-        for (int p = 0; p < parts; ++p) v += partial[((tl * parts + p) * 16 + ri) * M + m];
+        for (int w = w0; w <= w1; ++w) {
+          const int seg = tl - (w * c) / nrec;
+          const float* src = cluster.map_shared_rank(partial, w / GEMV_WARPS) +
+                             ((w % GEMV_WARPS) * SEG_CAP + seg) * (TR * M) + ri * M + m;
+          v += *src;
+        }
         store_out_dyn(a.y, a.y_dtype, (int64_t)m * a.ldy + row, v);
       }
     }
-    __syncthreads();
+    // the partial sums are reused by the next round, and no CTA may leave while another still reads its
+    // shared memory
+    cluster.sync();
   }
 }
 
 // ---------------------------------------------------------------------------------------------
 // Host side.
 
+static int g_force_direct = 0;
+static int g_force_cluster = 0;  // tests / experiments: 0 = choose, else 1, 2 or 4
 static int g_iq4_table_device_mask = 0;  // bit d set once device d has c_iq4nl_words
 
 int gemv_device_init(int device) {
@@ -585,39 +804,115 @@ int gemv_device_init(int device) {
   return GSQ_OK;
 }
 
-template <int KIND, int M, int RS, bool DUMP = false>
-static int launch_gemv(const GemvArgs& a, int grid, size_t smem, cudaStream_t st) {
-  auto kern = gemv_kernel<KIND, M, RS, DUMP>;
-  static int configured_mask = 0;  // per instantiation: devices whose smem attribute is set
+struct ClusterPlan {
+  int cs;        // CTAs per cluster
+  int clusters;  // clusters launched (all co-resident)
+};
+
+// Per kernel instantiation and device: the cluster size that keeps most SMs busy with every cluster resident.
+template <int KIND, int M, int RS, bool DUMP, bool TMA>
+static int plan_clusters(size_t smem, int sm_count, ClusterPlan* out) {
+  static ClusterPlan cache[32];
+  static bool have[32];
   int dev = 0;
   GSQ_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev >= 32 || !((configured_mask >> dev) & 1)) {
-    GSQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    if (dev < 32) configured_mask |= 1 << dev;
+  if (dev < 32 && have[dev] && !g_force_cluster) {
+    *out = cache[dev];
+    return GSQ_OK;
   }
-  kern<<<grid, GEMV_THREADS, smem, st>>>(a);
-  GSQ_CUDA_TRY(cudaGetLastError());
+  auto kern = gemv_kernel<KIND, M, RS, DUMP, TMA>;
+  GSQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+  ClusterPlan best{1, sm_count};
+  for (int cs : {4, 2}) {
+    if (g_force_cluster && cs != g_force_cluster) continue;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(sm_count / cs * cs));
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = cs;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      continue;
+    }
+    n = n < sm_count / cs ? n : sm_count / cs;
+    if (n * cs > best.cs * best.clusters || (best.cs == 1 && n * cs >= (sm_count * 15) / 16)) best = ClusterPlan{cs, n};
+  }
+  if (dev < 32 && !g_force_cluster) {
+    cache[dev] = best;
+    have[dev] = true;
+  }
+  *out = best;
   return GSQ_OK;
 }
 
+template <int KIND, int M, int RS, bool DUMP, bool TMA>
+static int launch_gemv_t(GemvArgs a, int sm_count, int max_smem, cudaStream_t st) {
+  // ring depth: the deepest power of two that fits beside the codebook and the partial sums
+  int shift = 0;
+  if (TMA) {
+    shift = 2;
+    while (shift > 1 && gemv_smem_bytes(KIND, RS, M, 1 << shift) > (size_t)max_smem) --shift;
+  }
+  a.stage_shift = shift;
+  if (TMA) a.nrec = ((a.k >> 8) + KindTraits<KIND>::rec_sb * SUB - 1) / (KindTraits<KIND>::rec_sb * SUB);
+  const size_t smem = gemv_smem_bytes(KIND, RS, M, TMA ? 1 << shift : 0);
+  if (smem > (size_t)max_smem) return GSQ_ERR_TOO_LARGE;
+  ClusterPlan plan;
+  int rc = plan_clusters<KIND, M, RS, DUMP, TMA>(smem, sm_count, &plan);
+  if (rc != GSQ_OK) return rc;
+  const int wc = plan.cs * GEMV_WARPS;
+  a.tiles_base = a.ntiles / plan.clusters;
+  a.tiles_extra = a.ntiles % plan.clusters;
+  a.tiles_round = (SEG_CAP - 2) * wc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(plan.clusters * plan.cs));
+  cfg.blockDim = dim3(GEMV_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = plan.cs;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<KIND, M, RS, DUMP, TMA>, a));
+  return GSQ_OK;
+}
+
+// The staged variant needs 16-byte aligned row segments of whole 16-byte multiples: always true for packed
+// IQ3_S and Q4_K (144-byte blocks), for IQ4_XS (136-byte blocks) only when K is a multiple of 1024.
+template <int KIND, int M, int RS, bool DUMP = false>
+static int launch_gemv(const GemvArgs& a, int sm_count, int max_smem, cudaStream_t st) {
+  constexpr bool can = KIND == KIND_IQ3S_PACKED || KIND == KIND_Q4K || KIND == KIND_IQ4XS;
+  if constexpr (can && !DUMP) {
+    if (!a.force_direct && (KIND != KIND_IQ4XS || a.k % 1024 == 0)) return launch_gemv_t<KIND, M, RS, DUMP, true>(a, sm_count, max_smem, st);
+  }
+  return launch_gemv_t<KIND, M, RS, DUMP, false>(a, sm_count, max_smem, st);
+}
+
 template <int KIND, int RS>
-static int launch_gemv_m(int m, const GemvArgs& a, int grid, size_t smem, cudaStream_t st) {
+static int launch_gemv_m(int m, const GemvArgs& a, int sm_count, int max_smem, cudaStream_t st) {
   switch (m) {
-    case 1: return launch_gemv<KIND, 1, RS>(a, grid, smem, st);
-    case 2: return launch_gemv<KIND, 2, RS>(a, grid, smem, st);
-    case 3: return launch_gemv<KIND, 3, RS>(a, grid, smem, st);
-    case 4: return launch_gemv<KIND, 4, RS>(a, grid, smem, st);
-    case 5: return launch_gemv<KIND, 5, RS>(a, grid, smem, st);
-    case 6: return launch_gemv<KIND, 6, RS>(a, grid, smem, st);
-    case 7: return launch_gemv<KIND, 7, RS>(a, grid, smem, st);
-    case 8: return launch_gemv<KIND, 8, RS>(a, grid, smem, st);
+    case 1: return launch_gemv<KIND, 1, RS>(a, sm_count, max_smem, st);
+    case 2: return launch_gemv<KIND, 2, RS>(a, sm_count, max_smem, st);
+    case 3: return launch_gemv<KIND, 3, RS>(a, sm_count, max_smem, st);
+    case 4: return launch_gemv<KIND, 4, RS>(a, sm_count, max_smem, st);
+    case 5: return launch_gemv<KIND, 5, RS>(a, sm_count, max_smem, st);
+    case 6: return launch_gemv<KIND, 6, RS>(a, sm_count, max_smem, st);
+    case 7: return launch_gemv<KIND, 7, RS>(a, sm_count, max_smem, st);
+    case 8: return launch_gemv<KIND, 8, RS>(a, sm_count, max_smem, st);
     default: return GSQ_ERR_UNSUPPORTED;
   }
 }
 
-}  // namespace gsq
-
-namespace gsq {
 static int gemv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_q8,
                      int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump,
                      int dump_m0) {
@@ -643,16 +938,6 @@ static int gemv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_ty
   const int tile_rows = kind == KIND_IQ3S_PACKED ? 16 : 4;
   const int rec_sb = (kind == KIND_IQ3S_PACKED || kind == KIND_Q6K) ? 1 : 4;
   const int nsb = (int)(k / 256);
-  const int nrec = (nsb + rec_sb - 1) / rec_sb;
-  const int ntiles = (int)((rows + tile_rows - 1) / tile_rows);
-  // column parts: as few as keep every SM busy (each extra part shortens a warp's run of records and
-  // adds to the shared-memory reduction), never more than the records of a tile
-  int parts = 1;
-  while (parts < GEMV_WARPS && parts * 2 <= nrec &&
-         (ntiles + (GEMV_WARPS / parts) - 1) / (GEMV_WARPS / parts) < 2 * di.sm_count) {
-    parts *= 2;
-  }
-  const int tiles = GEMV_WARPS / parts;
   GemvArgs a;
   a.w = (const uint8_t*)w;
   a.row_bytes = row_bytes;
@@ -662,56 +947,59 @@ static int gemv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_ty
   a.y = y;
   a.y_dtype = y_dtype;
   a.ldy = y_row_stride;
-  a.parts = parts;
-  a.n_units = (ntiles + tiles - 1) / tiles;
-  a.nrec = nrec;
-  a.rec_per_part = (nrec + parts - 1) / parts;
+  a.ntiles = (int)((rows + tile_rows - 1) / tile_rows);
+  a.nrec = (nsb + rec_sb - 1) / rec_sb;
+  a.tiles_base = a.tiles_extra = a.tiles_round = 0;
   a.dump = dump;
   a.dump_m0 = dump_m0;
-  const int grid = a.n_units < di.sm_count ? a.n_units : di.sm_count;
+  a.stage_shift = 0;
+  a.force_direct = g_force_direct;
   cudaStream_t st = (cudaStream_t)stream;
-
-  const bool uses_grid = kind == KIND_IQ3S_PACKED || kind == KIND_IQ3S_RAW;
-  int rs = 7;
-  size_t smem = gemv_smem_bytes(kind, rs, (int)m, (int)k);
-  if (uses_grid && smem > (size_t)di.max_smem_optin) {
-    rs = 5;
-    smem = gemv_smem_bytes(kind, rs, (int)m, (int)k);
-  }
-  if (smem > (size_t)di.max_smem_optin) return GSQ_ERR_TOO_LARGE;
+  const int sms = di.sm_count, smem = di.max_smem_optin;
 
   if (dump) {  // debug build of the same kernel, one activation row per launch
     if (m != 1) return GSQ_ERR_UNSUPPORTED;
     switch (kind) {
-      case KIND_IQ3S_PACKED:
-        return rs == 7 ? launch_gemv<KIND_IQ3S_PACKED, 1, 7, true>(a, grid, smem, st)
-                       : launch_gemv<KIND_IQ3S_PACKED, 1, 5, true>(a, grid, smem, st);
-      case KIND_IQ3S_RAW:
-        return rs == 7 ? launch_gemv<KIND_IQ3S_RAW, 1, 7, true>(a, grid, smem, st)
-                       : launch_gemv<KIND_IQ3S_RAW, 1, 5, true>(a, grid, smem, st);
-      case KIND_Q4K: return launch_gemv<KIND_Q4K, 1, 7, true>(a, grid, smem, st);
-      case KIND_IQ4XS: return launch_gemv<KIND_IQ4XS, 1, 7, true>(a, grid, smem, st);
-      default: return launch_gemv<KIND_Q6K, 1, 7, true>(a, grid, smem, st);
+      case KIND_IQ3S_PACKED: return launch_gemv<KIND_IQ3S_PACKED, 1, 7, true>(a, sms, smem, st);
+      case KIND_IQ3S_RAW: return launch_gemv<KIND_IQ3S_RAW, 1, 7, true>(a, sms, smem, st);
+      case KIND_Q4K: return launch_gemv<KIND_Q4K, 1, 7, true>(a, sms, smem, st);
+      case KIND_IQ4XS: return launch_gemv<KIND_IQ4XS, 1, 7, true>(a, sms, smem, st);
+      default: return launch_gemv<KIND_Q6K, 1, 7, true>(a, sms, smem, st);
     }
   }
   switch (kind) {
-    case KIND_IQ3S_PACKED:
-      return rs == 7 ? launch_gemv_m<KIND_IQ3S_PACKED, 7>((int)m, a, grid, smem, st)
-                     : launch_gemv_m<KIND_IQ3S_PACKED, 5>((int)m, a, grid, smem, st);
-    case KIND_IQ3S_RAW:
-      return rs == 7 ? launch_gemv_m<KIND_IQ3S_RAW, 7>((int)m, a, grid, smem, st)
-                     : launch_gemv_m<KIND_IQ3S_RAW, 5>((int)m, a, grid, smem, st);
-    case KIND_Q4K: return launch_gemv_m<KIND_Q4K, 7>((int)m, a, grid, smem, st);
-    case KIND_IQ4XS: return launch_gemv_m<KIND_IQ4XS, 7>((int)m, a, grid, smem, st);
-    default: return launch_gemv_m<KIND_Q6K, 7>((int)m, a, grid, smem, st);
+    case KIND_IQ3S_PACKED: return launch_gemv_m<KIND_IQ3S_PACKED, 7>((int)m, a, sms, smem, st);
+    case KIND_IQ3S_RAW: return launch_gemv_m<KIND_IQ3S_RAW, 7>((int)m, a, sms, smem, st);
+    case KIND_Q4K: return launch_gemv_m<KIND_Q4K, 7>((int)m, a, sms, smem, st);
+    case KIND_IQ4XS: return launch_gemv_m<KIND_IQ4XS, 7>((int)m, a, sms, smem, st);
+    default: return launch_gemv_m<KIND_Q6K, 7>((int)m, a, sms, smem, st);
   }
 }
+
 }  // namespace gsq
 
 extern "C" int gsq_mul_mat_vec_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,
                                   const void* x_q8, int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride,
                                   void* stream) {
   return gsq::gemv_host(w, row_bytes, rows, ggml_type, packed, x_q8, m, k, y, y_dtype, y_row_stride, stream, nullptr, 0);
+}
+
+extern "C" int gsq_debug_force_direct_loads(int on) {
+  const int old = gsq::g_force_direct;
+  gsq::g_force_direct = on ? 1 : 0;
+  return old;
+}
+
+extern "C" int gsq_debug_force_cluster_size(int cs) {
+  const int old = gsq::g_force_cluster;
+  gsq::g_force_cluster = (cs == 1 || cs == 2 || cs == 4) ? cs : 0;
+  return old;
+}
+
+extern "C" int gsq_device_error_flag(int* flag) {
+  if (!flag) return GSQ_ERR_UNSUPPORTED;
+  GSQ_CUDA_TRY(cudaMemcpyFromSymbol(flag, gsq::g_gemv_error, sizeof(int)));
+  return GSQ_OK;
 }
 
 extern "C" int gsq_debug_block_sums(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,

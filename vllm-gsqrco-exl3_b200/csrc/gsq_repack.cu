@@ -13,19 +13,20 @@
 //                 the stream holds 32 nine-bit codebook indices, row i group e (values 4e..4e+3 of the
 //                 slice) at bit 9 * (8 i + e): qs byte | qh bit << 8
 //   [1152, 1664)  16 bytes per lane: word i = the slice's 32 sign bits of row r_i, transposed so that
-//                 bit 8 p + e is the sign of value p of group e (GGUF order: bit 4 e + p)
+//                 bit 16 (e / 4) + 4 p + e % 4 is the sign of value p of group e (GGUF order: bit 4 e + p):
+//                 a shift and one AND/OR turn them into the byte-permute selector that picks +g or -g
 //   [1664, 1728)   2 bytes per lane: nibble i = 4-bit sub-scale of (row r_i, slice s)
 //   [1728, 1760)  fp16 d of row a + 4 i at halfword 4 a + i
 #include "gsq_common.cuh"
 
 namespace gsq {
 
-__device__ __forceinline__ uint32_t sign_spread(uint32_t g) {  // GGUF bit 4e+p -> bit 8p+e
+__device__ __forceinline__ uint32_t sign_spread(uint32_t g) {  // GGUF bit 4e+p -> bit 16(e/4) + 4p + e%4
   uint32_t o = 0;
 #pragma unroll
   for (int e = 0; e < 8; ++e)
 #pragma unroll
-    for (int p = 0; p < 4; ++p) o |= ((g >> (4 * e + p)) & 1u) << (8 * p + e);
+    for (int p = 0; p < 4; ++p) o |= ((g >> (4 * e + p)) & 1u) << (16 * (e >> 2) + 4 * p + (e & 3));
   return o;
 }
 __device__ __forceinline__ uint32_t sign_gather(uint32_t o) {  // inverse of sign_spread
@@ -33,7 +34,7 @@ __device__ __forceinline__ uint32_t sign_gather(uint32_t o) {  // inverse of sig
 #pragma unroll
   for (int e = 0; e < 8; ++e)
 #pragma unroll
-    for (int p = 0; p < 4; ++p) g |= ((o >> (8 * p + e)) & 1u) << (4 * e + p);
+    for (int p = 0; p < 4; ++p) g |= ((o >> (16 * (e >> 2) + 4 * p + (e & 3))) & 1u) << (4 * e + p);
   return g;
 }
 

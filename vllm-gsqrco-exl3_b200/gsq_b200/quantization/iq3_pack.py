@@ -8,7 +8,7 @@ lane l = 8a + s owns slice s of rows a, a+4, a+8, a+12:
 
   [0,1152)     9 words per lane (split 4 + 4 + 1 over three planes): 32 nine-bit codebook indices,
                row i group e at bit 9(8i+e)
-  [1152,1664)  4 words per lane: sign bits of row i, bit 8p+e = sign of value p of group e
+  [1152,1664)  4 words per lane: sign bits of row i, bit 16(e/4)+4p+e%4 = sign of value p of group e
   [1664,1728)  2 bytes per lane: nibble i = sub-scale of row i
   [1728,1760)  fp16 d of row a+4i at halfword 4a+i
 
@@ -53,8 +53,8 @@ def _pack_tiles(w: torch.Tensor) -> torch.Tensor:
     fbits = _bits(field, 9).permute(0, 1, 3, 4, 2, 5, 6).reshape(t, nb, 32, 288)   # lane, bit
     words = (fbits.reshape(t, nb, 32, 9, 32) << torch.arange(32, device=w.device)).sum(-1)   # lane, word
     sg = b[..., 74:106].reshape(t, nb, 4, 4, 8, 4)                   # i a s byte
-    sgbits = _bits(sg, 8).reshape(t, nb, 4, 4, 8, 8, 4)              # i a s e p   (bit 4e+p of the slice word)
-    spread = sgbits.permute(0, 1, 2, 3, 4, 6, 5).reshape(t, nb, 4, 4, 8, 32)       # bit 8p+e
+    sgbits = _bits(sg, 8).reshape(t, nb, 4, 4, 8, 2, 4, 4)           # i a s h e' p   (bit 4e+p of the slice word, e = 4h+e')
+    spread = sgbits.permute(0, 1, 2, 3, 4, 5, 7, 6).reshape(t, nb, 4, 4, 8, 32)    # bit 16h + 4p + e'
     sgw = (spread << torch.arange(32, device=w.device)).sum(-1)      # i a s
     sgw = sgw.permute(0, 1, 3, 4, 2)                                 # a s i
     sc = b[..., 106:110]                                             # i a byte
@@ -94,8 +94,8 @@ def _unpack_tiles(p: torch.Tensor) -> torch.Tensor:
     qs = field & 0xFF
     qh = ((field >> 8) << torch.arange(8, device=p.device)).sum(-1)                 # i a s
     sgw = word(r[..., 1152:1664], 4).reshape(t, nb, 4, 8, 4)                        # a s i
-    sbits = _bits(sgw, 32).reshape(t, nb, 4, 8, 4, 4, 8)                            # a s i p e
-    gg = sbits.permute(0, 1, 2, 3, 4, 6, 5).reshape(t, nb, 4, 8, 4, 4, 8)           # a s i byte bit (bit 4e+p)
+    sbits = _bits(sgw, 32).reshape(t, nb, 4, 8, 4, 2, 4, 4)                         # a s i h p e'
+    gg = sbits.permute(0, 1, 2, 3, 4, 5, 7, 6).reshape(t, nb, 4, 8, 4, 4, 8)        # a s i byte bit (bit 4e+p)
     sg = (gg << torch.arange(8, device=p.device)).sum(-1)                           # a s i byte
     sg = sg.permute(0, 1, 4, 2, 3, 5)                                               # i a s byte
     scw = word(r[..., 1664:1728], 2).reshape(t, nb, 4, 8)                           # a s
