@@ -143,6 +143,7 @@ int gsq_debug_force_direct_loads(int on);
  * instead of hanging. Copies the flag (0 = never happened) to *flag. Synchronises the device.
  */
 int gsq_device_error_flag(int* flag);
+int gsq_debug_force_cluster_size(int cs); /* 0 = choose; 1, 2, 4 = force (experiments) */
 
 /*
  * Test hook: the raw int32 dot product of every weight group with the matching activation quants, taken
@@ -164,6 +165,11 @@ int gsq_debug_block_sums(const void* w, int64_t row_bytes, int64_t rows, int ggm
  *                initialised and are not preserved
  */
 int gsq_q8_layout_for_type(int ggml_type);
+/* Test hooks of the GEMM: exchange the two stride fields of its shared-memory matrix descriptors (returns
+ * the previous setting); make every following gsq_mul_mat_q8 call also store its raw int32 slice sums to
+ * sums[m][rows][k/32] (NULL switches it off). */
+int gsq_debug_swap_descriptor_strides(int on);
+int gsq_debug_gemm_dump_sums(int32_t* sums);
 size_t gsq_mul_mat_scratch_bytes(int64_t rows, int64_t m, int64_t k, int ggml_type);
 int gsq_mul_mat_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,
                    const void* x_q8_mmq, int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride,

@@ -196,19 +196,19 @@ def test_row_argument_limits_output():
     assert part.shape == (2, 50) and torch.equal(part, full[:, :50])
 
 
-@pytest.mark.parametrize("name", list(TYPES))
+@pytest.mark.parametrize("name", ["Q6_K", "IQ3_S"])
 @pytest.mark.parametrize("m", [9, 16, 33])
-def test_many_rows_ops(name, m):
+def test_many_rows_ops_on_the_gemv(name, m):
+    """Q6_K and IQ3_S in GGUF order have no tensor-core kernel: the many-row op names run the dp4a kernel
+    8 rows at a time on block_q8_1 activations."""
     rows, k = 256, 1024
-    packed = name == "IQ3_S"
-    raw, w = _weights(name, rows, k, 50, packed)
+    raw, w = _weights(name, rows, k, 50, False)
     x = _x(m, k, torch.float32, 51)
-    op = "lcpp_mul_mat_iq3_packed" if packed else "lcpp_mul_mat_q"
-    y = getattr(torch.ops._C_gguf, op)(w, x.to(DEV), TYPES[name], rows)
+    y = torch.ops._C_gguf.lcpp_mul_mat_q(w, x.to(DEV), TYPES[name], rows)
     dec = blocks.decode(raw, TYPES[name])
     q, d, _ = _oracle_q8(x)
     ref = product.product_q81(dec, q, d.astype(np.float32))
-    assert product.rel_err(y.cpu().numpy(), ref) <= 1e-3
+    assert product.rel_err(y.cpu().numpy(), ref) <= 1e-5
 
 
 # ------------------------------------------------------------------------------------------ repack

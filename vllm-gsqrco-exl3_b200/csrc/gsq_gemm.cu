@@ -1,15 +1,578 @@
-// Tensor-core GEMM entry point (placeholder translation unit until the tcgen05 kernel lands).
+// Int8 tensor-core GEMM over GGUF superblocks for any number of activation rows (sm_100a: tcgen05 + TMEM).
+//
+// Replaces, behind gsq_mul_mat_q8, the reference's MMQ (csrc/lcpp/ggml/src/ggml-cuda/mmq.cuh:961-1385 with its
+// tile loaders mmq-load-tiles.cuh:711-800, 1359-1495 and mmq-vec-dot.cuh:143-279, 313-440) and the owned
+// mma.sync kernels mma_k (lcpp_owned_mma_k.cu:353-539) and iq3_packed_mmq (lcpp_owned_iq3_mma.cu:768-970).
+// The arithmetic is theirs: for every 32-value slice s an exact int32 dot product C_s of int8 weights and int8
+// activation quants, then  y += (d_w * sub_scale)[row, s] * d_q8[token, s] * C_s  in fp32 (Q4_K adds the min
+// term -(dmin * m)[row, s] * half(sum x)[token, s] and rounds d * sc and dmin * m to fp16 as MMQ's tile loader does).
+//
+// Operands are swapped relative to the usual GEMM: the 128 weight rows of a tile fill the MMA's M, tokens
+// sit on N. Because every slice has its own pair of fp scales, an MMA must not accumulate over slices:
+// each K = 32 instruction writes its own 128 x NT int32 block of tensor memory (8 slices x 64 columns =
+// all 512 columns), which the CUDA cores drain, scale and add into register accumulators.
+//
+// One persistent CTA of 8 warps per SM walks (token tile, row tile) pairs, row tiles fastest so that the
+// tile of activations stays in L2 while all SMs stream the weights once per token tile. Per superblock:
+//   1. all warps decode the 128 x 256 weight tile into int8 in shared memory, in the K-major "core matrix"
+//      layout the MMA descriptors describe (8 rows x 16 bytes contiguous), and copy the 64 x 256 activation
+//      quants next to it; the loads for the next superblock are already in flight in registers;
+//   2. one thread issues the 8 MMAs and commits them to an mbarrier;
+//   3. all warps read their quarter of tensor memory (tcgen05.ld), apply the scales and accumulate.
+// Every wait is bounded and raises a sticky error flag instead of hanging.
 #include "gsq_common.cuh"
+#include "gsq_tables.h"
+
+namespace gsq {
+
+enum { GK_IQ3S_PACKED = 0, GK_Q4K = 1, GK_IQ4XS = 2 };
+
+constexpr int GEMM_THREADS = 256;
+constexpr int TILE_ROWS = 128;   // weight rows per tile = MMA M
+constexpr int NT = 64;           // tokens per tile = MMA N
+constexpr int SL_A = 4096 + 16;  // bytes between slices of the weight tile (+16: decode stores of the 8 slices hit 8 banks)
+constexpr int SL_B = NT * 32 + 16;
+constexpr int TMEM_COLS = 512;
+
+__device__ const uint32_t g_iq3s_grid_gemm[512] = GSQ_IQ3S_GRID_INIT;
+__constant__ uint32_t c_iq4nl_words_gemm[4] = {0, 0, 0, 0};
+__device__ int g_gemm_error = 0;
+
+struct GemmArgs {
+  const uint8_t* w;
+  int64_t row_bytes;
+  int nrows;   // N
+  int k;
+  const uint8_t* xq;  // [k/128][m][144]
+  int m;       // tokens
+  void* y;
+  int y_dtype;
+  int64_t ldy;
+  int n_row_tiles, n_tok_tiles;
+  int swap_lbo_sbo;  // debug: exchange the two stride fields of the shared-memory descriptors
+  int* dump;         // debug: raw int32 slice sums, [m][nrows][k/32]
+};
+
+// ---------------------------------------------------------------------------------------------
+// tcgen05 / mbarrier wrappers
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] = A[smem] * B[smem], int8 x int8 -> int32, K = 32, no accumulation into D
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, 0, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void gemm_mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ bool gemm_mbar_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done = 0;
+  for (int spin = 0; spin < (1 << 22); ++spin) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  atomicExch(&g_gemm_error, 1);
+  return false;
+}
+
+// 32 lanes x 32 consecutive 32-bit columns of this warp's quarter of tensor memory
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major int8 operand stored as core matrices of 8 rows x 16 bytes
+// (128 contiguous bytes): the two core matrices of a row group (K bytes 0-15, 16-31) are 128 bytes apart,
+// consecutive 8-row groups 256 bytes apart; no swizzle; descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int swap) {
+  const uint64_t lbo = swap ? 256 : 128, sbo = swap ? 128 : 256;
+  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (lbo >> 4) << 16;
+  d |= (sbo >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+
+// Instruction descriptor: D = s32, A = B = s8, both K-major, N = NT, M = 128, dense, no negation/saturation.
+__host__ __device__ constexpr uint32_t make_idesc() {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t gprmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+
+// byte offset of (row r, 16-byte K chunk c16) inside one slice of a K-major core-matrix tile
+__device__ __forceinline__ int core_off(int r, int c16) { return (r >> 3) * 256 + c16 * 128 + (r & 7) * 16; }
+
+// ---------------------------------------------------------------------------------------------
+// Weights of one superblock of a 128-row tile: global -> registers (fetch), registers -> int8 tile + scales (decode).
+
+struct SmemView {
+  uint8_t* a;        // 8 slices x SL_A
+  uint8_t* b;        // 8 slices x SL_B
+  float* sa;         // [8][128] d_w * sub-scale
+  float* sam;        // [8][128] -(dmin * m)            (Q4_K)
+  float* sbd;        // [8][NT]  d of the activation block
+  float* sbs;        // [8][NT]  sum x of the activation block (Q4_K)
+  const uint8_t* grid;  // IQ3_S codebook pairs (g, -g), 16 replicas
+};
+
+template <int KIND>
+struct WRegs;
+
+template <>
+struct WRegs<GK_IQ3S_PACKED> {
+  uint32_t idx[9], sg[4], sc;
+  uint2 dd;
+  bool ok;
+  __device__ __forceinline__ void fetch(const GemmArgs& g, int rt, int sb, int tid) {
+    const int warp = tid >> 5, lane = tid & 31;
+    const int row0 = rt * TILE_ROWS + 16 * warp;
+    ok = row0 < g.nrows;
+    if (!ok) return;
+    const uint8_t* p = g.w + (int64_t)row0 * g.row_bytes + (int64_t)sb * 1760;
+    const uint4 ia = ldg_stream_v4(p + 16 * lane), ib = ldg_stream_v4(p + 512 + 16 * lane);
+    idx[0] = ia.x; idx[1] = ia.y; idx[2] = ia.z; idx[3] = ia.w;
+    idx[4] = ib.x; idx[5] = ib.y; idx[6] = ib.z; idx[7] = ib.w;
+    idx[8] = ldg_stream_u32(p + 1024 + 4 * lane);
+    const uint4 s = ldg_stream_v4(p + 1152 + 16 * lane);
+    sg[0] = s.x; sg[1] = s.y; sg[2] = s.z; sg[3] = s.w;
+    sc = ldg_stream_u16(p + 1664 + 2 * lane);
+    dd = ldg_stream_v2(p + 1728 + 8 * (lane >> 3));
+  }
+  __device__ __forceinline__ void decode(const SmemView& sm, int tid) const {
+    if (!ok) return;
+    const int warp = tid >> 5, lane = tid & 31, s = lane & 7;
+    const uint32_t lane_off = (uint32_t)(lane & 15) << 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t wv[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int bit = 9 * (8 * i + e), word = bit >> 5, off = bit & 31;
+        uint32_t t;
+        if (off + 9 <= 32) {
+          t = off >= 7 ? idx[word] >> (off - 7) : idx[word] << (7 - off);
+        } else {
+          t = __funnelshift_r(idx[word], idx[word + 1], off - 7);
+        }
+        const uint2 gp = *reinterpret_cast<const uint2*>(sm.grid + ((t & 0xFF80u) | lane_off));
+        const int sh = 16 * (e >> 2) + (e & 3) - 2;
+        const uint32_t sgs = sh >= 0 ? sg[i] >> sh : sg[i] << (-sh);
+        wv[e] = gprmt(gp.x, gp.y, (sgs & 0x4444u) | 0x3210u);
+      }
+      const int r = 16 * warp + (lane >> 3) + 4 * i;
+      uint8_t* dst = sm.a + s * SL_A;
+      *reinterpret_cast<uint4*>(dst + core_off(r, 0)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+      *reinterpret_cast<uint4*>(dst + core_off(r, 1)) = make_uint4(wv[4], wv[5], wv[6], wv[7]);
+      const float d = h2f((i < 2 ? dd.x : dd.y) >> (16 * (i & 1)));
+      sm.sa[s * TILE_ROWS + r] = d * (float)(1 + 2 * (int)((sc >> (4 * i)) & 15u));
+    }
+  }
+};
+
+template <>
+struct WRegs<GK_Q4K> {
+  uint4 hdr[4], qs[4];
+  __device__ __forceinline__ void fetch(const GemmArgs& g, int rt, int sb, int tid) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int item = tid + GEMM_THREADS * q, r = item >> 3, p = item & 7;
+      const int row = min(rt * TILE_ROWS + r, g.nrows - 1);
+      const uint8_t* b = g.w + (int64_t)row * g.row_bytes + (int64_t)sb * 144;
+      hdr[q] = ldg_stream_v4(b);
+      qs[q] = ldg_stream_v4(b + 16 + 16 * p);
+    }
+  }
+  __device__ __forceinline__ void decode(const SmemView& sm, int tid) const {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int item = tid + GEMM_THREADS * q, r = item >> 3, p = item & 7, jj = p >> 1, half = p & 1;
+      const uint4 v = qs[q];
+      uint8_t* lo = sm.a + (2 * jj) * SL_A + core_off(r, half);
+      *reinterpret_cast<uint4*>(lo) = make_uint4(v.x & 0x0F0F0F0Fu, v.y & 0x0F0F0F0Fu, v.z & 0x0F0F0F0Fu, v.w & 0x0F0F0F0Fu);
+      *reinterpret_cast<uint4*>(lo + SL_A) = make_uint4((v.x >> 4) & 0x0F0F0F0Fu, (v.y >> 4) & 0x0F0F0F0Fu,
+                                                       (v.z >> 4) & 0x0F0F0F0Fu, (v.w >> 4) & 0x0F0F0F0Fu);
+      if (half == 0) {
+        const uint32_t selh = (jj & 1) ? 0x4432u : 0x4410u;
+        const uint32_t A = gprmt(hdr[q].y, 0u, selh), B = gprmt(hdr[q].z, 0u, selh), C = gprmt(hdr[q].w, 0u, selh);
+        const uint32_t sc = jj < 2 ? (A & 0x3F3Fu) : ((C & 0x0F0Fu) | ((A & 0xC0C0u) >> 2));
+        const uint32_t mn = jj < 2 ? (B & 0x3F3Fu) : (((C >> 4) & 0x0F0Fu) | ((B & 0xC0C0u) >> 2));
+        // d * sc and dmin * m rounded to fp16, as the reference's tile loader keeps them (half2 products)
+        const __half2 dm = *reinterpret_cast<const __half2*>(&hdr[q].x);
+        const float2 p0 = __half22float2(__hmul2(dm, __floats2half2_rn((float)(sc & 0xFFu), (float)(mn & 0xFFu))));
+        const float2 p1 = __half22float2(__hmul2(dm, __floats2half2_rn((float)(sc >> 8), (float)(mn >> 8))));
+        sm.sa[(2 * jj) * TILE_ROWS + r] = p0.x;
+        sm.sam[(2 * jj) * TILE_ROWS + r] = -p0.y;
+        sm.sa[(2 * jj + 1) * TILE_ROWS + r] = p1.x;
+        sm.sam[(2 * jj + 1) * TILE_ROWS + r] = -p1.y;
+      }
+    }
+  }
+};
+
+template <>
+struct WRegs<GK_IQ4XS> {
+  uint2 hdr[4], qa[4], qb[4];
+  __device__ __forceinline__ void fetch(const GemmArgs& g, int rt, int sb, int tid) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int item = tid + GEMM_THREADS * q, r = item >> 3, p = item & 7;
+      const int row = min(rt * TILE_ROWS + r, g.nrows - 1);
+      const uint8_t* b = g.w + (int64_t)row * g.row_bytes + (int64_t)sb * 136;
+      hdr[q] = ldg_stream_v2(b);
+      qa[q] = ldg_stream_v2(b + 8 + 16 * p);
+      qb[q] = ldg_stream_v2(b + 16 + 16 * p);
+    }
+  }
+  static __device__ __forceinline__ void lookup(uint32_t v, uint32_t& lo, uint32_t& hi) {
+    const uint32_t t0 = c_iq4nl_words_gemm[0], t1 = c_iq4nl_words_gemm[1], t2 = c_iq4nl_words_gemm[2],
+                   t3 = c_iq4nl_words_gemm[3];
+    const uint32_t s01 = v & 0x7777u, s23 = (v >> 16) & 0x7777u;
+    const uint32_t pick01 = 0x3210u | ((v & 0x8888u) >> 1), pick23 = 0x3210u | (((v >> 16) & 0x8888u) >> 1);
+    const uint32_t r01 = gprmt(gprmt(t0, t1, s01), gprmt(t2, t3, s01), pick01);
+    const uint32_t r23 = gprmt(gprmt(t0, t1, s23), gprmt(t2, t3, s23), pick23);
+    lo = gprmt(r01, r23, 0x6420u);
+    hi = gprmt(r01, r23, 0x7531u);
+  }
+  __device__ __forceinline__ void decode(const SmemView& sm, int tid) const {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int item = tid + GEMM_THREADS * q, r = item >> 3, p = item & 7;
+      const uint32_t v[4] = {qa[q].x, qa[q].y, qb[q].x, qb[q].y};
+      uint32_t lo[4], hi[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) lookup(v[e], lo[e], hi[e]);
+      uint8_t* dst = sm.a + p * SL_A;
+      *reinterpret_cast<uint4*>(dst + core_off(r, 0)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      *reinterpret_cast<uint4*>(dst + core_off(r, 1)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      const uint32_t ls = ((hdr[q].y >> (4 * p)) & 0xFu) | (((hdr[q].x >> (16 + 2 * p)) & 3u) << 4);
+      sm.sa[p * TILE_ROWS + r] = h2f(hdr[q].x) * (float)((int)ls - 32);
+    }
+  }
+};
+
+// Activation quants of one superblock for the NT tokens of a tile (128-value blocks, 144 bytes each).
+template <bool DS4>
+struct XRegs {
+  uint4 q[4];
+  uint32_t sc[4];
+  __device__ __forceinline__ void fetch(const GemmArgs& g, int t0, int sb, int tid) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int item = tid + GEMM_THREADS * i, c = item >> 4, j = item & 15;
+      const int tok = t0 + c;
+      q[i] = make_uint4(0, 0, 0, 0);
+      sc[i] = 0;
+      if (tok < g.m) {
+        const uint8_t* b = g.xq + ((int64_t)(2 * sb + (j >> 3)) * g.m + tok) * 144;
+        q[i] = __ldg(reinterpret_cast<const uint4*>(b + 16 + (j & 7) * 16));
+        if ((j & 1) == 0) sc[i] = __ldg(reinterpret_cast<const uint32_t*>(b + 4 * ((j >> 1) & 3)));
+      }
+    }
+  }
+  __device__ __forceinline__ void store(const SmemView& sm, int tid) const {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int item = tid + GEMM_THREADS * i, c = item >> 4, j = item & 15, s = j >> 1;
+      *reinterpret_cast<uint4*>(sm.b + s * SL_B + core_off(c, j & 1)) = q[i];
+      if ((j & 1) == 0) {
+        if (DS4) {
+          const float2 ds = __half22float2(*reinterpret_cast<const __half2*>(&sc[i]));
+          sm.sbd[s * NT + c] = ds.x;
+          sm.sbs[s * NT + c] = ds.y;
+        } else {
+          sm.sbd[s * NT + c] = __uint_as_float(sc[i]);
+        }
+      }
+    }
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// The kernel.
+
+template <int KIND>
+__host__ __device__ constexpr size_t gemm_smem_bytes() {
+  return 128 + (KIND == GK_IQ3S_PACKED ? 65536 : 0) + 8 * SL_A + 8 * SL_B + (KIND == GK_Q4K ? 2 : 1) * 8 * TILE_ROWS * 4 +
+         2 * 8 * NT * 4;
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs g) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr bool DS4 = KIND == GK_Q4K;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem);
+  const uint32_t mbar = smem_addr(smem + 16);
+  uint8_t* sp = smem + 128;
+  SmemView sm;
+  sm.grid = sp;
+  if (KIND == GK_IQ3S_PACKED) sp += 65536;
+  sm.a = sp;
+  sp += 8 * SL_A;
+  sm.b = sp;
+  sp += 8 * SL_B;
+  sm.sa = reinterpret_cast<float*>(sp);
+  sp += 8 * TILE_ROWS * 4;
+  sm.sam = reinterpret_cast<float*>(sp);
+  if (KIND == GK_Q4K) sp += 8 * TILE_ROWS * 4;
+  sm.sbd = reinterpret_cast<float*>(sp);
+  sp += 8 * NT * 4;
+  sm.sbs = reinterpret_cast<float*>(sp);
+
+  if (warp == 0) tmem_alloc(smem_addr(tmem_slot), TMEM_COLS);
+  if (tid == 32) {
+    gemm_mbar_init(mbar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (KIND == GK_IQ3S_PACKED) {
+    for (int e = tid; e < 512; e += GEMM_THREADS) {
+      const uint32_t gv = g_iq3s_grid_gemm[e];
+      uint4* dst = reinterpret_cast<uint4*>(smem + 128 + e * 128);
+#pragma unroll
+      for (int r2 = 0; r2 < 8; ++r2) dst[r2] = make_uint4(gv, ~gv + 0x01010101u, gv, ~gv + 0x01010101u);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int nsb = g.k >> 8;
+  const int n_items = g.n_row_tiles * g.n_tok_tiles;
+  const uint32_t idesc = make_idesc();
+  const uint32_t a_addr = smem_addr(sm.a), b_addr = smem_addr(sm.b);
+  const int q4 = warp & 3, h = warp >> 2;        // tensor-memory lane quarter, column half of this warp
+  const int r_in = 32 * q4 + lane;               // row of the tile this thread accumulates
+  const uint32_t t_warp = tmem_base + ((uint32_t)(32 * q4) << 16) + (uint32_t)(32 * h);
+  constexpr int MAGIC = 0x4B400000;
+  constexpr float MAGIC_F = 12582912.0f;
+  uint32_t phase = 0;
+  bool alive = true;  // false once a bounded wait gave up: skip the remaining work, still free tensor memory
+
+  for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+    const int tt = item / g.n_row_tiles, rt = item - tt * g.n_row_tiles;
+    const int t0 = tt * NT;
+    const int ncols = min(NT, g.m - t0) - 32 * h;  // valid columns among this warp's 32
+    float acc[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
+    WRegs<KIND> wr;
+    XRegs<DS4> xr;
+    wr.fetch(g, rt, 0, tid);
+    xr.fetch(g, t0, 0, tid);
+    for (int sb = 0; sb < nsb; ++sb) {
+      wr.decode(sm, tid);
+      xr.store(sm, tid);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after();
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          mma_i8(tmem_base + (uint32_t)(s * NT), make_smem_desc(a_addr + s * SL_A, g.swap_lbo_sbo),
+                 make_smem_desc(b_addr + s * SL_B, g.swap_lbo_sbo), idesc);
+        }
+        mma_commit(mbar);
+      }
+      if (sb + 1 < nsb) {  // next superblock's loads fly while the tensor core and the epilogue work
+        wr.fetch(g, rt, sb + 1, tid);
+        xr.fetch(g, t0, sb + 1, tid);
+      }
+      alive = gemm_mbar_wait(mbar, phase);
+      phase ^= 1u;
+      tc_fence_after();
+      if (alive && ncols > 0) {
+#pragma unroll 1
+        for (int s = 0; s < 8; ++s) {
+          uint32_t c[32];
+          tmem_ld32(t_warp + (uint32_t)(s * NT), c);
+          if (g.dump) {
+            const int row_d = rt * TILE_ROWS + r_in;
+            if (row_d < g.nrows) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (j < ncols) g.dump[((int64_t)(t0 + 32 * h + j) * g.nrows + row_d) * (g.k >> 5) + sb * 8 + s] = (int)c[j];
+              }
+            }
+          }
+          const float da = sm.sa[s * TILE_ROWS + r_in];
+          const float dam = DS4 ? sm.sam[s * TILE_ROWS + r_in] : 0.0f;
+          const float4* bd = reinterpret_cast<const float4*>(sm.sbd + s * NT + 32 * h);
+          const float4* bs = reinterpret_cast<const float4*>(sm.sbs + s * NT + 32 * h);
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            if (4 * j4 < ncols) {
+              const float4 d = bd[j4];
+              const float dv[4] = {d.x, d.y, d.z, d.w};
+              float sv[4] = {0.f, 0.f, 0.f, 0.f};
+              if (DS4) {
+                const float4 t = bs[j4];
+                sv[0] = t.x; sv[1] = t.y; sv[2] = t.z; sv[3] = t.w;
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int j = 4 * j4 + u;
+                const float f = __int_as_float((int)c[j] + MAGIC) - MAGIC_F;
+                acc[j] = fmaf(da * dv[u], f, acc[j]);
+                if (DS4) acc[j] = fmaf(dam, sv[u], acc[j]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncthreads();  // tensor memory and the shared-memory tiles are free again
+    }
+    const int row = rt * TILE_ROWS + r_in;
+    if (alive && row < g.nrows) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (j < ncols) store_out_dyn(g.y, g.y_dtype, (int64_t)(t0 + 32 * h + j) * g.ldy + row, acc[j]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+static int g_swap_lbo_sbo = 0;
+static int* g_gemm_dump = nullptr;
+
+int gemm_error_flag(int* flag) {
+  GSQ_CUDA_TRY(cudaMemcpyFromSymbol(flag, g_gemm_error, sizeof(int)));
+  return GSQ_OK;
+}
+
+template <int KIND>
+static int launch_gemm(const GemmArgs& g, int sm_count, cudaStream_t st) {
+  static int configured_mask = 0;
+  int dev = 0;
+  GSQ_CUDA_TRY(cudaGetDevice(&dev));
+  constexpr size_t smem = gemm_smem_bytes<KIND>();
+  if (dev >= 32 || !((configured_mask >> dev) & 1)) {
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (KIND == GK_IQ4XS) {
+      const int8_t vals[16] = GSQ_IQ4NL_VALUES_INIT;
+      uint32_t words[4];
+      for (int i = 0; i < 4; ++i) {
+        words[i] = 0;
+        for (int j = 0; j < 4; ++j) words[i] |= (uint32_t)(uint8_t)vals[4 * i + j] << (8 * j);
+      }
+      GSQ_CUDA_TRY(cudaMemcpyToSymbol(c_iq4nl_words_gemm, words, sizeof(words)));
+    }
+    if (dev < 32) configured_mask |= 1 << dev;
+  }
+  const int n_items = g.n_row_tiles * g.n_tok_tiles;
+  const int grid = n_items < sm_count ? n_items : sm_count;
+  gemm_kernel<KIND><<<grid, GEMM_THREADS, smem, st>>>(g);
+  GSQ_CUDA_TRY(cudaGetLastError());
+  return GSQ_OK;
+}
+
+}  // namespace gsq
+
+extern "C" int gsq_debug_swap_descriptor_strides(int on) {
+  const int old = gsq::g_swap_lbo_sbo;
+  gsq::g_swap_lbo_sbo = on ? 1 : 0;
+  return old;
+}
+
+extern "C" int gsq_debug_gemm_dump_sums(int32_t* sums) {
+  gsq::g_gemm_dump = sums;
+  return GSQ_OK;
+}
 
 extern "C" size_t gsq_mul_mat_scratch_bytes(int64_t rows, int64_t m, int64_t k, int ggml_type) {
   (void)rows; (void)m; (void)k; (void)ggml_type;
-  return 0;
+  return 0;  // every CTA owns whole rows over all of K: nothing to combine through global memory
 }
 
 extern "C" int gsq_mul_mat_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,
                               const void* x_q8_mmq, int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride,
                               void* scratch, size_t scratch_bytes, void* stream) {
-  (void)w; (void)row_bytes; (void)rows; (void)ggml_type; (void)packed; (void)x_q8_mmq; (void)m; (void)k; (void)y;
-  (void)y_dtype; (void)y_row_stride; (void)scratch; (void)scratch_bytes; (void)stream;
-  return GSQ_ERR_UNSUPPORTED;
+  using namespace gsq;
+  (void)scratch;
+  (void)scratch_bytes;
+  if (m == 0 || rows == 0) return GSQ_OK;
+  if (m < 0 || rows < 0 || k <= 0 || k % 256 != 0 || !w || !x_q8_mmq || !y) return GSQ_ERR_UNSUPPORTED;
+  if (rows > INT32_MAX || k > INT32_MAX || m > INT32_MAX) return GSQ_ERR_TOO_LARGE;
+  const int bs = block_bytes(ggml_type);
+  if (bs == 0 || row_bytes != (k / 256) * bs) return GSQ_ERR_UNSUPPORTED;
+  if (y_dtype != GSQ_F32 && y_dtype != GSQ_F16 && y_dtype != GSQ_BF16) return GSQ_ERR_UNSUPPORTED;
+  int kind;
+  if (ggml_type == GSQ_TYPE_IQ3_S && packed && rows % 16 == 0) {
+    kind = GK_IQ3S_PACKED;
+  } else if (ggml_type == GSQ_TYPE_Q4_K) {
+    kind = GK_Q4K;
+  } else if (ggml_type == GSQ_TYPE_IQ4_XS) {
+    kind = GK_IQ4XS;
+  } else {
+    return GSQ_ERR_UNSUPPORTED;  // Q6_K and IQ3_S in GGUF order: the caller runs the GEMV 8 rows at a time
+  }
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc != GSQ_OK) return rc;
+  GemmArgs g;
+  g.w = (const uint8_t*)w;
+  g.row_bytes = row_bytes;
+  g.nrows = (int)rows;
+  g.k = (int)k;
+  g.xq = (const uint8_t*)x_q8_mmq;
+  g.m = (int)m;
+  g.y = y;
+  g.y_dtype = y_dtype;
+  g.ldy = y_row_stride;
+  g.n_row_tiles = (int)((rows + TILE_ROWS - 1) / TILE_ROWS);
+  g.n_tok_tiles = (int)((m + NT - 1) / NT);
+  g.swap_lbo_sbo = g_swap_lbo_sbo;
+  g.dump = g_gemm_dump;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (kind) {
+    case GK_IQ3S_PACKED: return launch_gemm<GK_IQ3S_PACKED>(g, di.sm_count, st);
+    case GK_Q4K: return launch_gemm<GK_Q4K>(g, di.sm_count, st);
+    default: return launch_gemm<GK_IQ4XS>(g, di.sm_count, st);
+  }
 }

@@ -996,9 +996,17 @@ extern "C" int gsq_debug_force_cluster_size(int cs) {
   return old;
 }
 
+namespace gsq {
+int gemm_error_flag(int* flag);  // gsq_gemm.cu
+}
+
 extern "C" int gsq_device_error_flag(int* flag) {
   if (!flag) return GSQ_ERR_UNSUPPORTED;
-  GSQ_CUDA_TRY(cudaMemcpyFromSymbol(flag, gsq::g_gemv_error, sizeof(int)));
+  int a = 0, b = 0;
+  GSQ_CUDA_TRY(cudaMemcpyFromSymbol(&a, gsq::g_gemv_error, sizeof(int)));
+  const int rc = gsq::gemm_error_flag(&b);
+  if (rc != GSQ_OK) return rc;
+  *flag = a | b;
   return GSQ_OK;
 }
 

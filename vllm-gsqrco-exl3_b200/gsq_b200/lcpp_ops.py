@@ -58,8 +58,9 @@ _DTYPES = {torch.float32: _cabi.F32, torch.float16: _cabi.F16, torch.bfloat16: _
 # K granularity the guards demand: 512 as in the reference (MATRIX_ROW_PADDING); the tensor-parallel
 # helpers lower it to 256 for K-sharded layers (gsq_b200.tp.relaxed_k).
 _k_multiple = 512
-# False while gsq_mul_mat_q8 is not built: the ops that would use it run the dp4a kernel 8 rows at a time
-_GEMM_READY = False
+# gsq_mul_mat_q8 covers Q4_K, IQ4_XS and packed IQ3_S; Q6_K and IQ3_S in GGUF order (and everything, if this
+# is switched off) run the dp4a kernel 8 rows at a time under the many-row op names
+_GEMM_READY = True
 
 
 def set_k_multiple(v: int) -> int:
@@ -146,7 +147,8 @@ def _run(op: str, W: torch.Tensor, X: torch.Tensor, type_: int, row: int, x_q8: 
     packed = bool(spec.get("packed", False))
     with torch.cuda.device(X.device):
         y = torch.empty((n, row), dtype=X.dtype, device=X.device)
-        if spec["mmvq"] or not _GEMM_READY:
+        gemm = (not spec["mmvq"]) and _GEMM_READY and (type_ in (Q4_K, IQ4_XS) or (type_ == IQ3_S and packed))
+        if not gemm:
             if x_q8 is None:
                 x_q8 = torch.empty(q8_bytes, dtype=torch.uint8, device=X.device)
                 quantize_q8_1_into(X, x_q8)
