@@ -107,19 +107,11 @@ class ClockSampler:
 # our arm
 
 def shard_plan(n: int, k: int, world: int, rank: int):
-    """Tensor-parallel shard of an [n, k] weight: ("N", row0, rows) or ("K", sb0, superblocks)."""
-    if world == 1:
-        return "N", 0, n
-    if k > n:  # down-projection-like: shard the columns at 256-column granularity, uneven if needed
-        nsb = k // 256
-        base, extra = divmod(nsb, world)
-        cnt = base + (1 if rank < extra else 0)
-        sb0 = rank * base + min(rank, extra)
-        return "K", sb0, cnt
-    per = n // world
-    per -= per % 16
-    row0 = rank * per
-    return "N", row0, (n - row0 if rank == world - 1 else per)
+    """(mode, start, count) of this rank's tensor-parallel shard (gsq_b200.tp.shard_plan)."""
+    from gsq_b200 import tp
+
+    p = tp.shard_plan(n, k, world, rank)
+    return p.mode, p.start, p.count
 
 
 def build_cells(dev, world, rank, l2_bytes):
@@ -378,12 +370,100 @@ def run_ours(args):
                          "avg_launch_us": round(roof_ms * 1e3 / max(1, roof_launches), 2)},
             "cells": cell_rows,
         }
+        out["config"]["cells"] = len(order)
+        if world == 1 and not args.no_extras:
+            del cells, xs
+            torch.cuda.empty_cache()
+            out["prefill"] = extra_prefill(dev, capture)
+            out["decode_stack"] = extra_decode_stack(dev, capture)
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline()
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
+
+
+# --------------------------------------------------------------------------------------------------
+# the other two quantities BASELINE.json's metric names, reported beside the headline (1 GPU)
+
+def extra_prefill(dev, capture):
+    """Prefill GEMM: M tokens x K=5120 -> N=17408 with IQ3_S weights, and M x K=17408 -> N=5120 with IQ4_XS;
+    bf16 activations ~ N(0,1) with 0.1 % outliers x20. Algorithmic ops = 2 M N K."""
+    import torch
+
+    from gsq_b200 import synth
+    from gsq_b200.quantization import iq3_pack, linear
+
+    out = []
+    for tname, t, n, k in (("IQ3_S", 21, 17408, 5120), ("IQ4_XS", 23, 5120, 17408)):
+        w = torch.from_numpy(synth.make_weight(t, n, k, 1300)).to(dev)
+        packed = t == 21
+        if packed:
+            iq3_pack.pack_(w, t)
+        for m in (2048, 8192):
+            x = torch.from_numpy(synth.make_activation(m, k, 1400 + m, outliers=1e-3)).to(torch.bfloat16).to(dev)
+            fn = lambda: linear.fused_mul_mat_gguf(x, w, t, None, packed)
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / 3
+            out.append({"type": tname, "m": m, "n": n, "k": k, "ms": round(ms, 3),
+                        "int8_TOPS": round(2.0 * m * n * k / (ms * 1e-3) / 1e12, 1)})
+            del x
+        del w
+    return out
+
+
+def extra_decode_stack(dev, capture, layers=64):
+    """64-layer dense decoder stack, linears only: per layer qkv IQ3_S 7168x5120, o_proj IQ3_S 5120x5120,
+    gate_up IQ3_S 34816x5120, down IQ4_XS 5120x17408 (150,978,560 weight bytes per layer, distinct weights per
+    layer so L2 cannot hold them); rows per step 4 / 8 / 16 / 32; one CUDA graph per step."""
+    import torch
+
+    from gsq_b200 import synth
+    from gsq_b200.quantization import iq3_pack, linear
+
+    shapes = [("qkv", 21, 7168, 5120), ("o", 21, 5120, 5120), ("gate_up", 21, 34816, 5120), ("down", 23, 5120, 17408)]
+    base = {}
+    for name, t, n, k in shapes:
+        w = torch.from_numpy(synth.make_weight(t, n, k, 2000 + len(base))).to(dev)
+        if t == 21:
+            iq3_pack.pack_(w, t)
+        base[name] = w
+    # distinct bytes per layer: each layer's copy is the base tile rolled by a layer-dependent row count
+    stack = [{name: torch.roll(base[name], shifts=16 * (l + 1), dims=0) if l else base[name] for name, *_ in shapes}
+             for l in range(layers)]
+    bytes_step = layers * sum(base[name].numel() for name, *_ in shapes)
+    res = []
+    for rows in (4, 8, 16, 32):
+        x5 = torch.randn(rows, 5120, device=dev, dtype=torch.bfloat16)
+        x17 = torch.randn(rows, 17408, device=dev, dtype=torch.bfloat16)
+
+        def step():
+            for lw in stack:
+                linear.fused_mul_mat_gguf(x5, lw["qkv"], 21, None, True)
+                linear.fused_mul_mat_gguf(x5, lw["o"], 21, None, True)
+                linear.fused_mul_mat_gguf(x5, lw["gate_up"], 21, None, True)
+                linear.fused_mul_mat_gguf(x17, lw["down"], 23, None, False)
+        g = capture(step)
+        best = 1e30
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        res.append({"rows": rows, "ms_per_step": round(best, 3), "GBps": round(bytes_step / best / 1e6, 1),
+                    "floor_ms_at_measured_hbm": round(bytes_step / 6547.2e6, 3)})
+    return {"layers": layers, "weight_bytes_per_step": bytes_step, "steps": res}
 
 # --------------------------------------------------------------------------------------------------
 # CPU baseline / reference arm (the only places bench.py executes oracle/)
@@ -439,6 +519,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the prefill-TOPS and decode-stack measurements")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -1,0 +1,82 @@
+"""Tensor-parallel sharding of GGUF weights for the quantised-linear path.
+
+The reference narrows the loaded bytes evenly (quantization/params.py:228-301) and was only ever run at
+TP = 1; its kernels demand K % 512 == 0 (lcpp_shim.cu:706-708), which K-shards of 5120 or 17408 columns
+break at TP = 4 and 8. Here:
+
+  * column-parallel layers (qkv, gate_up, lm_head) are cut along N in multiples of 16 rows (the IQ3_S
+    repack tile), the last rank taking the remainder; outputs are all-gathered;
+  * row-parallel layers (o_proj, down) are cut along K at superblock (256-column) granularity, the first
+    (K/256) % world ranks taking one superblock more; fp32 partial outputs are summed (all-reduce).
+
+`relaxed_k()` lowers the guards' K granularity from 512 to 256 for the duration of a block.
+"""
+
+from __future__ import annotations
+
+import contextlib
+from dataclasses import dataclass
+
+from . import lcpp_ops
+
+BLOCK_BYTES = {12: 144, 14: 210, 21: 110, 23: 136}
+
+
+@dataclass(frozen=True)
+class Shard:
+    mode: str      # "N": rows [start, start + count) ; "K": superblocks [start, start + count)
+    start: int
+    count: int
+
+
+def shard_plan(n: int, k: int, world: int, rank: int, mode: str | None = None) -> Shard:
+    """This rank's shard of an [n, k] weight. mode None: K-shard when k > n (down-projection-like), else N."""
+    if world == 1:
+        return Shard("N", 0, n)
+    if mode is None:
+        mode = "K" if k > n else "N"
+    if mode == "K":
+        base, extra = divmod(k // 256, world)
+        return Shard("K", rank * base + min(rank, extra), base + (1 if rank < extra else 0))
+    per = n // world
+    per -= per % 16
+    start = rank * per
+    return Shard("N", start, n - start if rank == world - 1 else per)
+
+
+def shard_bytes(raw, ggml_type: int, s: Shard):
+    """Rows / superblock columns of a [rows, row_bytes] byte matrix (numpy array or torch tensor) for a shard."""
+    if s.mode == "N":
+        return raw[s.start:s.start + s.count]
+    bs = BLOCK_BYTES[ggml_type]
+    return raw[:, s.start * bs:(s.start + s.count) * bs]
+
+
+def shard_activation(x, s: Shard):
+    """Columns of X that a K-shard multiplies (a strided view, accepted as is by the ops)."""
+    return x if s.mode == "N" else x[:, s.start * 256:(s.start + s.count) * 256]
+
+
+@contextlib.contextmanager
+def relaxed_k():
+    old = lcpp_ops.set_k_multiple(256)
+    try:
+        yield
+    finally:
+        lcpp_ops.set_k_multiple(old)
+
+
+def combine(y, s: Shard, n: int, k: int, world: int, group=None):
+    """Collective after a sharded product: all-gather of [M, rows_r] along N, or all-reduce of partial [M, N]."""
+    import torch
+    import torch.distributed as dist
+
+    if world == 1:
+        return y
+    if s.mode == "K":
+        dist.all_reduce(y, group=group)
+        return y
+    parts = [torch.empty(y.shape[0], shard_plan(n, k, world, r, "N").count, dtype=y.dtype, device=y.device)
+             for r in range(world)]
+    dist.all_gather(parts, y.contiguous(), group=group)
+    return torch.cat(parts, dim=1)
