@@ -256,7 +256,7 @@ def run_ours(args):
             fn()
         return g
 
-    use_graph = world == 1 and not args.eager   # NCCL collectives stay outside graphs here
+    use_graph = world == 1 and not args.eager   # with NCCL collectives in the step the launches stay eager
     for _ in range(max(3, args.warmup)):
         step()
     runner = step
