@@ -119,6 +119,23 @@ def test_gemm_int32_slice_sums_bit_exact(name, rows, k):
     assert np.array_equal(sums.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("ks", [1, 2, 4])
+@pytest.mark.parametrize("name", list(TYPES))
+def test_split_k_over_a_cluster(name, ks):
+    """Few tiles: the superblocks of a tile are split over the CTAs of a cluster and summed in rank order."""
+    raw, w = _weights(name, 256, 5120, 31)
+    x = _x(20, 5120, torch.float32, 32)
+    old = _cabi.lib.gsq_debug_gemm_ksplit(ks)
+    try:
+        y = getattr(torch.ops._C_gguf, _op(name))(w, x.to(DEV), TYPES[name], 256)
+        y2 = getattr(torch.ops._C_gguf, _op(name))(w, x.to(DEV), TYPES[name], 256)
+    finally:
+        _cabi.lib.gsq_debug_gemm_ksplit(old)
+    ref, _ = _reference(name, raw, x)
+    assert product.rel_err(y.cpu().numpy(), ref) <= 1e-3
+    assert torch.equal(y, y2)
+
+
 def test_mma_k_op_and_graph_replay():
     raw, w = _weights("IQ4_XS", 256, 1024, 21)
     x = _x(24, 1024, torch.bfloat16, 22).to(DEV)

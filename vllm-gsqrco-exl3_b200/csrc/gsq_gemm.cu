@@ -20,14 +20,19 @@
 //   2. one thread issues the 8 MMAs and commits them to an mbarrier;
 //   3. all warps read their quarter of tensor memory (tcgen05.ld), apply the scales and accumulate.
 // Every wait is bounded and raises a sticky error flag instead of hanging.
+#include <cooperative_groups.h>
+
 #include "gsq_common.cuh"
 #include "gsq_tables.h"
+
+namespace cg = cooperative_groups;
 
 namespace gsq {
 
 enum { GK_IQ3S_PACKED = 0, GK_Q4K = 1, GK_IQ4XS = 2 };
 
-constexpr int GEMM_THREADS = 256;
+constexpr int GEMM_THREADS = 512;
+constexpr int NITEM = 1024 / GEMM_THREADS;  // (row, chunk) items of a 128 x 256 tile per thread
 constexpr int TILE_ROWS = 128;   // weight rows per tile = MMA M
 constexpr int NT = 64;           // tokens per tile = MMA N
 constexpr int SL_A = 4096 + 16;  // bytes between slices of the weight tile (+16: decode stores of the 8 slices hit 8 banks)
@@ -118,6 +123,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// 32 lanes x 16 consecutive columns; the wait is separate so that a load can fly while the previous one is used
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 // Shared-memory matrix descriptor of a K-major int8 operand stored as core matrices of 8 rows x 16 bytes
 // (128 contiguous bytes): the two core matrices of a row group (K bytes 0-15, 16-31) are 128 bytes apart,
 // consecutive 8-row groups 256 bytes apart; no swizzle; descriptor version 1 (sm_100).
@@ -167,7 +184,7 @@ struct WRegs<GK_IQ3S_PACKED> {
   bool ok;
   __device__ __forceinline__ void fetch(const GemmArgs& g, int rt, int sb, int tid) {
     const int warp = tid >> 5, lane = tid & 31;
-    const int row0 = rt * TILE_ROWS + 16 * warp;
+    const int row0 = rt * TILE_ROWS + 16 * (warp >> 1);  // two warps per 16-row record, two of its four row groups each
     ok = row0 < g.nrows;
     if (!ok) return;
     const uint8_t* p = g.w + (int64_t)row0 * g.row_bytes + (int64_t)sb * 1760;
@@ -186,6 +203,7 @@ struct WRegs<GK_IQ3S_PACKED> {
     const uint32_t lane_off = (uint32_t)(lane & 15) << 3;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
+      if ((i >> 1) != (warp & 1)) continue;  // warp-uniform: this warp's half of the record
       uint32_t wv[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -201,7 +219,7 @@ struct WRegs<GK_IQ3S_PACKED> {
         const uint32_t sgs = sh >= 0 ? sg[i] >> sh : sg[i] << (-sh);
         wv[e] = gprmt(gp.x, gp.y, (sgs & 0x4444u) | 0x3210u);
       }
-      const int r = 16 * warp + (lane >> 3) + 4 * i;
+      const int r = 16 * (warp >> 1) + (lane >> 3) + 4 * i;
       uint8_t* dst = sm.a + s * SL_A;
       *reinterpret_cast<uint4*>(dst + core_off(r, 0)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
       *reinterpret_cast<uint4*>(dst + core_off(r, 1)) = make_uint4(wv[4], wv[5], wv[6], wv[7]);
@@ -213,10 +231,10 @@ struct WRegs<GK_IQ3S_PACKED> {
 
 template <>
 struct WRegs<GK_Q4K> {
-  uint4 hdr[4], qs[4];
+  uint4 hdr[NITEM], qs[NITEM];
   __device__ __forceinline__ void fetch(const GemmArgs& g, int rt, int sb, int tid) {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < NITEM; ++q) {
       const int item = tid + GEMM_THREADS * q, r = item >> 3, p = item & 7;
       const int row = min(rt * TILE_ROWS + r, g.nrows - 1);
       const uint8_t* b = g.w + (int64_t)row * g.row_bytes + (int64_t)sb * 144;
@@ -226,7 +244,7 @@ struct WRegs<GK_Q4K> {
   }
   __device__ __forceinline__ void decode(const SmemView& sm, int tid) const {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < NITEM; ++q) {
       const int item = tid + GEMM_THREADS * q, r = item >> 3, p = item & 7, jj = p >> 1, half = p & 1;
       const uint4 v = qs[q];
       uint8_t* lo = sm.a + (2 * jj) * SL_A + core_off(r, half);
@@ -253,10 +271,10 @@ struct WRegs<GK_Q4K> {
 
 template <>
 struct WRegs<GK_IQ4XS> {
-  uint2 hdr[4], qa[4], qb[4];
+  uint2 hdr[NITEM], qa[NITEM], qb[NITEM];
   __device__ __forceinline__ void fetch(const GemmArgs& g, int rt, int sb, int tid) {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < NITEM; ++q) {
       const int item = tid + GEMM_THREADS * q, r = item >> 3, p = item & 7;
       const int row = min(rt * TILE_ROWS + r, g.nrows - 1);
       const uint8_t* b = g.w + (int64_t)row * g.row_bytes + (int64_t)sb * 136;
@@ -277,7 +295,7 @@ struct WRegs<GK_IQ4XS> {
   }
   __device__ __forceinline__ void decode(const SmemView& sm, int tid) const {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < NITEM; ++q) {
       const int item = tid + GEMM_THREADS * q, r = item >> 3, p = item & 7;
       const uint32_t v[4] = {qa[q].x, qa[q].y, qb[q].x, qb[q].y};
       uint32_t lo[4], hi[4];
@@ -295,11 +313,11 @@ struct WRegs<GK_IQ4XS> {
 // Activation quants of one superblock for the NT tokens of a tile (128-value blocks, 144 bytes each).
 template <bool DS4>
 struct XRegs {
-  uint4 q[4];
-  uint32_t sc[4];
+  uint4 q[NITEM];
+  uint32_t sc[NITEM];
   __device__ __forceinline__ void fetch(const GemmArgs& g, int t0, int sb, int tid) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < NITEM; ++i) {
       const int item = tid + GEMM_THREADS * i, c = item >> 4, j = item & 15;
       const int tok = t0 + c;
       q[i] = make_uint4(0, 0, 0, 0);
@@ -313,7 +331,7 @@ struct XRegs {
   }
   __device__ __forceinline__ void store(const SmemView& sm, int tid) const {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < NITEM; ++i) {
       const int item = tid + GEMM_THREADS * i, c = item >> 4, j = item & 15, s = j >> 1;
       *reinterpret_cast<uint4*>(sm.b + s * SL_B + core_off(c, j & 1)) = q[i];
       if ((j & 1) == 0) {
@@ -332,34 +350,89 @@ struct XRegs {
 // ---------------------------------------------------------------------------------------------
 // The kernel.
 
+constexpr int STAGE_BYTES_BASE = 8 * SL_A + 8 * SL_B + 2 * 8 * NT * 4;  // + 1 or 2 weight-scale planes
+
+template <int KIND>
+__host__ __device__ constexpr size_t gemm_stage_bytes() {
+  return STAGE_BYTES_BASE + (KIND == GK_Q4K ? 2 : 1) * 8 * TILE_ROWS * 4;
+}
 template <int KIND>
 __host__ __device__ constexpr size_t gemm_smem_bytes() {
-  return 128 + (KIND == GK_IQ3S_PACKED ? 65536 : 0) + 8 * SL_A + 8 * SL_B + (KIND == GK_Q4K ? 2 : 1) * 8 * TILE_ROWS * 4 +
-         2 * 8 * NT * 4;
+  return 128 + (KIND == GK_IQ3S_PACKED ? 65536 : 0) + 2 * gemm_stage_bytes<KIND>();
 }
 
+template <int KIND>
+__device__ __forceinline__ SmemView stage_view(uint8_t* base, const uint8_t* grid) {
+  SmemView sm;
+  sm.grid = grid;
+  sm.a = base;
+  base += 8 * SL_A;
+  sm.b = base;
+  base += 8 * SL_B;
+  sm.sa = reinterpret_cast<float*>(base);
+  base += 8 * TILE_ROWS * 4;
+  sm.sam = reinterpret_cast<float*>(base);
+  if (KIND == GK_Q4K) base += 8 * TILE_ROWS * 4;
+  sm.sbd = reinterpret_cast<float*>(base);
+  base += 8 * NT * 4;
+  sm.sbs = reinterpret_cast<float*>(base);
+  return sm;
+}
+
+// One slice's 16 columns of this warp: scale and accumulate.
+template <bool DS4>
+__device__ __forceinline__ void epilogue_slice(const uint32_t (&c)[16], const SmemView& sm, int s, int r_in, int col0,
+                                               int ncols, float (&acc)[16]) {
+  constexpr int MAGIC = 0x4B400000;
+  constexpr float MAGIC_F = 12582912.0f;
+  const float da = sm.sa[s * TILE_ROWS + r_in];
+  const float dam = DS4 ? sm.sam[s * TILE_ROWS + r_in] : 0.0f;
+  const float4* bd = reinterpret_cast<const float4*>(sm.sbd + s * NT + col0);
+  const float4* bs = reinterpret_cast<const float4*>(sm.sbs + s * NT + col0);
+  // all 16 columns, valid or not (tokens past the end of X were staged as zeros and are never stored): no
+  // data-dependent branch in the hot loop
+  (void)ncols;
+#pragma unroll
+  for (int j4 = 0; j4 < 4; ++j4) {
+    const float4 d = bd[j4];
+    const float dv[4] = {d.x, d.y, d.z, d.w};
+    float sv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (DS4) {
+      const float4 t = bs[j4];
+      sv[0] = t.x; sv[1] = t.y; sv[2] = t.z; sv[3] = t.w;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = 4 * j4 + u;
+      const float f = __int_as_float((int)c[j] + MAGIC) - MAGIC_F;  // exact: |c| <= 32 * 127 * 127 < 2^22
+      acc[j] = fmaf(da * dv[u], f, acc[j]);
+      if (DS4) acc[j] = fmaf(dam, sv[u], acc[j]);
+    }
+  }
+}
+
+__device__ __forceinline__ void dump_slice(const GemmArgs& g, const uint32_t (&c)[16], int row, int tok0, int ncols, int slice) {
+  if (row >= g.nrows) return;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    if (j < ncols) g.dump[((int64_t)(tok0 + j) * g.nrows + row) * (g.k >> 5) + slice] = (int)c[j];
+  }
+}
+
+// Clusters of `ksplit` CTAs share one (token tile, row tile) item and split its superblocks; the partial
+// accumulators meet in the first CTA through distributed shared memory, added in rank order.
 template <int KIND>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs g) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr bool DS4 = KIND == GK_Q4K;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int cs = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem);
   const uint32_t mbar = smem_addr(smem + 16);
-  uint8_t* sp = smem + 128;
-  SmemView sm;
-  sm.grid = sp;
-  if (KIND == GK_IQ3S_PACKED) sp += 65536;
-  sm.a = sp;
-  sp += 8 * SL_A;
-  sm.b = sp;
-  sp += 8 * SL_B;
-  sm.sa = reinterpret_cast<float*>(sp);
-  sp += 8 * TILE_ROWS * 4;
-  sm.sam = reinterpret_cast<float*>(sp);
-  if (KIND == GK_Q4K) sp += 8 * TILE_ROWS * 4;
-  sm.sbd = reinterpret_cast<float*>(sp);
-  sp += 8 * NT * 4;
-  sm.sbs = reinterpret_cast<float*>(sp);
+  const uint8_t* grid = smem + 128;
+  uint8_t* stage0 = smem + 128 + (KIND == GK_IQ3S_PACKED ? 65536 : 0);
+  float* red = reinterpret_cast<float*>(stage0);  // [NT][128] partial accumulators (reuses the tile buffers)
 
   if (warp == 0) tmem_alloc(smem_addr(tmem_slot), TMEM_COLS);
   if (tid == 32) {
@@ -367,12 +440,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs g)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (KIND == GK_IQ3S_PACKED) {
-    for (int e = tid; e < 512; e += GEMM_THREADS) {
-      const uint32_t gv = g_iq3s_grid_gemm[e];
-      uint4* dst = reinterpret_cast<uint4*>(smem + 128 + e * 128);
+    const uint32_t gv = g_iq3s_grid_gemm[tid & 511];
+    uint4* dst = reinterpret_cast<uint4*>(smem + 128 + (tid & 511) * 128);
 #pragma unroll
-      for (int r2 = 0; r2 < 8; ++r2) dst[r2] = make_uint4(gv, ~gv + 0x01010101u, gv, ~gv + 0x01010101u);
-    }
+    for (int r2 = 0; r2 < 8; ++r2) dst[r2] = make_uint4(gv, ~gv + 0x01010101u, gv, ~gv + 0x01010101u);
   }
   tc_fence_before();
   __syncthreads();
@@ -380,98 +451,136 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs g)
   const uint32_t tmem_base = *tmem_slot;
 
   const int nsb = g.k >> 8;
+  const int sb_begin = (int)((int64_t)nsb * crank / cs), sb_end = (int)((int64_t)nsb * (crank + 1) / cs);
   const int n_items = g.n_row_tiles * g.n_tok_tiles;
+  const int n_clusters = (int)gridDim.x / cs, cluster_id = (int)blockIdx.x / cs;
   const uint32_t idesc = make_idesc();
-  const uint32_t a_addr = smem_addr(sm.a), b_addr = smem_addr(sm.b);
-  const int q4 = warp & 3, h = warp >> 2;        // tensor-memory lane quarter, column half of this warp
+  const int q4 = warp & 3, h = warp >> 2;        // tensor-memory lane quarter, 16-column group of this warp
   const int r_in = 32 * q4 + lane;               // row of the tile this thread accumulates
-  const uint32_t t_warp = tmem_base + ((uint32_t)(32 * q4) << 16) + (uint32_t)(32 * h);
-  constexpr int MAGIC = 0x4B400000;
-  constexpr float MAGIC_F = 12582912.0f;
   uint32_t phase = 0;
   bool alive = true;  // false once a bounded wait gave up: skip the remaining work, still free tensor memory
 
-  for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+  for (int item = cluster_id; item < n_items; item += n_clusters) {
     const int tt = item / g.n_row_tiles, rt = item - tt * g.n_row_tiles;
     const int t0 = tt * NT;
-    const int ncols = min(NT, g.m - t0) - 32 * h;  // valid columns among this warp's 32
-    float acc[32];
+    // The 4 warps of a lane quarter share the tile's 16-column groups: with 4 groups one group each (all 8
+    // slices), with 2 groups two warps per group (4 slices each), with 1 group four warps (2 slices each);
+    // warps that share a group add their accumulators through shared memory at the end.
+    const int mt = min(NT, g.m - t0);
+    const int cgc = mt > 32 ? 4 : mt > 16 ? 2 : 1, wpc = 4 / cgc;
+    const int col0 = 16 * (h % cgc), sl0 = h / cgc;
+    const int ncols = mt - col0;  // valid columns among this warp's 16 (> 0 by construction)
+    const uint32_t t_warp = tmem_base + ((uint32_t)(32 * q4) << 16) + (uint32_t)col0;
+    float acc[16];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
-    WRegs<KIND> wr;
-    XRegs<DS4> xr;
-    wr.fetch(g, rt, 0, tid);
-    xr.fetch(g, t0, 0, tid);
-    for (int sb = 0; sb < nsb; ++sb) {
-      wr.decode(sm, tid);
-      xr.store(sm, tid);
+    for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+    if (alive && sb_begin < sb_end) {
+      WRegs<KIND> wr;
+      XRegs<DS4> xr;
+      wr.fetch(g, rt, sb_begin, tid);
+      xr.fetch(g, t0, sb_begin, tid);
+      {
+        const SmemView first = stage_view<KIND>(stage0, grid);
+        wr.decode(first, tid);
+        xr.store(first, tid);
+      }
+      if (sb_begin + 1 < sb_end) {
+        wr.fetch(g, rt, sb_begin + 1, tid);
+        xr.fetch(g, t0, sb_begin + 1, tid);
+      }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
       __syncthreads();
-      if (tid == 0) {
+      for (int sb = sb_begin; sb < sb_end && alive; ++sb) {
+        const int st = (sb - sb_begin) & 1;
+        // views are rebuilt from the shared array each time (never indexed from memory) so that every access
+        // below compiles to a shared-memory instruction
+        const SmemView cur = stage_view<KIND>(stage0 + st * gemm_stage_bytes<KIND>(), grid);
+        const SmemView nxt = stage_view<KIND>(stage0 + (st ^ 1) * gemm_stage_bytes<KIND>(), grid);
+        if (tid == 0) {
+          tc_fence_after();
+          const uint32_t a_addr = smem_addr(cur.a), b_addr = smem_addr(cur.b);
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {
+            mma_i8(tmem_base + (uint32_t)(s * NT), make_smem_desc(a_addr + s * SL_A, g.swap_lbo_sbo),
+                   make_smem_desc(b_addr + s * SL_B, g.swap_lbo_sbo), idesc);
+          }
+          mma_commit(mbar);
+        }
+        // while the tensor core works: the next superblock goes into the other stage, the one after it
+        // into registers
+        if (sb + 1 < sb_end) {
+          wr.decode(nxt, tid);
+          xr.store(nxt, tid);
+          if (sb + 2 < sb_end) {
+            wr.fetch(g, rt, sb + 2, tid);
+            xr.fetch(g, t0, sb + 2, tid);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        alive = gemm_mbar_wait(mbar, phase);
+        phase ^= 1u;
         tc_fence_after();
-#pragma unroll
-        for (int s = 0; s < 8; ++s) {
-          mma_i8(tmem_base + (uint32_t)(s * NT), make_smem_desc(a_addr + s * SL_A, g.swap_lbo_sbo),
-                 make_smem_desc(b_addr + s * SL_B, g.swap_lbo_sbo), idesc);
-        }
-        mma_commit(mbar);
-      }
-      if (sb + 1 < nsb) {  // next superblock's loads fly while the tensor core and the epilogue work
-        wr.fetch(g, rt, sb + 1, tid);
-        xr.fetch(g, t0, sb + 1, tid);
-      }
-      alive = gemm_mbar_wait(mbar, phase);
-      phase ^= 1u;
-      tc_fence_after();
-      if (alive && ncols > 0) {
+        if (alive && ncols > 0) {
+          // this warp's slices: every wpc-th one starting at sl0 (all 8 when the tile has 4 column groups)
+          uint32_t c0[16], c1[16];
+          tmem_ld16_issue(t_warp + (uint32_t)(sl0 * NT), c0);
 #pragma unroll 1
-        for (int s = 0; s < 8; ++s) {
-          uint32_t c[32];
-          tmem_ld32(t_warp + (uint32_t)(s * NT), c);
-          if (g.dump) {
-            const int row_d = rt * TILE_ROWS + r_in;
-            if (row_d < g.nrows) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (j < ncols) g.dump[((int64_t)(t0 + 32 * h + j) * g.nrows + row_d) * (g.k >> 5) + sb * 8 + s] = (int)c[j];
-              }
-            }
-          }
-          const float da = sm.sa[s * TILE_ROWS + r_in];
-          const float dam = DS4 ? sm.sam[s * TILE_ROWS + r_in] : 0.0f;
-          const float4* bd = reinterpret_cast<const float4*>(sm.sbd + s * NT + 32 * h);
-          const float4* bs = reinterpret_cast<const float4*>(sm.sbs + s * NT + 32 * h);
-#pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            if (4 * j4 < ncols) {
-              const float4 d = bd[j4];
-              const float dv[4] = {d.x, d.y, d.z, d.w};
-              float sv[4] = {0.f, 0.f, 0.f, 0.f};
-              if (DS4) {
-                const float4 t = bs[j4];
-                sv[0] = t.x; sv[1] = t.y; sv[2] = t.z; sv[3] = t.w;
-              }
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const int j = 4 * j4 + u;
-                const float f = __int_as_float((int)c[j] + MAGIC) - MAGIC_F;
-                acc[j] = fmaf(da * dv[u], f, acc[j]);
-                if (DS4) acc[j] = fmaf(dam, sv[u], acc[j]);
-              }
+          for (int s = sl0; s < 8; s += 2 * wpc) {
+            const int s1 = s + wpc;
+            tmem_ld_wait();
+            if (s1 < 8) tmem_ld16_issue(t_warp + (uint32_t)(s1 * NT), c1);
+            if (g.dump) dump_slice(g, c0, rt * TILE_ROWS + r_in, t0 + col0, ncols, sb * 8 + s);
+            epilogue_slice<DS4>(c0, cur, s, r_in, col0, ncols, acc);
+            if (s1 < 8) {
+              tmem_ld_wait();
+              if (s1 + wpc < 8) tmem_ld16_issue(t_warp + (uint32_t)((s1 + wpc) * NT), c0);
+              if (g.dump) dump_slice(g, c1, rt * TILE_ROWS + r_in, t0 + col0, ncols, sb * 8 + s1);
+              epilogue_slice<DS4>(c1, cur, s1, r_in, col0, ncols, acc);
             }
           }
         }
+        tc_fence_before();
+        __syncthreads();  // tensor memory and stage st are free again; stage st ^ 1 is complete
       }
-      tc_fence_before();
-      __syncthreads();  // tensor memory and the shared-memory tiles are free again
     }
     const int row = rt * TILE_ROWS + r_in;
-    if (alive && row < g.nrows) {
+    if (wpc > 1) {
+      // warps sharing a column group: the one with sl0 == 0 adds the others' accumulators in warp order
+      if (sl0 != 0) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        if (j < ncols) store_out_dyn(g.y, g.y_dtype, (int64_t)(t0 + 32 * h + j) * g.ldy + row, acc[j]);
+        for (int j = 0; j < 16; ++j) red[((sl0 - 1) * NT + col0 + j) * TILE_ROWS + r_in] = acc[j];
+      }
+      __syncthreads();
+      if (sl0 == 0) {
+        for (int w = 1; w < wpc; ++w) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[j] += red[((w - 1) * NT + col0 + j) * TILE_ROWS + r_in];
+        }
+      }
+      __syncthreads();
+    }
+    if (cs > 1) {
+      // combine the K-parts: every CTA parks its accumulators, the first one adds them in rank order
+      if (sl0 == 0) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) red[(col0 + j) * TILE_ROWS + r_in] = acc[j];
+      }
+      cluster.sync();
+      if (crank == 0 && sl0 == 0) {
+        for (int r = 1; r < cs; ++r) {
+          const float* rr = cluster.map_shared_rank(red, r);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[j] += rr[(col0 + j) * TILE_ROWS + r_in];
+        }
       }
     }
+    if (alive && crank == 0 && sl0 == 0 && row < g.nrows) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (j < ncols) store_out_dyn(g.y, g.y_dtype, (int64_t)(t0 + col0 + j) * g.ldy + row, acc[j]);
+      }
+    }
+    if (cs > 1) cluster.sync();  // the partial sums have been read: the tile buffers may be overwritten
   }
   tc_fence_before();
   __syncthreads();
@@ -480,6 +589,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs g)
 
 static int g_swap_lbo_sbo = 0;
 static int* g_gemm_dump = nullptr;
+static int g_gemm_ksplit = 0;  // experiments: 0 = choose, else 1, 2 or 4
 
 int gemm_error_flag(int* flag) {
   GSQ_CUDA_TRY(cudaMemcpyFromSymbol(flag, g_gemm_error, sizeof(int)));
@@ -506,9 +616,28 @@ static int launch_gemm(const GemmArgs& g, int sm_count, cudaStream_t st) {
     if (dev < 32) configured_mask |= 1 << dev;
   }
   const int n_items = g.n_row_tiles * g.n_tok_tiles;
-  const int grid = n_items < sm_count ? n_items : sm_count;
-  gemm_kernel<KIND><<<grid, GEMM_THREADS, smem, st>>>(g);
-  GSQ_CUDA_TRY(cudaGetLastError());
+  // split K over a cluster when there are too few tiles to occupy the SMs (decode-sized token counts)
+  int ks = 1;
+  const int nsb = g.k >> 8;
+  if (g_gemm_ksplit) {
+    ks = g_gemm_ksplit;
+  } else {
+    while (ks < 4 && n_items * ks * 2 <= sm_count && nsb / (ks * 2) >= 2) ks *= 2;
+  }
+  int clusters = n_items < sm_count / ks ? n_items : sm_count / ks;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(clusters * ks));
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = ks;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_kernel<KIND>, g));
   return GSQ_OK;
 }
 
@@ -517,6 +646,12 @@ static int launch_gemm(const GemmArgs& g, int sm_count, cudaStream_t st) {
 extern "C" int gsq_debug_swap_descriptor_strides(int on) {
   const int old = gsq::g_swap_lbo_sbo;
   gsq::g_swap_lbo_sbo = on ? 1 : 0;
+  return old;
+}
+
+extern "C" int gsq_debug_gemm_ksplit(int ks) {
+  const int old = gsq::g_gemm_ksplit;
+  gsq::g_gemm_ksplit = (ks == 1 || ks == 2 || ks == 4) ? ks : 0;
   return old;
 }
 
