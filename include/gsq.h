@@ -132,6 +132,27 @@ int gsq_mul_mat_vec_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_
                        void* stream);
 
 /*
+ * No counterpart in the reference (its shim always takes scratch from torch's allocator, lcpp_shim.cu:250-263).
+ * Quantise X and run the 1..8-row GEMV in one call without any buffer from the caller besides X, W and Y:
+ * the q8_1 blocks in between are kept in a fixed device array inside the library. For hosts that cannot
+ * allocate where they need the product -- their memory manager owns the whole device, they are a plug-in that
+ * is handed only input and output pointers, or an allocator call is not allowed on that code path.
+ *   - Limit: m <= 8 and m * k/32 * 36 <= gsq_linear_vec_static_max_q8_bytes() (294,912 bytes, i.e. 8 rows of
+ *     32768 columns); anything larger returns GSQ_ERR_TOO_LARGE ("shape too large ...") and launches nothing.
+ *   - Calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current); make that first call before starting a stream capture.
+ *   - All calls on a device share the one array, which keeps what the last call wrote. Every call overwrites
+ *     all the bytes it reads, so nothing needs clearing; but two calls that overlap on the GPU (different
+ *     streams, no ordering) race on it. Order them, or use the two-call sequence with your own buffers.
+ * Arguments as gsq_quantize_q8_1 (x, x_dtype, m, k, x_row_stride) and gsq_mul_mat_vec_q8 (the rest).
+ */
+int64_t gsq_linear_vec_static_max_q8_bytes(void);
+int gsq_linear_vec_static(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x,
+                          int x_dtype, int64_t m, int64_t k, int64_t x_row_stride, void* y, int y_dtype,
+                          int64_t y_row_stride, void* stream);
+
+/*
  * The GEMV has two weight-streaming variants: bulk copies (cp.async.bulk + mbarrier) into a per-warp
  * shared-memory ring, used wherever row segments are 16-byte aligned, and direct 128-bit loads otherwise.
  * Test hook: on != 0 forces the direct variant everywhere; returns the previous setting.
