@@ -59,6 +59,14 @@ CASES = [("IQ3_S", 128, 512), ("IQ3_S", 272, 5120), ("IQ3_S", 48, 1024), ("Q4_K"
          ("IQ4_XS", 128, 512), ("IQ4_XS", 202, 5120), ("IQ4_XS", 300, 17408)]
 
 
+@pytest.fixture(params=["specialised", "lockstep"], autouse=True)
+def gemm_variant(request):
+    """Both GEMM kernels: warp-specialised (producer / MMA / consumer warps) and all-warps-in-lockstep."""
+    old = _cabi.lib.gsq_debug_gemm_variant(int(request.param == "specialised"))
+    yield request.param
+    _cabi.lib.gsq_debug_gemm_variant(old)
+
+
 @pytest.fixture(scope="module", autouse=True)
 def descriptor_strides():
     """Settle which stride field of the shared-memory descriptor is which on the first case; a wrong

@@ -32,7 +32,6 @@ namespace gsq {
 enum { GK_IQ3S_PACKED = 0, GK_Q4K = 1, GK_IQ4XS = 2 };
 
 constexpr int GEMM_THREADS = 512;
-constexpr int NITEM = 1024 / GEMM_THREADS;  // (row, chunk) items of a 128 x 256 tile per thread
 constexpr int TILE_ROWS = 128;   // weight rows per tile = MMA M
 constexpr int NT = 64;           // tokens per tile = MMA N
 constexpr int SL_A = 4096 + 16;  // bytes between slices of the weight tile (+16: decode stores of the 8 slices hit 8 banks)
@@ -174,17 +173,19 @@ struct SmemView {
   const uint8_t* grid;  // IQ3_S codebook pairs (g, -g), 16 replicas
 };
 
-template <int KIND>
+// P = number of threads that share the tile's 1024 (row, chunk) items
+template <int KIND, int P>
 struct WRegs;
 
-template <>
-struct WRegs<GK_IQ3S_PACKED> {
+template <int P>
+struct WRegs<GK_IQ3S_PACKED, P> {
   uint32_t idx[9], sg[4], sc;
   uint2 dd;
   bool ok;
   __device__ __forceinline__ void fetch(const GemmArgs& g, int rt, int sb, int tid) {
     const int warp = tid >> 5, lane = tid & 31;
-    const int row0 = rt * TILE_ROWS + 16 * (warp >> 1);  // two warps per 16-row record, two of its four row groups each
+    // P = 512: two warps per 16-row record, two of its four row groups each; P = 256: one warp per record
+    const int row0 = rt * TILE_ROWS + 16 * (P == 512 ? warp >> 1 : warp);
     ok = row0 < g.nrows;
     if (!ok) return;
     const uint8_t* p = g.w + (int64_t)row0 * g.row_bytes + (int64_t)sb * 1760;
@@ -203,7 +204,7 @@ struct WRegs<GK_IQ3S_PACKED> {
     const uint32_t lane_off = (uint32_t)(lane & 15) << 3;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      if ((i >> 1) != (warp & 1)) continue;  // warp-uniform: this warp's half of the record
+      if (P == 512 && (i >> 1) != (warp & 1)) continue;  // warp-uniform: this warp's half of the record
       uint32_t wv[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -219,7 +220,7 @@ struct WRegs<GK_IQ3S_PACKED> {
         const uint32_t sgs = sh >= 0 ? sg[i] >> sh : sg[i] << (-sh);
         wv[e] = gprmt(gp.x, gp.y, (sgs & 0x4444u) | 0x3210u);
       }
-      const int r = 16 * (warp >> 1) + (lane >> 3) + 4 * i;
+      const int r = 16 * (P == 512 ? warp >> 1 : warp) + (lane >> 3) + 4 * i;
       uint8_t* dst = sm.a + s * SL_A;
       *reinterpret_cast<uint4*>(dst + core_off(r, 0)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
       *reinterpret_cast<uint4*>(dst + core_off(r, 1)) = make_uint4(wv[4], wv[5], wv[6], wv[7]);
@@ -229,13 +230,14 @@ struct WRegs<GK_IQ3S_PACKED> {
   }
 };
 
-template <>
-struct WRegs<GK_Q4K> {
+template <int P>
+struct WRegs<GK_Q4K, P> {
+  static constexpr int NITEM = 1024 / P;
   uint4 hdr[NITEM], qs[NITEM];
   __device__ __forceinline__ void fetch(const GemmArgs& g, int rt, int sb, int tid) {
 #pragma unroll
     for (int q = 0; q < NITEM; ++q) {
-      const int item = tid + GEMM_THREADS * q, r = item >> 3, p = item & 7;
+      const int item = tid + P * q, r = item >> 3, p = item & 7;
       const int row = min(rt * TILE_ROWS + r, g.nrows - 1);
       const uint8_t* b = g.w + (int64_t)row * g.row_bytes + (int64_t)sb * 144;
       hdr[q] = ldg_stream_v4(b);
@@ -245,7 +247,7 @@ struct WRegs<GK_Q4K> {
   __device__ __forceinline__ void decode(const SmemView& sm, int tid) const {
 #pragma unroll
     for (int q = 0; q < NITEM; ++q) {
-      const int item = tid + GEMM_THREADS * q, r = item >> 3, p = item & 7, jj = p >> 1, half = p & 1;
+      const int item = tid + P * q, r = item >> 3, p = item & 7, jj = p >> 1, half = p & 1;
       const uint4 v = qs[q];
       uint8_t* lo = sm.a + (2 * jj) * SL_A + core_off(r, half);
       *reinterpret_cast<uint4*>(lo) = make_uint4(v.x & 0x0F0F0F0Fu, v.y & 0x0F0F0F0Fu, v.z & 0x0F0F0F0Fu, v.w & 0x0F0F0F0Fu);
@@ -269,13 +271,14 @@ struct WRegs<GK_Q4K> {
   }
 };
 
-template <>
-struct WRegs<GK_IQ4XS> {
+template <int P>
+struct WRegs<GK_IQ4XS, P> {
+  static constexpr int NITEM = 1024 / P;
   uint2 hdr[NITEM], qa[NITEM], qb[NITEM];
   __device__ __forceinline__ void fetch(const GemmArgs& g, int rt, int sb, int tid) {
 #pragma unroll
     for (int q = 0; q < NITEM; ++q) {
-      const int item = tid + GEMM_THREADS * q, r = item >> 3, p = item & 7;
+      const int item = tid + P * q, r = item >> 3, p = item & 7;
       const int row = min(rt * TILE_ROWS + r, g.nrows - 1);
       const uint8_t* b = g.w + (int64_t)row * g.row_bytes + (int64_t)sb * 136;
       hdr[q] = ldg_stream_v2(b);
@@ -296,7 +299,7 @@ struct WRegs<GK_IQ4XS> {
   __device__ __forceinline__ void decode(const SmemView& sm, int tid) const {
 #pragma unroll
     for (int q = 0; q < NITEM; ++q) {
-      const int item = tid + GEMM_THREADS * q, r = item >> 3, p = item & 7;
+      const int item = tid + P * q, r = item >> 3, p = item & 7;
       const uint32_t v[4] = {qa[q].x, qa[q].y, qb[q].x, qb[q].y};
       uint32_t lo[4], hi[4];
 #pragma unroll
@@ -311,14 +314,15 @@ struct WRegs<GK_IQ4XS> {
 };
 
 // Activation quants of one superblock for the NT tokens of a tile (128-value blocks, 144 bytes each).
-template <bool DS4>
+template <bool DS4, int P>
 struct XRegs {
+  static constexpr int NITEM = 1024 / P;
   uint4 q[NITEM];
   uint32_t sc[NITEM];
   __device__ __forceinline__ void fetch(const GemmArgs& g, int t0, int sb, int tid) {
 #pragma unroll
     for (int i = 0; i < NITEM; ++i) {
-      const int item = tid + GEMM_THREADS * i, c = item >> 4, j = item & 15;
+      const int item = tid + P * i, c = item >> 4, j = item & 15;
       const int tok = t0 + c;
       q[i] = make_uint4(0, 0, 0, 0);
       sc[i] = 0;
@@ -332,7 +336,7 @@ struct XRegs {
   __device__ __forceinline__ void store(const SmemView& sm, int tid) const {
 #pragma unroll
     for (int i = 0; i < NITEM; ++i) {
-      const int item = tid + GEMM_THREADS * i, c = item >> 4, j = item & 15, s = j >> 1;
+      const int item = tid + P * i, c = item >> 4, j = item & 15, s = j >> 1;
       *reinterpret_cast<uint4*>(sm.b + s * SL_B + core_off(c, j & 1)) = q[i];
       if ((j & 1) == 0) {
         if (DS4) {
@@ -379,6 +383,30 @@ __device__ __forceinline__ SmemView stage_view(uint8_t* base, const uint8_t* gri
   return sm;
 }
 
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
 // One slice's 16 columns of this warp: scale and accumulate.
 template <bool DS4>
 __device__ __forceinline__ void epilogue_slice(const uint32_t (&c)[16], const SmemView& sm, int s, int r_in, int col0,
@@ -390,23 +418,25 @@ __device__ __forceinline__ void epilogue_slice(const uint32_t (&c)[16], const Sm
   const float4* bd = reinterpret_cast<const float4*>(sm.sbd + s * NT + col0);
   const float4* bs = reinterpret_cast<const float4*>(sm.sbs + s * NT + col0);
   // all 16 columns, valid or not (tokens past the end of X were staged as zeros and are never stored): no
-  // data-dependent branch in the hot loop
+  // data-dependent branch in the hot loop. Two columns per instruction with the packed fp32 forms of sm_100
+  // (mul / add / fma .f32x2): 2 integer adds + 3 packed ops per pair of elements.
   (void)ncols;
+  const uint64_t da2 = pack2(da, da), nm2 = pack2(-MAGIC_F, -MAGIC_F), dam2 = pack2(dam, dam);
 #pragma unroll
   for (int j4 = 0; j4 < 4; ++j4) {
     const float4 d = bd[j4];
-    const float dv[4] = {d.x, d.y, d.z, d.w};
-    float sv[4] = {0.f, 0.f, 0.f, 0.f};
-    if (DS4) {
-      const float4 t = bs[j4];
-      sv[0] = t.x; sv[1] = t.y; sv[2] = t.z; sv[3] = t.w;
-    }
+    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (DS4) t = bs[j4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 4; u += 2) {
       const int j = 4 * j4 + u;
-      const float f = __int_as_float((int)c[j] + MAGIC) - MAGIC_F;  // exact: |c| <= 32 * 127 * 127 < 2^22
-      acc[j] = fmaf(da * dv[u], f, acc[j]);
-      if (DS4) acc[j] = fmaf(dam, sv[u], acc[j]);
+      const uint64_t dv2 = u == 0 ? pack2(d.x, d.y) : pack2(d.z, d.w);
+      // exact int -> float: |c| <= 32 * 127 * 127 < 2^22, so c + bits(1.5 * 2^23) read as a float is 1.5 * 2^23 + c
+      const uint64_t f2 = add2(pack2(__int_as_float((int)c[j] + MAGIC), __int_as_float((int)c[j + 1] + MAGIC)), nm2);
+      uint64_t a2 = pack2(acc[j], acc[j + 1]);
+      a2 = fma2(mul2(da2, dv2), f2, a2);
+      if (DS4) a2 = fma2(dam2, u == 0 ? pack2(t.x, t.y) : pack2(t.z, t.w), a2);
+      unpack2(a2, acc[j], acc[j + 1]);
     }
   }
 }
@@ -475,8 +505,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs g)
 #pragma unroll
     for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
     if (alive && sb_begin < sb_end) {
-      WRegs<KIND> wr;
-      XRegs<DS4> xr;
+      WRegs<KIND, GEMM_THREADS> wr;
+      XRegs<DS4, GEMM_THREADS> xr;
       wr.fetch(g, rt, sb_begin, tid);
       xr.fetch(g, t0, sb_begin, tid);
       {
@@ -587,9 +617,246 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs g)
   if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Warp-specialised variant: 8 producer warps (fetch + decode into a 2-stage ring), 1 MMA warp, 8 consumer
+// warps (tensor-memory drain + scaling). The phases of consecutive superblocks overlap: while the consumers
+// scale superblock sb, the tensor core multiplies sb + 1 (tensor memory is used as two halves of 4 slices)
+// and the producers decode sb + 2. Hand-offs are mbarriers; every wait is bounded and a wait that gives up
+// raises a CTA-wide abort flag that makes all other waits return at once.
+
+constexpr int WS_PROD = 256, WS_CONS = 256, WS_THREADS = WS_PROD + WS_CONS + 32;
+
+template <int KIND>
+__host__ __device__ constexpr size_t gemm_ws_smem_bytes() {
+  return 128 + (KIND == GK_IQ3S_PACKED ? 65536 : 0) + 2 * gemm_stage_bytes<KIND>() + NT * TILE_ROWS * 4;
+}
+
+__device__ __forceinline__ bool ws_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  uint32_t done = 0;
+  for (int spin = 0; spin < (1 << 22); ++spin) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((spin & 63) == 63 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(&g_gemm_error, 1);
+  return false;
+}
+__device__ __forceinline__ void ws_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(WS_THREADS, 1) gemm_ws_kernel(const GemmArgs g) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr bool DS4 = KIND == GK_Q4K;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int cs = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 4);
+  const uint32_t bars = smem_addr(smem + 16);
+  // barrier i at bars + 8 i: full[2] = 0,1; ab_free[2] = 2,3; sc_free[2] = 4,5; tmem_full[2] = 6,7; tmem_empty[2] = 8,9
+  const uint8_t* grid = smem + 128;
+  uint8_t* stage0 = smem + 128 + (KIND == GK_IQ3S_PACKED ? 65536 : 0);
+  float* red = reinterpret_cast<float*>(stage0 + 2 * gemm_stage_bytes<KIND>());  // [NT][128]
+
+  if (warp == 16) tmem_alloc(smem_addr(tmem_slot), TMEM_COLS);
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 2; ++i) {
+      gemm_mbar_init(bars + 8 * (0 + i), WS_PROD);
+      gemm_mbar_init(bars + 8 * (2 + i), 1);
+      gemm_mbar_init(bars + 8 * (4 + i), WS_CONS);
+      gemm_mbar_init(bars + 8 * (6 + i), 1);
+      gemm_mbar_init(bars + 8 * (8 + i), WS_CONS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (KIND == GK_IQ3S_PACKED && tid < 512) {
+    const uint32_t gv = g_iq3s_grid_gemm[tid];
+    uint4* dst = reinterpret_cast<uint4*>(smem + 128 + tid * 128);
+#pragma unroll
+    for (int r2 = 0; r2 < 8; ++r2) dst[r2] = make_uint4(gv, ~gv + 0x01010101u, gv, ~gv + 0x01010101u);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int nsb = g.k >> 8;
+  const int sb_begin = (int)((int64_t)nsb * crank / cs), sb_end = (int)((int64_t)nsb * (crank + 1) / cs);
+  const int n_items = g.n_row_tiles * g.n_tok_tiles;
+  const int n_clusters = (int)gridDim.x / cs, cluster_id = (int)blockIdx.x / cs;
+  uint32_t n = 0;      // superblocks handled so far by this role (ring position and barrier phases)
+  bool alive = true;
+
+  if (warp < 8) {
+    // ------------------------------------------------------------------ producers
+    for (int item = cluster_id; item < n_items; item += n_clusters) {
+      const int tt = item / g.n_row_tiles, rt = item - tt * g.n_row_tiles, t0 = tt * NT;
+      if (alive && sb_begin < sb_end) {
+        WRegs<KIND, WS_PROD> wr;
+        XRegs<DS4, WS_PROD> xr;
+        wr.fetch(g, rt, sb_begin, tid);
+        xr.fetch(g, t0, sb_begin, tid);
+        for (int sb = sb_begin; sb < sb_end; ++sb, ++n) {
+          const uint32_t st = n & 1u, par = ((n >> 1) & 1u) ^ 1u;
+          alive = ws_wait(bars + 8 * (2 + st), par, abort_flag) && ws_wait(bars + 8 * (4 + st), par, abort_flag);
+          if (!alive) break;
+          const SmemView v = stage_view<KIND>(stage0 + st * gemm_stage_bytes<KIND>(), grid);
+          wr.decode(v, tid);
+          xr.store(v, tid);
+          if (sb + 1 < sb_end) {
+            wr.fetch(g, rt, sb + 1, tid);
+            xr.fetch(g, t0, sb + 1, tid);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          ws_arrive(bars + 8 * (0 + st));
+        }
+      }
+      if (cs > 1) {
+        cluster.sync();
+        cluster.sync();
+      }
+    }
+  } else if (warp == 16) {
+    // ------------------------------------------------------------------ MMA issue (one thread)
+    const uint32_t idesc = make_idesc();
+    for (int item = cluster_id; item < n_items; item += n_clusters) {
+      if (lane == 0 && alive) {
+        for (int sb = sb_begin; sb < sb_end; ++sb, ++n) {
+          const uint32_t st = n & 1u;
+          alive = ws_wait(bars + 8 * (0 + st), (n >> 1) & 1u, abort_flag);
+          if (!alive) break;
+          tc_fence_after();
+          const SmemView v = stage_view<KIND>(stage0 + st * gemm_stage_bytes<KIND>(), grid);
+          const uint32_t a_addr = smem_addr(v.a), b_addr = smem_addr(v.b);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            alive = ws_wait(bars + 8 * (8 + half), (n & 1u) ^ 1u, abort_flag);
+            if (!alive) break;
+            tc_fence_after();
+#pragma unroll
+            for (int sl = 0; sl < 4; ++sl) {
+              const int s = 4 * half + sl;
+              mma_i8(tmem_base + (uint32_t)(s * NT), make_smem_desc(a_addr + s * SL_A, g.swap_lbo_sbo),
+                     make_smem_desc(b_addr + s * SL_B, g.swap_lbo_sbo), idesc);
+            }
+            mma_commit(bars + 8 * (6 + half));
+          }
+          if (!alive) break;
+          mma_commit(bars + 8 * (2 + st));  // the stage's operand tiles are free once these MMAs have read them
+        }
+      }
+      if (cs > 1) {
+        cluster.sync();
+        cluster.sync();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ consumers
+    const int cw = warp - 8, q4 = cw & 3, pair = cw >> 2;
+    const int r_in = 32 * q4 + lane;
+    for (int item = cluster_id; item < n_items; item += n_clusters) {
+      const int tt = item / g.n_row_tiles, rt = item - tt * g.n_row_tiles, t0 = tt * NT;
+      const int mt = min(NT, g.m - t0);
+      // more than 32 tokens: the two warps of a lane quarter take 32 columns each; otherwise both take columns
+      // 0..31 and share the slices (pair p: slices p and p + 2 of each half), summed through shared memory
+      const bool by_cols = mt > 32;
+      const int col0 = by_cols ? 32 * pair : 0;
+      const uint32_t t_warp = tmem_base + ((uint32_t)(32 * q4) << 16) + (uint32_t)col0;
+      float acc[32];  // [0,16): columns col0 .. col0 + 15, [16,32): the next 16
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
+      float (&acc_lo)[16] = *reinterpret_cast<float (*)[16]>(&acc[0]);
+      float (&acc_hi)[16] = *reinterpret_cast<float (*)[16]>(&acc[16]);
+      if (alive) {
+        for (int sb = sb_begin; sb < sb_end; ++sb, ++n) {
+          const uint32_t st = n & 1u;
+          const SmemView v = stage_view<KIND>(stage0 + st * gemm_stage_bytes<KIND>(), grid);
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            alive = ws_wait(bars + 8 * (6 + half), n & 1u, abort_flag);
+            if (!alive) break;
+            tc_fence_after();
+            // 16 columns at a time, the next load in flight while the previous one is scaled
+            uint32_t c0[16], c1[16];
+            const int sl_first = by_cols ? 0 : pair, sl_step = by_cols ? 1 : 2;
+            tmem_ld16_issue(t_warp + (uint32_t)((4 * half + sl_first) * NT), c0);
+#pragma unroll 1
+            for (int sl = sl_first; sl < 4; sl += sl_step) {
+              const int s = 4 * half + sl;
+              tmem_ld_wait();
+              tmem_ld16_issue(t_warp + (uint32_t)(s * NT + 16), c1);
+              if (g.dump) dump_slice(g, c0, rt * TILE_ROWS + r_in, t0 + col0, mt - col0, sb * 8 + s);
+              epilogue_slice<DS4>(c0, v, s, r_in, col0, 16, acc_lo);
+              tmem_ld_wait();
+              if (sl + sl_step < 4) tmem_ld16_issue(t_warp + (uint32_t)((s + sl_step) * NT), c0);
+              if (g.dump) dump_slice(g, c1, rt * TILE_ROWS + r_in, t0 + col0 + 16, mt - col0 - 16, sb * 8 + s);
+              epilogue_slice<DS4>(c1, v, s, r_in, col0 + 16, 16, acc_hi);
+            }
+            tc_fence_before();
+            ws_arrive(bars + 8 * (8 + half));  // this half of tensor memory may be overwritten
+          }
+          if (!alive) break;
+          ws_arrive(bars + 8 * (4 + st));      // the stage's scale planes have been read
+        }
+      }
+      const int row = rt * TILE_ROWS + r_in;
+      if (!by_cols) {
+        if (pair == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) red[j * TILE_ROWS + r_in] = acc[j];
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (pair == 0) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[j] += red[j * TILE_ROWS + r_in];
+        }
+      }
+      const bool owner = by_cols || pair == 0;
+      if (cs > 1) {
+        if (owner) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) red[(col0 + j) * TILE_ROWS + r_in] = acc[j];
+        }
+        cluster.sync();
+        if (crank == 0 && owner) {
+          for (int r = 1; r < cs; ++r) {
+            const float* rr = cluster.map_shared_rank(red, r);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[j] += rr[(col0 + j) * TILE_ROWS + r_in];
+          }
+        }
+      }
+      if (alive && crank == 0 && owner && row < g.nrows) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (col0 + j < mt) store_out_dyn(g.y, g.y_dtype, (int64_t)(t0 + col0 + j) * g.ldy + row, acc[j]);
+        }
+      }
+      if (cs > 1) cluster.sync();
+      if (!by_cols) asm volatile("bar.sync 1, 256;" ::: "memory");  // red is reused by the next item
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 16) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
 static int g_swap_lbo_sbo = 0;
 static int* g_gemm_dump = nullptr;
 static int g_gemm_ksplit = 0;  // experiments: 0 = choose, else 1, 2 or 4
+static int g_gemm_variant = 1;  // 1 = warp-specialised (default), 0 = all warps in lockstep
 
 int gemm_error_flag(int* flag) {
   GSQ_CUDA_TRY(cudaMemcpyFromSymbol(flag, g_gemm_error, sizeof(int)));
@@ -601,9 +868,13 @@ static int launch_gemm(const GemmArgs& g, int sm_count, cudaStream_t st) {
   static int configured_mask = 0;
   int dev = 0;
   GSQ_CUDA_TRY(cudaGetDevice(&dev));
-  constexpr size_t smem = gemm_smem_bytes<KIND>();
+  const bool ws = g_gemm_variant == 1;
+  const size_t smem = ws ? gemm_ws_smem_bytes<KIND>() : gemm_smem_bytes<KIND>();
   if (dev >= 32 || !((configured_mask >> dev) & 1)) {
-    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)gemm_smem_bytes<KIND>()));
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm_ws_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)gemm_ws_smem_bytes<KIND>()));
     if (KIND == GK_IQ4XS) {
       const int8_t vals[16] = GSQ_IQ4NL_VALUES_INIT;
       uint32_t words[4];
@@ -627,7 +898,7 @@ static int launch_gemm(const GemmArgs& g, int sm_count, cudaStream_t st) {
   int clusters = n_items < sm_count / ks ? n_items : sm_count / ks;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(clusters * ks));
-  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.blockDim = dim3(ws ? WS_THREADS : GEMM_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr;
@@ -637,7 +908,11 @@ static int launch_gemm(const GemmArgs& g, int sm_count, cudaStream_t st) {
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_kernel<KIND>, g));
+  if (ws) {
+    GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_ws_kernel<KIND>, g));
+  } else {
+    GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_kernel<KIND>, g));
+  }
   return GSQ_OK;
 }
 
@@ -646,6 +921,12 @@ static int launch_gemm(const GemmArgs& g, int sm_count, cudaStream_t st) {
 extern "C" int gsq_debug_swap_descriptor_strides(int on) {
   const int old = gsq::g_swap_lbo_sbo;
   gsq::g_swap_lbo_sbo = on ? 1 : 0;
+  return old;
+}
+
+extern "C" int gsq_debug_gemm_variant(int v) {
+  const int old = gsq::g_gemm_variant;
+  gsq::g_gemm_variant = v ? 1 : 0;
   return old;
 }
 

@@ -21,7 +21,7 @@ EXPORTS = (
     "gsq_strerror", "gsq_last_cuda_error", "gsq_abi_version", "gsq_type_block_bytes", "gsq_check_inputs",
     "gsq_device_init", "gsq_quantize_q8_1", "gsq_quantize_q8_1_mmq", "gsq_mul_mat_vec_q8",
     "gsq_debug_block_sums", "gsq_debug_force_direct_loads", "gsq_device_error_flag", "gsq_debug_force_cluster_size",
-    "gsq_debug_swap_descriptor_strides", "gsq_debug_gemm_dump_sums", "gsq_debug_gemm_ksplit", "gsq_q8_layout_for_type", "gsq_mul_mat_scratch_bytes", "gsq_mul_mat_q8", "gsq_iq3s_repack", "gsq_route", "gsq_linear_vec_static", "gsq_linear_vec_static_max_q8_bytes",
+    "gsq_debug_swap_descriptor_strides", "gsq_debug_gemm_dump_sums", "gsq_debug_gemm_ksplit", "gsq_debug_gemm_variant", "gsq_q8_layout_for_type", "gsq_mul_mat_scratch_bytes", "gsq_mul_mat_q8", "gsq_iq3s_repack", "gsq_route", "gsq_linear_vec_static", "gsq_linear_vec_static_max_q8_bytes",
 )
 
 
@@ -74,6 +74,8 @@ def _load() -> C.CDLL:
     lib.gsq_debug_force_cluster_size.argtypes = [ci]
     lib.gsq_debug_swap_descriptor_strides.restype = ci
     lib.gsq_debug_swap_descriptor_strides.argtypes = [ci]
+    lib.gsq_debug_gemm_variant.restype = ci
+    lib.gsq_debug_gemm_variant.argtypes = [ci]
     lib.gsq_debug_gemm_ksplit.restype = ci
     lib.gsq_debug_gemm_ksplit.argtypes = [ci]
     lib.gsq_debug_gemm_dump_sums.restype = ci
