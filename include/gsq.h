@@ -191,7 +191,7 @@ int gsq_q8_layout_for_type(int ggml_type);
  * sums[m][rows][k/32] (NULL switches it off). */
 int gsq_debug_swap_descriptor_strides(int on);
 int gsq_debug_gemm_dump_sums(int32_t* sums);
-int gsq_debug_gemm_variant(int v); /* 1 = warp-specialised kernel (default), 0 = lockstep kernel; returns previous */
+int gsq_debug_gemm_variant(int v); /* 0 = lockstep kernel (default), 1 = warp-specialised kernel; returns previous */
 int gsq_debug_gemm_ksplit(int ks); /* 0 = choose; 1, 2, 4 = CTAs per cluster that split K (experiments) */
 size_t gsq_mul_mat_scratch_bytes(int64_t rows, int64_t m, int64_t k, int ggml_type);
 int gsq_mul_mat_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,

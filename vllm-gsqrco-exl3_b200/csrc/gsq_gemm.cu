@@ -407,20 +407,21 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   return r;
 }
 
-// One slice's 16 columns of this warp: scale and accumulate.
+// One slice's 16 columns of this warp: scale and accumulate. The accumulators stay packed two per 64-bit
+// register pair (columns 2i, 2i + 1) for the packed fp32 instructions of sm_100 (mul / add / fma .f32x2):
+// per pair of elements 2 integer adds and 3 packed floating-point instructions. All 16 columns are processed,
+// valid or not (tokens past the end of X were staged as zeros and are never stored): no data-dependent
+// branch in the hot loop.
 template <bool DS4>
 __device__ __forceinline__ void epilogue_slice(const uint32_t (&c)[16], const SmemView& sm, int s, int r_in, int col0,
-                                               int ncols, float (&acc)[16]) {
+                                               int ncols, uint64_t (&acc2)[8]) {
   constexpr int MAGIC = 0x4B400000;
   constexpr float MAGIC_F = 12582912.0f;
+  (void)ncols;
   const float da = sm.sa[s * TILE_ROWS + r_in];
   const float dam = DS4 ? sm.sam[s * TILE_ROWS + r_in] : 0.0f;
   const float4* bd = reinterpret_cast<const float4*>(sm.sbd + s * NT + col0);
   const float4* bs = reinterpret_cast<const float4*>(sm.sbs + s * NT + col0);
-  // all 16 columns, valid or not (tokens past the end of X were staged as zeros and are never stored): no
-  // data-dependent branch in the hot loop. Two columns per instruction with the packed fp32 forms of sm_100
-  // (mul / add / fma .f32x2): 2 integer adds + 3 packed ops per pair of elements.
-  (void)ncols;
   const uint64_t da2 = pack2(da, da), nm2 = pack2(-MAGIC_F, -MAGIC_F), dam2 = pack2(dam, dam);
 #pragma unroll
   for (int j4 = 0; j4 < 4; ++j4) {
@@ -428,15 +429,13 @@ __device__ __forceinline__ void epilogue_slice(const uint32_t (&c)[16], const Sm
     float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
     if (DS4) t = bs[j4];
 #pragma unroll
-    for (int u = 0; u < 4; u += 2) {
-      const int j = 4 * j4 + u;
+    for (int u = 0; u < 2; ++u) {
+      const int j = 4 * j4 + 2 * u;
       const uint64_t dv2 = u == 0 ? pack2(d.x, d.y) : pack2(d.z, d.w);
       // exact int -> float: |c| <= 32 * 127 * 127 < 2^22, so c + bits(1.5 * 2^23) read as a float is 1.5 * 2^23 + c
       const uint64_t f2 = add2(pack2(__int_as_float((int)c[j] + MAGIC), __int_as_float((int)c[j + 1] + MAGIC)), nm2);
-      uint64_t a2 = pack2(acc[j], acc[j + 1]);
-      a2 = fma2(mul2(da2, dv2), f2, a2);
-      if (DS4) a2 = fma2(dam2, u == 0 ? pack2(t.x, t.y) : pack2(t.z, t.w), a2);
-      unpack2(a2, acc[j], acc[j + 1]);
+      acc2[2 * j4 + u] = fma2(mul2(da2, dv2), f2, acc2[2 * j4 + u]);
+      if (DS4) acc2[2 * j4 + u] = fma2(dam2, u == 0 ? pack2(t.x, t.y) : pack2(t.z, t.w), acc2[2 * j4 + u]);
     }
   }
 }
@@ -501,9 +500,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs g)
     const int col0 = 16 * (h % cgc), sl0 = h / cgc;
     const int ncols = mt - col0;  // valid columns among this warp's 16 (> 0 by construction)
     const uint32_t t_warp = tmem_base + ((uint32_t)(32 * q4) << 16) + (uint32_t)col0;
-    float acc[16];
+    uint64_t acc2[8];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+    for (int j = 0; j < 8; ++j) acc2[j] = 0ull;
     if (alive && sb_begin < sb_end) {
       WRegs<KIND, GEMM_THREADS> wr;
       XRegs<DS4, GEMM_THREADS> xr;
@@ -560,12 +559,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs g)
             tmem_ld_wait();
             if (s1 < 8) tmem_ld16_issue(t_warp + (uint32_t)(s1 * NT), c1);
             if (g.dump) dump_slice(g, c0, rt * TILE_ROWS + r_in, t0 + col0, ncols, sb * 8 + s);
-            epilogue_slice<DS4>(c0, cur, s, r_in, col0, ncols, acc);
+            epilogue_slice<DS4>(c0, cur, s, r_in, col0, ncols, acc2);
             if (s1 < 8) {
               tmem_ld_wait();
               if (s1 + wpc < 8) tmem_ld16_issue(t_warp + (uint32_t)((s1 + wpc) * NT), c0);
               if (g.dump) dump_slice(g, c1, rt * TILE_ROWS + r_in, t0 + col0, ncols, sb * 8 + s1);
-              epilogue_slice<DS4>(c1, cur, s1, r_in, col0, ncols, acc);
+              epilogue_slice<DS4>(c1, cur, s1, r_in, col0, ncols, acc2);
             }
           }
         }
@@ -573,6 +572,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const GemmArgs g)
         __syncthreads();  // tensor memory and stage st are free again; stage st ^ 1 is complete
       }
     }
+    float acc[16];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
     const int row = rt * TILE_ROWS + r_in;
     if (wpc > 1) {
       // warps sharing a column group: the one with sl0 == 0 adds the others' accumulators in warp order
@@ -774,11 +776,10 @@ __global__ void __launch_bounds__(WS_THREADS, 1) gemm_ws_kernel(const GemmArgs g
       const bool by_cols = mt > 32;
       const int col0 = by_cols ? 32 * pair : 0;
       const uint32_t t_warp = tmem_base + ((uint32_t)(32 * q4) << 16) + (uint32_t)col0;
-      float acc[32];  // [0,16): columns col0 .. col0 + 15, [16,32): the next 16
+      uint64_t acc_lo[8], acc_hi[8];  // columns col0 .. col0 + 15 and the next 16, two per register pair
 #pragma unroll
-      for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
-      float (&acc_lo)[16] = *reinterpret_cast<float (*)[16]>(&acc[0]);
-      float (&acc_hi)[16] = *reinterpret_cast<float (*)[16]>(&acc[16]);
+      for (int j = 0; j < 8; ++j) acc_lo[j] = acc_hi[j] = 0ull;
+      const bool need_hi = mt - col0 > 16;  // warp-uniform: skip the upper 16 columns when no token is there
       if (alive) {
         for (int sb = sb_begin; sb < sb_end; ++sb, ++n) {
           const uint32_t st = n & 1u;
@@ -796,13 +797,25 @@ __global__ void __launch_bounds__(WS_THREADS, 1) gemm_ws_kernel(const GemmArgs g
             for (int sl = sl_first; sl < 4; sl += sl_step) {
               const int s = 4 * half + sl;
               tmem_ld_wait();
-              tmem_ld16_issue(t_warp + (uint32_t)(s * NT + 16), c1);
+              if (need_hi) {
+                tmem_ld16_issue(t_warp + (uint32_t)(s * NT + 16), c1);
+              } else if (sl + sl_step < 4) {
+                tmem_ld16_issue(t_warp + (uint32_t)((s + sl_step) * NT), c1);
+              }
               if (g.dump) dump_slice(g, c0, rt * TILE_ROWS + r_in, t0 + col0, mt - col0, sb * 8 + s);
               epilogue_slice<DS4>(c0, v, s, r_in, col0, 16, acc_lo);
-              tmem_ld_wait();
-              if (sl + sl_step < 4) tmem_ld16_issue(t_warp + (uint32_t)((s + sl_step) * NT), c0);
-              if (g.dump) dump_slice(g, c1, rt * TILE_ROWS + r_in, t0 + col0 + 16, mt - col0 - 16, sb * 8 + s);
-              epilogue_slice<DS4>(c1, v, s, r_in, col0 + 16, 16, acc_hi);
+              if (need_hi) {
+                tmem_ld_wait();
+                if (sl + sl_step < 4) tmem_ld16_issue(t_warp + (uint32_t)((s + sl_step) * NT), c0);
+                if (g.dump) dump_slice(g, c1, rt * TILE_ROWS + r_in, t0 + col0 + 16, mt - col0 - 16, sb * 8 + s);
+                epilogue_slice<DS4>(c1, v, s, r_in, col0 + 16, 16, acc_hi);
+              } else if (sl + sl_step < 4) {
+                // lower 16 columns only: c1 receives the next slice (its load overlapped the scaling above);
+                // once it has landed make it the current one
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) c0[j] = c1[j];
+              }
             }
             tc_fence_before();
             ws_arrive(bars + 8 * (8 + half));  // this half of tensor memory may be overwritten
@@ -810,6 +823,12 @@ __global__ void __launch_bounds__(WS_THREADS, 1) gemm_ws_kernel(const GemmArgs g
           if (!alive) break;
           ws_arrive(bars + 8 * (4 + st));      // the stage's scale planes have been read
         }
+      }
+      float acc[32];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        unpack2(acc_lo[j], acc[2 * j], acc[2 * j + 1]);
+        unpack2(acc_hi[j], acc[16 + 2 * j], acc[17 + 2 * j]);
       }
       const int row = rt * TILE_ROWS + r_in;
       if (!by_cols) {
@@ -856,7 +875,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) gemm_ws_kernel(const GemmArgs g
 static int g_swap_lbo_sbo = 0;
 static int* g_gemm_dump = nullptr;
 static int g_gemm_ksplit = 0;  // experiments: 0 = choose, else 1, 2 or 4
-static int g_gemm_variant = 1;  // 1 = warp-specialised (default), 0 = all warps in lockstep
+static int g_gemm_variant = 0;  // 0 = all warps in lockstep (default: faster on every measured shape), 1 = warp-specialised
 
 int gemm_error_flag(int* flag) {
   GSQ_CUDA_TRY(cudaMemcpyFromSymbol(flag, g_gemm_error, sizeof(int)));
