@@ -105,7 +105,7 @@ int gsq_device_init(int device);
 /*
  * q8_1 quantisation, MMVQ layout: replaces quantize_q8_1_x (lcpp_shim.cu:274-294, launch 361-368).
  * x [m, k] with row stride x_row_stride elements -> out: m * k/32 blocks of 36 bytes
- * (32 x int8, half d, half sum), rows contiguous. k % 32 == 0.
+ * (half d, half sum, then 32 x int8: ggml's block_q8_1), rows contiguous. k % 32 == 0.
  */
 int gsq_quantize_q8_1(const void* x, int x_dtype, int64_t m, int64_t k, int64_t x_row_stride, void* out,
                       void* stream);

@@ -2,7 +2,7 @@
 
 Restates the reference's owned quantisers in numpy float32:
   * MMVQ layout  -- quantize_q8_1_x, plugin/vllm_gguf_plugin/csrc/lcpp_shim.cu:274-294
-    (block_q8_1 = 32 x int8 + half2(d, sum), 36 bytes, ggml-common.h:259-269);
+    (block_q8_1 = half2(d, sum) then 32 x int8, 36 bytes, ggml-common.h:259-269);
     the warp sums follow the xor-shuffle tree 16,8,4,2,1 of
     csrc/lcpp/ggml/src/ggml-cuda/common.cuh:468-475.
   * MMQ layouts  -- quantize_mmq_q8_1_x, lcpp_shim.cu:298-355 (block_q8_1_mmq =
@@ -63,14 +63,14 @@ def quantize_q8_1(x: np.ndarray):
 
 def q8_1_bytes(x: np.ndarray) -> np.ndarray:
     """The MMVQ-layout bytes lcpp_quantize_q8_1(X, type, mmq=False, vendored=False) returns:
-    uint8 [M * K/32 * 36], row-major blocks, each 32 x int8 then half d, half sum."""
+    uint8 [M * K/32 * 36], row-major blocks, each half d, half sum, then 32 x int8."""
     q, d, s = quantize_q8_1(x)
     m, k = q.shape
     nb = k // QK8_1
     out = np.empty((m, nb, BLOCK_Q8_1), dtype=np.uint8)
-    out[..., :32] = q.reshape(m, nb, 32).view(np.uint8)
-    out[..., 32:34] = d.reshape(m, nb, 1).view(np.uint8)
-    out[..., 34:36] = s.reshape(m, nb, 1).view(np.uint8)
+    out[..., 0:2] = d.reshape(m, nb, 1).view(np.uint8)
+    out[..., 2:4] = s.reshape(m, nb, 1).view(np.uint8)
+    out[..., 4:36] = q.reshape(m, nb, 32).view(np.uint8)
     return out.reshape(-1)
 
 
@@ -78,9 +78,9 @@ def parse_q8_1_bytes(buf: np.ndarray, m: int, k: int):
     """Inverse view of q8_1_bytes: (q int8 [M,K], d f16 [M,K/32], sum f16 [M,K/32])."""
     nb = k // QK8_1
     b = np.ascontiguousarray(buf[: m * nb * BLOCK_Q8_1]).reshape(m, nb, BLOCK_Q8_1)
-    q = np.ascontiguousarray(b[..., :32]).view(np.int8).reshape(m, k)
-    d = np.ascontiguousarray(b[..., 32:34]).view(np.float16)[..., 0]
-    s = np.ascontiguousarray(b[..., 34:36]).view(np.float16)[..., 0]
+    d = np.ascontiguousarray(b[..., 0:2]).view(np.float16)[..., 0]
+    s = np.ascontiguousarray(b[..., 2:4]).view(np.float16)[..., 0]
+    q = np.ascontiguousarray(b[..., 4:36]).view(np.int8).reshape(m, k)
     return q, d, s
 
 

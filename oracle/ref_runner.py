@@ -1,0 +1,67 @@
+"""Run the reference's own CUDA ops (oracle/_ref/ref_C_gguf.so, built by oracle/build_ref.py) on cases
+prepared by a test, in a process of its own (TEST INFRASTRUCTURE; the library defines the same
+torch.ops._C_gguf names as this repository, so the two never share a process).
+
+    python oracle/ref_runner.py cases.pt results.pt
+
+cases.pt: list of dicts {"op": name, "args": [tensors / ints / bools / None ...], "time": bool}. Tensors are
+moved to cuda:0. results.pt: list of {"out": CPU tensor, "us": float or None}.
+"""
+
+import os
+import sys
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def graph_us(fn, reps=10):
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(reps):
+            fn()
+    best = 1e30
+    for _ in range(3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) * 1e3 / reps)
+    return best
+
+
+def main():
+    torch.ops.load_library(os.path.join(HERE, "_ref", "ref_C_gguf.so"))
+    cases = torch.load(sys.argv[1])
+    out = []
+    for c in cases:
+        args = [a.to("cuda:0") if isinstance(a, torch.Tensor) else a for a in c["args"]]
+        op = getattr(torch.ops._C_gguf, c["op"])
+        if c.get("copies"):  # timing on several copies of W so that L2 cannot serve it
+            ws = [args[0]] + [args[0].clone() for _ in range(c["copies"] - 1)]
+            i = [0]
+
+            def fn():
+                w = ws[i[0] % len(ws)]
+                i[0] += 1
+                return op(w, *args[1:])
+        else:
+            def fn():
+                return op(*args)
+        y = fn()
+        torch.cuda.synchronize()
+        us = graph_us(fn) if c.get("time") else None
+        out.append({"out": y.cpu(), "us": us})
+    torch.save(out, sys.argv[2])
+
+
+if __name__ == "__main__":
+    main()

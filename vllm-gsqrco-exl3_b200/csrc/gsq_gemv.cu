@@ -268,8 +268,8 @@ __device__ __forceinline__ void dot_slice(const int (&wv)[4][8], const int (&isc
     const uint32_t* b = q8_block(cx, m, blk);
     int u[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) u[e] = (int)__ldg(b + e);
-    const float d8 = h2f(__ldg(b + 8));
+    for (int e = 0; e < 8; ++e) u[e] = (int)__ldg(b + 1 + e);  // word 0 of a block is (d, sum), the quants follow
+    const float d8 = h2f(__ldg(b));
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       int sumi = 0;
@@ -419,7 +419,7 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_Q4K>& r, int row0, int
     dmn0[i] = ndm * (__int_as_float((int)(mn & 0xFFu) + MAGIC) - MAGIC_F);
     dmn1[i] = ndm * (__int_as_float((int)(mn >> 8) + MAGIC) - MAGIC_F);
   }
-  const uint32_t* b0 = q8_block(cx, 0, blk) + 4 * half;
+  const uint32_t* b0 = q8_block(cx, 0, blk) + 1 + 4 * half;  // this lane's 4 quant words (word 0 of a block is (d, sum))
   const int64_t mstride = (int64_t)cx.nb32 * 9;
 #pragma unroll
   for (int m = 0; m < M; ++m) {
@@ -430,7 +430,7 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_Q4K>& r, int row0, int
       u0[e] = (int)__ldg(bm + e);
       u1[e] = (int)__ldg(bm + 9 + e);
     }
-    const float d80 = h2f(__ldg(bm + 8 - 4 * half)), d81 = h2f(__ldg(bm + 17 - 4 * half));
+    const float d80 = h2f(__ldg(bm - 1 - 4 * half)), d81 = h2f(__ldg(bm + 8 - 4 * half));
     // sum of the activation quants this lane pairs with its 16 + 16 weights (the min term's factor)
     int q0 = 0, q1 = 0;
 #pragma unroll
@@ -482,8 +482,8 @@ __device__ __forceinline__ void accumulate(const Rec<KIND_Q6K>& r, int row0, int
   for (int m = 0; m < M; ++m) {
     const uint32_t* b0 = q8_block(cx, m, blk);
     const uint32_t* b1 = q8_block(cx, m, blk + 2);  // 64 values further
-    const int u0 = (int)__ldg(b0 + (w16 & 7)), u1 = (int)__ldg(b1 + (w16 & 7));
-    const float d80 = h2f(__ldg(b0 + 8)), d81 = h2f(__ldg(b1 + 8));
+    const int u0 = (int)__ldg(b0 + 1 + (w16 & 7)), u1 = (int)__ldg(b1 + 1 + (w16 & 7));
+    const float d80 = h2f(__ldg(b0)), d81 = h2f(__ldg(b1));
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int p0 = dp4a(v0[i], u0, 0), p1 = dp4a(v1[i], u1, 0);

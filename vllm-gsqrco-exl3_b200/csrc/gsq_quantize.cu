@@ -57,7 +57,7 @@ __device__ __forceinline__ uint32_t pack4(float a, float b, float c, float d) {
   return (uint32_t)(ia & 0xFF) | ((uint32_t)(ib & 0xFF) << 8) | ((uint32_t)(ic & 0xFF) << 16) | ((uint32_t)(id & 0xFF) << 24);
 }
 
-// MMVQ layout: block_q8_1 = 32 x int8, half d, half sum (36 bytes).
+// MMVQ layout: block_q8_1 = half d, half sum, 32 x int8 (36 bytes).
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict__ x, uint8_t* __restrict__ out,
                                                            int64_t m, int64_t k, int64_t stride) {
@@ -94,11 +94,11 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
   for (int e = 0; e < 8; ++e) q[e] = amax == 0.0f ? 0.0f : roundf(div_approx(v[e], d));
   const int64_t blk = row * (k >> 5) + (c8 >> 2);
   uint8_t* b = out + blk * 36;
-  uint32_t* q32 = reinterpret_cast<uint32_t*>(b + (c8 & 3) * 8);
+  uint32_t* q32 = reinterpret_cast<uint32_t*>(b + 4 + (c8 & 3) * 8);  // the quants follow the (d, sum) pair
   q32[0] = pack4(q[0], q[1], q[2], q[3]);
   q32[1] = pack4(q[4], q[5], q[6], q[7]);
   if ((c8 & 3) == 0) {
-    *reinterpret_cast<__half2*>(b + 32) = __floats2half2_rn(d, sum);
+    *reinterpret_cast<__half2*>(b) = __floats2half2_rn(d, sum);
   }
 }
 
