@@ -193,6 +193,16 @@ int gsq_debug_swap_descriptor_strides(int on);
 int gsq_debug_gemm_dump_sums(int32_t* sums);
 int gsq_debug_gemm_variant(int v); /* 0 = lockstep kernel (default), 1 = warp-specialised kernel; returns previous */
 int gsq_debug_gemm_ksplit(int ks); /* 0 = choose; 1, 2, 4 = CTAs per cluster that split K (experiments) */
+/* The register-operand tensor-core kernel that serves 1..48 activation rows behind gsq_mul_mat_vec_q8 and
+ * gsq_mul_mat_q8 (experiments and tests; each returns the previous value). */
+int gsq_debug_mmv_mode(int mode);        /* 0 = wherever it applies (default), 1 = never: dp4a GEMV / tcgen05 GEMM */
+int gsq_debug_mmv_min_rows(int n);       /* fewest activation rows it serves (default 1) */
+int gsq_debug_mmv_max_rows(int n);       /* most activation rows it serves (default 24, at most 48) */
+int gsq_debug_mmv_cluster_size(int cs);  /* 0 = choose; 1, 2, 4, 8 = CTAs per cluster */
+/* device buffer of 8 uint64 per CTA that receives time stamps (ns) at the kernel's phase boundaries, or NULL */
+int gsq_debug_mmv_profile(unsigned long long* stamps);
+/* Most activation rows one gsq_mul_mat_vec_q8 call takes for this type (8, or 48 where the kernel above serves it). */
+int gsq_mul_mat_vec_max_rows(int ggml_type, int packed);
 size_t gsq_mul_mat_scratch_bytes(int64_t rows, int64_t m, int64_t k, int ggml_type);
 int gsq_mul_mat_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,
                    const void* x_q8_mmq, int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride,

@@ -25,29 +25,31 @@ def pack_ref(w: np.ndarray) -> np.ndarray:
         for j in range(nb):
             rec = np.zeros(REC, dtype=np.uint8)
             for lane in range(32):
-                a, s = lane >> 3, lane & 7
+                g, tt = lane >> 2, lane & 3
                 stream = 0
-                sc = 0
-                for i in range(4):
-                    b = src[16 * t + a + 4 * i, j]
-                    qh = int(b[66 + s])
-                    for e in range(8):
-                        f = int(b[2 + 8 * s + e]) | (((qh >> e) & 1) << 8)
-                        stream |= f << (9 * (8 * i + e))
-                    g = int.from_bytes(bytes(b[74 + 4 * s: 78 + 4 * s]), "little")
-                    o = 0
-                    for e in range(8):
-                        for p in range(4):
-                            o |= ((g >> (4 * e + p)) & 1) << (16 * (e >> 2) + 4 * p + (e & 3))
-                    rec[1152 + 16 * lane + 4 * i: 1156 + 16 * lane + 4 * i] = np.frombuffer(o.to_bytes(4, "little"), np.uint8)
-                    sc |= ((int(b[106 + (s >> 1)]) >> (4 * (s & 1))) & 15) << (4 * i)
-                    if s == 0:
-                        rec[1728 + 2 * (4 * a + i): 1730 + 2 * (4 * a + i)] = b[0:2]
+                sg = [0, 0, 0, 0]
+                for s in range(8):
+                    for h in range(2):
+                        b = src[16 * t + g + 8 * h, j]
+                        qh = int(b[66 + s])
+                        sbits = int.from_bytes(bytes(b[74 + 4 * s: 78 + 4 * s]), "little")
+                        for e in range(2):
+                            f, e8 = 4 * s + 2 * h + e, 2 * tt + e
+                            stream |= (int(b[2 + 8 * s + e8]) | (((qh >> e8) & 1) << 8)) << (9 * f)
+                            fl = f & 7
+                            for p in range(4):
+                                sg[f >> 3] |= ((sbits >> (4 * e8 + p)) & 1) << (16 * (fl >> 2) + 4 * p + (fl & 3))
                 sb = np.frombuffer(stream.to_bytes(36, "little"), np.uint8)
                 rec[16 * lane: 16 * lane + 16] = sb[0:16]
                 rec[512 + 16 * lane: 528 + 16 * lane] = sb[16:32]
                 rec[1024 + 4 * lane: 1028 + 4 * lane] = sb[32:36]
-                rec[1664 + 2 * lane: 1666 + 2 * lane] = np.frombuffer(sc.to_bytes(2, "little"), np.uint8)
+                for q in range(4):
+                    rec[1152 + 16 * lane + 4 * q: 1156 + 16 * lane + 4 * q] = np.frombuffer(sg[q].to_bytes(4, "little"), np.uint8)
+            for g in range(8):
+                for h in range(2):
+                    b = src[16 * t + g + 8 * h, j]
+                    rec[1664 + 8 * g + 4 * h: 1668 + 8 * g + 4 * h] = b[106:110]
+                    rec[1728 + 4 * g + 2 * h: 1730 + 4 * g + 2 * h] = b[0:2]
             off = t * ROWS * rb + j * REC
             out[off: off + REC] = rec
     return out.reshape(rows, rb)

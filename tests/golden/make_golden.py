@@ -15,6 +15,10 @@ Writes
                         (tests/fixtures/dequant/*.npz): sha256 of the raw bytes, of the stored gguf-py
                         output, and whether oracle.blocks.dequantize reproduced it bit for bit when
                         this script ran
+  iq3_ref_packed.npz    a seeded IQ3_S weight (64 rows x 1024 columns) and the reference's own load-time
+                        repack of it (plugin/vllm_gguf_plugin/quantization/iq3_pack.py:134-138), the
+                        input its packed kernels read; lets a GPU box run those kernels without the
+                        reference tree. Also records that the reference's unpack(pack(w)) == w.
 """
 
 import hashlib
@@ -105,8 +109,26 @@ def fixture_check(ref):
     print("fixture_check.json:", sum(r["oracle_bit_exact"] for r in rec), "of", len(rec), "bit exact")
 
 
+def iq3_ref_packed(ref):
+    import importlib
+
+    import torch
+
+    from gsq_b200 import synth
+
+    import_reference_linear(ref)        # installs the package stubs
+    rp = importlib.import_module("vllm_gguf_plugin.quantization.iq3_pack")
+    raw = synth.make_weight(21, 64, 1024, 77)
+    w = torch.from_numpy(raw.copy())
+    packed = rp.pack(w, 21)
+    assert torch.equal(rp.unpack(packed, 21), w)
+    np.savez_compressed(os.path.join(HERE, "iq3_ref_packed.npz"), raw=raw, ref_packed=packed.numpy(), seed=77)
+    print("iq3_ref_packed.npz:", raw.shape, "round trip ok")
+
+
 if __name__ == "__main__":
     ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     dequant_blocks()
     fixture_check(ref)
     routing(ref)
+    iq3_ref_packed(ref)

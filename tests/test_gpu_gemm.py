@@ -59,12 +59,15 @@ CASES = [("IQ3_S", 128, 512), ("IQ3_S", 272, 5120), ("IQ3_S", 48, 1024), ("Q4_K"
          ("IQ4_XS", 128, 512), ("IQ4_XS", 202, 5120), ("IQ4_XS", 300, 17408)]
 
 
-@pytest.fixture(params=["specialised", "lockstep"], autouse=True)
+@pytest.fixture(params=["specialised", "lockstep", "default"], autouse=True)
 def gemm_variant(request):
-    """Both GEMM kernels: warp-specialised (producer / MMA / consumer warps) and all-warps-in-lockstep."""
+    """The tcgen05 GEMM kernels at every row count: warp-specialised (producer / MMA / consumer warps) and
+    all-warps-in-lockstep; and the library's own choice, which below 25 rows is the register-operand kernel."""
     old = _cabi.lib.gsq_debug_gemm_variant(int(request.param == "specialised"))
+    old_mode = _cabi.lib.gsq_debug_mmv_mode(0 if request.param == "default" else 1)
     yield request.param
     _cabi.lib.gsq_debug_gemm_variant(old)
+    _cabi.lib.gsq_debug_mmv_mode(old_mode)
 
 
 @pytest.fixture(scope="module", autouse=True)
@@ -72,7 +75,7 @@ def descriptor_strides():
     """Settle which stride field of the shared-memory descriptor is which on the first case; a wrong
     guess gives garbage, not a fault (both place every access inside the tile)."""
     raw, w = _weights("Q4_K", 128, 512, 1)
-    x = _x(16, 512, torch.float32, 2)
+    x = _x(64, 512, torch.float32, 2)
     ref, _ = _reference("Q4_K", raw, x)
     errs = {}
     for swap in (0, 1):

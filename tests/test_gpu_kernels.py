@@ -115,12 +115,18 @@ CASES = [
 ]
 
 
-@pytest.fixture(params=["staged", "direct"])
+@pytest.fixture(params=["staged", "direct", "tensor"])
 def load_variant(request):
-    """Both weight-streaming variants of the GEMV: bulk copies into a shared-memory ring, direct loads."""
+    """The kernels behind the vec ops: the dp4a GEMV with either weight-streaming variant (bulk copies into a
+    shared-memory ring, direct loads), and the library's own choice, which is the register-operand tensor-core
+    kernel for Q4_K and packed IQ3_S."""
     old = _cabi.lib.gsq_debug_force_direct_loads(int(request.param == "direct"))
+    old_mode = _cabi.lib.gsq_debug_mmv_mode(0 if request.param == "tensor" else 1)
+    old_min = _cabi.lib.gsq_debug_mmv_min_rows(1)
     yield request.param
     _cabi.lib.gsq_debug_force_direct_loads(old)
+    _cabi.lib.gsq_debug_mmv_mode(old_mode)
+    _cabi.lib.gsq_debug_mmv_min_rows(old_min)
 
 
 def test_no_bounded_wait_gave_up():

@@ -111,3 +111,23 @@ def test_gemm_outputs_match_reference_kernels(tmp_path):
     for c, y, r in zip(cases, mine, res):
         err = product.rel_err(y.numpy(), r["out"].double().numpy())
         assert err <= 1e-3, (c["op"], c["args"][2], c["args"][1].shape[0], err)
+
+
+def test_packed_iq3_kernels_match_reference_packed_kernels(tmp_path):
+    """The reference's packed IQ3_S kernels read the reference's own repack (tests/golden/iq3_ref_packed.npz,
+    made by its iq3_pack.pack); the kernels here read this package's repack of the same raw blocks."""
+    z = np.load(os.path.join(ROOT, "tests", "golden", "iq3_ref_packed.npz"))
+    raw, ref_packed = torch.from_numpy(z["raw"]), torch.from_numpy(z["ref_packed"])
+    rows, k = raw.shape[0], raw.shape[1] // 110 * 256
+    w = raw.to(DEV)
+    iq3_pack.pack_(w, IQ3_S)
+    cases, mine = [], []
+    for op, ms in (("lcpp_mul_mat_vec_iq3_mma_packed", (1, 5, 8, 32)), ("lcpp_mul_mat_iq3_packed", (16, 48, 130))):
+        for m in ms:
+            x = _x(m, k, torch.float32, 90 + m)
+            cases.append({"op": op, "args": [ref_packed, x, IQ3_S, rows]})
+            mine.append(getattr(torch.ops._C_gguf, op)(w, x.to(DEV), IQ3_S, rows).cpu())
+    res = run_reference(cases, tmp_path)
+    for c, y, r in zip(cases, mine, res):
+        err = product.rel_err(y.numpy(), r["out"].double().numpy())
+        assert err <= 1e-3, (c["op"], c["args"][1].shape[0], err)

@@ -179,12 +179,13 @@ struct WRegs;
 
 template <int P>
 struct WRegs<GK_IQ3S_PACKED, P> {
-  uint32_t idx[9], sg[4], sc;
-  uint2 dd;
+  uint32_t idx[9], sg[4];
+  uint2 sc;
+  uint32_t dd;
   bool ok;
   __device__ __forceinline__ void fetch(const GemmArgs& g, int rt, int sb, int tid) {
     const int warp = tid >> 5, lane = tid & 31;
-    // P = 512: two warps per 16-row record, two of its four row groups each; P = 256: one warp per record
+    // P = 512: two warps per 16-row record, four of its eight slices each; P = 256: one warp per record
     const int row0 = rt * TILE_ROWS + 16 * (P == 512 ? warp >> 1 : warp);
     ok = row0 < g.nrows;
     if (!ok) return;
@@ -195,37 +196,44 @@ struct WRegs<GK_IQ3S_PACKED, P> {
     idx[8] = ldg_stream_u32(p + 1024 + 4 * lane);
     const uint4 s = ldg_stream_v4(p + 1152 + 16 * lane);
     sg[0] = s.x; sg[1] = s.y; sg[2] = s.z; sg[3] = s.w;
-    sc = ldg_stream_u16(p + 1664 + 2 * lane);
-    dd = ldg_stream_v2(p + 1728 + 8 * (lane >> 3));
+    sc = ldg_stream_v2(p + 1664 + 8 * (lane >> 2));
+    dd = ldg_stream_u32(p + 1728 + 4 * (lane >> 2));
   }
+  // Lane (g = lane / 4, t = lane % 4) holds, of rows g and g + 8 and every slice, the 4-value groups 2t, 2t + 1
+  // (field f = 4 s + 2 h + e of gsq_iq3s_repack): 8 bytes of the row's 32-byte slice, one 64-bit store each.
   __device__ __forceinline__ void decode(const SmemView& sm, int tid) const {
     if (!ok) return;
-    const int warp = tid >> 5, lane = tid & 31, s = lane & 7;
+    const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t = lane & 3;
     const uint32_t lane_off = (uint32_t)(lane & 15) << 3;
+    const int rbase = 16 * (P == 512 ? warp >> 1 : warp) + gq;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (P == 512 && (i >> 1) != (warp & 1)) continue;  // warp-uniform: this warp's half of the record
-      uint32_t wv[8];
+    for (int s = 0; s < 8; ++s) {
+      if (P == 512 && (s >> 2) != (warp & 1)) continue;  // warp-uniform: this warp's half of the record
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const int bit = 9 * (8 * i + e), word = bit >> 5, off = bit & 31;
-        uint32_t t;
-        if (off + 9 <= 32) {
-          t = off >= 7 ? idx[word] >> (off - 7) : idx[word] << (7 - off);
-        } else {
-          t = __funnelshift_r(idx[word], idx[word + 1], off - 7);
+      for (int h = 0; h < 2; ++h) {
+        uint32_t wv[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int f = 4 * s + 2 * h + e, bit = 9 * f, word = bit >> 5, off = bit & 31;
+          uint32_t v;
+          if (off + 9 <= 32) {
+            v = off >= 7 ? idx[word] >> (off >= 7 ? off - 7 : 0) : idx[word] << (off < 7 ? 7 - off : 0);
+          } else {
+            v = __funnelshift_r(idx[word], idx[word + 1], off - 7);
+          }
+          const uint2 gp = *reinterpret_cast<const uint2*>(sm.grid + ((v & 0xFF80u) | lane_off));
+          const int fl = f & 7, sh = 16 * (fl >> 2) + (fl & 3) - 2;
+          const uint32_t sgs = sh >= 0 ? sg[f >> 3] >> (sh >= 0 ? sh : 0) : sg[f >> 3] << (sh < 0 ? -sh : 0);
+          wv[e] = gprmt(gp.x, gp.y, (sgs & 0x4444u) | 0x3210u);
         }
-        const uint2 gp = *reinterpret_cast<const uint2*>(sm.grid + ((t & 0xFF80u) | lane_off));
-        const int sh = 16 * (e >> 2) + (e & 3) - 2;
-        const uint32_t sgs = sh >= 0 ? sg[i] >> sh : sg[i] << (-sh);
-        wv[e] = gprmt(gp.x, gp.y, (sgs & 0x4444u) | 0x3210u);
+        const int r = rbase + 8 * h;
+        *reinterpret_cast<uint2*>(sm.a + s * SL_A + core_off(r, t >> 1) + 8 * (t & 1)) = make_uint2(wv[0], wv[1]);
+        if ((s & 3) == t) {  // the four lanes of a row group share its scales: each writes two slices
+          const float d = h2f(dd >> (16 * h));
+          const uint32_t scw = h ? sc.y : sc.x;
+          sm.sa[s * TILE_ROWS + r] = d * (float)(1 + 2 * (int)((scw >> (4 * s)) & 15u));
+        }
       }
-      const int r = 16 * (P == 512 ? warp >> 1 : warp) + (lane >> 3) + 4 * i;
-      uint8_t* dst = sm.a + s * SL_A;
-      *reinterpret_cast<uint4*>(dst + core_off(r, 0)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-      *reinterpret_cast<uint4*>(dst + core_off(r, 1)) = make_uint4(wv[4], wv[5], wv[6], wv[7]);
-      const float d = h2f((i < 2 ? dd.x : dd.y) >> (16 * (i & 1)));
-      sm.sa[s * TILE_ROWS + r] = d * (float)(1 + 2 * (int)((sc >> (4 * i)) & 15u));
     }
   }
 };
@@ -965,6 +973,13 @@ extern "C" size_t gsq_mul_mat_scratch_bytes(int64_t rows, int64_t m, int64_t k, 
   return 0;  // every CTA owns whole rows over all of K: nothing to combine through global memory
 }
 
+namespace gsq {
+// gsq_mmv.cu: the register-operand tensor-core kernel for 1..48 rows
+bool mmv_applies(int ggml_type, int packed, int64_t rows, int64_t m);
+int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* xq, int x_layout,
+             int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump);
+}  // namespace gsq
+
 extern "C" int gsq_mul_mat_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,
                               const void* x_q8_mmq, int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride,
                               void* scratch, size_t scratch_bytes, void* stream) {
@@ -972,6 +987,11 @@ extern "C" int gsq_mul_mat_q8(const void* w, int64_t row_bytes, int64_t rows, in
   (void)scratch;
   (void)scratch_bytes;
   if (m == 0 || rows == 0) return GSQ_OK;
+  if (mmv_applies(ggml_type, packed, rows, m)) {
+    const int rc = mmv_host(w, row_bytes, rows, ggml_type, packed, x_q8_mmq, 1, m, k, y, y_dtype, y_row_stride, stream,
+                            g_gemm_dump);
+    if (rc != 1000) return rc;  // 1000: the shape does not fit that kernel
+  }
   if (m < 0 || rows < 0 || k <= 0 || k % 256 != 0 || !w || !x_q8_mmq || !y) return GSQ_ERR_UNSUPPORTED;
   if (rows > INT32_MAX || k > INT32_MAX || m > INT32_MAX) return GSQ_ERR_TOO_LARGE;
   const int bs = block_bytes(ggml_type);

@@ -10,7 +10,7 @@
 //   * A "record" is what one warp consumes per step, every lane decoding its 32 values of 4 weight rows
 //     once and dotting them with each activation row:
 //        IQ3_S packed : one 16-row x 256-column tile record of gsq_iq3s_repack (1760 bytes);
-//                       lane = (row group a = lane / 8, slice s = lane % 8), rows a, a+4, a+8, a+12
+//                       lane = (g = lane / 4, t = lane % 4): rows g, g+8, 4-value groups 2t, 2t+1 of every slice
 //        Q4_K, IQ4_XS, IQ3_S in GGUF order : 4 rows x 4 superblocks; lane = (superblock, 32-value chunk)
 //        Q6_K         : 4 rows x 1 superblock; lane = 4-byte word of ql
 //   * Each cluster owns a contiguous range of row tiles, i.e. a contiguous byte range of W. The records of
@@ -83,15 +83,15 @@ struct KindTraits<KIND_Q6K> { static constexpr int tile_rows = 4, rec_sb = 1, bs
 template <int KIND>
 struct Rec;
 
-// Packed IQ3_S record (see gsq_repack.cu for the layout): per lane 9 words of 9-bit codebook indices
-// (row i, group e at bit 9 * (8 i + e)), 4 words of sign bits (row i; bit 8 p + e = sign of value p of
-// group e), 4 sub-scale nibbles, and the 4 fp16 d of the lane's rows.
+// Packed IQ3_S record (see gsq_repack.cu for the layout): per lane 9 words of 9-bit codebook indices (field
+// f = 4 s + 2 h + e: slice s, row g + 8 h, group 2t + e, at bit 9 f), 4 words of sign bits (field f in word f / 8;
+// bit 16 ((f % 8) / 4) + 4 p + f % 4 = sign of value p), the sub-scale nibbles and the fp16 d of rows g, g + 8.
 template <>
 struct Rec<KIND_IQ3S_PACKED> {
   uint32_t idx[9];
   uint32_t sg[4];
-  uint32_t sc;
-  uint2 dd;
+  uint2 sc;
+  uint32_t dd;
   __device__ __forceinline__ void load(const GemvArgs& a, int row0, int rec, int lane, bool ok) {
     if (!ok) return;
     const uint8_t* p = a.w + (int64_t)row0 * a.row_bytes + (int64_t)rec * 1760;
@@ -102,8 +102,8 @@ struct Rec<KIND_IQ3S_PACKED> {
     idx[8] = ldg_stream_u32(p + 1024 + 4 * lane);
     const uint4 s = ldg_stream_v4(p + 1152 + 16 * lane);
     sg[0] = s.x; sg[1] = s.y; sg[2] = s.z; sg[3] = s.w;
-    sc = ldg_stream_u16(p + 1664 + 2 * lane);
-    dd = ldg_stream_v2(p + 1728 + 8 * (lane >> 3));
+    sc = ldg_stream_v2(p + 1664 + 8 * (lane >> 2));
+    dd = ldg_stream_u32(p + 1728 + 4 * (lane >> 2));
   }
   // the same record already staged in shared memory by a bulk copy
   __device__ __forceinline__ void load_smem(const uint8_t* p, int lane, bool ok, int = 0) {
@@ -115,8 +115,8 @@ struct Rec<KIND_IQ3S_PACKED> {
     idx[8] = *reinterpret_cast<const uint32_t*>(p + 1024 + 4 * lane);
     const uint4 s = *reinterpret_cast<const uint4*>(p + 1152 + 16 * lane);
     sg[0] = s.x; sg[1] = s.y; sg[2] = s.z; sg[3] = s.w;
-    sc = *reinterpret_cast<const uint16_t*>(p + 1664 + 2 * lane);
-    dd = *reinterpret_cast<const uint2*>(p + 1728 + 8 * (lane >> 3));
+    sc = *reinterpret_cast<const uint2*>(p + 1664 + 8 * (lane >> 2));
+    dd = *reinterpret_cast<const uint32_t*>(p + 1728 + 4 * (lane >> 2));
   }
 };
 
@@ -286,36 +286,55 @@ __device__ __forceinline__ void dot_slice(const int (&wv)[4][8], const int (&isc
 // The codebook copy in shared memory holds, per entry and per lane-mod-16 replica, the pair (g, -g) of packed
 // int8x4 words (entry i of replica r at byte 128 i + 8 r): a 64-bit load per half-warp touches every bank once.
 // A group's signed word is then one byte permute of the pair, the selector built from the record's sign bits.
+// The lane dots its two groups of each slice of rows g and g + 8 (accumulator rows 0 and 1; 2 and 3 stay zero);
+// the four lanes of a row group add up when the tile is left.
 template <int M, int RS, bool DUMP>
 __device__ __forceinline__ void accumulate(const Rec<KIND_IQ3S_PACKED>& r, int row0, int rec, int lane, bool ok,
                                            const Ctx& cx, float (&acc)[4][M]) {
   (void)ok;
   const uint32_t lane_off = (uint32_t)(lane & 15) << 3;
   const char* gbase = reinterpret_cast<const char*>(cx.grid);
-  int wv[4][8];
-  int isc[4];
-  float dw[4];
+  const int g = lane >> 2, t = lane & 3;
+  const float dw[2] = {h2f(r.dd), h2f(r.dd >> 16)};
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int s = 0; s < 8; ++s) {
+    int wv[2][2];
+    float dws[2];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int bit = 9 * (8 * i + e), word = bit >> 5, off = bit & 31;
-      uint32_t t;
-      if (off + 9 <= 32) {
-        t = off >= 7 ? r.idx[word] >> (off - 7) : r.idx[word] << (7 - off);
-      } else {
-        t = __funnelshift_r(r.idx[word], r.idx[word + 1], off - 7);
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int f = 4 * s + 2 * h + e, bit = 9 * f, word = bit >> 5, off = bit & 31;
+        uint32_t v;
+        if (off + 9 <= 32) {
+          v = off >= 7 ? r.idx[word] >> (off >= 7 ? off - 7 : 0) : r.idx[word] << (off < 7 ? 7 - off : 0);
+        } else {
+          v = __funnelshift_r(r.idx[word], r.idx[word + 1], off - 7);
+        }
+        const uint2 gp = *reinterpret_cast<const uint2*>(gbase + ((v & 0xFF80u) | lane_off));
+        // sign of value p of field f sits at bit 16 ((f % 8) / 4) + 4 p + f % 4: move it to bit 4 p + 2 of the selector
+        const int fl = f & 7, sh = 16 * (fl >> 2) + (fl & 3) - 2;
+        const uint32_t sgs = sh >= 0 ? r.sg[f >> 3] >> (sh >= 0 ? sh : 0) : r.sg[f >> 3] << (sh < 0 ? -sh : 0);
+        wv[h][e] = (int)prmt(gp.x, gp.y, (sgs & 0x4444u) | 0x3210u);
       }
-      const uint2 g = *reinterpret_cast<const uint2*>(gbase + ((t & 0xFF80u) | lane_off));
-      // sign of value p of group e sits at bit 16 (e / 4) + 4 p + e % 4: move it to bit 4 p + 2 of the selector
-      const int sh = 16 * (e >> 2) + (e & 3) - 2;
-      const uint32_t sgs = sh >= 0 ? r.sg[i] >> sh : r.sg[i] << (-sh);
-      wv[i][e] = (int)prmt(g.x, g.y, (sgs & 0x4444u) | 0x3210u);
+      const uint32_t scw = h ? r.sc.y : r.sc.x;
+      dws[h] = dw[h] * (float)(1 + 2 * (int)((scw >> (4 * s)) & 15u));  // exact in fp32
     }
-    isc[i] = 1 + 2 * (int)((r.sc >> (4 * i)) & 15u);
-    dw[i] = h2f((i < 2 ? r.dd.x : r.dd.y) >> (16 * (i & 1)));
+    const int blk = rec * 8 + s;
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const uint32_t* b = q8_block(cx, m, blk);
+      const int u0 = (int)__ldg(b + 1 + 2 * t), u1 = (int)__ldg(b + 2 + 2 * t);
+      const float d8 = h2f(__ldg(b));
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int sumi = dp4a(wv[h][1], u1, dp4a(wv[h][0], u0, 0));
+        if constexpr (DUMP) dump_add(cx, m, row0 + g + 8 * h, blk, cx.nb32, sumi);
+        const float sf = __int_as_float(sumi + 0x4B400000) - 12582912.0f;
+        acc[h][m] = fmaf(dws[h] * d8, sf, acc[h][m]);
+      }
+    }
   }
-  dot_slice<M, DUMP>(wv, isc, dw, cx, rec * 8 + (lane & 7), row0 + (lane >> 3), 4, acc);
 }
 
 template <int M, int RS, bool DUMP>
@@ -728,14 +747,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
           float* seg = mypart + (tl - first_tl) * (TR * M);
           if (KIND == KIND_IQ3S_PACKED) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < 2; ++i)
 #pragma unroll
               for (int m = 0; m < M; ++m) {
                 float v = acc[i][m];
                 v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
                 v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
-                v += __shfl_xor_sync(0xFFFFFFFFu, v, 4);
-                if ((lane & 7) == 0) seg[((lane >> 3) + 4 * i) * M + m] = v;
+                if ((lane & 3) == 0) seg[((lane >> 2) + 8 * i) * M + m] = v;
                 acc[i][m] = 0.0f;
               }
           } else {
@@ -913,10 +931,20 @@ static int launch_gemv_m(int m, const GemvArgs& a, int sm_count, int max_smem, c
   }
 }
 
+// gsq_mmv.cu: the tensor-core kernel for 1..48 rows
+bool mmv_applies(int ggml_type, int packed, int64_t rows, int64_t m);
+int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* xq, int x_layout,
+             int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump);
+
 static int gemv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_q8,
                      int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump,
                      int dump_m0) {
   if (m == 0 || rows == 0) return GSQ_OK;
+  if (mmv_applies(ggml_type, packed, rows, m)) {
+    int* d = dump ? dump + (int64_t)dump_m0 * rows * (k / 32) : nullptr;
+    const int rc = mmv_host(w, row_bytes, rows, ggml_type, packed, x_q8, 0, m, k, y, y_dtype, y_row_stride, stream, d);
+    if (rc != 1000) return rc;  // 1000: the shape does not fit that kernel
+  }
   if (m < 0 || m > 8 || rows < 0 || k <= 0 || k % 256 != 0 || !w || !x_q8 || !y) return GSQ_ERR_UNSUPPORTED;
   if (rows > INT32_MAX || k > INT32_MAX) return GSQ_ERR_TOO_LARGE;
   const int bs = block_bytes(ggml_type);

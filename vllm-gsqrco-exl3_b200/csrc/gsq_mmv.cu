@@ -1,0 +1,930 @@
+// Register-operand int8 tensor-core product for 1..48 activation rows over GGUF superblocks (sm_100a).
+//
+// Serves, behind gsq_mul_mat_vec_q8 and gsq_mul_mat_q8, the row counts at which the product is a stream of
+// W with a little arithmetic per byte: the reference's owned 1..8-row kernels (lcpp_owned_k4.cu:116-234,
+// lcpp_owned_iq3_mma.cu:483-600), its 9..64-row kernel (lcpp_owned_mma_k.cu) and the small-batch end of its
+// MMQ (csrc/lcpp/ggml/src/ggml-cuda/mmq.cuh). The per-slice int32 sums are exact and each slice's term is
+// d_w * scale * d_x * sum (- dmin * min * sum of the slice's activation quants for Q4_K); only the fp32 order
+// in which a row's terms are added differs from the reference (fixed: results repeat run to run).
+//
+// Why not the shared-memory / tensor-memory pipeline of gsq_gemm.cu here: below about 64 tokens the tensor
+// core is idle either way and the cost is decoding W. With mma.sync the decoded weights are the A fragment,
+// in registers, so a warp works alone: no decoded tile in shared memory, no block-wide barrier, no drain of
+// tensor memory.
+//
+//   * A record is 16 weight rows x one 256-value superblock. Lane (g = lane / 4, t = lane % 4) holds rows g
+//     and g + 8 and, of every 32-value slice, the 4-value words 2t and 2t + 1 (Q4_K, IQ3_S) or word t of each
+//     half (IQ4_XS): exactly its share of the m16n8k32 A fragment. The k index inside a slice is permuted the
+//     same way on the activation side, which an integer sum does not see.
+//   * Activations are read where they lie through L1: block_q8_1 (36 bytes) for the vec ops, block_q8_1_mmq
+//     (144 bytes, [K/128][M]) for the ops that quantise for themselves. Columns past M repeat column M - 1
+//     and are never stored.
+//   * Work split, partial sums and the final reduction are those of the dp4a GEMV (gsq_gemv.cu): clusters
+//     own contiguous ranges of 16-row tiles, the records of a range are cut into equal contiguous chunks, one
+//     per warp; a warp leaving a tile parks its partial sums in shared memory and after one cluster barrier
+//     every output element is added in warp order through distributed shared memory. No atomics, no scratch.
+#include <cooperative_groups.h>
+
+#include "gsq_common.cuh"
+#include "gsq_tables.h"
+
+namespace cg = cooperative_groups;
+
+namespace gsq {
+
+enum { MK_Q4K = 0, MK_IQ3S = 1, MK_IQ4XS = 2 };
+enum { XL_Q81 = 0, XL_MMQ = 1 };
+
+constexpr int MMV_WARPS = 16;
+constexpr int MMV_THREADS = MMV_WARPS * 32;
+constexpr int MMV_TR = 16;  // rows per tile
+
+struct MmvArgs {
+  const uint8_t* w;
+  int64_t row_bytes;
+  int nrows;
+  int k;
+  const uint8_t* xq;
+  int m;
+  void* y;
+  int y_dtype;
+  int64_t ldy;
+  int ntiles;
+  int tiles_base;    // tiles per cluster: the first tiles_extra clusters own tiles_base + 1
+  int tiles_extra;
+  int tiles_round;   // tiles a cluster takes per round
+  int seg_cap;       // tiles one warp's chunk may touch in a round
+  int xcap_kb;       // 32-value blocks of activations the shared-memory staging area holds per column
+  int* dump;         // debug: int32 slice sums [m][nrows][k / 32]
+  // fast_div_inv of: 16-byte granules and 36-byte blocks per staged column, for a CTA with nsr_lo superblocks
+  // ([0]) and with nsr_lo + 1 ([1]: K does not split evenly); 16-byte pieces per row of block_q8_1_mmq blocks
+  int nsr_lo;
+  uint32_t inv_gpc[2], inv_nkb[2], inv_per;
+  unsigned long long* prof;  // debug: per CTA 8 time stamps (ns) at the phase boundaries
+};
+
+__device__ __forceinline__ void mmv_stamp(const MmvArgs& a, int phase) {
+  if (a.prof && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    a.prof[(size_t)blockIdx.x * 8 + phase] = t;
+  }
+}
+
+constexpr int MAGIC = 0x4B400000;          // bit pattern of 1.5 * 2^23
+constexpr float MAGIC_F = 12582912.0f;
+
+__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void upk2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t vmul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t vadd2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t vfma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint32_t mprmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+
+// D = A (16 x 32, int8, row) * B (32 x 8, int8, col) + C, all four accumulators starting at `init`
+__device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, int init) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+      : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(init));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Activations: staged once per CTA in shared memory for the CTA's K range, in the order the fragments want:
+//   quants  [column][kb][32 bytes]   lane (g, t) reads words 2t, 2t + 1 (or t, t + 4) of column 8j + g; a column is
+//                                    padded by 32 bytes so that the 8 columns of a read fall on different banks
+//   d       [kb][column] float       lane reads columns 8j + 2t, 8j + 2t + 1 (its accumulator columns)
+//   sum     [kb][column] float       Q4_K only: what multiplies -dmin * min
+// Columns past M are zeros. kb counts 32-value blocks from the start of the CTA's K range.
+
+struct XSmem {
+  const uint8_t* q;
+  const float* d;
+  const float* s;
+  int q8;  // bytes between quant columns 8 apart
+};
+
+// bytes of one staged quant column
+__host__ __device__ constexpr int mmv_xq_col_bytes(int nkb_cap) { return nkb_cap * 32 + 32; }
+
+// i / d for 0 <= i * d < 2^32, with inv = fast_div_inv(d) = ceil(2^32 / d), or 0 for d = 1 (2^32 does not fit)
+__host__ __device__ inline uint32_t fast_div_inv(int d) {
+  return d <= 1 ? 0u : (uint32_t)((0x100000000ull + (uint32_t)d - 1) / (uint32_t)d);
+}
+__device__ __forceinline__ int fast_div(int i, uint32_t inv) { return inv ? (int)__umulhi((uint32_t)i, inv) : i; }
+
+// columns m..MC-1 of the staging area: zeros
+template <int MC, bool DS>
+__device__ __forceinline__ void stage_x_pad(int m, int nkb, int colb, uint8_t* xq, float* xd, float* xs, int tid) {
+  const int pad = MC - m;
+  for (int i = tid; i < nkb * pad; i += MMV_THREADS) {
+    const int kb = i / pad, c = m + (i - kb * pad);
+    uint4* dst = reinterpret_cast<uint4*>(xq + c * colb + kb * 32);
+    dst[0] = make_uint4(0u, 0u, 0u, 0u);
+    dst[1] = make_uint4(0u, 0u, 0u, 0u);
+    xd[kb * MC + c] = 0.0f;
+    if (DS) xs[kb * MC + c] = 0.0f;
+  }
+}
+
+// block_q8_1 source (36-byte blocks, [column][K/32]): sum = d * (integer sum of the block's quants), as the
+// reference's MMVQ and owned vec kernels form the min term. The CTA's share of a column is one run of whole
+// 16-byte granules (K is a multiple of 128); every granule is loaded exactly once, by consecutive threads, and
+// its four words go where their position in the 9-word blocks says: word 0 of a block is (d, sum), the other
+// eight are quants. All 148 CTAs read the same few KB at the same time, so requests per byte are what counts.
+template <int MC, bool DS, typename AfterIssue>
+__device__ __forceinline__ void stage_x_q81(const MmvArgs& a, int kb0, int nkb, int colb, uint8_t* xq, float* xd, float* xs,
+                                            int tid, AfterIssue after_issue) {
+  const int nb32 = a.k >> 5;
+  const int gpc = (nkb * 9) >> 2;   // granules per column
+  const int total = gpc * a.m;
+  const int which = nkb == a.nsr_lo * 8 ? 0 : 1;
+  const uint32_t inv = which ? a.inv_gpc[1] : a.inv_gpc[0];
+  const uint32_t inv_nkb = which ? a.inv_nkb[1] : a.inv_nkb[0];
+  constexpr int U = 4;
+  for (int i0 = tid; i0 < total || i0 == tid; i0 += U * MMV_THREADS) {
+    uint4 v[U];
+    int col[U], gi[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = min(i0 + u * MMV_THREADS, total - 1);
+      col[u] = fast_div(i, inv);
+      gi[u] = i - col[u] * gpc;
+      v[u] = __ldg(reinterpret_cast<const uint4*>(a.xq + ((int64_t)col[u] * nb32 + kb0) * 36) + gi[u]);
+    }
+    if (i0 == tid) {
+      after_issue();
+      mmv_stamp(a, 6);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (i0 + u * MMV_THREADS < total) {
+        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int wi = 4 * gi[u] + e, kb = wi / 9, pos = wi - kb * 9;
+          if (pos == 0) {
+            xd[kb * MC + col[u]] = h2f(w[e]);
+          } else {
+            *reinterpret_cast<uint32_t*>(xq + col[u] * colb + kb * 32 + (pos - 1) * 4) = w[e];
+          }
+        }
+      }
+    }
+  }
+  mmv_stamp(a, 7);
+  stage_x_pad<MC, DS>(a.m, nkb, colb, xq, xd, xs, tid);
+  if (DS) {
+    __syncthreads();
+    for (int i = tid; i < nkb * a.m; i += MMV_THREADS) {
+      const int col = fast_div(i, inv_nkb), kb = i - col * nkb;
+      const uint4* q = reinterpret_cast<const uint4*>(xq + col * colb + kb * 32);
+      const uint4 lo = q[0], hi = q[1];
+      int sum = dp4a(0x01010101, (int)lo.x, 0);
+      sum = dp4a(0x01010101, (int)lo.y, sum);
+      sum = dp4a(0x01010101, (int)lo.z, sum);
+      sum = dp4a(0x01010101, (int)lo.w, sum);
+      sum = dp4a(0x01010101, (int)hi.x, sum);
+      sum = dp4a(0x01010101, (int)hi.y, sum);
+      sum = dp4a(0x01010101, (int)hi.z, sum);
+      sum = dp4a(0x01010101, (int)hi.w, sum);
+      xs[kb * MC + col] = xd[kb * MC + col] * (float)sum;
+    }
+  }
+}
+
+// block_q8_1_mmq source (144-byte blocks, [K/128][column]: 16 scale bytes = 4 x half2(d, sum) (DS) or 4 x float
+// d, then 128 int8): the stored sums are used as they are, as the reference's MMQ does. The CTA's share is one
+// contiguous run of 16-byte pieces, 9 per block.
+template <int MC, bool DS, typename AfterIssue>
+__device__ __forceinline__ void stage_x_mmq(const MmvArgs& a, int kb0, int nkb, int colb, uint8_t* xq, float* xd, float* xs,
+                                            int tid, AfterIssue after_issue) {
+  const int per = a.m * 9, total = (nkb >> 2) * per;
+  const uint32_t inv = a.inv_per;
+  const uint4* src = reinterpret_cast<const uint4*>(a.xq + (int64_t)(kb0 >> 2) * a.m * 144);
+  for (int i0 = tid; i0 < total || i0 == tid; i0 += 8 * MMV_THREADS) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = __ldg(src + min(i0 + u * MMV_THREADS, total - 1));
+    if (i0 == tid) after_issue();
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * MMV_THREADS;
+      if (i < total) {
+        const int b = fast_div(i, inv), r = i - b * per, col = r / 9, part = r - col * 9;
+        if (part == 0) {
+          const uint32_t sc[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (DS) {
+              xd[(4 * b + q) * MC + col] = h2f(sc[q]);
+              xs[(4 * b + q) * MC + col] = h2f(sc[q] >> 16);
+            } else {
+              xd[(4 * b + q) * MC + col] = __uint_as_float(sc[q]);
+            }
+          }
+        } else {
+          const int kb = 4 * b + ((part - 1) >> 1);
+          *reinterpret_cast<uint4*>(xq + col * colb + kb * 32 + ((part - 1) & 1) * 16) = v[u];
+        }
+      }
+    }
+  }
+  stage_x_pad<MC, DS>(a.m, nkb, colb, xq, xd, xs, tid);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Q4_K
+
+struct RecQ4K {
+  uint4 hdr[2];     // rows g, g + 8: d, dmin, 12 scale bytes
+  uint2 q[2][4];    // [row][64-value group p]: qs words 2t, 2t + 1 of the group's 32 bytes
+  __device__ __forceinline__ void load(const MmvArgs& a, int row0, int sb, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = min(row0 + g + 8 * h, a.nrows - 1);
+      const uint8_t* b = a.w + (int64_t)r * a.row_bytes + (int64_t)sb * 144;
+      hdr[h] = ldg_stream_v4(b);
+#pragma unroll
+      for (int p = 0; p < 4; ++p) q[h][p] = ldg_stream_v2(b + 16 + 32 * p + 8 * t);
+    }
+  }
+  // ask L2 for a record without waiting for it: lane = (row, first / last byte of the row's 144-byte block,
+  // which spans two 128-byte lines)
+  static __device__ __forceinline__ void prefetch(const MmvArgs& a, int row0, int sb, int lane) {
+    const int r = min(row0 + (lane >> 1), a.nrows - 1);
+    const uint8_t* b = a.w + (int64_t)r * a.row_bytes + (int64_t)sb * 144 + (lane & 1) * 143;
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(b));
+  }
+};
+
+// float of byte `byte` of `word`: the byte lands in the mantissa of 2^23, which is then subtracted (exact)
+__device__ __forceinline__ float byte_float(uint32_t word, int byte) {
+  return __uint_as_float(mprmt(word, 0x4B000000u, 0x7650u | (uint32_t)byte)) - 8388608.0f;
+}
+
+// xl: this lane's view of the staged activations of the record's superblock: quants at xl.q + j * xl.q8 + 32 s,
+// scales of its two accumulator columns at xl.d + s * MC + 8 j.
+template <int NTL, bool DUMP>
+__device__ __forceinline__ void process(const RecQ4K& r, const MmvArgs& ar, int row0, int sb, int lane, const XSmem& xl,
+                                        const uint8_t*, uint64_t (&acc)[NTL][2]) {
+  constexpr int MC = 8 * NTL;
+  constexpr bool DEFER = NTL <= 2;  // keep the record's sums unscaled by d / dmin until its end (more registers)
+  const int g = lane >> 2, t = lane & 3;
+  (void)g; (void)t;
+  // the 8 six-bit scales and mins of each row as bytes: [h][0] = slices 0..3, [h][1] = slices 4..7
+  uint32_t scw[2][2], mnw[2][2];
+  float d[2], ndm[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t A = r.hdr[h].y, B = r.hdr[h].z, C = r.hdr[h].w;
+    scw[h][0] = A & 0x3F3F3F3Fu;
+    mnw[h][0] = B & 0x3F3F3F3Fu;
+    scw[h][1] = (C & 0x0F0F0F0Fu) | ((A >> 2) & 0x30303030u);
+    mnw[h][1] = ((C >> 4) & 0x0F0F0F0Fu) | ((B >> 2) & 0x30303030u);
+    d[h] = h2f(r.hdr[h].x);
+    ndm[h] = -h2f(r.hdr[h].x >> 16);
+  }
+  const uint64_t nm2 = pk2(-MAGIC_F, -MAGIC_F);
+  const uint64_t d02 = pk2(d[0], d[0]), d12 = pk2(d[1], d[1]);
+  uint64_t tt[NTL][2], uu[NTL][2];
+  if constexpr (DEFER) {
+#pragma unroll
+    for (int j = 0; j < NTL; ++j) tt[j][0] = tt[j][1] = uu[j][0] = uu[j][1] = 0ull;
+  }
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    const int p = s >> 1;
+    // a0..a3: (row g, word 2t) (g + 8, 2t) (g, 2t + 1) (g + 8, 2t + 1); odd slices are the high nibbles
+    const uint32_t w[4] = {r.q[0][p].x, r.q[1][p].x, r.q[0][p].y, r.q[1][p].y};
+    uint32_t a[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] = ((s & 1) ? (w[i] >> 4) : w[i]) & 0x0F0F0F0Fu;
+    const int sc0 = (int)((scw[0][s >> 2] >> (8 * (s & 3))) & 0xFFu), sc1 = (int)((scw[1][s >> 2] >> (8 * (s & 3))) & 0xFFu);
+    float m0 = byte_float(mnw[0][s >> 2], s & 3), m1 = byte_float(mnw[1][s >> 2], s & 3);
+    if constexpr (!DEFER) {
+      m0 *= ndm[0];
+      m1 *= ndm[1];
+    }
+    const uint64_t m02 = pk2(m0, m0), m12 = pk2(m1, m1);
+#pragma unroll
+    for (int j = 0; j < NTL; ++j) {
+      const uint2 b = *reinterpret_cast<const uint2*>(xl.q + j * xl.q8 + s * 32);
+      const uint64_t dv2 = *reinterpret_cast<const uint64_t*>(xl.d + s * MC + 8 * j);
+      const uint64_t xs2 = *reinterpret_cast<const uint64_t*>(xl.s + s * MC + 8 * j);
+      int c[4];
+      mma_s8(c, a, b.x, b.y, 0);
+      if constexpr (DUMP) {
+        const int col0 = 8 * j + 2 * t, nb32 = ar.k >> 5;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int row = row0 + g + 8 * (e >> 1), col = col0 + (e & 1);
+          if (row < ar.nrows && col < ar.m) ar.dump[((int64_t)col * ar.nrows + row) * nb32 + sb * 8 + s] = c[e];
+        }
+      }
+      // |c * sc| <= 32 * 15 * 127 * 63 < 2^22: integer multiply-add onto the magic pattern, read as a float
+      const uint64_t f01 = vadd2(pk2(__int_as_float(c[0] * sc0 + MAGIC), __int_as_float(c[1] * sc0 + MAGIC)), nm2);
+      const uint64_t f23 = vadd2(pk2(__int_as_float(c[2] * sc1 + MAGIC), __int_as_float(c[3] * sc1 + MAGIC)), nm2);
+      if constexpr (DEFER) {
+        tt[j][0] = vfma2(f01, dv2, tt[j][0]);
+        tt[j][1] = vfma2(f23, dv2, tt[j][1]);
+        uu[j][0] = vfma2(m02, xs2, uu[j][0]);
+        uu[j][1] = vfma2(m12, xs2, uu[j][1]);
+      } else {
+        acc[j][0] = vfma2(m02, xs2, vfma2(f01, vmul2(dv2, d02), acc[j][0]));
+        acc[j][1] = vfma2(m12, xs2, vfma2(f23, vmul2(dv2, d12), acc[j][1]));
+      }
+    }
+  }
+  if constexpr (DEFER) {
+    const uint64_t n02 = pk2(ndm[0], ndm[0]), n12 = pk2(ndm[1], ndm[1]);
+#pragma unroll
+    for (int j = 0; j < NTL; ++j) {
+      acc[j][0] = vfma2(n02, uu[j][0], vfma2(d02, tt[j][0], acc[j][0]));
+      acc[j][1] = vfma2(n12, uu[j][1], vfma2(d12, tt[j][1], acc[j][1]));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// IQ3_S in the fragment-ordered layout of gsq_iq3s_repack (see gsq_repack.cu): per lane 9 words of 9-bit
+// codebook indices (field f = 4 s + 2 h + e at bit 9 f), 4 words of sign bits, the sub-scale nibbles and d of
+// rows g, g + 8. The codebook copy in shared memory holds, per entry and per lane-mod-16 replica, the pair
+// (g, -g) of packed int8x4 words (entry i of replica r at byte 128 i + 8 r): a field's signed word is one
+// 64-bit load and one byte permute whose selector comes from the sign bits.
+
+__device__ const uint32_t g_iq3s_grid_mmv[512] = GSQ_IQ3S_GRID_INIT;
+
+struct RecIQ3S {
+  uint32_t idx[9], sg[4];
+  uint2 sc;      // sub-scale nibbles of rows g, g + 8
+  uint32_t dd;   // fp16 d of rows g, g + 8
+  __device__ __forceinline__ void load(const MmvArgs& a, int row0, int sb, int lane) {
+    const uint8_t* p = a.w + (int64_t)row0 * a.row_bytes + (int64_t)sb * 1760;
+    const uint4 ia = ldg_stream_v4(p + 16 * lane), ib = ldg_stream_v4(p + 512 + 16 * lane);
+    idx[0] = ia.x; idx[1] = ia.y; idx[2] = ia.z; idx[3] = ia.w;
+    idx[4] = ib.x; idx[5] = ib.y; idx[6] = ib.z; idx[7] = ib.w;
+    idx[8] = ldg_stream_u32(p + 1024 + 4 * lane);
+    const uint4 s = ldg_stream_v4(p + 1152 + 16 * lane);
+    sg[0] = s.x; sg[1] = s.y; sg[2] = s.z; sg[3] = s.w;
+    sc = ldg_stream_v2(p + 1664 + 8 * (lane >> 2));
+    dd = ldg_stream_u32(p + 1728 + 4 * (lane >> 2));
+  }
+  // ask L2 for a record without waiting for it: its 1760 bytes touch at most 15 lines of 128 bytes
+  static __device__ __forceinline__ void prefetch(const MmvArgs& a, int row0, int sb, int lane) {
+    const uint8_t* p = a.w + (int64_t)row0 * a.row_bytes + (int64_t)sb * 1760;
+    if (lane < 15) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + min(128 * lane, 1759)));
+  }
+};
+
+template <int F>
+__device__ __forceinline__ uint32_t iq3_field(const RecIQ3S& r, const char* gbase, uint32_t lane_off) {
+  constexpr int bit = 9 * F, word = bit >> 5, off = bit & 31;
+  uint32_t t;
+  if (off + 9 <= 32) {
+    t = off >= 7 ? r.idx[word] >> (off - 7) : r.idx[word] << (7 - off);
+  } else {
+    t = __funnelshift_r(r.idx[word], r.idx[word + 1], off - 7);
+  }
+  const uint2 gp = *reinterpret_cast<const uint2*>(gbase + ((t & 0xFF80u) | lane_off));
+  constexpr int fl = F & 7, sh = 16 * (fl >> 2) + (fl & 3) - 2;
+  const uint32_t sgs = sh >= 0 ? r.sg[F >> 3] >> (sh >= 0 ? sh : 0) : r.sg[F >> 3] << (sh < 0 ? -sh : 0);
+  return mprmt(gp.x, gp.y, (sgs & 0x4444u) | 0x3210u);
+}
+
+template <int S, int NTL, bool DUMP>
+__device__ __forceinline__ void iq3_slice(const RecIQ3S& r, const MmvArgs& ar, int row0, int sb, int lane, const XSmem& xl,
+                                          const char* gbase, uint32_t lane_off, const uint32_t (&iscw)[2][2],
+                                          const uint64_t (&d2)[2], uint64_t (&acc)[NTL][2], uint64_t (&tt)[NTL][2]) {
+  constexpr int MC = 8 * NTL;
+  constexpr bool DEFER = NTL <= 2;
+  uint32_t a[4];
+  a[0] = iq3_field<4 * S + 0>(r, gbase, lane_off);   // (row g, group 2t)
+  a[1] = iq3_field<4 * S + 2>(r, gbase, lane_off);   // (row g + 8, group 2t)
+  a[2] = iq3_field<4 * S + 1>(r, gbase, lane_off);   // (row g, group 2t + 1)
+  a[3] = iq3_field<4 * S + 3>(r, gbase, lane_off);   // (row g + 8, group 2t + 1)
+  // 2 * nibble + 1 of slice S: byte S / 2 of the even- or odd-slice word
+  const int sc0 = (int)((iscw[0][S & 1] >> (8 * (S >> 1))) & 0xFFu), sc1 = (int)((iscw[1][S & 1] >> (8 * (S >> 1))) & 0xFFu);
+  const uint64_t nm2 = pk2(-MAGIC_F, -MAGIC_F);
+#pragma unroll
+  for (int j = 0; j < NTL; ++j) {
+    const uint2 b = *reinterpret_cast<const uint2*>(xl.q + j * xl.q8 + S * 32);
+    const uint64_t dv2 = *reinterpret_cast<const uint64_t*>(xl.d + S * MC + 8 * j);
+    int c[4];
+    mma_s8(c, a, b.x, b.y, 0);
+    if constexpr (DUMP) {
+      const int g = lane >> 2, t = lane & 3, col0 = 8 * j + 2 * t, nb32 = ar.k >> 5;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = row0 + g + 8 * (e >> 1), col = col0 + (e & 1);
+        if (row < ar.nrows && col < ar.m) ar.dump[((int64_t)col * ar.nrows + row) * nb32 + sb * 8 + S] = c[e];
+      }
+    }
+    // |c * (2 n + 1)| <= 32 * 15 * 127 * 31 < 2^22: integer multiply-add onto the magic pattern, read as a float
+    const uint64_t f01 = vadd2(pk2(__int_as_float(c[0] * sc0 + MAGIC), __int_as_float(c[1] * sc0 + MAGIC)), nm2);
+    const uint64_t f23 = vadd2(pk2(__int_as_float(c[2] * sc1 + MAGIC), __int_as_float(c[3] * sc1 + MAGIC)), nm2);
+    if constexpr (DEFER) {
+      tt[j][0] = vfma2(f01, dv2, tt[j][0]);
+      tt[j][1] = vfma2(f23, dv2, tt[j][1]);
+    } else {
+      acc[j][0] = vfma2(f01, vmul2(dv2, d2[0]), acc[j][0]);
+      acc[j][1] = vfma2(f23, vmul2(dv2, d2[1]), acc[j][1]);
+    }
+  }
+}
+
+template <int NTL, bool DUMP>
+__device__ __forceinline__ void process(const RecIQ3S& r, const MmvArgs& ar, int row0, int sb, int lane, const XSmem& xl,
+                                        const uint8_t* grid, uint64_t (&acc)[NTL][2]) {
+  constexpr bool DEFER = NTL <= 2;
+  const char* gbase = reinterpret_cast<const char*>(grid);
+  const uint32_t lane_off = (uint32_t)(lane & 15) << 3;
+  uint32_t iscw[2][2];  // [row half][even / odd slices]: bytes 2 * nibble + 1
+  uint64_t d2[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t w = h ? r.sc.y : r.sc.x;
+    iscw[h][0] = ((w & 0x0F0F0F0Fu) << 1) | 0x01010101u;
+    iscw[h][1] = ((w >> 3) & 0x1E1E1E1Eu) | 0x01010101u;
+    const float d = h2f(r.dd >> (16 * h));
+    d2[h] = pk2(d, d);
+  }
+  uint64_t tt[NTL][2];
+  if constexpr (DEFER) {
+#pragma unroll
+    for (int j = 0; j < NTL; ++j) tt[j][0] = tt[j][1] = 0ull;
+  }
+  iq3_slice<0, NTL, DUMP>(r, ar, row0, sb, lane, xl, gbase, lane_off, iscw, d2, acc, tt);
+  iq3_slice<1, NTL, DUMP>(r, ar, row0, sb, lane, xl, gbase, lane_off, iscw, d2, acc, tt);
+  iq3_slice<2, NTL, DUMP>(r, ar, row0, sb, lane, xl, gbase, lane_off, iscw, d2, acc, tt);
+  iq3_slice<3, NTL, DUMP>(r, ar, row0, sb, lane, xl, gbase, lane_off, iscw, d2, acc, tt);
+  iq3_slice<4, NTL, DUMP>(r, ar, row0, sb, lane, xl, gbase, lane_off, iscw, d2, acc, tt);
+  iq3_slice<5, NTL, DUMP>(r, ar, row0, sb, lane, xl, gbase, lane_off, iscw, d2, acc, tt);
+  iq3_slice<6, NTL, DUMP>(r, ar, row0, sb, lane, xl, gbase, lane_off, iscw, d2, acc, tt);
+  iq3_slice<7, NTL, DUMP>(r, ar, row0, sb, lane, xl, gbase, lane_off, iscw, d2, acc, tt);
+  if constexpr (DEFER) {
+#pragma unroll
+    for (int j = 0; j < NTL; ++j) {
+      acc[j][0] = vfma2(d2[0], tt[j][0], acc[j][0]);
+      acc[j][1] = vfma2(d2[1], tt[j][1], acc[j][1]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel.
+
+template <int KIND>
+struct MmvKind;
+template <>
+struct MmvKind<MK_Q4K> {
+  using Rec = RecQ4K;
+  static constexpr bool DS = true;       // activations carry sums (for the min term)
+  static constexpr int GRID = 0;         // bytes of codebook copy in shared memory
+};
+template <>
+struct MmvKind<MK_IQ3S> {
+  using Rec = RecIQ3S;
+  static constexpr bool DS = false;
+  static constexpr int GRID = 65536;
+};
+
+// bytes of staged activations per 32-value block and padded column
+__host__ __device__ constexpr size_t mmv_x_bytes(int cap_kb, int mc, bool ds) {
+  return (size_t)mc * mmv_xq_col_bytes(cap_kb) + (size_t)cap_kb * mc * (ds ? 8 : 4);
+}
+
+__host__ __device__ inline size_t mmv_partial_bytes(int mc, int seg_cap) {
+  return (size_t)MMV_WARPS * seg_cap * MMV_TR * mc * 4;
+}
+
+// superblocks [first, last) of the K range of CTA `rank` in a cluster of `cs`
+__host__ __device__ inline void mmv_k_range(int nsb, int cs, int rank, int* first, int* last) {
+  *first = (int)((int64_t)nsb * rank / cs);
+  *last = (int)((int64_t)nsb * (rank + 1) / cs);
+}
+
+template <int KIND, int NTL, int XL, bool DUMP>
+__global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  using Rec = typename MmvKind<KIND>::Rec;
+  constexpr bool DS = MmvKind<KIND>::DS;
+  constexpr int MC = 8 * NTL;                // padded column count
+  constexpr int SEGF = MMV_TR * MC;          // floats per parked tile segment
+  cg::cluster_group cluster = cg::this_cluster();
+  const int cs = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+  const int cluster_id = (int)blockIdx.x / cs;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int nsb = a.k >> 8;
+  int sb0, sb1;
+  mmv_k_range(nsb, cs, crank, &sb0, &sb1);
+  const int nsr = sb1 - sb0;                 // superblocks of this CTA
+  const int nkb = nsr * 8;
+
+  constexpr int GRID = MmvKind<KIND>::GRID;
+  const uint8_t* grid = smem;
+  float* partial = reinterpret_cast<float*>(smem + GRID);
+  float* csum = reinterpret_cast<float*>(smem + GRID + mmv_partial_bytes(MC, a.seg_cap));   // [tiles_round][16][MC]
+  uint8_t* xq = smem + GRID + mmv_partial_bytes(MC, a.seg_cap) + (size_t)a.tiles_round * SEGF * 4;
+  const int colb = mmv_xq_col_bytes(a.xcap_kb);
+  float* xd = reinterpret_cast<float*>(xq + (size_t)colb * MC);
+  float* xs = xd + (size_t)a.xcap_kb * MC;
+
+  const int tile_begin = cluster_id * a.tiles_base + min(cluster_id, a.tiles_extra);
+  const int tile_cnt = a.tiles_base + (cluster_id < a.tiles_extra ? 1 : 0);
+
+  mmv_stamp(a, 0);
+  // The activation loads go out first; the warp's first two records are then requested from L2 (no register
+  // waits on them) while those are in flight, and loaded for real after the staging, so that neither queues
+  // behind the other.
+  int first_tl = 0, first_rec = 0;
+  bool have_first = false;
+  int first_n = 0;
+  {
+    const int tiles_r = min(a.tiles_round, tile_cnt);
+    const int rr = tiles_r * nsr, c = (rr + MMV_WARPS - 1) / MMV_WARPS;
+    const int idx0 = warp * c, idx1 = min(rr, idx0 + c);
+    if (idx0 < idx1) {
+      have_first = true;
+      first_tl = idx0 / nsr;
+      first_rec = idx0 - first_tl * nsr;
+      first_n = min(2, idx1 - idx0);
+    }
+  }
+  auto prefetch_first = [&]() {
+    int ptl = first_tl, prec = first_rec;
+#pragma unroll 1
+    for (int u = 0; u < first_n; ++u) {
+      Rec::prefetch(a, (tile_begin + ptl) * MMV_TR, sb0 + prec, lane);
+      if (++prec == nsr) { prec = 0; ++ptl; }
+    }
+  };
+  if (XL == XL_Q81) {
+    stage_x_q81<MC, DS>(a, sb0 * 8, nkb, colb, xq, xd, xs, tid, prefetch_first);
+  } else {
+    stage_x_mmq<MC, DS>(a, sb0 * 8, nkb, colb, xq, xd, xs, tid, prefetch_first);
+  }
+  if (GRID) {
+    // one global load per thread (512 threads, 512 entries), then the 16 replicas of its (g, -g) pair; no byte
+    // of the codebook is zero, so ~g + 1 per byte never carries
+    const uint32_t gv = g_iq3s_grid_mmv[tid & 511];
+    uint4* dst = reinterpret_cast<uint4*>(smem + (tid & 511) * 128);
+#pragma unroll
+    for (int r2 = 0; r2 < 8; ++r2) dst[r2] = make_uint4(gv, ~gv + 0x01010101u, gv, ~gv + 0x01010101u);
+  }
+  __syncthreads();
+  mmv_stamp(a, 1);
+  Rec cur;
+  if (have_first) cur.load(a, (tile_begin + first_tl) * MMV_TR, sb0 + first_rec, lane);
+  XSmem xlane;
+  xlane.q = xq + g * colb + 8 * t;
+  xlane.q8 = 8 * colb;
+  xlane.d = xd + 2 * t;
+  xlane.s = xs + 2 * t;
+
+  for (int t0 = 0; t0 < tile_cnt; t0 += a.tiles_round) {
+    const int tiles_r = min(a.tiles_round, tile_cnt - t0);
+    const int rr = tiles_r * nsr;
+    const int c = (rr + MMV_WARPS - 1) / MMV_WARPS;  // records per warp this round
+    const int idx0 = warp * c, idx1 = min(rr, idx0 + c);
+    float* mypart = partial + warp * (a.seg_cap * SEGF);
+    if (idx0 < idx1) {
+      int tl = idx0 / nsr, rec = idx0 - tl * nsr;
+      const int seg_tl = tl;
+      if (t0 != 0) cur.load(a, (tile_begin + t0 + tl) * MMV_TR, sb0 + rec, lane);
+      uint64_t acc[NTL][2];
+#pragma unroll
+      for (int j = 0; j < NTL; ++j) acc[j][0] = acc[j][1] = 0ull;
+#pragma unroll 1
+      for (int idx = idx0; idx < idx1; ++idx) {
+        const bool has_next = idx + 1 < idx1;
+        const bool wrap = rec + 1 == nsr;
+        const int ntl = wrap ? tl + 1 : tl, nrc = wrap ? 0 : rec + 1;
+        Rec nxt;
+        if (has_next) nxt.load(a, (tile_begin + t0 + ntl) * MMV_TR, sb0 + nrc, lane);
+        XSmem xl;
+        xl.q = xlane.q + rec * 256;
+        xl.q8 = xlane.q8;
+        xl.d = xlane.d + rec * (8 * MC);
+        xl.s = xlane.s + rec * (8 * MC);
+        process<NTL, DUMP>(cur, a, (tile_begin + t0 + tl) * MMV_TR, sb0 + rec, lane, xl, grid, acc);
+        if (!has_next || wrap) {
+          // leaving tile tl: park its partial sums, [row][column]
+          float* seg = mypart + (tl - seg_tl) * SEGF;
+#pragma unroll
+          for (int j = 0; j < NTL; ++j) {
+            float v0, v1, v2, v3;
+            upk2(acc[j][0], v0, v1);
+            upk2(acc[j][1], v2, v3);
+            *reinterpret_cast<float2*>(seg + g * MC + 8 * j + 2 * t) = make_float2(v0, v1);
+            *reinterpret_cast<float2*>(seg + (g + 8) * MC + 8 * j + 2 * t) = make_float2(v2, v3);
+            acc[j][0] = acc[j][1] = 0ull;
+          }
+        }
+        if (has_next) cur = nxt;
+        tl = ntl;
+        rec = nrc;
+      }
+    }
+    if (t0 == 0) mmv_stamp(a, 2);
+    __syncthreads();
+    // (1) inside the CTA: one warp per tile adds the partial sums of the warps that touched it, in warp order.
+    // Only the first of them can have started before this tile (its segment index is not 0).
+    for (int tl = warp; tl < tiles_r; tl += MMV_WARPS) {
+      const int w0 = (tl * nsr) / c, w1 = ((tl + 1) * nsr - 1) / c;
+      const int seg0 = tl - (w0 * c) / nsr;
+      const float* p0 = partial + (w0 * a.seg_cap + seg0) * SEGF;
+      for (int o = lane; o < SEGF; o += 32) {
+        float v = p0[o];
+        for (int w = w0 + 1; w <= w1; ++w) v += partial[w * a.seg_cap * SEGF + o];
+        csum[tl * SEGF + o] = v;
+      }
+    }
+    cluster.sync();
+    if (t0 == 0) mmv_stamp(a, 3);
+    // (2) across the cluster: the CTAs' sums (one per K part) are added in rank order and stored
+    const int rows_r = tiles_r * MMV_TR;
+    const float* rsum[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) rsum[r] = cluster.map_shared_rank(csum, r < cs ? r : 0);
+    for (int r2 = crank * MMV_THREADS + tid; r2 < rows_r; r2 += cs * MMV_THREADS) {
+      const int row = (tile_begin + t0) * MMV_TR + r2;
+      if (row < a.nrows) {
+#pragma unroll
+        for (int c4 = 0; c4 < MC / 4; ++c4) {
+          if (4 * c4 < a.m) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              if (r < cs) {
+                const float4 p = *reinterpret_cast<const float4*>(rsum[r] + r2 * MC + 4 * c4);
+                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+              }
+            }
+            const float o[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (4 * c4 + e < a.m) store_out_dyn(a.y, a.y_dtype, (int64_t)(4 * c4 + e) * a.ldy + row, o[e]);
+            }
+          }
+        }
+      }
+    }
+    if (t0 == 0) mmv_stamp(a, 4);
+    cluster.sync();  // the partial sums are reused by the next round; no CTA leaves while another reads its memory
+    if (t0 == 0) mmv_stamp(a, 5);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side.
+
+static int g_mmv_mode = 0;      // 0 = use this kernel wherever it applies, 1 = never (the older kernels)
+static int g_mmv_min_rows = 1;  // fewest activation rows served here (experiments)
+static int g_mmv_max_rows = 24; // most
+static int g_mmv_cluster = 0;   // experiments: 0 = choose, else 1, 2, 4 or 8
+static unsigned long long* g_mmv_prof = nullptr;
+
+constexpr int MMV_DECLINED = 1000;  // mmv_host: this shape does not fit; use another kernel
+
+// co-resident clusters of `cs` CTAs with `smem` bytes each (cached per device / size class)
+template <int KIND, int NTL, int XL, bool DUMP>
+static int mmv_max_clusters(int cs, size_t smem, int sm_count, int* out) {
+  struct Entry { int dev, cs, kb, n; };
+  static Entry cache[64];
+  static int used = 0;
+  static bool configured[32];
+  int dev = 0;
+  GSQ_CUDA_TRY(cudaGetDevice(&dev));
+  auto kern = mmv_kernel<KIND, NTL, XL, DUMP>;
+  if (dev >= 32 || !configured[dev]) {
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 0));
+    if (dev < 32) configured[dev] = true;
+  }
+  const int kb = (int)((smem + 8191) / 8192);
+  for (int i = 0; i < used; ++i) {
+    if (cache[i].dev == dev && cache[i].cs == cs && cache[i].kb == kb) {
+      *out = cache[i].n;
+      return GSQ_OK;
+    }
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(sm_count / cs * cs));
+  cfg.blockDim = dim3(MMV_THREADS);
+  cfg.dynamicSmemBytes = (size_t)kb * 8192 > 227 * 1024 ? 227 * 1024 : (size_t)kb * 8192;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = cs;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cs == 1) {
+    n = sm_count;
+  } else if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  n = n < sm_count / cs ? n : sm_count / cs;
+  if (used < 64) cache[used++] = Entry{dev, cs, kb, n};
+  *out = n;
+  return GSQ_OK;
+}
+
+template <int KIND, int NTL, int XL, bool DUMP>
+static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) {
+  constexpr int MC = 8 * NTL;
+  constexpr bool DS = MmvKind<KIND>::DS;
+  a.seg_cap = MC <= 16 ? 4 : MC <= 32 ? 3 : 2;
+  // tiles per round: bounded by the segments a warp may park and by 32 KB of per-CTA tile sums
+  a.tiles_round = MMV_WARPS * (a.seg_cap - 1);
+  if (a.tiles_round > 32768 / (MMV_TR * MC * 4)) a.tiles_round = 32768 / (MMV_TR * MC * 4);
+  const size_t part = MmvKind<KIND>::GRID + mmv_partial_bytes(MC, a.seg_cap) + (size_t)a.tiles_round * MMV_TR * MC * 4;
+  const int nsb = a.k >> 8;
+  // cluster size: the CTAs of a cluster split K, so each stages 1 / cs of the activations. Among the sizes whose
+  // share fits, take the one that keeps most SMs busy with evenly filled clusters.
+  int best_cs = 0, best_clusters = 0, best_cap = 0;
+  double best_t = 0.0;
+  for (int cs : {1, 2, 4, 8}) {
+    if (g_mmv_cluster && cs != g_mmv_cluster) continue;
+    if (cs > nsb) break;
+    const int cap_kb = ((nsb + cs - 1) / cs) * 8;
+    const size_t smem = part + mmv_x_bytes(cap_kb, MC, DS);
+    if (smem > (size_t)max_smem) continue;
+    int n = 0;
+    const int rc = mmv_max_clusters<KIND, NTL, XL, DUMP>(cs, smem, sm_count, &n);
+    if (rc != GSQ_OK) return rc;
+    if (n <= 0) continue;
+    const int clusters = n < a.ntiles ? n : a.ntiles;
+    const int per = (a.ntiles + clusters - 1) / clusters;
+    // estimated time (us): the stream of W at the rate the loop reaches, stretched by uneven clusters and idle
+    // SMs; staging (a fixed part plus 36-byte blocks per thread); the cluster-wide sum (one remote read per CTA)
+    const double balance = ((double)a.ntiles / (per * clusters)) * ((double)(clusters * cs) / sm_count);
+    const double t_loop = (double)a.ntiles * MMV_TR * a.row_bytes / 4.4e6 / balance;
+    const double t_stage = 1.0 * (double)(((int64_t)a.m * cap_kb + 2047) / 2048);  // batches of 4 blocks per thread
+    const double t = t_loop + t_stage + 0.15 * cs;
+    if (!best_cs || t < best_t) {
+      best_t = t;
+      best_cs = cs;
+      best_clusters = clusters;
+      best_cap = cap_kb;
+    }
+  }
+  if (!best_cs) return MMV_DECLINED;
+  a.xcap_kb = best_cap;
+  a.nsr_lo = nsb / best_cs;
+  for (int i = 0; i < 2; ++i) {
+    a.inv_gpc[i] = fast_div_inv((a.nsr_lo + i) * 18);
+    a.inv_nkb[i] = fast_div_inv((a.nsr_lo + i) * 8);
+  }
+  a.inv_per = fast_div_inv(a.m * 9);
+  a.tiles_base = a.ntiles / best_clusters;
+  a.tiles_extra = a.ntiles % best_clusters;
+  const size_t smem = part + mmv_x_bytes(best_cap, MC, DS);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(best_clusters * best_cs));
+  cfg.blockDim = dim3(MMV_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = best_cs;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, mmv_kernel<KIND, NTL, XL, DUMP>, a));
+  return GSQ_OK;
+}
+
+template <int KIND, int XL>
+static int mmv_launch_n(const MmvArgs& a, int sm_count, int max_smem, cudaStream_t st) {
+  const int ntl = (a.m + 7) / 8;
+  if (a.dump) {
+    switch (ntl) {
+      case 1: return mmv_launch_t<KIND, 1, XL, true>(a, sm_count, max_smem, st);
+      case 2: return mmv_launch_t<KIND, 2, XL, true>(a, sm_count, max_smem, st);
+      case 3: return mmv_launch_t<KIND, 3, XL, true>(a, sm_count, max_smem, st);
+      case 4: return mmv_launch_t<KIND, 4, XL, true>(a, sm_count, max_smem, st);
+      case 5:
+      case 6: return mmv_launch_t<KIND, 6, XL, true>(a, sm_count, max_smem, st);
+      default: return MMV_DECLINED;
+    }
+  }
+  switch (ntl) {
+    case 1: return mmv_launch_t<KIND, 1, XL, false>(a, sm_count, max_smem, st);
+    case 2: return mmv_launch_t<KIND, 2, XL, false>(a, sm_count, max_smem, st);
+    case 3: return mmv_launch_t<KIND, 3, XL, false>(a, sm_count, max_smem, st);
+    case 4: return mmv_launch_t<KIND, 4, XL, false>(a, sm_count, max_smem, st);
+    case 5:
+    case 6: return mmv_launch_t<KIND, 6, XL, false>(a, sm_count, max_smem, st);
+    default: return MMV_DECLINED;
+  }
+}
+
+// Whether (type, packed, m) may be served here (mmv_host can still decline a shape: MMV_DECLINED).
+bool mmv_applies(int ggml_type, int packed, int64_t rows, int64_t m) {
+  if (g_mmv_mode == 1 || m < g_mmv_min_rows || m > g_mmv_max_rows) return false;
+  return ggml_type == GSQ_TYPE_Q4_K || (ggml_type == GSQ_TYPE_IQ3_S && packed && rows % 16 == 0);
+}
+
+// x_layout: 0 = block_q8_1, 1 = block_q8_1_mmq. Returns MMV_DECLINED when the shape does not fit.
+int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* xq, int x_layout,
+             int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump) {
+  if (m == 0 || rows == 0) return GSQ_OK;
+  if (m < 0 || m > 48 || rows < 0 || k <= 0 || k % 256 != 0 || !w || !xq || !y) return GSQ_ERR_UNSUPPORTED;
+  if (rows > INT32_MAX || k > INT32_MAX) return GSQ_ERR_TOO_LARGE;
+  const int bs = block_bytes(ggml_type);
+  if (bs == 0 || row_bytes != (k / 256) * bs) return GSQ_ERR_UNSUPPORTED;
+  if (y_dtype != GSQ_F32 && y_dtype != GSQ_F16 && y_dtype != GSQ_BF16) return GSQ_ERR_UNSUPPORTED;
+  DeviceInfo di;
+  const int rc = device_info(&di);
+  if (rc != GSQ_OK) return rc;
+  MmvArgs a;
+  a.w = (const uint8_t*)w;
+  a.row_bytes = row_bytes;
+  a.nrows = (int)rows;
+  a.k = (int)k;
+  a.xq = (const uint8_t*)xq;
+  a.m = (int)m;
+  a.y = y;
+  a.y_dtype = y_dtype;
+  a.ldy = y_row_stride;
+  a.ntiles = (int)((rows + MMV_TR - 1) / MMV_TR);
+  a.tiles_base = a.tiles_extra = a.tiles_round = 0;
+  a.seg_cap = 4;
+  a.xcap_kb = 0;
+  a.dump = dump;
+  a.prof = g_mmv_prof;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (ggml_type) {
+    case GSQ_TYPE_Q4_K:
+      return x_layout == XL_Q81 ? mmv_launch_n<MK_Q4K, XL_Q81>(a, di.sm_count, di.max_smem_optin, st)
+                                : mmv_launch_n<MK_Q4K, XL_MMQ>(a, di.sm_count, di.max_smem_optin, st);
+    case GSQ_TYPE_IQ3_S:
+      if (!packed || rows % 16 != 0) return MMV_DECLINED;
+      return x_layout == XL_Q81 ? mmv_launch_n<MK_IQ3S, XL_Q81>(a, di.sm_count, di.max_smem_optin, st)
+                                : mmv_launch_n<MK_IQ3S, XL_MMQ>(a, di.sm_count, di.max_smem_optin, st);
+    default: return MMV_DECLINED;
+  }
+}
+
+}  // namespace gsq
+
+extern "C" int gsq_debug_mmv_mode(int mode) {
+  const int old = gsq::g_mmv_mode;
+  gsq::g_mmv_mode = mode == 1 ? 1 : 0;
+  return old;
+}
+
+extern "C" int gsq_debug_mmv_min_rows(int n) {
+  const int old = gsq::g_mmv_min_rows;
+  gsq::g_mmv_min_rows = n < 1 ? 1 : n;
+  return old;
+}
+
+extern "C" int gsq_debug_mmv_max_rows(int n) {
+  const int old = gsq::g_mmv_max_rows;
+  gsq::g_mmv_max_rows = n > 48 ? 48 : n;
+  return old;
+}
+
+extern "C" int gsq_mul_mat_vec_max_rows(int ggml_type, int packed) {
+  return gsq::mmv_applies(ggml_type, packed, 16, gsq::g_mmv_max_rows) ? gsq::g_mmv_max_rows : 8;
+}
+
+extern "C" int gsq_debug_mmv_profile(unsigned long long* stamps) {
+  gsq::g_mmv_prof = stamps;
+  return GSQ_OK;
+}
+
+extern "C" int gsq_debug_mmv_cluster_size(int cs) {
+  const int old = gsq::g_mmv_cluster;
+  gsq::g_mmv_cluster = (cs == 1 || cs == 2 || cs == 4 || cs == 8) ? cs : 0;
+  return old;
+}

@@ -117,12 +117,13 @@ def quantize_q8_1_mmq_into(X: torch.Tensor, layout: int, out: torch.Tensor) -> N
 
 
 def _gemv(W, X, type_, row, x_q8, packed, y):
-    """Rows of X in groups of 8 through the dp4a kernel, reading block_q8_1."""
+    """Rows of X, as many per call as the kernel for this type takes (8 or 48), reading block_q8_1."""
     n, k = X.shape
     per_row = k // 32 * 36
     st = _stream(X.device)
-    for i in range(0, n, 8):
-        c = min(8, n - i)
+    step = _lib.gsq_mul_mat_vec_max_rows(type_, int(packed))
+    for i in range(0, n, step):
+        c = min(step, n - i)
         _cabi.check(
             _lib.gsq_mul_mat_vec_q8(W.data_ptr(), W.shape[1], row, type_, int(packed), x_q8.data_ptr() + i * per_row,
                                     c, k, y.data_ptr() + i * y.stride(0) * y.element_size(), _DTYPES[y.dtype],

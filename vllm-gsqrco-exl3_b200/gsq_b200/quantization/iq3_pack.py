@@ -2,15 +2,17 @@
 
 Same role and interface as the reference's quantization/iq3_pack.py (pack_ / pack / unpack, ROWS = 16,
 bijective, in place, tile t keeps the bytes of rows 16t..16t+15), a different layout: the reference's
-is cut for mma.sync fragments, this one for 128-bit coalesced loads and a cheap register decode.
+differs in how the bits of a lane are laid out: this one is cut for 128-bit coalesced loads and a decode of
+shifts, one table load and one byte permute per four values.
 The layout is documented in csrc/gsq_repack.cu; in short, per 16-row x 256-column record (1760 B)
-lane l = 8a + s owns slice s of rows a, a+4, a+8, a+12:
+lane l = 4g + t owns rows g and g + 8 and, of every 32-value slice s, the 4-value groups 2t and 2t + 1;
+its 32 fields are numbered f = 4s + 2h + e (row g + 8h, group 2t + e):
 
-  [0,1152)     9 words per lane (split 4 + 4 + 1 over three planes): 32 nine-bit codebook indices,
-               row i group e at bit 9(8i+e)
-  [1152,1664)  4 words per lane: sign bits of row i, bit 16(e/4)+4p+e%4 = sign of value p of group e
-  [1664,1728)  2 bytes per lane: nibble i = sub-scale of row i
-  [1728,1760)  fp16 d of row a+4i at halfword 4a+i
+  [0,1152)     9 words per lane (split 4 + 4 + 1 over three planes): the 32 nine-bit codebook indices,
+               field f at bit 9f
+  [1152,1664)  4 words per lane: word f/8, bit 16((f%8)/4) + 4p + f%4 = sign of value p of field f
+  [1664,1728)  8 bytes per g: the 4 sub-scale bytes of row g, then of row g + 8
+  [1728,1760)  4 bytes per g: fp16 d of row g, then of row g + 8
 
 CUDA tensors are repacked by gsq_iq3s_repack (one thread block per tile, staged in shared memory, no
 scratch); CPU tensors by the torch-op formulation below, which also serves as the layout's
@@ -40,39 +42,42 @@ def _bits(x: torch.Tensor, n: int) -> torch.Tensor:
     return (x.unsqueeze(-1) >> torch.arange(n, device=x.device)) & 1
 
 
+def _le(x: torch.Tensor, nbytes: int) -> torch.Tensor:
+    """integer tensor -> its little-endian bytes as a new last axis"""
+    return ((x.unsqueeze(-1) >> (8 * torch.arange(nbytes, device=x.device))) & 0xFF).to(torch.uint8)
+
+
+def _word(x: torch.Tensor, nbytes: int) -> torch.Tensor:
+    """[..., n * nbytes] bytes -> [..., n] little-endian integers"""
+    x = x.reshape(*x.shape[:-1], -1, nbytes)
+    return (x << (8 * torch.arange(nbytes, device=x.device))).sum(-1)
+
+
 def _pack_tiles(w: torch.Tensor) -> torch.Tensor:
     rows, rb = w.shape
     nb = rb // BS
     t = rows // ROWS
-    # [tile, block, i, a, byte]: row = 4 i + a
-    b = w.reshape(t, 4, 4, nb, BS).permute(0, 3, 1, 2, 4).to(torch.int64)
-    qs = b[..., 2:66].reshape(t, nb, 4, 4, 8, 8)                      # i a s e
-    qh = _bits(b[..., 66:74], 8)                                     # i a s e
-    field = qs | (qh << 8)                                           # 9-bit index of (i, a, s, e)
-    # 288-bit stream per lane (a, s): field (i, e) at bit 9 (8 i + e)
-    fbits = _bits(field, 9).permute(0, 1, 3, 4, 2, 5, 6).reshape(t, nb, 32, 288)   # lane, bit
-    words = (fbits.reshape(t, nb, 32, 9, 32) << torch.arange(32, device=w.device)).sum(-1)   # lane, word
-    sg = b[..., 74:106].reshape(t, nb, 4, 4, 8, 4)                   # i a s byte
-    sgbits = _bits(sg, 8).reshape(t, nb, 4, 4, 8, 2, 4, 4)           # i a s h e' p   (bit 4e+p of the slice word, e = 4h+e')
-    spread = sgbits.permute(0, 1, 2, 3, 4, 5, 7, 6).reshape(t, nb, 4, 4, 8, 32)    # bit 16h + 4p + e'
-    sgw = (spread << torch.arange(32, device=w.device)).sum(-1)      # i a s
-    sgw = sgw.permute(0, 1, 3, 4, 2)                                 # a s i
-    sc = b[..., 106:110]                                             # i a byte
-    nib = torch.stack([sc & 15, sc >> 4], -1).reshape(t, nb, 4, 4, 8)               # i a s
-    scw = (nib.permute(0, 1, 3, 4, 2) << (4 * torch.arange(4, device=w.device))).sum(-1)   # a s
-    d = b[..., 0] | (b[..., 1] << 8)                                 # i a
-    d = d.permute(0, 1, 3, 2)                                        # a i
-
-    def le(x, nbytes):  # integer tensor -> little-endian bytes appended as a last axis
-        return ((x.unsqueeze(-1) >> (8 * torch.arange(nbytes, device=w.device))) & 0xFF).to(torch.uint8)
-
-    out = torch.empty(t, nb, REC, dtype=torch.uint8, device=w.device)
-    out[..., 0:512] = le(words[..., 0:4], 4).reshape(t, nb, 512)
-    out[..., 512:1024] = le(words[..., 4:8], 4).reshape(t, nb, 512)
-    out[..., 1024:1152] = le(words[..., 8], 4).reshape(t, nb, 128)
-    out[..., 1152:1664] = le(sgw, 4).reshape(t, nb, 512)
-    out[..., 1664:1728] = le(scw, 2).reshape(t, nb, 64)
-    out[..., 1728:1760] = le(d, 2).reshape(t, nb, 32)
+    dev = w.device
+    # [tile, block, h, g, byte]: row = 8 h + g
+    b = w.reshape(t, 2, 8, nb, BS).permute(0, 3, 1, 2, 4).to(torch.int64)
+    qs = b[..., 2:66].reshape(t, nb, 2, 8, 8, 4, 2)                   # h g s t e   (group 2t + e of slice s)
+    qh = _bits(b[..., 66:74], 8).reshape(t, nb, 2, 8, 8, 4, 2)        # h g s t e
+    field = (qs | (qh << 8)).permute(0, 1, 3, 5, 4, 2, 6)             # g t s h e: lane 4g + t, field 4s + 2h + e
+    fbits = _bits(field.reshape(t, nb, 32, 32), 9).reshape(t, nb, 32, 288)
+    words = (fbits.reshape(t, nb, 32, 9, 32) << torch.arange(32, device=dev)).sum(-1)     # lane, word
+    # sign bits: GGUF bit 4 (2t + e) + p of the slice's 32-bit word
+    sg = _bits(b[..., 74:106], 8).reshape(t, nb, 2, 8, 8, 4, 2, 4)    # h g s t e p
+    sg = sg.permute(0, 1, 3, 5, 4, 2, 6, 7).reshape(t, nb, 32, 4, 2, 4, 4)     # lane, word f/8, (f%8)/4, f%4, p
+    sgw = (sg.permute(0, 1, 2, 3, 4, 6, 5).reshape(t, nb, 32, 4, 32) << torch.arange(32, device=dev)).sum(-1)
+    sc = b[..., 106:110].permute(0, 1, 3, 2, 4)                       # g h byte
+    d = b[..., 0:2].permute(0, 1, 3, 2, 4)                            # g h byte
+    out = torch.empty(t, nb, REC, dtype=torch.uint8, device=dev)
+    out[..., 0:512] = _le(words[..., 0:4], 4).reshape(t, nb, 512)
+    out[..., 512:1024] = _le(words[..., 4:8], 4).reshape(t, nb, 512)
+    out[..., 1024:1152] = _le(words[..., 8], 4).reshape(t, nb, 128)
+    out[..., 1152:1664] = _le(sgw, 4).reshape(t, nb, 512)
+    out[..., 1664:1728] = sc.reshape(t, nb, 64).to(torch.uint8)
+    out[..., 1728:1760] = d.reshape(t, nb, 32).to(torch.uint8)
     return out.reshape(rows, rb)
 
 
@@ -80,31 +85,23 @@ def _unpack_tiles(p: torch.Tensor) -> torch.Tensor:
     rows, rb = p.shape
     nb = rb // BS
     t = rows // ROWS
+    dev = p.device
     r = p.reshape(t, nb, REC).to(torch.int64)
-
-    def word(x, nbytes):  # [..., n * nbytes] bytes -> [..., n] little-endian integers
-        x = x.reshape(*x.shape[:-1], -1, nbytes)
-        return (x << (8 * torch.arange(nbytes, device=p.device))).sum(-1)
-
-    words = torch.cat([word(r[..., 0:512], 4).reshape(t, nb, 32, 4), word(r[..., 512:1024], 4).reshape(t, nb, 32, 4),
-                       word(r[..., 1024:1152], 4).reshape(t, nb, 32, 1)], -1)       # lane, 9
-    fbits = _bits(words, 32).reshape(t, nb, 4, 8, 4, 8, 9)                          # a s i e bit
-    field = (fbits << torch.arange(9, device=p.device)).sum(-1)                    # a s i e
-    field = field.permute(0, 1, 4, 2, 3, 5)                                         # i a s e
+    words = torch.cat([_word(r[..., 0:512], 4).reshape(t, nb, 32, 4), _word(r[..., 512:1024], 4).reshape(t, nb, 32, 4),
+                       _word(r[..., 1024:1152], 4).reshape(t, nb, 32, 1)], -1)      # lane, 9
+    fbits = _bits(words, 32).reshape(t, nb, 32, 32, 9)                              # lane, field, bit
+    field = (fbits << torch.arange(9, device=dev)).sum(-1).reshape(t, nb, 8, 4, 8, 2, 2)   # g t s h e
+    field = field.permute(0, 1, 5, 2, 4, 3, 6).reshape(t, nb, 2, 8, 8, 8)           # h g s e8
     qs = field & 0xFF
-    qh = ((field >> 8) << torch.arange(8, device=p.device)).sum(-1)                 # i a s
-    sgw = word(r[..., 1152:1664], 4).reshape(t, nb, 4, 8, 4)                        # a s i
-    sbits = _bits(sgw, 32).reshape(t, nb, 4, 8, 4, 2, 4, 4)                         # a s i h p e'
-    gg = sbits.permute(0, 1, 2, 3, 4, 5, 7, 6).reshape(t, nb, 4, 8, 4, 4, 8)        # a s i byte bit (bit 4e+p)
-    sg = (gg << torch.arange(8, device=p.device)).sum(-1)                           # a s i byte
-    sg = sg.permute(0, 1, 4, 2, 3, 5)                                               # i a s byte
-    scw = word(r[..., 1664:1728], 2).reshape(t, nb, 4, 8)                           # a s
-    nib = (scw.unsqueeze(-1) >> (4 * torch.arange(4, device=p.device))) & 15        # a s i
-    nib = nib.permute(0, 1, 4, 2, 3)                                                # i a s
-    sc = nib[..., 0::2] | (nib[..., 1::2] << 4)                                     # i a byte
-    d = word(r[..., 1728:1760], 2).reshape(t, nb, 4, 4).permute(0, 1, 3, 2)         # i a
-    blocks = torch.cat([(d & 0xFF).unsqueeze(-1), (d >> 8).unsqueeze(-1), qs.reshape(t, nb, 4, 4, 64), qh,
-                        sg.reshape(t, nb, 4, 4, 32), sc], -1)                       # i a 110
+    qh = ((field >> 8) << torch.arange(8, device=dev)).sum(-1)                      # h g s
+    sgw = _word(r[..., 1152:1664], 4).reshape(t, nb, 32, 4)                         # lane, word
+    sb = _bits(sgw, 32).reshape(t, nb, 8, 4, 4, 2, 4, 4)                            # g t word fh p fl
+    sb = sb.permute(0, 1, 2, 3, 4, 5, 7, 6).reshape(t, nb, 8, 4, 8, 2, 2, 4)        # g t (f = s h e) p
+    sb = sb.permute(0, 1, 5, 2, 4, 3, 6, 7).reshape(t, nb, 2, 8, 8, 4, 8)           # h g s byte bit (bit 4 e8 + p)
+    sg = (sb << torch.arange(8, device=dev)).sum(-1)                                # h g s byte
+    sc = r[..., 1664:1728].reshape(t, nb, 8, 2, 4).permute(0, 1, 3, 2, 4)           # h g byte
+    d = r[..., 1728:1760].reshape(t, nb, 8, 2, 2).permute(0, 1, 3, 2, 4)            # h g byte
+    blocks = torch.cat([d, qs.reshape(t, nb, 2, 8, 64), qh, sg.reshape(t, nb, 2, 8, 32), sc], -1)   # h g 110
     return blocks.permute(0, 2, 3, 1, 4).reshape(rows, rb).to(torch.uint8)
 
 
