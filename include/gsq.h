@@ -196,7 +196,7 @@ int gsq_debug_gemm_ksplit(int ks); /* 0 = choose; 1, 2, 4 = CTAs per cluster tha
 /* The register-operand tensor-core kernel that serves 1..48 activation rows behind gsq_mul_mat_vec_q8 and
  * gsq_mul_mat_q8 (experiments and tests; each returns the previous value). */
 int gsq_debug_mmv_mode(int mode);        /* 0 = wherever it applies (default), 1 = never: dp4a GEMV / tcgen05 GEMM */
-int gsq_debug_mmv_min_rows(int n);       /* fewest activation rows it serves (default 1) */
+int gsq_debug_mmv_min_rows(int n);       /* fewest activation rows it serves; 0 = per type (default) */
 int gsq_debug_mmv_max_rows(int n);       /* most activation rows it serves (default 24, at most 48) */
 int gsq_debug_mmv_cluster_size(int cs);  /* 0 = choose; 1, 2, 4, 8 = CTAs per cluster */
 /* device buffer of 8 uint64 per CTA that receives time stamps (ns) at the kernel's phase boundaries, or NULL */

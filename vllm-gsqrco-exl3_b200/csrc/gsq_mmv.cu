@@ -153,7 +153,12 @@ __device__ __forceinline__ void stage_x_pad(int m, int nkb, int colb, uint8_t* x
 // 16-byte granules (K is a multiple of 128); every granule is loaded exactly once, by consecutive threads, and
 // its four words go where their position in the 9-word blocks says: word 0 of a block is (d, sum), the other
 // eight are quants. All 148 CTAs read the same few KB at the same time, so requests per byte are what counts.
-template <int MC, bool DS, typename AfterIssue>
+// slot of quant word w in a staged 32-byte block. PERM: words (t, t + 4) side by side for the kinds whose 4-byte
+// weight word holds values 4t..4t+3 in its low and 16+4t..16+4t+3 in its high nibbles (IQ4_XS).
+template <bool PERM>
+__device__ __forceinline__ int x_slot(int w) { return PERM ? ((w & 3) << 1) | (w >> 2) : w; }
+
+template <int MC, bool DS, bool PERM, typename AfterIssue>
 __device__ __forceinline__ void stage_x_q81(const MmvArgs& a, int kb0, int nkb, int colb, uint8_t* xq, float* xd, float* xs,
                                             int tid, AfterIssue after_issue) {
   const int nb32 = a.k >> 5;
@@ -187,7 +192,7 @@ __device__ __forceinline__ void stage_x_q81(const MmvArgs& a, int kb0, int nkb, 
           if (pos == 0) {
             xd[kb * MC + col[u]] = h2f(w[e]);
           } else {
-            *reinterpret_cast<uint32_t*>(xq + col[u] * colb + kb * 32 + (pos - 1) * 4) = w[e];
+            *reinterpret_cast<uint32_t*>(xq + col[u] * colb + kb * 32 + x_slot<PERM>(pos - 1) * 4) = w[e];
           }
         }
       }
@@ -217,7 +222,7 @@ __device__ __forceinline__ void stage_x_q81(const MmvArgs& a, int kb0, int nkb, 
 // block_q8_1_mmq source (144-byte blocks, [K/128][column]: 16 scale bytes = 4 x half2(d, sum) (DS) or 4 x float
 // d, then 128 int8): the stored sums are used as they are, as the reference's MMQ does. The CTA's share is one
 // contiguous run of 16-byte pieces, 9 per block.
-template <int MC, bool DS, typename AfterIssue>
+template <int MC, bool DS, bool PERM, typename AfterIssue>
 __device__ __forceinline__ void stage_x_mmq(const MmvArgs& a, int kb0, int nkb, int colb, uint8_t* xq, float* xd, float* xs,
                                             int tid, AfterIssue after_issue) {
   const int per = a.m * 9, total = (nkb >> 2) * per;
@@ -246,7 +251,16 @@ __device__ __forceinline__ void stage_x_mmq(const MmvArgs& a, int kb0, int nkb, 
           }
         } else {
           const int kb = 4 * b + ((part - 1) >> 1);
-          *reinterpret_cast<uint4*>(xq + col * colb + kb * 32 + ((part - 1) & 1) * 16) = v[u];
+          uint8_t* dst = xq + col * colb + kb * 32;
+          if (PERM) {
+            const int w0 = ((part - 1) & 1) * 4;
+            *reinterpret_cast<uint32_t*>(dst + x_slot<true>(w0) * 4) = v[u].x;
+            *reinterpret_cast<uint32_t*>(dst + x_slot<true>(w0 + 1) * 4) = v[u].y;
+            *reinterpret_cast<uint32_t*>(dst + x_slot<true>(w0 + 2) * 4) = v[u].z;
+            *reinterpret_cast<uint32_t*>(dst + x_slot<true>(w0 + 3) * 4) = v[u].w;
+          } else {
+            *reinterpret_cast<uint4*>(dst + ((part - 1) & 1) * 16) = v[u];
+          }
         }
       }
     }
@@ -494,6 +508,108 @@ __device__ __forceinline__ void process(const RecIQ3S& r, const MmvArgs& ar, int
 }
 
 // ---------------------------------------------------------------------------------------------
+// IQ4_XS (136-byte blocks as stored: fp16 d, 16 bits of scale high parts, 4 bytes of scale low nibbles, 128
+// bytes of 4-bit indices into a 16-entry table). Lane (g, t) takes word t of each 16-byte slice of rows g and
+// g + 8: its low nibbles are values 4t..4t+3 (fragment words a0 / a1), its high nibbles 16+4t..16+4t+3 (a2 / a3);
+// the activations are staged with words t and t + 4 side by side to match.
+
+__constant__ __align__(16) int8_t c_iq4nl_mmv[16] = GSQ_IQ4NL_VALUES_INIT;
+
+struct RecIQ4XS {
+  uint2 hdr[2];
+  uint32_t q[2][8];
+  __device__ __forceinline__ void load(const MmvArgs& a, int row0, int sb, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = min(row0 + g + 8 * h, a.nrows - 1);
+      const uint8_t* b = a.w + (int64_t)r * a.row_bytes + (int64_t)sb * 136;
+      hdr[h] = ldg_stream_v2(b);
+#pragma unroll
+      for (int s = 0; s < 8; ++s) q[h][s] = __ldg(reinterpret_cast<const uint32_t*>(b + 8 + 16 * s + 4 * t));
+    }
+  }
+  static __device__ __forceinline__ void prefetch(const MmvArgs& a, int row0, int sb, int lane) {
+    const int r = min(row0 + (lane >> 1), a.nrows - 1);
+    const uint8_t* b = a.w + (int64_t)r * a.row_bytes + (int64_t)sb * 136 + (lane & 1) * 135;
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(b));
+  }
+};
+
+// 8 four-bit indices of v -> the table bytes: lo = entries of the 4 low nibbles, hi = of the 4 high nibbles
+__device__ __forceinline__ void iq4_lookup_mmv(uint32_t v, const uint32_t (&tb)[4], uint32_t& lo, uint32_t& hi) {
+  const uint32_t s01 = v & 0x7777u, s23 = (v >> 16) & 0x7777u;
+  const uint32_t pick01 = 0x3210u | ((v & 0x8888u) >> 1), pick23 = 0x3210u | (((v >> 16) & 0x8888u) >> 1);
+  const uint32_t r01 = mprmt(mprmt(tb[0], tb[1], s01), mprmt(tb[2], tb[3], s01), pick01);  // nibbles 0..3 of v
+  const uint32_t r23 = mprmt(mprmt(tb[0], tb[1], s23), mprmt(tb[2], tb[3], s23), pick23);  // nibbles 4..7 of v
+  lo = mprmt(r01, r23, 0x6420u);
+  hi = mprmt(r01, r23, 0x7531u);
+}
+
+template <int NTL, bool DUMP>
+__device__ __forceinline__ void process(const RecIQ4XS& r, const MmvArgs& ar, int row0, int sb, int lane, const XSmem& xl,
+                                        const uint8_t*, uint64_t (&acc)[NTL][2]) {
+  constexpr int MC = 8 * NTL;
+  constexpr bool DEFER = NTL <= 2;
+  const uint32_t* tw = reinterpret_cast<const uint32_t*>(c_iq4nl_mmv);
+  const uint32_t tb[4] = {tw[0], tw[1], tw[2], tw[3]};
+  uint64_t d2[2];
+  uint32_t sh4[2];  // the 2-bit high parts, pre-shifted to bits 4, 5
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float d = h2f(r.hdr[h].x);
+    d2[h] = pk2(d, d);
+    sh4[h] = (r.hdr[h].x >> 16) << 4;
+  }
+  uint64_t tt[NTL][2];
+  if constexpr (DEFER) {
+#pragma unroll
+    for (int j = 0; j < NTL; ++j) tt[j][0] = tt[j][1] = 0ull;
+  }
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    uint32_t a[4];
+    iq4_lookup_mmv(r.q[0][s], tb, a[0], a[2]);
+    iq4_lookup_mmv(r.q[1][s], tb, a[1], a[3]);
+    // 6-bit sub-scale minus 32: low nibble from scales_l, bits 4, 5 from scales_h
+    const int sc0 = (int)(((r.hdr[0].y >> (4 * s)) & 0xFu) | ((sh4[0] >> (2 * s)) & 0x30u)) - 32;
+    const int sc1 = (int)(((r.hdr[1].y >> (4 * s)) & 0xFu) | ((sh4[1] >> (2 * s)) & 0x30u)) - 32;
+#pragma unroll
+    for (int j = 0; j < NTL; ++j) {
+      const uint2 b = *reinterpret_cast<const uint2*>(xl.q + j * xl.q8 + s * 32);
+      const uint64_t dv2 = *reinterpret_cast<const uint64_t*>(xl.d + s * MC + 8 * j);
+      int c[4];
+      mma_s8(c, a, b.x, b.y, 0);
+      if constexpr (DUMP) {
+        const int g = lane >> 2, t = lane & 3, col0 = 8 * j + 2 * t, nb32 = ar.k >> 5;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int row = row0 + g + 8 * (e >> 1), col = col0 + (e & 1);
+          if (row < ar.nrows && col < ar.m) ar.dump[((int64_t)col * ar.nrows + row) * nb32 + sb * 8 + s] = c[e];
+        }
+      }
+      // |c * scale| <= 32 * 127 * 127 * 32 < 2^24: the conversion is exact
+      const uint64_t f01 = pk2(__int2float_rn(c[0] * sc0), __int2float_rn(c[1] * sc0));
+      const uint64_t f23 = pk2(__int2float_rn(c[2] * sc1), __int2float_rn(c[3] * sc1));
+      if constexpr (DEFER) {
+        tt[j][0] = vfma2(f01, dv2, tt[j][0]);
+        tt[j][1] = vfma2(f23, dv2, tt[j][1]);
+      } else {
+        acc[j][0] = vfma2(f01, vmul2(dv2, d2[0]), acc[j][0]);
+        acc[j][1] = vfma2(f23, vmul2(dv2, d2[1]), acc[j][1]);
+      }
+    }
+  }
+  if constexpr (DEFER) {
+#pragma unroll
+    for (int j = 0; j < NTL; ++j) {
+      acc[j][0] = vfma2(d2[0], tt[j][0], acc[j][0]);
+      acc[j][1] = vfma2(d2[1], tt[j][1], acc[j][1]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // The kernel.
 
 template <int KIND>
@@ -503,12 +619,21 @@ struct MmvKind<MK_Q4K> {
   using Rec = RecQ4K;
   static constexpr bool DS = true;       // activations carry sums (for the min term)
   static constexpr int GRID = 0;         // bytes of codebook copy in shared memory
+  static constexpr bool PERM = false;    // staged quant words in the order 0 4 1 5 2 6 3 7
 };
 template <>
 struct MmvKind<MK_IQ3S> {
   using Rec = RecIQ3S;
   static constexpr bool DS = false;
   static constexpr int GRID = 65536;
+  static constexpr bool PERM = false;
+};
+template <>
+struct MmvKind<MK_IQ4XS> {
+  using Rec = RecIQ4XS;
+  static constexpr bool DS = false;
+  static constexpr int GRID = 0;
+  static constexpr bool PERM = true;
 };
 
 // bytes of staged activations per 32-value block and padded column
@@ -583,9 +708,9 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
     }
   };
   if (XL == XL_Q81) {
-    stage_x_q81<MC, DS>(a, sb0 * 8, nkb, colb, xq, xd, xs, tid, prefetch_first);
+    stage_x_q81<MC, DS, MmvKind<KIND>::PERM>(a, sb0 * 8, nkb, colb, xq, xd, xs, tid, prefetch_first);
   } else {
-    stage_x_mmq<MC, DS>(a, sb0 * 8, nkb, colb, xq, xd, xs, tid, prefetch_first);
+    stage_x_mmq<MC, DS, MmvKind<KIND>::PERM>(a, sb0 * 8, nkb, colb, xq, xd, xs, tid, prefetch_first);
   }
   if (GRID) {
     // one global load per thread (512 threads, 512 entries), then the 16 replicas of its (g, -g) pair; no byte
@@ -703,7 +828,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
 // Host side.
 
 static int g_mmv_mode = 0;      // 0 = use this kernel wherever it applies, 1 = never (the older kernels)
-static int g_mmv_min_rows = 1;  // fewest activation rows served here (experiments)
+static int g_mmv_min_rows = 0;  // fewest activation rows served here; 0 = per type (see mmv_applies)
 static int g_mmv_max_rows = 24; // most
 static int g_mmv_cluster = 0;   // experiments: 0 = choose, else 1, 2, 4 or 8
 static unsigned long long* g_mmv_prof = nullptr;
@@ -849,8 +974,20 @@ static int mmv_launch_n(const MmvArgs& a, int sm_count, int max_smem, cudaStream
 
 // Whether (type, packed, m) may be served here (mmv_host can still decline a shape: MMV_DECLINED).
 bool mmv_applies(int ggml_type, int packed, int64_t rows, int64_t m) {
-  if (g_mmv_mode == 1 || m < g_mmv_min_rows || m > g_mmv_max_rows) return false;
-  return ggml_type == GSQ_TYPE_Q4_K || (ggml_type == GSQ_TYPE_IQ3_S && packed && rows % 16 == 0);
+  if (g_mmv_mode == 1 || m > g_mmv_max_rows) return false;
+  // Below these row counts the dp4a GEMV is faster on the measured shapes (its start-up is shorter: no staging of
+  // the activations, no cluster-wide sum); packed IQ3_S has no faster kernel at any count.
+  int min_rows;
+  switch (ggml_type) {
+    case GSQ_TYPE_Q4_K: min_rows = 2; break;
+    case GSQ_TYPE_IQ4_XS: min_rows = 4; break;
+    case GSQ_TYPE_IQ3_S:
+      if (!packed || rows % 16 != 0) return false;
+      min_rows = 1;
+      break;
+    default: return false;
+  }
+  return m >= (g_mmv_min_rows > 0 ? g_mmv_min_rows : min_rows);
 }
 
 // x_layout: 0 = block_q8_1, 1 = block_q8_1_mmq. Returns MMV_DECLINED when the shape does not fit.
@@ -886,6 +1023,9 @@ int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int 
     case GSQ_TYPE_Q4_K:
       return x_layout == XL_Q81 ? mmv_launch_n<MK_Q4K, XL_Q81>(a, di.sm_count, di.max_smem_optin, st)
                                 : mmv_launch_n<MK_Q4K, XL_MMQ>(a, di.sm_count, di.max_smem_optin, st);
+    case GSQ_TYPE_IQ4_XS:
+      return x_layout == XL_Q81 ? mmv_launch_n<MK_IQ4XS, XL_Q81>(a, di.sm_count, di.max_smem_optin, st)
+                                : mmv_launch_n<MK_IQ4XS, XL_MMQ>(a, di.sm_count, di.max_smem_optin, st);
     case GSQ_TYPE_IQ3_S:
       if (!packed || rows % 16 != 0) return MMV_DECLINED;
       return x_layout == XL_Q81 ? mmv_launch_n<MK_IQ3S, XL_Q81>(a, di.sm_count, di.max_smem_optin, st)
@@ -904,7 +1044,7 @@ extern "C" int gsq_debug_mmv_mode(int mode) {
 
 extern "C" int gsq_debug_mmv_min_rows(int n) {
   const int old = gsq::g_mmv_min_rows;
-  gsq::g_mmv_min_rows = n < 1 ? 1 : n;
+  gsq::g_mmv_min_rows = n < 0 ? 0 : n;
   return old;
 }
 
