@@ -1,4 +1,4 @@
-// Register-operand int8 tensor-core product for 1..48 activation rows over GGUF superblocks (sm_100a).
+// Register-operand int8 tensor-core product for 1..32 activation rows over GGUF superblocks (sm_100a).
 //
 // Serves, behind gsq_mul_mat_vec_q8 and gsq_mul_mat_q8, the row counts at which the product is a stream of
 // W with a little arithmetic per byte: the reference's owned 1..8-row kernels (lcpp_owned_k4.cu:116-234,
@@ -16,13 +16,18 @@
 //     and g + 8 and, of every 32-value slice, the 4-value words 2t and 2t + 1 (Q4_K, IQ3_S) or word t of each
 //     half (IQ4_XS): exactly its share of the m16n8k32 A fragment. The k index inside a slice is permuted the
 //     same way on the activation side, which an integer sum does not see.
-//   * Activations are read where they lie through L1: block_q8_1 (36 bytes) for the vec ops, block_q8_1_mmq
-//     (144 bytes, [K/128][M]) for the ops that quantise for themselves. Columns past M repeat column M - 1
-//     and are never stored.
-//   * Work split, partial sums and the final reduction are those of the dp4a GEMV (gsq_gemv.cu): clusters
-//     own contiguous ranges of 16-row tiles, the records of a range are cut into equal contiguous chunks, one
-//     per warp; a warp leaving a tile parks its partial sums in shared memory and after one cluster barrier
-//     every output element is added in warp order through distributed shared memory. No atomics, no scratch.
+//   * A cluster of 1, 2, 4 or 8 CTAs owns a contiguous range of 16-row tiles; its CTAs split K. Each CTA first
+//     stages its K range of the activations in shared memory, in fragment order and with the scales as fp32
+//     (from block_q8_1, 36 bytes, for the vec ops; from block_q8_1_mmq, 144 bytes, [K/128][M], for the ops that
+//     quantise for themselves). Columns past M are zeros. The cluster size is the one with the least estimated
+//     time among those whose staging area fits.
+//   * The records (tile, superblock) of a CTA, in memory order, are cut into equal contiguous chunks, one per
+//     warp, so every warp streams the same number of bytes whatever the shape. A warp reads a record with
+//     128-bit no-allocate loads, one record ahead of the arithmetic; there is no block-wide barrier in the loop.
+//   * A tile a warp covers whole goes straight to the CTA's tile sums; the tile a chunk starts inside and the
+//     one it ends inside are parked and added in warp order after one block barrier. After one cluster barrier
+//     the CTAs' tile sums (one per K part) are added in rank order through distributed shared memory and stored
+//     in Y's dtype. No atomics, no global scratch, the same order every run.
 #include <cooperative_groups.h>
 
 #include "gsq_common.cuh"
@@ -53,7 +58,6 @@ struct MmvArgs {
   int tiles_base;    // tiles per cluster: the first tiles_extra clusters own tiles_base + 1
   int tiles_extra;
   int tiles_round;   // tiles a cluster takes per round
-  int seg_cap;       // tiles one warp's chunk may touch in a round
   int xcap_kb;       // 32-value blocks of activations the shared-memory staging area holds per column
   int* dump;         // debug: int32 slice sums [m][nrows][k / 32]
   // fast_div_inv of: 16-byte granules and 36-byte blocks per staged column, for a CTA with nsr_lo superblocks
@@ -391,6 +395,10 @@ __device__ __forceinline__ void process(const RecQ4K& r, const MmvArgs& ar, int 
 
 __device__ const uint32_t g_iq3s_grid_mmv[512] = GSQ_IQ3S_GRID_INIT;
 
+// 16 replicas (64 KB) keep the lookups free of bank conflicts; from 25 activation rows on the staged activations
+// need the room and 8 replicas (32 KB, two lanes per replica) are used
+__host__ __device__ constexpr int iq3_replica_shift(int ntl) { return ntl >= 4 ? 3 : 4; }
+
 struct RecIQ3S {
   uint32_t idx[9], sg[4];
   uint2 sc;      // sub-scale nibbles of rows g, g + 8
@@ -413,16 +421,17 @@ struct RecIQ3S {
   }
 };
 
-template <int F>
+// RS: log2 of the codebook replicas in shared memory (entry i of replica r at byte (8 << RS) i + 8 r)
+template <int F, int RS>
 __device__ __forceinline__ uint32_t iq3_field(const RecIQ3S& r, const char* gbase, uint32_t lane_off) {
-  constexpr int bit = 9 * F, word = bit >> 5, off = bit & 31;
+  constexpr int bit = 9 * F, word = bit >> 5, off = bit & 31, P = 3 + RS;  // the index goes to bits P .. P + 8
   uint32_t t;
   if (off + 9 <= 32) {
-    t = off >= 7 ? r.idx[word] >> (off - 7) : r.idx[word] << (7 - off);
+    t = off >= P ? r.idx[word] >> (off >= P ? off - P : 0) : r.idx[word] << (off < P ? P - off : 0);
   } else {
-    t = __funnelshift_r(r.idx[word], r.idx[word + 1], off - 7);
+    t = __funnelshift_r(r.idx[word], r.idx[word + 1], off - P);
   }
-  const uint2 gp = *reinterpret_cast<const uint2*>(gbase + ((t & 0xFF80u) | lane_off));
+  const uint2 gp = *reinterpret_cast<const uint2*>(gbase + ((t & (0x1FFu << P)) | lane_off));
   constexpr int fl = F & 7, sh = 16 * (fl >> 2) + (fl & 3) - 2;
   const uint32_t sgs = sh >= 0 ? r.sg[F >> 3] >> (sh >= 0 ? sh : 0) : r.sg[F >> 3] << (sh < 0 ? -sh : 0);
   return mprmt(gp.x, gp.y, (sgs & 0x4444u) | 0x3210u);
@@ -435,10 +444,11 @@ __device__ __forceinline__ void iq3_slice(const RecIQ3S& r, const MmvArgs& ar, i
   constexpr int MC = 8 * NTL;
   constexpr bool DEFER = NTL <= 2;
   uint32_t a[4];
-  a[0] = iq3_field<4 * S + 0>(r, gbase, lane_off);   // (row g, group 2t)
-  a[1] = iq3_field<4 * S + 2>(r, gbase, lane_off);   // (row g + 8, group 2t)
-  a[2] = iq3_field<4 * S + 1>(r, gbase, lane_off);   // (row g, group 2t + 1)
-  a[3] = iq3_field<4 * S + 3>(r, gbase, lane_off);   // (row g + 8, group 2t + 1)
+  constexpr int RS = iq3_replica_shift(NTL);
+  a[0] = iq3_field<4 * S + 0, RS>(r, gbase, lane_off);   // (row g, group 2t)
+  a[1] = iq3_field<4 * S + 2, RS>(r, gbase, lane_off);   // (row g + 8, group 2t)
+  a[2] = iq3_field<4 * S + 1, RS>(r, gbase, lane_off);   // (row g, group 2t + 1)
+  a[3] = iq3_field<4 * S + 3, RS>(r, gbase, lane_off);   // (row g + 8, group 2t + 1)
   // 2 * nibble + 1 of slice S: byte S / 2 of the even- or odd-slice word
   const int sc0 = (int)((iscw[0][S & 1] >> (8 * (S >> 1))) & 0xFFu), sc1 = (int)((iscw[1][S & 1] >> (8 * (S >> 1))) & 0xFFu);
   const uint64_t nm2 = pk2(-MAGIC_F, -MAGIC_F);
@@ -474,7 +484,7 @@ __device__ __forceinline__ void process(const RecIQ3S& r, const MmvArgs& ar, int
                                         const uint8_t* grid, uint64_t (&acc)[NTL][2]) {
   constexpr bool DEFER = NTL <= 2;
   const char* gbase = reinterpret_cast<const char*>(grid);
-  const uint32_t lane_off = (uint32_t)(lane & 15) << 3;
+  const uint32_t lane_off = (uint32_t)(lane & ((1 << iq3_replica_shift(NTL)) - 1)) << 3;
   uint32_t iscw[2][2];  // [row half][even / odd slices]: bytes 2 * nibble + 1
   uint64_t d2[2];
 #pragma unroll
@@ -618,21 +628,21 @@ template <>
 struct MmvKind<MK_Q4K> {
   using Rec = RecQ4K;
   static constexpr bool DS = true;       // activations carry sums (for the min term)
-  static constexpr int GRID = 0;         // bytes of codebook copy in shared memory
+  static constexpr int grid_bytes(int) { return 0; }   // codebook copy in shared memory
   static constexpr bool PERM = false;    // staged quant words in the order 0 4 1 5 2 6 3 7
 };
 template <>
 struct MmvKind<MK_IQ3S> {
   using Rec = RecIQ3S;
   static constexpr bool DS = false;
-  static constexpr int GRID = 65536;
+  static constexpr int grid_bytes(int ntl) { return 512 * (8 << iq3_replica_shift(ntl)); }
   static constexpr bool PERM = false;
 };
 template <>
 struct MmvKind<MK_IQ4XS> {
   using Rec = RecIQ4XS;
   static constexpr bool DS = false;
-  static constexpr int GRID = 0;
+  static constexpr int grid_bytes(int) { return 0; }
   static constexpr bool PERM = true;
 };
 
@@ -641,9 +651,9 @@ __host__ __device__ constexpr size_t mmv_x_bytes(int cap_kb, int mc, bool ds) {
   return (size_t)mc * mmv_xq_col_bytes(cap_kb) + (size_t)cap_kb * mc * (ds ? 8 : 4);
 }
 
-__host__ __device__ inline size_t mmv_partial_bytes(int mc, int seg_cap) {
-  return (size_t)MMV_WARPS * seg_cap * MMV_TR * mc * 4;
-}
+// a warp parks at most two incomplete tile segments per round: the tile its chunk starts inside and the one
+// it ends inside (tiles it covers whole go straight to the CTA's tile sums)
+__host__ __device__ inline size_t mmv_partial_bytes(int mc) { return (size_t)MMV_WARPS * 2 * MMV_TR * mc * 4; }
 
 // superblocks [first, last) of the K range of CTA `rank` in a cluster of `cs`
 __host__ __device__ inline void mmv_k_range(int nsb, int cs, int rank, int* first, int* last) {
@@ -669,11 +679,11 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
   const int nsr = sb1 - sb0;                 // superblocks of this CTA
   const int nkb = nsr * 8;
 
-  constexpr int GRID = MmvKind<KIND>::GRID;
+  constexpr int GRID = MmvKind<KIND>::grid_bytes(NTL);
   const uint8_t* grid = smem;
   float* partial = reinterpret_cast<float*>(smem + GRID);
-  float* csum = reinterpret_cast<float*>(smem + GRID + mmv_partial_bytes(MC, a.seg_cap));   // [tiles_round][16][MC]
-  uint8_t* xq = smem + GRID + mmv_partial_bytes(MC, a.seg_cap) + (size_t)a.tiles_round * SEGF * 4;
+  float* csum = reinterpret_cast<float*>(smem + GRID + mmv_partial_bytes(MC));   // [tiles_round][16][MC]
+  uint8_t* xq = smem + GRID + mmv_partial_bytes(MC) + (size_t)a.tiles_round * SEGF * 4;
   const int colb = mmv_xq_col_bytes(a.xcap_kb);
   float* xd = reinterpret_cast<float*>(xq + (size_t)colb * MC);
   float* xs = xd + (size_t)a.xcap_kb * MC;
@@ -713,12 +723,12 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
     stage_x_mmq<MC, DS, MmvKind<KIND>::PERM>(a, sb0 * 8, nkb, colb, xq, xd, xs, tid, prefetch_first);
   }
   if (GRID) {
-    // one global load per thread (512 threads, 512 entries), then the 16 replicas of its (g, -g) pair; no byte
+    // one global load per thread (512 threads, 512 entries), then the replicas of its (g, -g) pair; no byte
     // of the codebook is zero, so ~g + 1 per byte never carries
     const uint32_t gv = g_iq3s_grid_mmv[tid & 511];
-    uint4* dst = reinterpret_cast<uint4*>(smem + (tid & 511) * 128);
+    uint4* dst = reinterpret_cast<uint4*>(smem + (tid & 511) * (GRID / 512));
 #pragma unroll
-    for (int r2 = 0; r2 < 8; ++r2) dst[r2] = make_uint4(gv, ~gv + 0x01010101u, gv, ~gv + 0x01010101u);
+    for (int r2 = 0; r2 < GRID / 512 / 16; ++r2) dst[r2] = make_uint4(gv, ~gv + 0x01010101u, gv, ~gv + 0x01010101u);
   }
   __syncthreads();
   mmv_stamp(a, 1);
@@ -735,7 +745,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
     const int rr = tiles_r * nsr;
     const int c = (rr + MMV_WARPS - 1) / MMV_WARPS;  // records per warp this round
     const int idx0 = warp * c, idx1 = min(rr, idx0 + c);
-    float* mypart = partial + warp * (a.seg_cap * SEGF);
+    float* mypart = partial + warp * (2 * SEGF);
     if (idx0 < idx1) {
       int tl = idx0 / nsr, rec = idx0 - tl * nsr;
       const int seg_tl = tl;
@@ -757,8 +767,10 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
         xl.s = xlane.s + rec * (8 * MC);
         process<NTL, DUMP>(cur, a, (tile_begin + t0 + tl) * MMV_TR, sb0 + rec, lane, xl, grid, acc);
         if (!has_next || wrap) {
-          // leaving tile tl: park its partial sums, [row][column]
-          float* seg = mypart + (tl - seg_tl) * SEGF;
+          // leaving tile tl, [row][column]: a tile this warp covered whole is final for this CTA; otherwise the
+          // sums are parked, slot 0 for the tile the chunk started in, slot 1 for the one it ends in
+          const bool whole = idx0 <= tl * nsr && idx1 >= (tl + 1) * nsr;
+          float* seg = whole ? csum + tl * SEGF : mypart + (tl == seg_tl ? 0 : SEGF);
 #pragma unroll
           for (int j = 0; j < NTL; ++j) {
             float v0, v1, v2, v3;
@@ -776,15 +788,14 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
     }
     if (t0 == 0) mmv_stamp(a, 2);
     __syncthreads();
-    // (1) inside the CTA: one warp per tile adds the partial sums of the warps that touched it, in warp order.
-    // Only the first of them can have started before this tile (its segment index is not 0).
+    // (1) inside the CTA: one warp per tile shared by several warps adds their parked sums in warp order (a tile
+    // with a single contributor was written whole)
     for (int tl = warp; tl < tiles_r; tl += MMV_WARPS) {
       const int w0 = (tl * nsr) / c, w1 = ((tl + 1) * nsr - 1) / c;
-      const int seg0 = tl - (w0 * c) / nsr;
-      const float* p0 = partial + (w0 * a.seg_cap + seg0) * SEGF;
+      if (w0 == w1) continue;
       for (int o = lane; o < SEGF; o += 32) {
-        float v = p0[o];
-        for (int w = w0 + 1; w <= w1; ++w) v += partial[w * a.seg_cap * SEGF + o];
+        float v = 0.0f;
+        for (int w = w0; w <= w1; ++w) v += partial[(2 * w + ((w * c) / nsr == tl ? 0 : 1)) * SEGF + o];
         csum[tl * SEGF + o] = v;
       }
     }
@@ -829,7 +840,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
 
 static int g_mmv_mode = 0;      // 0 = use this kernel wherever it applies, 1 = never (the older kernels)
 static int g_mmv_min_rows = 0;  // fewest activation rows served here; 0 = per type (see mmv_applies)
-static int g_mmv_max_rows = 24; // most
+static int g_mmv_max_rows = 32; // most
 static int g_mmv_cluster = 0;   // experiments: 0 = choose, else 1, 2, 4 or 8
 static unsigned long long* g_mmv_prof = nullptr;
 
@@ -885,39 +896,42 @@ template <int KIND, int NTL, int XL, bool DUMP>
 static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) {
   constexpr int MC = 8 * NTL;
   constexpr bool DS = MmvKind<KIND>::DS;
-  a.seg_cap = MC <= 16 ? 4 : MC <= 32 ? 3 : 2;
-  // tiles per round: bounded by the segments a warp may park and by 32 KB of per-CTA tile sums
-  a.tiles_round = MMV_WARPS * (a.seg_cap - 1);
-  if (a.tiles_round > 32768 / (MMV_TR * MC * 4)) a.tiles_round = 32768 / (MMV_TR * MC * 4);
-  const size_t part = MmvKind<KIND>::GRID + mmv_partial_bytes(MC, a.seg_cap) + (size_t)a.tiles_round * MMV_TR * MC * 4;
+  const size_t fixed = MmvKind<KIND>::grid_bytes(NTL) + mmv_partial_bytes(MC);
   const int nsb = a.k >> 8;
-  // cluster size: the CTAs of a cluster split K, so each stages 1 / cs of the activations. Among the sizes whose
-  // share fits, take the one that keeps most SMs busy with evenly filled clusters.
-  int best_cs = 0, best_clusters = 0, best_cap = 0;
+  // Cluster size: the CTAs of a cluster split K, so each stages 1 / cs of the activations, and the cluster takes
+  // its tiles in rounds of as many as the per-CTA tile sums have room for. Among the sizes that fit, the one
+  // with the least estimated time.
+  int best_cs = 0, best_clusters = 0, best_cap = 0, best_round = 0;
   double best_t = 0.0;
   for (int cs : {1, 2, 4, 8}) {
     if (g_mmv_cluster && cs != g_mmv_cluster) continue;
     if (cs > nsb) break;
     const int cap_kb = ((nsb + cs - 1) / cs) * 8;
-    const size_t smem = part + mmv_x_bytes(cap_kb, MC, DS);
-    if (smem > (size_t)max_smem) continue;
+    const size_t xb = mmv_x_bytes(cap_kb, MC, DS);
+    if (fixed + xb + (size_t)MMV_TR * MC * 4 > (size_t)max_smem) continue;
+    // occupancy is asked for with the largest footprint this cluster size could use
     int n = 0;
-    const int rc = mmv_max_clusters<KIND, NTL, XL, DUMP>(cs, smem, sm_count, &n);
+    const int rc = mmv_max_clusters<KIND, NTL, XL, DUMP>(cs, (size_t)max_smem, sm_count, &n);
     if (rc != GSQ_OK) return rc;
     if (n <= 0) continue;
     const int clusters = n < a.ntiles ? n : a.ntiles;
     const int per = (a.ntiles + clusters - 1) / clusters;
+    int round = (int)(((size_t)max_smem - fixed - xb) / ((size_t)MMV_TR * MC * 4));
+    if (round > per) round = per;
+    const int rounds = (per + round - 1) / round;
+    if (NTL >= 4 && rounds > 1) continue;  // measured: beyond 24 rows a second round costs more than the tcgen05 GEMM
     // estimated time (us): the stream of W at the rate the loop reaches, stretched by uneven clusters and idle
-    // SMs; staging (a fixed part plus 36-byte blocks per thread); the cluster-wide sum (one remote read per CTA)
+    // SMs; staging (36-byte blocks per thread, in batches of 4); per round two cluster barriers and the sums
     const double balance = ((double)a.ntiles / (per * clusters)) * ((double)(clusters * cs) / sm_count);
     const double t_loop = (double)a.ntiles * MMV_TR * a.row_bytes / 4.4e6 / balance;
-    const double t_stage = 1.0 * (double)(((int64_t)a.m * cap_kb + 2047) / 2048);  // batches of 4 blocks per thread
-    const double t = t_loop + t_stage + 0.15 * cs;
+    const double t_stage = 1.0 * (double)(((int64_t)a.m * cap_kb + 2047) / 2048);
+    const double t = t_loop + t_stage + 0.15 * cs + 2.5 * (rounds - 1);
     if (!best_cs || t < best_t) {
       best_t = t;
       best_cs = cs;
       best_clusters = clusters;
       best_cap = cap_kb;
+      best_round = round;
     }
   }
   if (!best_cs) return MMV_DECLINED;
@@ -930,7 +944,8 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
   a.inv_per = fast_div_inv(a.m * 9);
   a.tiles_base = a.ntiles / best_clusters;
   a.tiles_extra = a.ntiles % best_clusters;
-  const size_t smem = part + mmv_x_bytes(best_cap, MC, DS);
+  a.tiles_round = best_round;
+  const size_t smem = fixed + mmv_x_bytes(best_cap, MC, DS) + (size_t)best_round * MMV_TR * MC * 4;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(best_clusters * best_cs));
   cfg.blockDim = dim3(MMV_THREADS);
@@ -1014,7 +1029,6 @@ int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int 
   a.ldy = y_row_stride;
   a.ntiles = (int)((rows + MMV_TR - 1) / MMV_TR);
   a.tiles_base = a.tiles_extra = a.tiles_round = 0;
-  a.seg_cap = 4;
   a.xcap_kb = 0;
   a.dump = dump;
   a.prof = g_mmv_prof;
