@@ -101,6 +101,12 @@ __device__ __forceinline__ uint64_t vfma2(uint64_t a, uint64_t b, uint64_t c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
+// (a & b) | c in one logic instruction
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
 __device__ __forceinline__ uint32_t mprmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t r;
   asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
@@ -431,10 +437,10 @@ __device__ __forceinline__ uint32_t iq3_field(const RecIQ3S& r, const char* gbas
   } else {
     t = __funnelshift_r(r.idx[word], r.idx[word + 1], off - P);
   }
-  const uint2 gp = *reinterpret_cast<const uint2*>(gbase + ((t & (0x1FFu << P)) | lane_off));
+  const uint2 gp = *reinterpret_cast<const uint2*>(gbase + and_or(t, 0x1FFu << P, lane_off));
   constexpr int fl = F & 7, sh = 16 * (fl >> 2) + (fl & 3) - 2;
   const uint32_t sgs = sh >= 0 ? r.sg[F >> 3] >> (sh >= 0 ? sh : 0) : r.sg[F >> 3] << (sh < 0 ? -sh : 0);
-  return mprmt(gp.x, gp.y, (sgs & 0x4444u) | 0x3210u);
+  return mprmt(gp.x, gp.y, and_or(sgs, 0x4444u, 0x3210u));
 }
 
 template <int S, int NTL, bool DUMP>
