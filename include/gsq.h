@@ -119,10 +119,11 @@ int gsq_quantize_q8_1_mmq(const void* x, int x_dtype, int64_t m, int64_t k, int6
                           void* out, void* stream);
 
 /*
- * Streaming GEMV, 1..8 activation rows: replaces the vendored MMVQ (ggml_cuda_op_mul_mat_vec_q,
- * mmvq.cu:1538) and the owned 1..8-row kernels iq3_mul_mat_vec (lcpp_shim.cu:498-572),
- * own_mul_mat_vec (lcpp_owned_k4.cu:116-234), iq3_mma / iq3_mma_packed
- * (lcpp_owned_iq3_mma.cu:179-328, 483-600).
+ * Product with block_q8_1 activations, 1 .. gsq_mul_mat_vec_max_rows(type, packed) activation rows (8, or 32
+ * for Q4_K, IQ4_XS and packed IQ3_S): replaces the vendored MMVQ (ggml_cuda_op_mul_mat_vec_q, mmvq.cu:1538) and
+ * the owned small-batch kernels iq3_mul_mat_vec (lcpp_shim.cu:498-572), own_mul_mat_vec
+ * (lcpp_owned_k4.cu:116-234), iq3_mma / iq3_mma_packed (lcpp_owned_iq3_mma.cu:179-328, 483-600).
+ * Runs the dp4a GEMV or the register-operand tensor-core kernel, whichever is faster for the type and count.
  *   w            uint8 [rows, row_bytes] GGUF blocks (packed != 0: IQ3_S in gsq_iq3s_repack's layout)
  *   x_q8         m * k/32 block_q8_1 (36 bytes each)
  *   y            [m, rows] in y_dtype, row stride y_row_stride elements
@@ -178,7 +179,8 @@ int gsq_debug_block_sums(const void* w, int64_t row_bytes, int64_t rows, int ggm
                          const void* x_q8, int64_t m, int64_t k, int32_t* sums, float* y_scratch, void* stream);
 
 /*
- * Tensor-core GEMM (tcgen05 kind::i8, TMEM accumulators), any number of activation rows: replaces
+ * Product with block_q8_1_mmq activations, any number of activation rows (the register-operand tensor-core
+ * kernel up to 32 rows where it fits, the tcgen05 kind::i8 GEMM with TMEM accumulators above): replaces
  * the vendored MMQ (mul_mat_q, mmq.cuh:961-1385 + shim host side lcpp_shim.cu:626-671) and the owned
  * mma_k (lcpp_owned_mma_k.cu:353-539) and iq3_packed_mmq (lcpp_owned_iq3_mma.cu:768-970).
  *   x_q8_mmq     k/128 * m blocks of 144 bytes in the type's layout (gsq_q8_layout_for_type)
