@@ -698,9 +698,8 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
   const int tile_cnt = a.tiles_base + (cluster_id < a.tiles_extra ? 1 : 0);
 
   mmv_stamp(a, 0);
-  // The activation loads go out first; the warp's first two records are then requested from L2 (no register
-  // waits on them) while those are in flight, and loaded for real after the staging, so that neither queues
-  // behind the other.
+  // The warp's first two records are requested from L2 (no register waits on them) ahead of the staging and
+  // loaded for real after it.
   int first_tl = 0, first_rec = 0;
   bool have_first = false;
   int first_n = 0;
@@ -715,18 +714,16 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
       first_n = min(2, idx1 - idx0);
     }
   }
-  auto prefetch_first = [&]() {
+  // Everything up to here, the requests to L2 for the warp's first two records and the codebook copy do not
+  // depend on the kernel that produced the activations: with programmatic dependent launch they overlap its
+  // tail. The wait is a no-op when the launch carries no such dependency.
+  {
     int ptl = first_tl, prec = first_rec;
 #pragma unroll 1
     for (int u = 0; u < first_n; ++u) {
       Rec::prefetch(a, (tile_begin + ptl) * MMV_TR, sb0 + prec, lane);
       if (++prec == nsr) { prec = 0; ++ptl; }
     }
-  };
-  if (XL == XL_Q81) {
-    stage_x_q81<MC, DS, MmvKind<KIND>::PERM>(a, sb0 * 8, nkb, colb, xq, xd, xs, tid, prefetch_first);
-  } else {
-    stage_x_mmq<MC, DS, MmvKind<KIND>::PERM>(a, sb0 * 8, nkb, colb, xq, xd, xs, tid, prefetch_first);
   }
   if (GRID) {
     // one global load per thread (512 threads, 512 entries), then the replicas of its (g, -g) pair; no byte
@@ -735,6 +732,13 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
     uint4* dst = reinterpret_cast<uint4*>(smem + (tid & 511) * (GRID / 512));
 #pragma unroll
     for (int r2 = 0; r2 < GRID / 512 / 16; ++r2) dst[r2] = make_uint4(gv, ~gv + 0x01010101u, gv, ~gv + 0x01010101u);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  auto nothing = []() {};
+  if (XL == XL_Q81) {
+    stage_x_q81<MC, DS, MmvKind<KIND>::PERM>(a, sb0 * 8, nkb, colb, xq, xd, xs, tid, nothing);
+  } else {
+    stage_x_mmq<MC, DS, MmvKind<KIND>::PERM>(a, sb0 * 8, nkb, colb, xq, xd, xs, tid, nothing);
   }
   __syncthreads();
   mmv_stamp(a, 1);
@@ -849,6 +853,7 @@ static int g_mmv_min_rows = 0;  // fewest activation rows served here; 0 = per t
 static int g_mmv_max_rows = 32; // most
 static int g_mmv_cluster = 0;   // experiments: 0 = choose, else 1, 2, 4 or 8
 static unsigned long long* g_mmv_prof = nullptr;
+static int g_mmv_pdl = 1;       // launch with programmatic stream serialisation
 
 constexpr int MMV_DECLINED = 1000;  // mmv_host: this shape does not fit; use another kernel
 
@@ -957,13 +962,17 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
   cfg.blockDim = dim3(MMV_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = best_cs;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = best_cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  // programmatic dependent launch: this kernel may start while the previous one in the stream drains; it
+  // waits (griddepcontrol.wait) before it reads the activations
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_mmv_pdl ? 2 : 1;
   GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, mmv_kernel<KIND, NTL, XL, DUMP>, a));
   return GSQ_OK;
 }
@@ -1076,6 +1085,12 @@ extern "C" int gsq_debug_mmv_max_rows(int n) {
 
 extern "C" int gsq_mul_mat_vec_max_rows(int ggml_type, int packed) {
   return gsq::mmv_applies(ggml_type, packed, 16, gsq::g_mmv_max_rows) ? gsq::g_mmv_max_rows : 8;
+}
+
+extern "C" int gsq_debug_mmv_pdl(int on) {
+  const int old = gsq::g_mmv_pdl;
+  gsq::g_mmv_pdl = on ? 1 : 0;
+  return old;
 }
 
 extern "C" int gsq_debug_mmv_profile(unsigned long long* stamps) {

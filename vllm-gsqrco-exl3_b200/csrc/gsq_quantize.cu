@@ -61,6 +61,9 @@ __device__ __forceinline__ uint32_t pack4(float a, float b, float c, float d) {
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict__ x, uint8_t* __restrict__ out,
                                                            int64_t m, int64_t k, int64_t stride) {
+  // a product kernel launched behind this one with programmatic stream serialisation may start its prologue now;
+  // it waits for this grid to finish before it reads `out`
+  asm volatile("griddepcontrol.launch_dependents;");
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 8 values
   const int64_t per_row = k >> 3;
   // whole warps stay together: k % 32 == 0 makes per_row a multiple of 4, so a 4-thread group never
@@ -106,6 +109,7 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
 template <typename T, bool VEC, int LAYOUT>
 __global__ void __launch_bounds__(256) quantize_q8_1_mmq_kernel(const T* __restrict__ x, uint8_t* __restrict__ out,
                                                                int64_t m, int64_t k, int64_t stride) {
+  asm volatile("griddepcontrol.launch_dependents;");
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t per_row = k >> 3;
   const bool live = t < m * per_row;
