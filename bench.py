@@ -200,32 +200,63 @@ def run_ours(args):
 
     method = linear.GGUFLinearMethod(None)
 
-    def product(c, x):
-        """One cell: GGUFLinearMethod.apply() on this rank's shard (+ the tensor-parallel collective)."""
+    # Tensor parallel (world > 1): every product writes its shard's result into one of two flat buffers, and the
+    # step ends with one all-gather (N-sharded cells: qkv / gate-up style) and one all-reduce (K-sharded cells:
+    # o_proj / down style) over them -- the collectives of a step bucketed, as a TP runtime would.
+    tp_slots, flat_n, flat_k, gath_n = {}, None, None, None
+    if world > 1:
+        off_n = off_k = 0
+        for key, m in order:
+            c = cells[key]
+            if c["mode"] == "N":
+                tp_slots[(key, m)] = ("N", off_n, m * c["local_rows"])
+                off_n += m * c["local_rows"]
+            else:
+                tp_slots[(key, m)] = ("K", off_k, m * c["n"])
+                off_k += m * c["n"]
+        flat_n = torch.empty(max(off_n, 1), dtype=torch.float16, device=dev)
+        flat_k = torch.empty(max(off_k, 1), dtype=torch.float16, device=dev)
+        gath_n = torch.empty(world * flat_n.numel(), dtype=torch.float16, device=dev)
+
+    def product(c, x, key_m=None):
+        """One cell: GGUFLinearMethod.apply() on this rank's shard."""
         layer = c["layers"][c["use"] % len(c["layers"])]
         c["use"] += 1
         xl = x if c["mode"] == "N" else x[:, c["a0"] * 256:(c["a0"] + c["cnt"]) * 256]
         y = method.apply(layer, xl)
         m = x.shape[0]
         launches["n"] += 1 + (m + 7) // 8
-        if world > 1:
-            if c["mode"] == "N":
-                parts = [torch.empty(m, shard_plan(c["n"], c["k"], world, r)[2], dtype=y.dtype, device=dev) for r in range(world)]
-                dist.all_gather(parts, y.contiguous())
-                y = torch.cat(parts, dim=1)
-            else:
-                dist.all_reduce(y)
+        if world > 1 and key_m is not None:
+            kind, off, cnt = tp_slots[key_m]
+            (flat_n if kind == "N" else flat_k)[off:off + cnt].view_as(y).copy_(y)
         return y
 
-    def step():
-        for key, m in order:
-            product(cells[key], xs[(key[2], m)])
+    def collectives():
+        if world > 1:
+            dist.all_gather_into_tensor(gath_n, flat_n)
+            dist.all_reduce(flat_k)
 
-    def step_e2e(outs):
+    def compute():
+        for key, m in order:
+            product(cells[key], xs[(key[2], m)], (key, m))
+
+    def step():
+        compute()
+        collectives()
+
+    def compute_e2e(outs):
         for i, (key, m) in enumerate(order):
             x = xs_pinned[(key[2], m)].to(dev, non_blocking=True)
-            y = product(cells[key], x)
-            outs[i].copy_(y, non_blocking=True)
+            y = product(cells[key], x, (key, m))
+            if world == 1:
+                outs[i].copy_(y, non_blocking=True)
+
+    def step_e2e(outs):
+        compute_e2e(outs)
+        if world > 1:  # the step's results are the two collective buffers
+            collectives()
+            outs[0][:gath_n.numel()].copy_(gath_n, non_blocking=True)
+            outs[0][gath_n.numel():gath_n.numel() + flat_k.numel()].copy_(flat_k, non_blocking=True)
 
     def barrier():
         if world > 1:
@@ -258,13 +289,18 @@ def run_ours(args):
             fn()
         return g
 
-    use_graph = world == 1 and not args.eager   # with NCCL collectives in the step the launches stay eager
+    # The products (and, end to end, the copies) are replayed as one CUDA graph, as vLLM runs decode. NCCL
+    # collectives stay outside the graph (captured together with the products they hung a 2-GPU run).
+    use_graph = not args.eager
     for _ in range(max(3, args.warmup)):
         step()
     runner = step
     if use_graph:
-        g_step = capture(step)
-        runner = g_step.replay
+        g_step = capture(compute)
+
+        def runner():
+            g_step.replay()
+            collectives()
         for _ in range(3):
             runner()
     launches["n"] = 0
@@ -276,16 +312,29 @@ def run_ours(args):
     value = step_bytes * args.steps / (ms * 1e-3) / 1e9
 
     # end to end through GGUFLinearMethod.apply() with host buffers (pinned), copies inside the timed region
-    outs = [torch.empty(m, cells[key]["n"], dtype=torch.float16).pin_memory() for key, m in order]
+    if world == 1:
+        outs = [torch.empty(m, cells[key]["n"], dtype=torch.float16).pin_memory() for key, m in order]
+    else:
+        outs = [torch.empty(gath_n.numel() + flat_k.numel(), dtype=torch.float16).pin_memory()]
     for _ in range(3):
         step_e2e(outs)
     ms_e2e_eager = timed(lambda: step_e2e(outs), args.steps)
     ms_e2e = ms_e2e_eager
     if use_graph:
-        g_e2e = capture(lambda: step_e2e(outs))
+        if world == 1:
+            g_e2e = capture(lambda: step_e2e(outs))
+            run_e2e = g_e2e.replay
+        else:
+            g_e2e = capture(lambda: compute_e2e(outs))
+
+            def run_e2e():
+                g_e2e.replay()
+                collectives()
+                outs[0][:gath_n.numel()].copy_(gath_n, non_blocking=True)
+                outs[0][gath_n.numel():gath_n.numel() + flat_k.numel()].copy_(flat_k, non_blocking=True)
         for _ in range(3):
-            g_e2e.replay()
-        ms_e2e = timed(g_e2e.replay, args.steps)
+            run_e2e()
+        ms_e2e = timed(run_e2e, args.steps)
     e2e = step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9
     h2d = sum(m * key[2] * 2 for key, m in order)
     d2h = sum(m * cells[key]["n"] * 2 for key, m in order)
@@ -297,7 +346,7 @@ def run_ours(args):
     reps = 10
 
     def best_us(fn):
-        if world > 1 or args.eager:
+        if args.eager:
             for _ in range(3):
                 fn()
             torch.cuda.synchronize()
@@ -356,13 +405,15 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": "gemv_row_sweep", "types": [t for t, _ in TYPES], "shapes": SHAPES, "rows": ROWS,
                        "x_dtype": "fp16", "l2_defeat": "weight copies cycled, > 3 x L2 between reuses",
-                       "launch": "cuda graph replay of one step" if use_graph else "eager",
+                       "launch": ("cuda graph replay of one step" + (" + one all-gather and one all-reduce over the step's outputs"
+                                                                    if world > 1 else "")) if use_graph else "eager",
                        "parallelism": "tp%d" % world if world > 1 else "single"},
             "clocks": clk.summary(),
             "e2e": {"value": round(e2e, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": round(ms_e2e / args.steps, 4),
                     "eager_ms_per_step": round(ms_e2e_eager / args.steps, 4),
-                    "launch": "cuda graph replay of apply() + copies" if use_graph else "eager"},
+                    "launch": ("cuda graph replay of apply() + copies" + (", collectives and result copies eager" if world > 1 else ""))
+                    if use_graph else "eager"},
             "gpu_launches": n_launch,
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1) if achieved else None,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s",
