@@ -120,6 +120,34 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(init));
 }
 
+// From two column groups on, the integer sub-scale is applied on the floating-point side: the tensor-core
+// instruction accumulates onto the bit pattern of 1.5 * 2^23, so its outputs, read as floats, only need that
+// constant subtracted (|sum| < 2^22), in place, as the two packed pairs they already are; the row's
+// d * sub-scale then joins the column scale in one packed multiply. Per slice and column group 6 packed
+// instructions instead of 4 integer multiply-adds, their moves into pairs and 6 packed instructions.
+constexpr bool mmv_float_scale(int ntl) { return ntl >= 2; }
+
+__device__ __forceinline__ void scale_acc(const int (&c)[4], uint64_t dv2, uint64_t ds0, uint64_t ds1, uint64_t& a0,
+                                          uint64_t& a1) {
+  const uint64_t nm2 = pk2(-MAGIC_F, -MAGIC_F);
+  const uint64_t f01 = vadd2(pk2(__int_as_float(c[0]), __int_as_float(c[1])), nm2);
+  const uint64_t f23 = vadd2(pk2(__int_as_float(c[2]), __int_as_float(c[3])), nm2);
+  a0 = vfma2(f01, vmul2(dv2, ds0), a0);
+  a1 = vfma2(f23, vmul2(dv2, ds1), a1);
+}
+
+template <bool DUMP>
+__device__ __forceinline__ void dump_c(const MmvArgs& ar, const int (&c)[4], int bias, int row0, int lane, int j, int kb) {
+  if constexpr (DUMP) {
+    const int g = lane >> 2, t = lane & 3, col0 = 8 * j + 2 * t, nb32 = ar.k >> 5;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int row = row0 + g + 8 * (e >> 1), col = col0 + (e & 1);
+      if (row < ar.nrows && col < ar.m) ar.dump[((int64_t)col * ar.nrows + row) * nb32 + kb] = c[e] - bias;
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Activations: staged once per CTA in shared memory for the CTA's K range, in the order the fragments want:
 //   quants  [column][kb][32 bytes]   lane (g, t) reads words 2t, 2t + 1 (or t, t + 4) of column 8j + g; a column is
@@ -353,32 +381,39 @@ __device__ __forceinline__ void process(const RecQ4K& r, const MmvArgs& ar, int 
       m1 *= ndm[1];
     }
     const uint64_t m02 = pk2(m0, m0), m12 = pk2(m1, m1);
+    uint64_t ds0 = 0ull, ds1 = 0ull;
+    if constexpr (mmv_float_scale(NTL)) {
+      const float f0 = d[0] * byte_float(scw[0][s >> 2], s & 3), f1 = d[1] * byte_float(scw[1][s >> 2], s & 3);
+      ds0 = pk2(f0, f0);
+      ds1 = pk2(f1, f1);
+    }
 #pragma unroll
     for (int j = 0; j < NTL; ++j) {
       const uint2 b = *reinterpret_cast<const uint2*>(xl.q + j * xl.q8 + s * 32);
       const uint64_t dv2 = *reinterpret_cast<const uint64_t*>(xl.d + s * MC + 8 * j);
       const uint64_t xs2 = *reinterpret_cast<const uint64_t*>(xl.s + s * MC + 8 * j);
       int c[4];
-      mma_s8(c, a, b.x, b.y, 0);
-      if constexpr (DUMP) {
-        const int col0 = 8 * j + 2 * t, nb32 = ar.k >> 5;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int row = row0 + g + 8 * (e >> 1), col = col0 + (e & 1);
-          if (row < ar.nrows && col < ar.m) ar.dump[((int64_t)col * ar.nrows + row) * nb32 + sb * 8 + s] = c[e];
+      if constexpr (mmv_float_scale(NTL)) {
+        mma_s8(c, a, b.x, b.y, MAGIC);
+        dump_c<DUMP>(ar, c, MAGIC, row0, lane, j, sb * 8 + s);
+        scale_acc(c, dv2, ds0, ds1, acc[j][0], acc[j][1]);
+        if constexpr (DEFER) {
+          uu[j][0] = vfma2(m02, xs2, uu[j][0]);
+          uu[j][1] = vfma2(m12, xs2, uu[j][1]);
+        } else {
+          acc[j][0] = vfma2(m02, xs2, acc[j][0]);
+          acc[j][1] = vfma2(m12, xs2, acc[j][1]);
         }
-      }
-      // |c * sc| <= 32 * 15 * 127 * 63 < 2^22: integer multiply-add onto the magic pattern, read as a float
-      const uint64_t f01 = vadd2(pk2(__int_as_float(c[0] * sc0 + MAGIC), __int_as_float(c[1] * sc0 + MAGIC)), nm2);
-      const uint64_t f23 = vadd2(pk2(__int_as_float(c[2] * sc1 + MAGIC), __int_as_float(c[3] * sc1 + MAGIC)), nm2);
-      if constexpr (DEFER) {
+      } else {
+        mma_s8(c, a, b.x, b.y, 0);
+        dump_c<DUMP>(ar, c, 0, row0, lane, j, sb * 8 + s);
+        // |c * sc| <= 32 * 15 * 127 * 63 < 2^22: integer multiply-add onto the magic pattern, read as a float
+        const uint64_t f01 = vadd2(pk2(__int_as_float(c[0] * sc0 + MAGIC), __int_as_float(c[1] * sc0 + MAGIC)), nm2);
+        const uint64_t f23 = vadd2(pk2(__int_as_float(c[2] * sc1 + MAGIC), __int_as_float(c[3] * sc1 + MAGIC)), nm2);
         tt[j][0] = vfma2(f01, dv2, tt[j][0]);
         tt[j][1] = vfma2(f23, dv2, tt[j][1]);
         uu[j][0] = vfma2(m02, xs2, uu[j][0]);
         uu[j][1] = vfma2(m12, xs2, uu[j][1]);
-      } else {
-        acc[j][0] = vfma2(m02, xs2, vfma2(f01, vmul2(dv2, d02), acc[j][0]));
-        acc[j][1] = vfma2(m12, xs2, vfma2(f23, vmul2(dv2, d12), acc[j][1]));
       }
     }
   }
@@ -386,8 +421,13 @@ __device__ __forceinline__ void process(const RecQ4K& r, const MmvArgs& ar, int 
     const uint64_t n02 = pk2(ndm[0], ndm[0]), n12 = pk2(ndm[1], ndm[1]);
 #pragma unroll
     for (int j = 0; j < NTL; ++j) {
-      acc[j][0] = vfma2(n02, uu[j][0], vfma2(d02, tt[j][0], acc[j][0]));
-      acc[j][1] = vfma2(n12, uu[j][1], vfma2(d12, tt[j][1], acc[j][1]));
+      if constexpr (mmv_float_scale(NTL)) {
+        acc[j][0] = vfma2(n02, uu[j][0], acc[j][0]);
+        acc[j][1] = vfma2(n12, uu[j][1], acc[j][1]);
+      } else {
+        acc[j][0] = vfma2(n02, uu[j][0], vfma2(d02, tt[j][0], acc[j][0]));
+        acc[j][1] = vfma2(n12, uu[j][1], vfma2(d12, tt[j][1], acc[j][1]));
+      }
     }
   }
 }
@@ -456,31 +496,37 @@ __device__ __forceinline__ void iq3_slice(const RecIQ3S& r, const MmvArgs& ar, i
   a[2] = iq3_field<4 * S + 1, RS>(r, gbase, lane_off);   // (row g, group 2t + 1)
   a[3] = iq3_field<4 * S + 3, RS>(r, gbase, lane_off);   // (row g + 8, group 2t + 1)
   // 2 * nibble + 1 of slice S: byte S / 2 of the even- or odd-slice word
-  const int sc0 = (int)((iscw[0][S & 1] >> (8 * (S >> 1))) & 0xFFu), sc1 = (int)((iscw[1][S & 1] >> (8 * (S >> 1))) & 0xFFu);
   const uint64_t nm2 = pk2(-MAGIC_F, -MAGIC_F);
+  if constexpr (mmv_float_scale(NTL)) {
+    float h0, h1;
+    upk2(d2[0], h0, h1);
+    const float f0 = h0 * byte_float(iscw[0][S & 1], S >> 1);   // d * (2 n + 1), exact
+    upk2(d2[1], h0, h1);
+    const float f1 = h0 * byte_float(iscw[1][S & 1], S >> 1);
+    const uint64_t ds0 = pk2(f0, f0), ds1 = pk2(f1, f1);
 #pragma unroll
-  for (int j = 0; j < NTL; ++j) {
-    const uint2 b = *reinterpret_cast<const uint2*>(xl.q + j * xl.q8 + S * 32);
-    const uint64_t dv2 = *reinterpret_cast<const uint64_t*>(xl.d + S * MC + 8 * j);
-    int c[4];
-    mma_s8(c, a, b.x, b.y, 0);
-    if constexpr (DUMP) {
-      const int g = lane >> 2, t = lane & 3, col0 = 8 * j + 2 * t, nb32 = ar.k >> 5;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int row = row0 + g + 8 * (e >> 1), col = col0 + (e & 1);
-        if (row < ar.nrows && col < ar.m) ar.dump[((int64_t)col * ar.nrows + row) * nb32 + sb * 8 + S] = c[e];
-      }
+    for (int j = 0; j < NTL; ++j) {
+      const uint2 b = *reinterpret_cast<const uint2*>(xl.q + j * xl.q8 + S * 32);
+      const uint64_t dv2 = *reinterpret_cast<const uint64_t*>(xl.d + S * MC + 8 * j);
+      int c[4];
+      mma_s8(c, a, b.x, b.y, MAGIC);
+      dump_c<DUMP>(ar, c, MAGIC, row0, lane, j, sb * 8 + S);
+      scale_acc(c, dv2, ds0, ds1, acc[j][0], acc[j][1]);
     }
-    // |c * (2 n + 1)| <= 32 * 15 * 127 * 31 < 2^22: integer multiply-add onto the magic pattern, read as a float
-    const uint64_t f01 = vadd2(pk2(__int_as_float(c[0] * sc0 + MAGIC), __int_as_float(c[1] * sc0 + MAGIC)), nm2);
-    const uint64_t f23 = vadd2(pk2(__int_as_float(c[2] * sc1 + MAGIC), __int_as_float(c[3] * sc1 + MAGIC)), nm2);
-    if constexpr (DEFER) {
+  } else {
+    const int sc0 = (int)((iscw[0][S & 1] >> (8 * (S >> 1))) & 0xFFu), sc1 = (int)((iscw[1][S & 1] >> (8 * (S >> 1))) & 0xFFu);
+#pragma unroll
+    for (int j = 0; j < NTL; ++j) {
+      const uint2 b = *reinterpret_cast<const uint2*>(xl.q + j * xl.q8 + S * 32);
+      const uint64_t dv2 = *reinterpret_cast<const uint64_t*>(xl.d + S * MC + 8 * j);
+      int c[4];
+      mma_s8(c, a, b.x, b.y, 0);
+      dump_c<DUMP>(ar, c, 0, row0, lane, j, sb * 8 + S);
+      // |c * (2 n + 1)| <= 32 * 15 * 127 * 31 < 2^22: integer multiply-add onto the magic pattern, read as a float
+      const uint64_t f01 = vadd2(pk2(__int_as_float(c[0] * sc0 + MAGIC), __int_as_float(c[1] * sc0 + MAGIC)), nm2);
+      const uint64_t f23 = vadd2(pk2(__int_as_float(c[2] * sc1 + MAGIC), __int_as_float(c[3] * sc1 + MAGIC)), nm2);
       tt[j][0] = vfma2(f01, dv2, tt[j][0]);
       tt[j][1] = vfma2(f23, dv2, tt[j][1]);
-    } else {
-      acc[j][0] = vfma2(f01, vmul2(dv2, d2[0]), acc[j][0]);
-      acc[j][1] = vfma2(f23, vmul2(dv2, d2[1]), acc[j][1]);
     }
   }
 }
@@ -514,7 +560,7 @@ __device__ __forceinline__ void process(const RecIQ3S& r, const MmvArgs& ar, int
   iq3_slice<5, NTL, DUMP>(r, ar, row0, sb, lane, xl, gbase, lane_off, iscw, d2, acc, tt);
   iq3_slice<6, NTL, DUMP>(r, ar, row0, sb, lane, xl, gbase, lane_off, iscw, d2, acc, tt);
   iq3_slice<7, NTL, DUMP>(r, ar, row0, sb, lane, xl, gbase, lane_off, iscw, d2, acc, tt);
-  if constexpr (DEFER) {
+  if constexpr (!mmv_float_scale(NTL)) {
 #pragma unroll
     for (int j = 0; j < NTL; ++j) {
       acc[j][0] = vfma2(d2[0], tt[j][0], acc[j][0]);
@@ -566,7 +612,6 @@ template <int NTL, bool DUMP>
 __device__ __forceinline__ void process(const RecIQ4XS& r, const MmvArgs& ar, int row0, int sb, int lane, const XSmem& xl,
                                         const uint8_t*, uint64_t (&acc)[NTL][2]) {
   constexpr int MC = 8 * NTL;
-  constexpr bool DEFER = NTL <= 2;
   const uint32_t* tw = reinterpret_cast<const uint32_t*>(c_iq4nl_mmv);
   const uint32_t tb[4] = {tw[0], tw[1], tw[2], tw[3]};
   uint64_t d2[2];
@@ -577,11 +622,6 @@ __device__ __forceinline__ void process(const RecIQ4XS& r, const MmvArgs& ar, in
     d2[h] = pk2(d, d);
     sh4[h] = (r.hdr[h].x >> 16) << 4;
   }
-  uint64_t tt[NTL][2];
-  if constexpr (DEFER) {
-#pragma unroll
-    for (int j = 0; j < NTL; ++j) tt[j][0] = tt[j][1] = 0ull;
-  }
 #pragma unroll
   for (int s = 0; s < 8; ++s) {
     uint32_t a[4];
@@ -590,37 +630,21 @@ __device__ __forceinline__ void process(const RecIQ4XS& r, const MmvArgs& ar, in
     // 6-bit sub-scale minus 32: low nibble from scales_l, bits 4, 5 from scales_h
     const int sc0 = (int)(((r.hdr[0].y >> (4 * s)) & 0xFu) | ((sh4[0] >> (2 * s)) & 0x30u)) - 32;
     const int sc1 = (int)(((r.hdr[1].y >> (4 * s)) & 0xFu) | ((sh4[1] >> (2 * s)) & 0x30u)) - 32;
+    // d * sub-scale, applied on the floating-point side (|sum| <= 32 * 127 * 127 < 2^22)
+    float h0, h1;
+    upk2(d2[0], h0, h1);
+    const float f0 = h0 * (float)sc0;
+    upk2(d2[1], h0, h1);
+    const float f1 = h0 * (float)sc1;
+    const uint64_t ds0 = pk2(f0, f0), ds1 = pk2(f1, f1);
 #pragma unroll
     for (int j = 0; j < NTL; ++j) {
       const uint2 b = *reinterpret_cast<const uint2*>(xl.q + j * xl.q8 + s * 32);
       const uint64_t dv2 = *reinterpret_cast<const uint64_t*>(xl.d + s * MC + 8 * j);
       int c[4];
-      mma_s8(c, a, b.x, b.y, 0);
-      if constexpr (DUMP) {
-        const int g = lane >> 2, t = lane & 3, col0 = 8 * j + 2 * t, nb32 = ar.k >> 5;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int row = row0 + g + 8 * (e >> 1), col = col0 + (e & 1);
-          if (row < ar.nrows && col < ar.m) ar.dump[((int64_t)col * ar.nrows + row) * nb32 + sb * 8 + s] = c[e];
-        }
-      }
-      // |c * scale| <= 32 * 127 * 127 * 32 < 2^24: the conversion is exact
-      const uint64_t f01 = pk2(__int2float_rn(c[0] * sc0), __int2float_rn(c[1] * sc0));
-      const uint64_t f23 = pk2(__int2float_rn(c[2] * sc1), __int2float_rn(c[3] * sc1));
-      if constexpr (DEFER) {
-        tt[j][0] = vfma2(f01, dv2, tt[j][0]);
-        tt[j][1] = vfma2(f23, dv2, tt[j][1]);
-      } else {
-        acc[j][0] = vfma2(f01, vmul2(dv2, d2[0]), acc[j][0]);
-        acc[j][1] = vfma2(f23, vmul2(dv2, d2[1]), acc[j][1]);
-      }
-    }
-  }
-  if constexpr (DEFER) {
-#pragma unroll
-    for (int j = 0; j < NTL; ++j) {
-      acc[j][0] = vfma2(d2[0], tt[j][0], acc[j][0]);
-      acc[j][1] = vfma2(d2[1], tt[j][1], acc[j][1]);
+      mma_s8(c, a, b.x, b.y, MAGIC);
+      dump_c<DUMP>(ar, c, MAGIC, row0, lane, j, sb * 8 + s);
+      scale_acc(c, dv2, ds0, ds1, acc[j][0], acc[j][1]);
     }
   }
 }
