@@ -120,7 +120,7 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(init));
 }
 
-// From two column groups on, the integer sub-scale is applied on the floating-point side: the tensor-core
+// For IQ3_S from two column groups on, and for IQ4_XS always, the integer sub-scale is applied on the floating-point side: the tensor-core
 // instruction accumulates onto the bit pattern of 1.5 * 2^23, so its outputs, read as floats, only need that
 // constant subtracted (|sum| < 2^22), in place, as the two packed pairs they already are; the row's
 // d * sub-scale then joins the column scale in one packed multiply. Per slice and column group 6 packed
@@ -381,39 +381,28 @@ __device__ __forceinline__ void process(const RecQ4K& r, const MmvArgs& ar, int 
       m1 *= ndm[1];
     }
     const uint64_t m02 = pk2(m0, m0), m12 = pk2(m1, m1);
-    uint64_t ds0 = 0ull, ds1 = 0ull;
-    if constexpr (mmv_float_scale(NTL)) {
-      const float f0 = d[0] * byte_float(scw[0][s >> 2], s & 3), f1 = d[1] * byte_float(scw[1][s >> 2], s & 3);
-      ds0 = pk2(f0, f0);
-      ds1 = pk2(f1, f1);
-    }
 #pragma unroll
     for (int j = 0; j < NTL; ++j) {
       const uint2 b = *reinterpret_cast<const uint2*>(xl.q + j * xl.q8 + s * 32);
       const uint64_t dv2 = *reinterpret_cast<const uint64_t*>(xl.d + s * MC + 8 * j);
       const uint64_t xs2 = *reinterpret_cast<const uint64_t*>(xl.s + s * MC + 8 * j);
       int c[4];
-      if constexpr (mmv_float_scale(NTL)) {
-        mma_s8(c, a, b.x, b.y, MAGIC);
-        dump_c<DUMP>(ar, c, MAGIC, row0, lane, j, sb * 8 + s);
-        scale_acc(c, dv2, ds0, ds1, acc[j][0], acc[j][1]);
-        if constexpr (DEFER) {
-          uu[j][0] = vfma2(m02, xs2, uu[j][0]);
-          uu[j][1] = vfma2(m12, xs2, uu[j][1]);
-        } else {
-          acc[j][0] = vfma2(m02, xs2, acc[j][0]);
-          acc[j][1] = vfma2(m12, xs2, acc[j][1]);
-        }
-      } else {
+      {
         mma_s8(c, a, b.x, b.y, 0);
         dump_c<DUMP>(ar, c, 0, row0, lane, j, sb * 8 + s);
+        // (applying the sub-scale on the floating-point side, as the other two types do, measured slower here)
         // |c * sc| <= 32 * 15 * 127 * 63 < 2^22: integer multiply-add onto the magic pattern, read as a float
         const uint64_t f01 = vadd2(pk2(__int_as_float(c[0] * sc0 + MAGIC), __int_as_float(c[1] * sc0 + MAGIC)), nm2);
         const uint64_t f23 = vadd2(pk2(__int_as_float(c[2] * sc1 + MAGIC), __int_as_float(c[3] * sc1 + MAGIC)), nm2);
-        tt[j][0] = vfma2(f01, dv2, tt[j][0]);
-        tt[j][1] = vfma2(f23, dv2, tt[j][1]);
-        uu[j][0] = vfma2(m02, xs2, uu[j][0]);
-        uu[j][1] = vfma2(m12, xs2, uu[j][1]);
+        if constexpr (DEFER) {
+          tt[j][0] = vfma2(f01, dv2, tt[j][0]);
+          tt[j][1] = vfma2(f23, dv2, tt[j][1]);
+          uu[j][0] = vfma2(m02, xs2, uu[j][0]);
+          uu[j][1] = vfma2(m12, xs2, uu[j][1]);
+        } else {
+          acc[j][0] = vfma2(m02, xs2, vfma2(f01, vmul2(dv2, d02), acc[j][0]));
+          acc[j][1] = vfma2(m12, xs2, vfma2(f23, vmul2(dv2, d12), acc[j][1]));
+        }
       }
     }
   }
@@ -421,13 +410,8 @@ __device__ __forceinline__ void process(const RecQ4K& r, const MmvArgs& ar, int 
     const uint64_t n02 = pk2(ndm[0], ndm[0]), n12 = pk2(ndm[1], ndm[1]);
 #pragma unroll
     for (int j = 0; j < NTL; ++j) {
-      if constexpr (mmv_float_scale(NTL)) {
-        acc[j][0] = vfma2(n02, uu[j][0], acc[j][0]);
-        acc[j][1] = vfma2(n12, uu[j][1], acc[j][1]);
-      } else {
-        acc[j][0] = vfma2(n02, uu[j][0], vfma2(d02, tt[j][0], acc[j][0]));
-        acc[j][1] = vfma2(n12, uu[j][1], vfma2(d12, tt[j][1], acc[j][1]));
-      }
+      acc[j][0] = vfma2(n02, uu[j][0], vfma2(d02, tt[j][0], acc[j][0]));
+      acc[j][1] = vfma2(n12, uu[j][1], vfma2(d12, tt[j][1], acc[j][1]));
     }
   }
 }
