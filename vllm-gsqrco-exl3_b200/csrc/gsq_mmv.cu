@@ -30,6 +30,9 @@
 //     in Y's dtype. No atomics, no global scratch, the same order every run.
 #include <cooperative_groups.h>
 
+#include <cstdio>
+#include <cstdlib>
+
 #include "gsq_common.cuh"
 #include "gsq_tables.h"
 
@@ -58,6 +61,8 @@ struct MmvArgs {
   int tiles_base;    // tiles per cluster: the first tiles_extra clusters own tiles_base + 1
   int tiles_extra;
   int tiles_round;   // tiles a cluster takes per round
+  int share_cap;     // most tiles of a round one CTA owns (ceil(tiles_round / cluster size))
+  int gather_bufs;   // 1: a single round; 2: rounds alternate between two gather areas
   int xcap_kb;       // 32-value blocks of activations the shared-memory staging area holds per column
   int* dump;         // debug: int32 slice sums [m][nrows][k / 32]
   // fast_div_inv of: 16-byte granules and 36-byte blocks per staged column, for a CTA with nsr_lo superblocks
@@ -696,8 +701,11 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
   constexpr int GRID = MmvKind<KIND>::grid_bytes(NTL);
   const uint8_t* grid = smem;
   float* partial = reinterpret_cast<float*>(smem + GRID);
-  float* csum = reinterpret_cast<float*>(smem + GRID + mmv_partial_bytes(MC));   // [tiles_round][16][MC]
-  uint8_t* xq = smem + GRID + mmv_partial_bytes(MC) + (size_t)a.tiles_round * SEGF * 4;
+  // gather area: [buffer][source CTA][owned tile][16][MC]; every CTA of the cluster owns a contiguous share of
+  // the round's tiles and receives, through distributed shared memory, each CTA's sums (one K part each) for them
+  float* gath = reinterpret_cast<float*>(smem + GRID + mmv_partial_bytes(MC));
+  const size_t gath_bytes = (size_t)a.gather_bufs * cs * a.share_cap * SEGF * 4;
+  uint8_t* xq = smem + GRID + mmv_partial_bytes(MC) + gath_bytes;
   const int colb = mmv_xq_col_bytes(a.xcap_kb);
   float* xd = reinterpret_cast<float*>(xq + (size_t)colb * MC);
   float* xs = xd + (size_t)a.xcap_kb * MC;
@@ -764,6 +772,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
     const int c = (rr + MMV_WARPS - 1) / MMV_WARPS;  // records per warp this round
     const int idx0 = warp * c, idx1 = min(rr, idx0 + c);
     float* mypart = partial + warp * (2 * SEGF);
+
     if (idx0 < idx1) {
       int tl = idx0 / nsr, rec = idx0 - tl * nsr;
       const int seg_tl = tl;
@@ -776,8 +785,18 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
         const bool has_next = idx + 1 < idx1;
         const bool wrap = rec + 1 == nsr;
         const int ntl = wrap ? tl + 1 : tl, nrc = wrap ? 0 : rec + 1;
+        // Up to 16 columns the next record is loaded into registers while this one is multiplied. Wider than
+        // that the accumulators need the registers: the next record is only requested from L2 and loaded after
+        // the arithmetic (the other warps of the SM cover the wait; a record then takes ~1000 instructions).
+        constexpr bool REGPF = NTL <= 2;
         Rec nxt;
-        if (has_next) nxt.load(a, (tile_begin + t0 + ntl) * MMV_TR, sb0 + nrc, lane);
+        if (has_next) {
+          if constexpr (REGPF) {
+            nxt.load(a, (tile_begin + t0 + ntl) * MMV_TR, sb0 + nrc, lane);
+          } else {
+            Rec::prefetch(a, (tile_begin + t0 + ntl) * MMV_TR, sb0 + nrc, lane);
+          }
+        }
         XSmem xl;
         xl.q = xlane.q + rec * 256;
         xl.q8 = xlane.q8;
@@ -788,7 +807,14 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
           // leaving tile tl, [row][column]: a tile this warp covered whole is final for this CTA; otherwise the
           // sums are parked, slot 0 for the tile the chunk started in, slot 1 for the one it ends in
           const bool whole = idx0 <= tl * nsr && idx1 >= (tl + 1) * nsr;
-          float* seg = whole ? csum + tl * SEGF : mypart + (tl == seg_tl ? 0 : SEGF);
+          float* seg = mypart + (tl == seg_tl ? 0 : SEGF);
+          if (whole) {
+            // everything about the destination is worked out here, once per tile, so that the loop carries no
+            // state for it: owner = tl / share_cap, slot of this CTA in the owner's gather area
+            const int o = tl / a.share_cap;
+            const int bufn = a.gather_bufs == 2 ? (t0 / a.tiles_round) & 1 : 0;
+            seg = cluster.map_shared_rank(gath, o) + ((bufn * cs + crank) * a.share_cap + (tl - o * a.share_cap)) * SEGF;
+          }
 #pragma unroll
           for (int j = 0; j < NTL; ++j) {
             float v0, v1, v2, v3;
@@ -799,33 +825,43 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
             acc[j][0] = acc[j][1] = 0ull;
           }
         }
-        if (has_next) cur = nxt;
+        if (has_next) {
+          if constexpr (REGPF) {
+            cur = nxt;
+          } else {
+            cur.load(a, (tile_begin + t0 + ntl) * MMV_TR, sb0 + nrc, lane);
+          }
+        }
         tl = ntl;
         rec = nrc;
       }
     }
     if (t0 == 0) mmv_stamp(a, 2);
     __syncthreads();
-    // (1) inside the CTA: one warp per tile shared by several warps adds their parked sums in warp order (a tile
-    // with a single contributor was written whole)
+    // Tile tl of the round is owned by CTA tl / share_cap of the cluster.
+    const int buf = a.gather_bufs == 2 ? (t0 / a.tiles_round) & 1 : 0;
+    // (1) inside the CTA: one warp per tile shared by several warps adds their parked sums in warp order and
+    // sends them to the tile's owner (a tile with a single contributor was sent whole from the loop)
     for (int tl = warp; tl < tiles_r; tl += MMV_WARPS) {
       const int w0 = (tl * nsr) / c, w1 = ((tl + 1) * nsr - 1) / c;
       if (w0 == w1) continue;
+      const int o = tl / a.share_cap;
+      float* dst = cluster.map_shared_rank(gath, o) + ((buf * cs + crank) * a.share_cap + (tl - o * a.share_cap)) * SEGF;
       for (int o = lane; o < SEGF; o += 32) {
         float v = 0.0f;
         for (int w = w0; w <= w1; ++w) v += partial[(2 * w + ((w * c) / nsr == tl ? 0 : 1)) * SEGF + o];
-        csum[tl * SEGF + o] = v;
+        dst[o] = v;
       }
     }
     cluster.sync();
     if (t0 == 0) mmv_stamp(a, 3);
-    // (2) across the cluster: the CTAs' sums (one per K part) are added in rank order and stored
-    const int rows_r = tiles_r * MMV_TR;
-    const float* rsum[8];
-#pragma unroll
-    for (int r = 0; r < 8; ++r) rsum[r] = cluster.map_shared_rank(csum, r < cs ? r : 0);
-    for (int r2 = crank * MMV_THREADS + tid; r2 < rows_r; r2 += cs * MMV_THREADS) {
-      const int row = (tile_begin + t0) * MMV_TR + r2;
+    // (2) the owner adds the CTAs' sums (one per K part) of its tiles in rank order, from its own shared
+    // memory, and stores them. Nothing remote is read after the barrier, so no second barrier is needed: the
+    // next round writes the other gather area, and a CTA that has passed the last barrier only reads locally.
+    const int own_tiles = max(0, min(a.share_cap, tiles_r - crank * a.share_cap));
+    const float* g0 = gath + (size_t)buf * cs * a.share_cap * SEGF;
+    for (int r2 = tid; r2 < own_tiles * MMV_TR; r2 += MMV_THREADS) {
+      const int row = (tile_begin + t0 + crank * a.share_cap) * MMV_TR + r2;
       if (row < a.nrows) {
 #pragma unroll
         for (int c4 = 0; c4 < MC / 4; ++c4) {
@@ -834,7 +870,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
               if (r < cs) {
-                const float4 p = *reinterpret_cast<const float4*>(rsum[r] + r2 * MC + 4 * c4);
+                const float4 p = *reinterpret_cast<const float4*>(g0 + (size_t)r * a.share_cap * SEGF + r2 * MC + 4 * c4);
                 v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
               }
             }
@@ -848,7 +884,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
       }
     }
     if (t0 == 0) mmv_stamp(a, 4);
-    cluster.sync();  // the partial sums are reused by the next round; no CTA leaves while another reads its memory
+    __syncthreads();  // the parked sums are reused by the next round
     if (t0 == 0) mmv_stamp(a, 5);
   }
 }
@@ -920,14 +956,14 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
   // Cluster size: the CTAs of a cluster split K, so each stages 1 / cs of the activations, and the cluster takes
   // its tiles in rounds of as many as the per-CTA tile sums have room for. Among the sizes that fit, the one
   // with the least estimated time.
-  int best_cs = 0, best_clusters = 0, best_cap = 0, best_round = 0;
+  int best_cs = 0, best_clusters = 0, best_cap = 0, best_round = 0, best_bufs = 1;
   double best_t = 0.0;
   for (int cs : {1, 2, 4, 8}) {
     if (g_mmv_cluster && cs != g_mmv_cluster) continue;
     if (cs > nsb) break;
     const int cap_kb = ((nsb + cs - 1) / cs) * 8;
     const size_t xb = mmv_x_bytes(cap_kb, MC, DS);
-    if (fixed + xb + (size_t)MMV_TR * MC * 4 > (size_t)max_smem) continue;
+    if (fixed + xb + (size_t)cs * MMV_TR * MC * 4 > (size_t)max_smem) continue;
     // occupancy is asked for with the largest footprint this cluster size could use
     int n = 0;
     const int rc = mmv_max_clusters<KIND, NTL, XL, DUMP>(cs, (size_t)max_smem, sm_count, &n);
@@ -935,12 +971,19 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
     if (n <= 0) continue;
     const int clusters = n < a.ntiles ? n : a.ntiles;
     const int per = (a.ntiles + clusters - 1) / clusters;
-    int round = (int)(((size_t)max_smem - fixed - xb) / ((size_t)MMV_TR * MC * 4));
-    if (round > per) round = per;
+    // tiles per round: all of a cluster's tiles if one gather area for them fits, else rounds that alternate
+    // between two areas
+    const size_t avail = (size_t)max_smem - fixed - xb, tile_b = (size_t)MMV_TR * MC * 4;
+    int round = per, bufs = 1;
+    if ((size_t)cs * ((per + cs - 1) / cs) * tile_b > avail) {
+      bufs = 2;
+      round = (int)(avail / (2 * tile_b)) / cs * cs;
+      if (round < cs) continue;
+    }
     const int rounds = (per + round - 1) / round;
     if (NTL >= 4 && rounds > 1) continue;  // measured: beyond 24 rows a second round costs more than the tcgen05 GEMM
     // estimated time (us): the stream of W at the rate the loop reaches, stretched by uneven clusters and idle
-    // SMs; staging (36-byte blocks per thread, in batches of 4); per round two cluster barriers and the sums
+    // SMs; staging (36-byte blocks per thread, in batches of 4); per round a cluster barrier and the sums
     const double balance = ((double)a.ntiles / (per * clusters)) * ((double)(clusters * cs) / sm_count);
     const double t_loop = (double)a.ntiles * MMV_TR * a.row_bytes / 4.4e6 / balance;
     const double t_stage = 1.0 * (double)(((int64_t)a.m * cap_kb + 2047) / 2048);
@@ -951,7 +994,14 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
       best_clusters = clusters;
       best_cap = cap_kb;
       best_round = round;
+      best_bufs = bufs;
     }
+  }
+  static const bool trace = getenv("GSQ_MMV_TRACE") != nullptr;  // one line per launch plan on stderr
+  if (trace) {
+    fprintf(stderr, "mmv plan kind=%d ntl=%d xl=%d m=%d rows=%d k=%d: cs=%d clusters=%d round=%d bufs=%d est=%.1f us%s\n",
+            KIND, NTL, XL, a.m, a.nrows, a.k, best_cs, best_clusters, best_round, best_bufs, best_t,
+            best_cs ? "" : " (declined)");
   }
   if (!best_cs) return MMV_DECLINED;
   a.xcap_kb = best_cap;
@@ -964,7 +1014,9 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
   a.tiles_base = a.ntiles / best_clusters;
   a.tiles_extra = a.ntiles % best_clusters;
   a.tiles_round = best_round;
-  const size_t smem = fixed + mmv_x_bytes(best_cap, MC, DS) + (size_t)best_round * MMV_TR * MC * 4;
+  a.share_cap = (best_round + best_cs - 1) / best_cs;
+  a.gather_bufs = best_bufs;
+  const size_t smem = fixed + mmv_x_bytes(best_cap, MC, DS) + (size_t)best_bufs * best_cs * a.share_cap * MMV_TR * MC * 4;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(best_clusters * best_cs));
   cfg.blockDim = dim3(MMV_THREADS);
