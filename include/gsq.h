@@ -119,7 +119,7 @@ int gsq_quantize_q8_1_mmq(const void* x, int x_dtype, int64_t m, int64_t k, int6
                           void* out, void* stream);
 
 /*
- * Product with block_q8_1 activations, 1 .. gsq_mul_mat_vec_max_rows(type, packed) activation rows (8, or 32
+ * Product with block_q8_1 activations, 1 .. gsq_mul_mat_vec_max_rows(type, packed) activation rows (8, or 48
  * for Q4_K, IQ4_XS and packed IQ3_S): replaces the vendored MMVQ (ggml_cuda_op_mul_mat_vec_q, mmvq.cu:1538) and
  * the owned small-batch kernels iq3_mul_mat_vec (lcpp_shim.cu:498-572), own_mul_mat_vec
  * (lcpp_owned_k4.cu:116-234), iq3_mma / iq3_mma_packed (lcpp_owned_iq3_mma.cu:179-328, 483-600).
@@ -180,7 +180,7 @@ int gsq_debug_block_sums(const void* w, int64_t row_bytes, int64_t rows, int ggm
 
 /*
  * Product with block_q8_1_mmq activations, any number of activation rows (the register-operand tensor-core
- * kernel up to 32 rows where it fits, the tcgen05 kind::i8 GEMM with TMEM accumulators above): replaces
+ * kernel up to 48 rows where it fits, the tcgen05 kind::i8 GEMM with TMEM accumulators above): replaces
  * the vendored MMQ (mul_mat_q, mmq.cuh:961-1385 + shim host side lcpp_shim.cu:626-671) and the owned
  * mma_k (lcpp_owned_mma_k.cu:353-539) and iq3_packed_mmq (lcpp_owned_iq3_mma.cu:768-970).
  *   x_q8_mmq     k/128 * m blocks of 144 bytes in the type's layout (gsq_q8_layout_for_type)
@@ -199,7 +199,7 @@ int gsq_debug_gemm_ksplit(int ks); /* 0 = choose; 1, 2, 4 = CTAs per cluster tha
  * gsq_mul_mat_q8 (experiments and tests; each returns the previous value). */
 int gsq_debug_mmv_mode(int mode);        /* 0 = wherever it applies (default), 1 = never: dp4a GEMV / tcgen05 GEMM */
 int gsq_debug_mmv_min_rows(int n);       /* fewest activation rows it serves; 0 = per type (default) */
-int gsq_debug_mmv_max_rows(int n);       /* most activation rows it serves (default 24, at most 48) */
+int gsq_debug_mmv_max_rows(int n);       /* most activation rows it serves (default and at most 48) */
 int gsq_debug_mmv_cluster_size(int cs);  /* 0 = choose; 1, 2, 4, 8 = CTAs per cluster */
 int gsq_debug_mmv_pdl(int on);           /* programmatic dependent launch of that kernel (default on) */
 /* device buffer of 8 uint64 per CTA that receives time stamps (ns) at the kernel's phase boundaries, or NULL */

@@ -89,7 +89,7 @@ def descriptor_strides():
 
 
 @pytest.mark.parametrize("name,rows,k", CASES)
-@pytest.mark.parametrize("m", [9, 16, 33, 64, 65, 200])
+@pytest.mark.parametrize("m", [9, 16, 24, 33, 48, 64, 65, 200])
 def test_gemm_fp32_vs_reference_model(name, rows, k, m):
     raw, w = _weights(name, rows, k, 300 + rows)
     x = _x(m, k, torch.float32, 400 + m)

@@ -1,4 +1,4 @@
-// Register-operand int8 tensor-core product for 1..32 activation rows over GGUF superblocks (sm_100a).
+// Register-operand int8 tensor-core product for 1..48 activation rows over GGUF superblocks (sm_100a).
 //
 // Serves, behind gsq_mul_mat_vec_q8 and gsq_mul_mat_q8, the row counts at which the product is a stream of
 // W with a little arithmetic per byte: the reference's owned 1..8-row kernels (lcpp_owned_k4.cu:116-234,
@@ -63,6 +63,7 @@ struct MmvArgs {
   int tiles_round;   // tiles a cluster takes per round
   int share_cap;     // most tiles of a round one CTA owns (ceil(tiles_round / cluster size))
   int gather_bufs;   // 1: a single round; 2: rounds alternate between two gather areas
+  int aligned;       // 1: a warp's chunk is whole tiles (no parked segments, no room reserved for them)
   int xcap_kb;       // 32-value blocks of activations the shared-memory staging area holds per column
   int* dump;         // debug: int32 slice sums [m][nrows][k / 32]
   // fast_div_inv of: 16-byte granules and 36-byte blocks per staged column, for a CTA with nsr_lo superblocks
@@ -674,6 +675,12 @@ __host__ __device__ constexpr size_t mmv_x_bytes(int cap_kb, int mc, bool ds) {
 // it ends inside (tiles it covers whole go straight to the CTA's tile sums)
 __host__ __device__ inline size_t mmv_partial_bytes(int mc) { return (size_t)MMV_WARPS * 2 * MMV_TR * mc * 4; }
 
+// Records per warp in a round of tiles_r tiles of nsr records each: equal chunks (perfect balance, chunks cut
+// tiles), or, aligned, whole tiles per warp (nothing to park; used where the parked segments would not fit)
+__host__ __device__ inline int mmv_chunk(int tiles_r, int nsr, int aligned) {
+  return aligned ? ((tiles_r + MMV_WARPS - 1) / MMV_WARPS) * nsr : (tiles_r * nsr + MMV_WARPS - 1) / MMV_WARPS;
+}
+
 // superblocks [first, last) of the K range of CTA `rank` in a cluster of `cs`
 __host__ __device__ inline void mmv_k_range(int nsb, int cs, int rank, int* first, int* last) {
   *first = (int)((int64_t)nsb * rank / cs);
@@ -703,9 +710,10 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
   float* partial = reinterpret_cast<float*>(smem + GRID);
   // gather area: [buffer][source CTA][owned tile][16][MC]; every CTA of the cluster owns a contiguous share of
   // the round's tiles and receives, through distributed shared memory, each CTA's sums (one K part each) for them
-  float* gath = reinterpret_cast<float*>(smem + GRID + mmv_partial_bytes(MC));
+  const size_t part_bytes = a.aligned ? 0 : mmv_partial_bytes(MC);
+  float* gath = reinterpret_cast<float*>(smem + GRID + part_bytes);
   const size_t gath_bytes = (size_t)a.gather_bufs * cs * a.share_cap * SEGF * 4;
-  uint8_t* xq = smem + GRID + mmv_partial_bytes(MC) + gath_bytes;
+  uint8_t* xq = smem + GRID + part_bytes + gath_bytes;
   const int colb = mmv_xq_col_bytes(a.xcap_kb);
   float* xd = reinterpret_cast<float*>(xq + (size_t)colb * MC);
   float* xs = xd + (size_t)a.xcap_kb * MC;
@@ -721,7 +729,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
   int first_n = 0;
   {
     const int tiles_r = min(a.tiles_round, tile_cnt);
-    const int rr = tiles_r * nsr, c = (rr + MMV_WARPS - 1) / MMV_WARPS;
+    const int rr = tiles_r * nsr, c = mmv_chunk(tiles_r, nsr, a.aligned);
     const int idx0 = warp * c, idx1 = min(rr, idx0 + c);
     if (idx0 < idx1) {
       have_first = true;
@@ -769,7 +777,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
   for (int t0 = 0; t0 < tile_cnt; t0 += a.tiles_round) {
     const int tiles_r = min(a.tiles_round, tile_cnt - t0);
     const int rr = tiles_r * nsr;
-    const int c = (rr + MMV_WARPS - 1) / MMV_WARPS;  // records per warp this round
+    const int c = mmv_chunk(tiles_r, nsr, a.aligned);  // records per warp this round
     const int idx0 = warp * c, idx1 = min(rr, idx0 + c);
     float* mypart = partial + warp * (2 * SEGF);
 
@@ -894,7 +902,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
 
 static int g_mmv_mode = 0;      // 0 = use this kernel wherever it applies, 1 = never (the older kernels)
 static int g_mmv_min_rows = 0;  // fewest activation rows served here; 0 = per type (see mmv_applies)
-static int g_mmv_max_rows = 32; // most
+static int g_mmv_max_rows = 48; // most
 static int g_mmv_cluster = 0;   // experiments: 0 = choose, else 1, 2, 4 or 8
 static unsigned long long* g_mmv_prof = nullptr;
 static int g_mmv_pdl = 1;       // launch with programmatic stream serialisation
@@ -951,56 +959,63 @@ template <int KIND, int NTL, int XL, bool DUMP>
 static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) {
   constexpr int MC = 8 * NTL;
   constexpr bool DS = MmvKind<KIND>::DS;
-  const size_t fixed = MmvKind<KIND>::grid_bytes(NTL) + mmv_partial_bytes(MC);
   const int nsb = a.k >> 8;
   // Cluster size: the CTAs of a cluster split K, so each stages 1 / cs of the activations, and the cluster takes
-  // its tiles in rounds of as many as the per-CTA tile sums have room for. Among the sizes that fit, the one
-  // with the least estimated time.
-  int best_cs = 0, best_clusters = 0, best_cap = 0, best_round = 0, best_bufs = 1;
+  // its tiles in rounds of as many as the gather areas have room for. Chunking: equal chunks per warp, or (from
+  // 17 columns on, where the parked segments take a third of shared memory) whole tiles per warp. Among the
+  // combinations that fit, the one with the least estimated time.
+  int best_cs = 0, best_clusters = 0, best_cap = 0, best_round = 0, best_bufs = 1, best_aligned = 0;
   double best_t = 0.0;
-  for (int cs : {1, 2, 4, 8}) {
-    if (g_mmv_cluster && cs != g_mmv_cluster) continue;
-    if (cs > nsb) break;
-    const int cap_kb = ((nsb + cs - 1) / cs) * 8;
-    const size_t xb = mmv_x_bytes(cap_kb, MC, DS);
-    if (fixed + xb + (size_t)cs * MMV_TR * MC * 4 > (size_t)max_smem) continue;
-    // occupancy is asked for with the largest footprint this cluster size could use
-    int n = 0;
-    const int rc = mmv_max_clusters<KIND, NTL, XL, DUMP>(cs, (size_t)max_smem, sm_count, &n);
-    if (rc != GSQ_OK) return rc;
-    if (n <= 0) continue;
-    const int clusters = n < a.ntiles ? n : a.ntiles;
-    const int per = (a.ntiles + clusters - 1) / clusters;
-    // tiles per round: all of a cluster's tiles if one gather area for them fits, else rounds that alternate
-    // between two areas
-    const size_t avail = (size_t)max_smem - fixed - xb, tile_b = (size_t)MMV_TR * MC * 4;
-    int round = per, bufs = 1;
-    if ((size_t)cs * ((per + cs - 1) / cs) * tile_b > avail) {
-      bufs = 2;
-      round = (int)(avail / (2 * tile_b)) / cs * cs;
-      if (round < cs) continue;
-    }
-    const int rounds = (per + round - 1) / round;
-    if (NTL >= 4 && rounds > 1) continue;  // measured: beyond 24 rows a second round costs more than the tcgen05 GEMM
-    // estimated time (us): the stream of W at the rate the loop reaches, stretched by uneven clusters and idle
-    // SMs; staging (36-byte blocks per thread, in batches of 4); per round a cluster barrier and the sums
-    const double balance = ((double)a.ntiles / (per * clusters)) * ((double)(clusters * cs) / sm_count);
-    const double t_loop = (double)a.ntiles * MMV_TR * a.row_bytes / 4.4e6 / balance;
-    const double t_stage = 1.0 * (double)(((int64_t)a.m * cap_kb + 2047) / 2048);
-    const double t = t_loop + t_stage + 0.15 * cs + 2.5 * (rounds - 1);
-    if (!best_cs || t < best_t) {
-      best_t = t;
-      best_cs = cs;
-      best_clusters = clusters;
-      best_cap = cap_kb;
-      best_round = round;
-      best_bufs = bufs;
+  for (int aligned = 0; aligned <= (NTL >= 3 ? 1 : 0); ++aligned) {
+    const size_t fixed = MmvKind<KIND>::grid_bytes(NTL) + (aligned ? 0 : mmv_partial_bytes(MC));
+    for (int cs : {1, 2, 4, 8}) {
+      if (g_mmv_cluster && cs != g_mmv_cluster) continue;
+      if (cs > nsb) break;
+      const int cap_kb = ((nsb + cs - 1) / cs) * 8;
+      const size_t xb = mmv_x_bytes(cap_kb, MC, DS);
+      if (fixed + xb + (size_t)cs * MMV_TR * MC * 4 > (size_t)max_smem) continue;
+      // occupancy is asked for with the largest footprint this cluster size could use
+      int n = 0;
+      const int rc = mmv_max_clusters<KIND, NTL, XL, DUMP>(cs, (size_t)max_smem, sm_count, &n);
+      if (rc != GSQ_OK) return rc;
+      if (n <= 0) continue;
+      const int clusters = n < a.ntiles ? n : a.ntiles;
+      const int per = (a.ntiles + clusters - 1) / clusters;
+      // tiles per round: all of a cluster's tiles if one gather area for them fits, else rounds that alternate
+      // between two areas
+      const size_t avail = (size_t)max_smem - fixed - xb, tile_b = (size_t)MMV_TR * MC * 4;
+      int round = per, bufs = 1;
+      if ((size_t)cs * ((per + cs - 1) / cs) * tile_b > avail) {
+        bufs = 2;
+        round = (int)(avail / (2 * tile_b)) / cs * cs;
+        if (round < cs) continue;
+      }
+      const int rounds = (per + round - 1) / round;
+      if (NTL >= 4 && rounds > 1) continue;  // measured: beyond 24 rows a second round costs more than the tcgen05 GEMM
+      // estimated time (us): the stream of W at the rate the loop reaches, stretched by uneven clusters, idle
+      // SMs and (aligned) idle warps; staging (36-byte blocks per thread, in batches of 4); per round a cluster
+      // barrier and the sums
+      double balance = ((double)a.ntiles / (per * clusters)) * ((double)(clusters * cs) / sm_count);
+      if (aligned) balance *= (double)per / (MMV_WARPS * ((per + MMV_WARPS - 1) / MMV_WARPS));
+      const double t_loop = (double)a.ntiles * MMV_TR * a.row_bytes / 4.4e6 / balance * (NTL >= 3 ? 0.5 * NTL : 1.0);
+      const double t_stage = 1.0 * (double)(((int64_t)a.m * cap_kb + 2047) / 2048);
+      const double t = t_loop + t_stage + 0.15 * cs + 2.5 * (rounds - 1);
+      if (!best_cs || t < best_t) {
+        best_t = t;
+        best_cs = cs;
+        best_clusters = clusters;
+        best_cap = cap_kb;
+        best_round = round;
+        best_bufs = bufs;
+        best_aligned = aligned;
+      }
     }
   }
+  const size_t fixed = MmvKind<KIND>::grid_bytes(NTL) + (best_aligned ? 0 : mmv_partial_bytes(MC));
   static const bool trace = getenv("GSQ_MMV_TRACE") != nullptr;  // one line per launch plan on stderr
   if (trace) {
-    fprintf(stderr, "mmv plan kind=%d ntl=%d xl=%d m=%d rows=%d k=%d: cs=%d clusters=%d round=%d bufs=%d est=%.1f us%s\n",
-            KIND, NTL, XL, a.m, a.nrows, a.k, best_cs, best_clusters, best_round, best_bufs, best_t,
+    fprintf(stderr, "mmv plan kind=%d ntl=%d xl=%d m=%d rows=%d k=%d: cs=%d clusters=%d round=%d bufs=%d aligned=%d est=%.1f us%s\n",
+            KIND, NTL, XL, a.m, a.nrows, a.k, best_cs, best_clusters, best_round, best_bufs, best_aligned, best_t,
             best_cs ? "" : " (declined)");
   }
   if (!best_cs) return MMV_DECLINED;
@@ -1016,6 +1031,7 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
   a.tiles_round = best_round;
   a.share_cap = (best_round + best_cs - 1) / best_cs;
   a.gather_bufs = best_bufs;
+  a.aligned = best_aligned;
   const size_t smem = fixed + mmv_x_bytes(best_cap, MC, DS) + (size_t)best_bufs * best_cs * a.share_cap * MMV_TR * MC * 4;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(best_clusters * best_cs));
@@ -1104,6 +1120,7 @@ int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int 
   a.ldy = y_row_stride;
   a.ntiles = (int)((rows + MMV_TR - 1) / MMV_TR);
   a.tiles_base = a.tiles_extra = a.tiles_round = 0;
+  a.aligned = 0;
   a.xcap_kb = 0;
   a.dump = dump;
   a.prof = g_mmv_prof;
