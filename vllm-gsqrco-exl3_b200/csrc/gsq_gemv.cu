@@ -678,6 +678,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
     __syncthreads();
   }
 
+  // Up to here nothing depends on the kernel that wrote the activations: launched with programmatic stream
+  // serialisation, the first weight loads and the codebook copy overlap its tail (a no-op otherwise).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   for (int t0 = 0; t0 < tile_cnt; t0 += a.tiles_round) {
     const int tiles_r = min(a.tiles_round, tile_cnt - t0);
     const int rr = tiles_r * nrec;
@@ -894,13 +897,15 @@ static int launch_gemv_t(GemvArgs a, int sm_count, int max_smem, cudaStream_t st
   cfg.blockDim = dim3(GEMV_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = plan.cs;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = plan.cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see griddepcontrol.wait in the kernel
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
   GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_kernel<KIND, M, RS, DUMP, TMA>, a));
   return GSQ_OK;
 }

@@ -964,10 +964,14 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
   // its tiles in rounds of as many as the gather areas have room for. Chunking: equal chunks per warp, or (from
   // 17 columns on, where the parked segments take a third of shared memory) whole tiles per warp. Among the
   // combinations that fit, the one with the least estimated time.
-  int best_cs = 0, best_clusters = 0, best_cap = 0, best_round = 0, best_bufs = 1, best_aligned = 0;
-  double best_t = 0.0;
-  for (int aligned = 0; aligned <= (NTL >= 3 ? 1 : 0); ++aligned) {
+  struct Plan { int cs, clusters, cap, round, bufs, per; double t; };
+  Plan plans[2] = {{0, 0, 0, 0, 1, 0, 0.0}, {0, 0, 0, 0, 1, 0, 0.0}};
+  static const char* force_env = getenv("GSQ_MMV_ALIGNED");  // experiments: "0" / "1" forces the chunking
+  const int force_aligned = force_env ? atoi(force_env) : -1;
+  for (int aligned = 0; aligned <= (NTL >= 2 ? 1 : 0); ++aligned) {
+    if (force_aligned >= 0 && NTL >= 2 && aligned != force_aligned) continue;
     const size_t fixed = MmvKind<KIND>::grid_bytes(NTL) + (aligned ? 0 : mmv_partial_bytes(MC));
+    Plan& best = plans[aligned];
     for (int cs : {1, 2, 4, 8}) {
       if (g_mmv_cluster && cs != g_mmv_cluster) continue;
       if (cs > nsb) break;
@@ -992,25 +996,29 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
       }
       const int rounds = (per + round - 1) / round;
       if (NTL >= 4 && rounds > 1) continue;  // measured: beyond 24 rows a second round costs more than the tcgen05 GEMM
-      // estimated time (us): the stream of W at the rate the loop reaches, stretched by uneven clusters, idle
-      // SMs and (aligned) idle warps; staging (36-byte blocks per thread, in batches of 4); per round a cluster
-      // barrier and the sums
+      // estimated time (us): the stream of W at the rate the loop reaches, stretched by uneven clusters and idle
+      // SMs; staging (36-byte blocks per thread, in batches of 4); per round a cluster barrier and the sums
       double balance = ((double)a.ntiles / (per * clusters)) * ((double)(clusters * cs) / sm_count);
+      // whole tiles per warp: warps without a tile idle (this ranks the cluster sizes of that mode; the choice
+      // between the modes is made below, from measurements)
       if (aligned) balance *= (double)per / (MMV_WARPS * ((per + MMV_WARPS - 1) / MMV_WARPS));
       const double t_loop = (double)a.ntiles * MMV_TR * a.row_bytes / 4.4e6 / balance * (NTL >= 3 ? 0.5 * NTL : 1.0);
       const double t_stage = 1.0 * (double)(((int64_t)a.m * cap_kb + 2047) / 2048);
       const double t = t_loop + t_stage + 0.15 * cs + 2.5 * (rounds - 1);
-      if (!best_cs || t < best_t) {
-        best_t = t;
-        best_cs = cs;
-        best_clusters = clusters;
-        best_cap = cap_kb;
-        best_round = round;
-        best_bufs = bufs;
-        best_aligned = aligned;
-      }
+      if (!best.cs || t < best.t) best = Plan{cs, clusters, cap_kb, round, bufs, per, t};
     }
   }
+  // Chunking, as measured: from 17 columns on whole tiles per warp win (no parking code in the loop, the parked
+  // segments' third of shared memory goes to a smaller cluster); at 9-16 columns they win where a CTA has few
+  // records (parking then costs as much as the arithmetic); below, equal chunks.
+  int best_aligned = 0;
+  if (plans[1].cs) {
+    const int recs_per_cta = plans[1].per * ((nsb + plans[1].cs - 1) / plans[1].cs);
+    if (!plans[0].cs || NTL >= 3 || recs_per_cta <= 64) best_aligned = 1;
+  }
+  const int best_cs = plans[best_aligned].cs, best_clusters = plans[best_aligned].clusters, best_cap = plans[best_aligned].cap,
+            best_round = plans[best_aligned].round, best_bufs = plans[best_aligned].bufs;
+  const double best_t = plans[best_aligned].t;
   const size_t fixed = MmvKind<KIND>::grid_bytes(NTL) + (best_aligned ? 0 : mmv_partial_bytes(MC));
   static const bool trace = getenv("GSQ_MMV_TRACE") != nullptr;  // one line per launch plan on stderr
   if (trace) {
