@@ -968,8 +968,8 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
   Plan plans[2] = {{0, 0, 0, 0, 1, 0, 0.0}, {0, 0, 0, 0, 1, 0, 0.0}};
   static const char* force_env = getenv("GSQ_MMV_ALIGNED");  // experiments: "0" / "1" forces the chunking
   const int force_aligned = force_env ? atoi(force_env) : -1;
-  for (int aligned = 0; aligned <= (NTL >= 2 ? 1 : 0); ++aligned) {
-    if (force_aligned >= 0 && NTL >= 2 && aligned != force_aligned) continue;
+  for (int aligned = 0; aligned <= 1; ++aligned) {
+    if (force_aligned >= 0 && aligned != force_aligned) continue;
     const size_t fixed = MmvKind<KIND>::grid_bytes(NTL) + (aligned ? 0 : mmv_partial_bytes(MC));
     Plan& best = plans[aligned];
     for (int cs : {1, 2, 4, 8}) {
@@ -1009,8 +1009,8 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
     }
   }
   // Chunking, as measured: from 17 columns on whole tiles per warp win (no parking code in the loop, the parked
-  // segments' third of shared memory goes to a smaller cluster); at 9-16 columns they win where a CTA has few
-  // records (parking then costs as much as the arithmetic); below, equal chunks.
+  // segments' third of shared memory goes to a smaller cluster); up to 16 columns they win where a CTA has few
+  // records (parking then costs as much as the arithmetic), equal chunks otherwise.
   int best_aligned = 0;
   if (plans[1].cs) {
     const int recs_per_cta = plans[1].per * ((nsb + plans[1].cs - 1) / plans[1].cs);

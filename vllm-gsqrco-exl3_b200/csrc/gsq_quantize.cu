@@ -64,6 +64,9 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
   // a product kernel launched behind this one with programmatic stream serialisation may start its prologue now;
   // it waits for this grid to finish before it reads `out`
   asm volatile("griddepcontrol.launch_dependents;");
+  // this kernel is itself launched with programmatic stream serialisation: it may be scheduled while the kernel
+  // before it drains, and waits here until that one has finished and its writes (X, perhaps) are visible
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 8 values
   const int64_t per_row = k >> 3;
   // whole warps stay together: k % 32 == 0 makes per_row a multiple of 4, so a 4-thread group never
@@ -110,6 +113,9 @@ template <typename T, bool VEC, int LAYOUT>
 __global__ void __launch_bounds__(256) quantize_q8_1_mmq_kernel(const T* __restrict__ x, uint8_t* __restrict__ out,
                                                                int64_t m, int64_t k, int64_t stride) {
   asm volatile("griddepcontrol.launch_dependents;");
+  // this kernel is itself launched with programmatic stream serialisation: it may be scheduled while the kernel
+  // before it drains, and waits here until that one has finished and its writes (X, perhaps) are visible
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t per_row = k >> 3;
   const bool live = t < m * per_row;
@@ -157,19 +163,31 @@ __global__ void __launch_bounds__(256) quantize_q8_1_mmq_kernel(const T* __restr
   }
 }
 
+// launch with programmatic stream serialisation (see griddepcontrol.wait in the kernels)
+template <typename... KArgs, typename... Args>
+static int launch_pdl(void (*kern)(KArgs...), unsigned grid, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, args...));
+  return GSQ_OK;
+}
+
 template <typename T>
 static int launch_q8_1(const void* x, int64_t m, int64_t k, int64_t stride, void* out, cudaStream_t st) {
   const int64_t threads = m * (k >> 3);
   if (threads == 0) return GSQ_OK;
   const unsigned grid = (unsigned)((threads + 255) / 256);
   const bool vec = ((uintptr_t)x % 16 == 0) && ((stride * (int64_t)sizeof(T)) % 16 == 0);
-  if (vec) {
-    quantize_q8_1_kernel<T, true><<<grid, 256, 0, st>>>((const T*)x, (uint8_t*)out, m, k, stride);
-  } else {
-    quantize_q8_1_kernel<T, false><<<grid, 256, 0, st>>>((const T*)x, (uint8_t*)out, m, k, stride);
-  }
-  GSQ_CUDA_TRY(cudaGetLastError());
-  return GSQ_OK;
+  return vec ? launch_pdl(quantize_q8_1_kernel<T, true>, grid, st, (const T*)x, (uint8_t*)out, m, k, stride)
+             : launch_pdl(quantize_q8_1_kernel<T, false>, grid, st, (const T*)x, (uint8_t*)out, m, k, stride);
 }
 
 template <typename T, int LAYOUT>
@@ -178,13 +196,8 @@ static int launch_q8_1_mmq(const void* x, int64_t m, int64_t k, int64_t stride, 
   if (threads == 0) return GSQ_OK;
   const unsigned grid = (unsigned)((threads + 255) / 256);
   const bool vec = ((uintptr_t)x % 16 == 0) && ((stride * (int64_t)sizeof(T)) % 16 == 0);
-  if (vec) {
-    quantize_q8_1_mmq_kernel<T, true, LAYOUT><<<grid, 256, 0, st>>>((const T*)x, (uint8_t*)out, m, k, stride);
-  } else {
-    quantize_q8_1_mmq_kernel<T, false, LAYOUT><<<grid, 256, 0, st>>>((const T*)x, (uint8_t*)out, m, k, stride);
-  }
-  GSQ_CUDA_TRY(cudaGetLastError());
-  return GSQ_OK;
+  return vec ? launch_pdl(quantize_q8_1_mmq_kernel<T, true, LAYOUT>, grid, st, (const T*)x, (uint8_t*)out, m, k, stride)
+             : launch_pdl(quantize_q8_1_mmq_kernel<T, false, LAYOUT>, grid, st, (const T*)x, (uint8_t*)out, m, k, stride);
 }
 
 }  // namespace gsq
