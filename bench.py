@@ -44,8 +44,9 @@ for p in (ROOT, os.path.join(ROOT, "vllm-gsqrco-exl3_b200")):
         sys.path.insert(0, p)
 
 SHAPES = [(5120, 5120), (17408, 5120), (5120, 17408)]
-# DRAM bytes moved per weight byte by the small-batch kernels (profiles/: 38.38 MB read + 0.3 MB written for 38.30 MB)
-NCU_TRAFFIC_RATIO = 1.01
+# DRAM bytes moved per weight byte by the small-batch kernel (profiles/mmv_iq3s_m8.txt: 38.384 MB read, 256 B
+# written, for 38.298 MB of weights)
+NCU_TRAFFIC_RATIO = 1.0023
 TYPES = [("IQ3_S", 21), ("Q4_K", 12)]
 ROWS = [1, 2, 4, 8, 12, 16, 24, 32, 48]
 BLOCK_BYTES = {21: 110, 12: 144, 23: 136, 14: 210}
