@@ -229,8 +229,15 @@ def run_ours(args):
         launches["n"] += 1 + (m + 7) // 8
         if world > 1 and key_m is not None:
             kind, off, cnt = tp_slots[key_m]
-            (flat_n if kind == "N" else flat_k)[off:off + cnt].view_as(y).copy_(y)
+            tp_pending.append(((flat_n if kind == "N" else flat_k)[off:off + cnt].view_as(y), y))
         return y
+
+    tp_pending = []   # (slot in a flat buffer, result): copied by one multi-tensor kernel at the end of a step
+
+    def tp_flush():
+        if tp_pending:
+            torch._foreach_copy_([d for d, _ in tp_pending], [y for _, y in tp_pending])
+            tp_pending.clear()
 
     def collectives():
         if world > 1:
@@ -240,6 +247,7 @@ def run_ours(args):
     def compute():
         for key, m in order:
             product(cells[key], xs[(key[2], m)], (key, m))
+        tp_flush()
 
     def step():
         compute()
@@ -272,6 +280,7 @@ def run_ours(args):
                 with torch.cuda.stream(s_out):
                     outs[i].copy_(y, non_blocking=True)
                 keep.append(y)
+        tp_flush()
         cur.wait_stream(s_in)
         cur.wait_stream(s_out)
         del keep
