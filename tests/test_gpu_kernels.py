@@ -321,3 +321,30 @@ def test_apply_single_type_and_unfused():
     y2 = m2.apply(layer2, x.to(DEV))
     ref2 = product.product_q81(blocks.decode(raw, IQ4_XS), q, d.astype(np.float32))
     assert product.rel_err(_to_np(y2), ref2) <= 1e-3
+
+
+@pytest.mark.parametrize("name,packed", [("Q4_K", False), ("IQ3_S", True), ("IQ4_XS", False)])
+@pytest.mark.parametrize("rows,k", [(2176, 5120), (640, 5120), (5120, 2048), (5120, 2304), (5120, 4352)])
+def test_tensor_parallel_shard_shapes(name, packed, rows, k):
+    """The shard shapes of 4- and 8-way tensor parallelism of the benchmark's layers (row shards of 17408 / 5120 rows,
+    K shards of 8, 9 and 17 superblocks): the library's own choice of kernel against the other kernel behind the same
+    op (dp4a GEMV, tcgen05 GEMM), at 1, 8 and 32 activation rows."""
+    from gsq_b200 import lcpp_ops
+
+    old_k = lcpp_ops.set_k_multiple(256)
+    try:
+        raw, w = _weights(name, rows, k, 900 + rows % 97 + k % 89, packed)
+        many = {"Q4_K": "lcpp_mul_mat_q", "IQ4_XS": "lcpp_mul_mat_q", "IQ3_S": "lcpp_mul_mat_iq3_packed"}[name]
+        for m in (1, 8, 32):
+            x = _x(m, k, torch.float32, 950 + m).to(DEV)
+            op = _op_for(name, packed) if m <= 8 else many
+            y = getattr(torch.ops._C_gguf, op)(w, x, TYPES[name], rows)
+            old = _cabi.lib.gsq_debug_mmv_mode(1)
+            try:
+                ref = getattr(torch.ops._C_gguf, op)(w, x, TYPES[name], rows)   # dp4a GEMV / tcgen05 GEMM
+            finally:
+                _cabi.lib.gsq_debug_mmv_mode(old)
+            err = product.rel_err(y.cpu().numpy(), ref.double().cpu().numpy())
+            assert err <= 1e-3, (name, rows, k, m, err)
+    finally:
+        lcpp_ops.set_k_multiple(old_k)
