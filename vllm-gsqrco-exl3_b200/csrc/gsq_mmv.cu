@@ -64,6 +64,7 @@ struct MmvArgs {
   int share_cap;     // most tiles of a round one CTA owns (ceil(tiles_round / cluster size))
   int gather_bufs;   // 1: a single round; 2: rounds alternate between two gather areas
   int aligned;       // 1: a warp's chunk is whole tiles (no parked segments, no room reserved for them)
+  int pf_first;      // records of its chunk a warp requests from L2 before the activations are staged
   int xcap_kb;       // 32-value blocks of activations the shared-memory staging area holds per column
   int* dump;         // debug: int32 slice sums [m][nrows][k / 32]
   // fast_div_inv of: 16-byte granules and 36-byte blocks per staged column, for a CTA with nsr_lo superblocks
@@ -735,7 +736,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
       have_first = true;
       first_tl = idx0 / nsr;
       first_rec = idx0 - first_tl * nsr;
-      first_n = min(2, idx1 - idx0);
+      first_n = min(a.pf_first, idx1 - idx0);
     }
   }
   // Everything up to here, the requests to L2 for the warp's first two records and the codebook copy do not
@@ -906,6 +907,7 @@ static int g_mmv_max_rows = 48; // most
 static int g_mmv_cluster = 0;   // experiments: 0 = choose, else 1, 2, 4 or 8
 static unsigned long long* g_mmv_prof = nullptr;
 static int g_mmv_pdl = 1;       // launch with programmatic stream serialisation
+static int g_mmv_pf_first = 2;  // records requested from L2 ahead of the staging
 
 constexpr int MMV_DECLINED = 1000;  // mmv_host: this shape does not fit; use another kernel
 
@@ -1040,6 +1042,7 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
   a.share_cap = (best_round + best_cs - 1) / best_cs;
   a.gather_bufs = best_bufs;
   a.aligned = best_aligned;
+  a.pf_first = g_mmv_pf_first;
   const size_t smem = fixed + mmv_x_bytes(best_cap, MC, DS) + (size_t)best_bufs * best_cs * a.share_cap * MMV_TR * MC * 4;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(best_clusters * best_cs));
@@ -1170,6 +1173,12 @@ extern "C" int gsq_debug_mmv_max_rows(int n) {
 
 extern "C" int gsq_mul_mat_vec_max_rows(int ggml_type, int packed) {
   return gsq::mmv_applies(ggml_type, packed, 16, gsq::g_mmv_max_rows) ? gsq::g_mmv_max_rows : 8;
+}
+
+extern "C" int gsq_debug_mmv_prefetch_first(int n) {
+  const int old = gsq::g_mmv_pf_first;
+  gsq::g_mmv_pf_first = n < 0 ? 0 : n > 64 ? 64 : n;
+  return old;
 }
 
 extern "C" int gsq_debug_mmv_pdl(int on) {
