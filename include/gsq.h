@@ -202,7 +202,7 @@ int gsq_debug_mmv_min_rows(int n);       /* fewest activation rows it serves; 0 
 int gsq_debug_mmv_max_rows(int n);       /* most activation rows it serves (default and at most 48) */
 int gsq_debug_mmv_cluster_size(int cs);  /* 0 = choose; 1, 2, 4, 8 = CTAs per cluster */
 int gsq_debug_mmv_prefetch_first(int n); /* records a warp requests from L2 before the staging (default 2) */
-int gsq_debug_mmv_pdl(int on);           /* programmatic dependent launch of that kernel (default on) */
+int gsq_debug_mmv_pdl(int on);           /* programmatic dependent launch: 0 = off, 1 = on, 2 = and the kernel lets the next one start early where that measured faster (default), 3 = everywhere */
 /* device buffer of 8 uint64 per CTA that receives time stamps (ns) at the kernel's phase boundaries, or NULL */
 int gsq_debug_mmv_profile(unsigned long long* stamps);
 /* Most activation rows one gsq_mul_mat_vec_q8 call takes for this type (8, or 48 where the kernel above serves it). */

@@ -348,3 +348,41 @@ def test_tensor_parallel_shard_shapes(name, packed, rows, k):
             assert err <= 1e-3, (name, rows, k, m, err)
     finally:
         lcpp_ops.set_k_multiple(old_k)
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 24])
+def test_chained_launches_do_not_depend_on_overlap(m):
+    """Back-to-back products in one stream (quantiser -> product -> quantiser -> ..., each launched as a programmatic
+    dependent of the one before, the products letting the next kernels start before they have finished): every
+    result, the ones feeding the next product included, is bit-equal to the chain run with that overlap switched off."""
+    k = 5120
+    ws = []
+    for name, packed, rows in (("IQ3_S", True, 5120), ("Q4_K", False, 5120), ("IQ4_XS", False, 5120), ("IQ3_S", True, 5120),
+                               ("Q6_K", False, 5120)):
+        ws.append((name, packed, rows, _weights(name, rows, k, 1300 + len(ws), packed)[1]))
+    # fp32 results, and a start small enough that the fp16 block scales and block sums of the fifth quantisation still
+    # fit: the synthetic weights gain 20x to 1000x per product, 1e7 over the first four (largest gain last)
+    x0 = (_x(m, k, torch.float32, 1310 + m) * 3e-5).to(DEV)
+
+    def chain():
+        outs, x = [], x0
+        for name, packed, rows, w in ws:
+            op = linear._lcpp_op(m, TYPES[name], rows, k, packed)
+            y = getattr(torch.ops._C_gguf, op)(w, x, TYPES[name], rows)
+            outs.append(y)
+            x = y  # the next product quantises this result (5120 -> 5120), with no other kernel in between
+        torch.cuda.synchronize()
+        return [o.clone() for o in outs]
+
+    results = {}
+    for mode in (0, 1, 2, 3):
+        old = _cabi.lib.gsq_debug_mmv_pdl(mode)
+        try:
+            results[mode] = chain()
+            results[(mode, "again")] = chain()
+        finally:
+            _cabi.lib.gsq_debug_mmv_pdl(old)
+    for key, outs in results.items():
+        for i, (a, b) in enumerate(zip(outs, results[0])):
+            assert torch.isfinite(a).all()
+            assert torch.equal(a, b), (key, i, ws[i][0])

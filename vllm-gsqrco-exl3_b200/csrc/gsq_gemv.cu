@@ -62,6 +62,7 @@ struct GemvArgs {
   int force_direct;  // tests: use the direct-load variant even where the staged one applies
   int* dump;         // debug only: integer slice sums
   int dump_m0;
+  int early;         // let the next kernel of a programmatic-launch chain start while this one runs
 };
 
 template <int KIND>
@@ -781,6 +782,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
       }
     }
     cluster.sync();
+    // The next kernels of a programmatic-launch chain write nothing before their own wait, which holds until this
+    // grid has finished, so they may start while the sums are added. Not earlier than this barrier: the warps read
+    // the activations through L1 for as long as they stream records, and a kernel launched meanwhile that reads new
+    // activations at the same address through the same L1 could be served the old lines.
+    if (a.early && t0 + a.tiles_round >= tile_cnt) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // every row of the round: add the partial sums of the warps that touched its tile, in warp order
     const int rows_r = tiles_r * TR;
     for (int e = crank * GEMV_THREADS + tid; e < rows_r * M; e += cs * GEMV_THREADS) {
@@ -938,6 +944,7 @@ static int launch_gemv_m(int m, const GemvArgs& a, int sm_count, int max_smem, c
 
 // gsq_mmv.cu: the tensor-core kernel for 1..48 rows
 bool mmv_applies(int ggml_type, int packed, int64_t rows, int64_t m);
+bool mmv_early_trigger();
 int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* xq, int x_layout,
              int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump);
 
@@ -987,6 +994,7 @@ static int gemv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_ty
   a.dump_m0 = dump_m0;
   a.stage_shift = 0;
   a.force_direct = g_force_direct;
+  a.early = mmv_early_trigger() ? 1 : 0;
   cudaStream_t st = (cudaStream_t)stream;
   const int sms = di.sm_count, smem = di.max_smem_optin;
 

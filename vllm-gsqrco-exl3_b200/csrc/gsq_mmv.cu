@@ -65,6 +65,7 @@ struct MmvArgs {
   int gather_bufs;   // 1: a single round; 2: rounds alternate between two gather areas
   int aligned;       // 1: a warp's chunk is whole tiles (no parked segments, no room reserved for them)
   int pf_first;      // records of its chunk a warp requests from L2 before the activations are staged
+  int early;         // let the next kernel of a programmatic-launch chain start its prologue while this one runs
   int xcap_kb;       // 32-value blocks of activations the shared-memory staging area holds per column
   int* dump;         // debug: int32 slice sums [m][nrows][k / 32]
   // fast_div_inv of: 16-byte granules and 36-byte blocks per staged column, for a CTA with nsr_lo superblocks
@@ -198,6 +199,8 @@ __device__ __forceinline__ void stage_x_pad(int m, int nkb, int colb, uint8_t* x
 // 16-byte granules (K is a multiple of 128); every granule is loaded exactly once, by consecutive threads, and
 // its four words go where their position in the 9-word blocks says: word 0 of a block is (d, sum), the other
 // eight are quants. All 148 CTAs read the same few KB at the same time, so requests per byte are what counts.
+// The activations are read with ld.global.cg (L2, never L1): each granule is needed once per CTA, and a kernel that may
+// be resident while its predecessors still run must not meet lines they left in this SM's L1.
 // slot of quant word w in a staged 32-byte block. PERM: words (t, t + 4) side by side for the kinds whose 4-byte
 // weight word holds values 4t..4t+3 in its low and 16+4t..16+4t+3 in its high nibbles (IQ4_XS).
 template <bool PERM>
@@ -221,7 +224,7 @@ __device__ __forceinline__ void stage_x_q81(const MmvArgs& a, int kb0, int nkb, 
       const int i = min(i0 + u * MMV_THREADS, total - 1);
       col[u] = fast_div(i, inv);
       gi[u] = i - col[u] * gpc;
-      v[u] = __ldg(reinterpret_cast<const uint4*>(a.xq + ((int64_t)col[u] * nb32 + kb0) * 36) + gi[u]);
+      v[u] = __ldcg(reinterpret_cast<const uint4*>(a.xq + ((int64_t)col[u] * nb32 + kb0) * 36) + gi[u]);
     }
     if (i0 == tid) {
       after_issue();
@@ -276,7 +279,7 @@ __device__ __forceinline__ void stage_x_mmq(const MmvArgs& a, int kb0, int nkb, 
   for (int i0 = tid; i0 < total || i0 == tid; i0 += 8 * MMV_THREADS) {
     uint4 v[8];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) v[u] = __ldg(src + min(i0 + u * MMV_THREADS, total - 1));
+    for (int u = 0; u < 8; ++u) v[u] = __ldcg(src + min(i0 + u * MMV_THREADS, total - 1));
     if (i0 == tid) after_issue();
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
@@ -845,6 +848,12 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
         rec = nrc;
       }
     }
+    // The next kernels of a programmatic-launch chain (an activation quantiser, then the next product) write nothing
+    // before their own griddepcontrol.wait, which holds until this grid has finished. Letting them start once the
+    // warp has streamed its last record hides their launch, and their prologue (codebook copy, first requests to
+    // L2) overlaps the barrier, the sums and the stores here. It comes after this kernel's own wait, so the chain
+    // never runs more than one product ahead.
+    if (a.early && t0 + a.tiles_round >= tile_cnt) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (t0 == 0) mmv_stamp(a, 2);
     __syncthreads();
     // Tile tl of the round is owned by CTA tl / share_cap of the cluster.
@@ -906,8 +915,11 @@ static int g_mmv_min_rows = 0;  // fewest activation rows served here; 0 = per t
 static int g_mmv_max_rows = 48; // most
 static int g_mmv_cluster = 0;   // experiments: 0 = choose, else 1, 2, 4 or 8
 static unsigned long long* g_mmv_prof = nullptr;
-static int g_mmv_pdl = 1;       // launch with programmatic stream serialisation
+static int g_mmv_pdl = 2;       // programmatic stream serialisation: 0 off, 1 on, 2 + early start of the dependents where it pays, 3 + everywhere
 static int g_mmv_pf_first = 2;  // records requested from L2 ahead of the staging
+
+// shared with the dp4a kernel: whether a product lets the next kernels of a programmatic-launch chain start early
+bool mmv_early_trigger() { return g_mmv_pdl >= 2; }
 
 constexpr int MMV_DECLINED = 1000;  // mmv_host: this shape does not fit; use another kernel
 
@@ -1043,6 +1055,9 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
   a.gather_bufs = best_bufs;
   a.aligned = best_aligned;
   a.pf_first = g_mmv_pf_first;
+  // measured: the early start pays where the next product has a codebook to copy meanwhile (IQ3_S: -1 us on most
+  // shapes) and costs up to 1 us elsewhere (the quantiser's blocks then land on the few SMs that drained first)
+  a.early = g_mmv_pdl >= 3 || (g_mmv_pdl == 2 && KIND == MK_IQ3S);
   const size_t smem = fixed + mmv_x_bytes(best_cap, MC, DS) + (size_t)best_bufs * best_cs * a.share_cap * MMV_TR * MC * 4;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(best_clusters * best_cs));
@@ -1183,7 +1198,7 @@ extern "C" int gsq_debug_mmv_prefetch_first(int n) {
 
 extern "C" int gsq_debug_mmv_pdl(int on) {
   const int old = gsq::g_mmv_pdl;
-  gsq::g_mmv_pdl = on ? 1 : 0;
+  gsq::g_mmv_pdl = on < 0 ? 0 : on > 3 ? 3 : on;
   return old;
 }
 

@@ -33,21 +33,23 @@ template <>
 __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
 // 8 consecutive values of row `row` starting at column c (c % 8 == 0). VEC: 16-byte aligned rows.
+// Loads go to L2 (ld.global.cg): launched as a programmatic dependent, this kernel can be resident while the
+// kernel that writes X still runs, so X is not read-only for its lifetime and the non-coherent path is not valid.
 template <typename T, bool VEC>
 __device__ __forceinline__ void load8(const T* __restrict__ x, int64_t off, float (&v)[8]) {
   if constexpr (VEC && sizeof(T) == 2) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(x + off);
+    const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(x + off));
     const T* p = reinterpret_cast<const T*>(&raw);
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = to_f32<T>(p[e]);
   } else if constexpr (VEC && sizeof(T) == 4) {
-    const float4 a = *reinterpret_cast<const float4*>(x + off);
-    const float4 b = *reinterpret_cast<const float4*>(x + off + 4);
+    const float4 a = __ldcg(reinterpret_cast<const float4*>(x + off));
+    const float4 b = __ldcg(reinterpret_cast<const float4*>(x + off + 4));
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
     v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
   } else {
 #pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = to_f32<T>(x[off + e]);
+    for (int e = 0; e < 8; ++e) v[e] = to_f32<T>(__ldcg(x + off + e));
   }
 }
 
