@@ -1024,11 +1024,13 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
   }
   // Chunking, as measured: from 17 columns on whole tiles per warp win (no parking code in the loop, the parked
   // segments' third of shared memory goes to a smaller cluster); up to 16 columns they win where a CTA has few
-  // records (parking then costs as much as the arithmetic), equal chunks otherwise.
+  // records (parking then costs as much as the arithmetic) or where the tiles of a round nearly fill the warps
+  // (15 tiles on 16 warps: the estimate, which leaves the parking out, then puts whole tiles within 1 us of equal
+  // chunks, and they measured 0.5 - 1.2 us faster); equal chunks otherwise.
   int best_aligned = 0;
   if (plans[1].cs) {
     const int recs_per_cta = plans[1].per * ((nsb + plans[1].cs - 1) / plans[1].cs);
-    if (!plans[0].cs || NTL >= 3 || recs_per_cta <= 64) best_aligned = 1;
+    if (!plans[0].cs || NTL >= 3 || recs_per_cta <= 64 || plans[1].t <= plans[0].t + 1.0) best_aligned = 1;
   }
   const int best_cs = plans[best_aligned].cs, best_clusters = plans[best_aligned].clusters, best_cap = plans[best_aligned].cap,
             best_round = plans[best_aligned].round, best_bufs = plans[best_aligned].bufs;
@@ -1055,9 +1057,10 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
   a.gather_bufs = best_bufs;
   a.aligned = best_aligned;
   a.pf_first = g_mmv_pf_first;
-  // measured: the early start pays where the next product has a codebook to copy meanwhile (IQ3_S: -1 us on most
-  // shapes) and costs up to 1 us elsewhere (the quantiser's blocks then land on the few SMs that drained first)
-  a.early = g_mmv_pdl >= 3 || (g_mmv_pdl == 2 && KIND == MK_IQ3S);
+  // measured: the early start pays where the next product has a codebook to copy meanwhile and this grid leaves
+  // some SMs free for the waiting quantiser (IQ3_S, 132 of 148 SMs: -1 us); it costs up to 1 us elsewhere (on a
+  // full GPU the quantiser's blocks all land on the few SMs that drained first)
+  a.early = g_mmv_pdl >= 3 || (g_mmv_pdl == 2 && KIND == MK_IQ3S && best_clusters * best_cs + 8 <= sm_count);
   const size_t smem = fixed + mmv_x_bytes(best_cap, MC, DS) + (size_t)best_bufs * best_cs * a.share_cap * MMV_TR * MC * 4;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(best_clusters * best_cs));
