@@ -386,3 +386,28 @@ def test_chained_launches_do_not_depend_on_overlap(m):
         for i, (a, b) in enumerate(zip(outs, results[0])):
             assert torch.isfinite(a).all()
             assert torch.equal(a, b), (key, i, ws[i][0])
+
+
+@pytest.mark.parametrize("k", [2304, 4352])
+@pytest.mark.parametrize("mmq", [False, True])
+def test_quantize_op_on_tensor_parallel_k_shards(k, mmq):
+    """The stand-alone quantise op follows the same relaxed K granularity as the products (K shards of 9 and 17
+    superblocks are multiples of 256, not of 512) and its bytes feed a product to the same result."""
+    from gsq_b200 import lcpp_ops
+
+    x = _x(5, k, torch.float16, 1400 + k).to(DEV)
+    with pytest.raises(RuntimeError, match="bad arguments"):
+        torch.ops._C_gguf.lcpp_quantize_q8_1(x, Q4_K, mmq, False)
+    old_k = lcpp_ops.set_k_multiple(256)
+    try:
+        xq = torch.ops._C_gguf.lcpp_quantize_q8_1(x, Q4_K, mmq, False)
+        assert xq.numel() == (5 * k // 128 * 144 if mmq else 5 * k // 32 * 36)
+        if not mmq:
+            g, w = xq.cpu().numpy().reshape(-1, 36), q8_1.q8_1_bytes(_to_np(x)).reshape(-1, 36)
+            assert np.array_equal(g[:, 2:], w[:, 2:])   # half(sum x) and the quants; d may differ by one fp16 step
+            raw, w = _weights("Q4_K", 640, k, 1410, False)
+            y0 = torch.ops._C_gguf.lcpp_mul_mat_vec_q(w, x, Q4_K, 640)
+            y1 = torch.ops._C_gguf.lcpp_mul_mat_vec_q(w, x, Q4_K, 640, xq)
+            assert torch.equal(y0, y1)
+    finally:
+        lcpp_ops.set_k_multiple(old_k)

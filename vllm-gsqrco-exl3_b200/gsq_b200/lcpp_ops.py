@@ -171,7 +171,7 @@ def lcpp_quantize_q8_1(X: torch.Tensor, type_: int, mmq: bool, vendored: bool) -
     """lcpp_shim.cu:949-971. `vendored` asked the reference for llama.cpp's own fp32 quantiser (a test
     hook); the arithmetic is the same, so it runs the same kernel under the same argument check."""
     ok = (_lib.gsq_type_block_bytes(int(type_)) > 0 and X.is_cuda and X.dim() == 2 and X.stride(1) == 1
-          and X.shape[1] % 512 == 0 and X.dtype in _DTYPES)
+          and X.shape[1] % _k_multiple == 0 and X.dtype in _DTYPES)
     if not ok:
         raise RuntimeError("lcpp_quantize_q8_1: bad arguments")
     n, k = X.shape
