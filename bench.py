@@ -44,8 +44,8 @@ for p in (ROOT, os.path.join(ROOT, "vllm-gsqrco-exl3_b200")):
         sys.path.insert(0, p)
 
 SHAPES = [(5120, 5120), (17408, 5120), (5120, 17408)]
-# DRAM bytes moved per weight byte by the small-batch kernel (profiles/mmv_iq3s_m8.txt: 38.384 MB read, 256 B
-# written, for 38.298 MB of weights)
+# DRAM bytes moved per weight byte by the small-batch kernel (profiles/mmv_iq3s_m8.txt: 38.384 MB read, the
+# results staying in L2, for 38.298 MB of weights)
 NCU_TRAFFIC_RATIO = 1.0023
 TYPES = [("IQ3_S", 21), ("Q4_K", 12)]
 ROWS = [1, 2, 4, 8, 12, 16, 24, 32, 48]
