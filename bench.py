@@ -23,8 +23,15 @@ With --gpus N > 1 (one process per GPU under torchrun) the weights are tensor-pa
 along N for the (*, 5120) shapes with an all-gather of Y, along K (256-column granularity) for
 (5120, 17408) with an all-reduce of the partial Y. Total work is fixed ("strong" scaling).
 
---impl reference times the reference's CPU implementation of the path (oracle port: gguf-py
-dequantisation restated in numpy + torch fp32 matmul on all host threads) on a bounded sample.
+Before anything is timed every cell's output is compared once, on 64 sampled weight rows, with the CPU
+oracle (`parity_checked`), and every cell's graph replay is compared bit for bit with the eager call
+(`graph_exact`). `ref_kernels` times the reference's own CUDA kernels (oracle/_ref, built from the reference
+tree for sm_100a; a process of its own) on the same cells by the same method.
+
+--impl reference times the reference's CPU path (gguf-py dequantisation, which the reference's tests use as
+their CPU model, + torch fp32 matmul on all host threads) on a bounded sample of the same workload.
+
+--cell TYPE N K M runs one product a few times on distinct weight copies (for profilers).
 """
 
 from __future__ import annotations
@@ -137,6 +144,7 @@ def build_cells(dev, world, rank, l2_bytes):
                 bs = BLOCK_BYTES[t]
                 raw = np.ascontiguousarray(raw[:, a0 * bs:(a0 + cnt) * bs])
                 kk = cnt * 256
+            raw_host = raw
             w0 = torch.from_numpy(raw).to(dev)
             packed = t == 21 and w0.shape[0] % 16 == 0
             if packed:
@@ -153,7 +161,7 @@ def build_cells(dev, world, rank, l2_bytes):
                 layer.register_parameter("weight_type", GGUFWeightTypeParameter(t))
                 layers.append(layer)
             cells[(tname, n, k)] = dict(t=t, n=n, k=k, kk=kk, mode=mode, a0=a0, cnt=cnt, ws=ws, layers=layers, packed=packed,
-                                        bytes=full_bytes, local_rows=w0.shape[0], use=0)
+                                        bytes=full_bytes, local_rows=w0.shape[0], use=0, raw=raw_host)
     return cells
 
 
@@ -323,6 +331,12 @@ def run_ours(args):
             fn()
         return g
 
+    # Checker leg (untimed, before anything is measured): every cell's output against the CPU oracle on 64 sampled
+    # weight rows, and every cell's graph replay against its eager call, bit for bit.
+    parity, exact = {}, {}
+    if world == 1 and not args.no_check:
+        parity, exact = check_cells(cells, xs, xs_host, order, product, capture)
+
     # The products (and, end to end, the copies) are replayed as one CUDA graph, as vLLM runs decode. NCCL
     # collectives stay outside the graph (captured together with the products they hung a 2-GPU run).
     use_graph = not args.eager
@@ -373,13 +387,13 @@ def run_ours(args):
     h2d = sum(m * key[2] * 2 for key, m in order)
     d2h = sum(m * cells[key]["n"] * 2 for key, m in order)
 
-    # per-cell table and the GEMV kernel's roofline (this rank's shard; kernel alone, x already quantised).
-    # Each cell: `reps` calls on successive weight copies in one graph, best of 3 replays.
+    # per-cell table and the small-batch kernel's roofline (this rank's shard; kernel alone, x already quantised).
+    # Each cell: one call per weight copy in one graph (a copy is read again only after all the others, more than
+    # 3 x L2 later, also across replays), best of 3 replays.
     cell_rows, roof_bytes, roof_ms, roof_launches = [], 0, 0.0, 0
     peaks, peak_kind = measured_peaks()
-    reps = 10
 
-    def best_us(fn):
+    def best_us(fn, reps):
         if args.eager:
             for _ in range(3):
                 fn()
@@ -410,9 +424,11 @@ def run_ours(args):
         c = cells[key]
         x = xs[(key[2], m)]
         xl = x if c["mode"] == "N" else x[:, c["a0"] * 256:(c["a0"] + c["cnt"]) * 256].contiguous()
-        us = best_us(lambda: product(c, x))
+        reps = len(c["ws"])
+        us = best_us(lambda: product(c, x), reps)
         row = {"type": key[0], "n": key[1], "k": key[2], "m": m, "us": round(us, 2),
-               "GBps": round(c["bytes"] / us / 1e3, 1)}
+               "GBps": round(c["bytes"] / us / 1e3, 1), "graph_exact": exact.get((key, m)),
+               "parity_rel_err": parity.get((key, m))}
         if m <= 8:
             xq = torch.ops._C_gguf.lcpp_quantize_q8_1(xl, c["t"], False, False)
             name = linear._lcpp_op(m, c["t"], c["local_rows"], c["kk"], c["packed"])
@@ -422,7 +438,7 @@ def run_ours(args):
                 w = c["ws"][c["use"] % len(c["ws"])]
                 c["use"] += 1
                 op(w, xl, c["t"], c["local_rows"], xq)
-            kus = best_us(kernel_only)
+            kus = best_us(kernel_only, reps)
             local_bytes = c["ws"][0].numel()
             row["kernel_us"] = round(kus, 2)
             row["kernel_GBps"] = round(local_bytes / kus / 1e3, 1)
@@ -462,11 +478,23 @@ def run_ours(args):
             "cells": cell_rows,
         }
         out["config"]["cells"] = len(order)
+        if parity:
+            worst = max(parity.values())
+            out["parity_checked"] = bool(worst <= PARITY_TOL)
+            out["parity"] = {"against": "CPU oracle (oracle.product: exact int32 slice sums, q8_1 model of the reference "
+                                        "kernels) on 64 sampled weight rows per cell", "cells": len(parity),
+                             "max_rel_err": worst, "tolerance": PARITY_TOL}
+            out["graph_exact"] = "%d/%d" % (sum(1 for v in exact.values() if v), len(exact))
+        else:
+            out["parity_checked"] = False
+        raws = {key: c["raw"] for key, c in cells.items()}
         if world == 1 and not args.no_extras:
             del cells, xs
             torch.cuda.empty_cache()
             out["prefill"] = extra_prefill(dev, capture)
             out["decode_stack"] = extra_decode_stack(dev, capture)
+        if world == 1 and not args.no_ref_kernels:
+            out["ref_kernels"] = ref_kernels(cell_rows, raws, l2)
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline()
         print(json.dumps(out), flush=True)
@@ -476,23 +504,163 @@ def run_ours(args):
 
 
 # --------------------------------------------------------------------------------------------------
+# checker leg (untimed; the only part of the GPU arm that imports oracle/)
+
+PARITY_TOL = 2e-3   # 1e-3 of the reference kernels' model + the fp16 rounding of the outputs
+
+
+def check_cells(cells, xs, xs_host, order, product, capture):
+    """({cell: rel_err vs the CPU oracle on 64 sampled weight rows}, {cell: graph replay == eager})."""
+    import numpy as np
+    import torch
+
+    from gsq_b200.quantization import linear
+    from oracle import blocks, product as oproduct, q8_1
+
+    parity, exact, dec_cache = {}, {}, {}
+    for key, m in order:
+        c = cells[key]
+        t, n, k = c["t"], c["n"], c["k"]
+        if key not in dec_cache:
+            rows = np.unique(np.concatenate([np.linspace(0, n - 1, 56).astype(np.int64), np.arange(n - 8, n)]))
+            dec_cache[key] = (rows, blocks.decode(np.ascontiguousarray(c["raw"][rows]), t))
+        rows, dec = dec_cache[key]
+        x = xs[(k, m)]
+        y = product(c, x)
+        torch.cuda.synchronize()
+        xf = xs_host[(k, m)].float().numpy()
+        op = linear._lcpp_op(m, t, n, k, c["packed"])
+        if op in linear._OWN_QUANTIZE_OPS:     # 128-value activation blocks; Q4_K's min term from the stored sums
+            if t == 12:
+                q, d, sm = q8_1.quantize_mmq(xf, q8_1.LAYOUT_DS4)
+                ref = oproduct.product_xsum(dec, q, d.astype(np.float16).astype(np.float64),
+                                            sm.astype(np.float16).astype(np.float64))
+            else:
+                q, d, _ = q8_1.quantize_mmq(xf, q8_1.LAYOUT_D4)
+                ref = oproduct.product_q81(dec, q, d)
+        else:
+            q, d, _ = q8_1.quantize_q8_1(xf)
+            ref = oproduct.product_q81(dec, q, d.astype(np.float32))
+        got = y.float().cpu().numpy()[:, rows]
+        parity[(key, m)] = round(oproduct.rel_err(got, ref), 7)
+        # graph replay of the same call, on the same weight copy, bit for bit
+        c["use"] -= 1
+        holder = {}
+
+        def once():
+            holder["y"] = product(c, x)
+        use0 = c["use"]
+        g = capture(once)
+        c["use"] = use0 + 1
+        g.replay()
+        torch.cuda.synchronize()
+        exact[(key, m)] = bool(torch.equal(holder["y"], y))
+        del g
+    return parity, exact
+
+
+def ref_kernels(cell_rows, raws, l2_bytes):
+    """The reference's own CUDA kernels (oracle/_ref/ref_C_gguf.so, the routed op of each cell on GGUF-order bytes;
+    for IQ3_S also its packed route, timed on the same bytes: same traffic, meaningless values) in a process of
+    their own, timed like the cells above: one call per weight copy in one graph, best of 3 replays."""
+    import tempfile
+
+    import torch
+
+    from gsq_b200.quantization import linear
+
+    so = os.path.join(ROOT, "oracle", "_ref", "ref_C_gguf.so")
+    if not os.path.exists(so):
+        return {"unavailable": "oracle/_ref/ref_C_gguf.so not built (oracle/build_ref.py needs the reference tree)"}
+    tens = {key: torch.from_numpy(r) for key, r in raws.items()}
+    xs, cases, tags = {}, [], []
+    for row in cell_rows:
+        key = (row["type"], row["n"], row["k"])
+        t = dict(TYPES)[row["type"]]
+        m, n, k = row["m"], row["n"], row["k"]
+        if (k, m) not in xs:
+            from gsq_b200 import synth
+            xs[(k, m)] = torch.from_numpy(synth.make_activation(m, k, 1200 + m)).half()
+        copies = max(2, -(-3 * l2_bytes // tens[key].numel()) + 1)
+        for packed in ([False, True] if t == 21 else [False]):
+            op = linear._lcpp_op(m, t, n, k, packed)
+            a = [tens[key], xs[(k, m)], t, n] + ([] if op in linear._OWN_QUANTIZE_OPS else [None])
+            cases.append({"op": op, "args": a, "time": True, "copies": copies, "no_out": True})
+            tags.append((row, op, packed))
+    with tempfile.TemporaryDirectory() as td:
+        cin, cout = os.path.join(td, "cases.pt"), os.path.join(td, "res.pt")
+        torch.save(cases, cin)
+        del cases
+        p = subprocess.run([sys.executable, os.path.join(ROOT, "oracle", "ref_runner.py"), cin, cout],
+                           capture_output=True, text=True, timeout=1500)
+        if p.returncode != 0:
+            return {"unavailable": "reference kernels failed: " + p.stderr.strip().splitlines()[-1][:300]}
+        res = torch.load(cout)
+    best = {}
+    for (row, op, packed), r in zip(tags, res):
+        k = (row["type"], row["n"], row["k"], row["m"])
+        if k not in best or r["us"] < best[k]["us"]:
+            best[k] = {"us": r["us"], "op": op + (" (packed)" if packed else "")}
+    out_cells, ahead = [], 0
+    for row in cell_rows:
+        b = best[(row["type"], row["n"], row["k"], row["m"])]
+        sp = b["us"] / row["us"]
+        ahead += sp >= 1.0
+        out_cells.append({"type": row["type"], "n": row["n"], "k": row["k"], "m": row["m"], "ref_us": round(b["us"], 2),
+                          "ref_op": b["op"], "us": row["us"], "speedup": round(sp, 3)})
+    tot_ref = sum(c["ref_us"] for c in out_cells)
+    tot = sum(c["us"] for c in out_cells)
+    return {"what": "reference kernels rebuilt for sm_100a, same cells, quantise + product per call, graph replay, "
+                    "weight copies cycled beyond 3 x L2; for IQ3_S the faster of its packed and unpacked routes",
+            "cells_ahead": "%d/%d" % (ahead, len(out_cells)), "sum_ref_us": round(tot_ref, 1), "sum_us": round(tot, 1),
+            "speedup_sum": round(tot_ref / tot, 3), "cells": out_cells}
+
+
+# --------------------------------------------------------------------------------------------------
 # the other two quantities BASELINE.json's metric names, reported beside the headline (1 GPU)
+
+def int8_peak(dev):
+    """Dense int8 tensor-core rate of this GPU as a library GEMM reaches it (torch._int_mm 8192^3, best of 5), the
+    way the reference's kit/micro_gguf.py:134-161 measures its card: the measured denominator beside the nominal one."""
+    import torch
+
+    try:
+        a = torch.randint(-127, 127, (8192, 8192), dtype=torch.int8, device=dev)
+        b = torch.randint(-127, 127, (8192, 8192), dtype=torch.int8, device=dev)
+        for _ in range(2):
+            torch._int_mm(a, b)
+        best = 1e30
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return round(2.0 * 8192 ** 3 / (best * 1e-3) / 1e12, 1)
+    except Exception as e:  # noqa: BLE001
+        return None
+
+
+NOMINAL_INT8_TOPS = 4500.0
+
 
 def extra_prefill(dev, capture):
     """Prefill GEMM: M tokens x K=5120 -> N=17408 with IQ3_S weights, and M x K=17408 -> N=5120 with IQ4_XS;
-    bf16 activations ~ N(0,1) with 0.1 % outliers x20. Algorithmic ops = 2 M N K."""
+    bf16 activations ~ N(0,1) with 0.1 % outliers x20, M in {2048, 8192, 16384}. Algorithmic ops = 2 M N K."""
     import torch
 
     from gsq_b200 import synth
     from gsq_b200.quantization import iq3_pack, linear
 
-    out = []
+    peak = int8_peak(dev)
+    rows = []
     for tname, t, n, k in (("IQ3_S", 21, 17408, 5120), ("IQ4_XS", 23, 5120, 17408)):
         w = torch.from_numpy(synth.make_weight(t, n, k, 1300)).to(dev)
         packed = t == 21
         if packed:
             iq3_pack.pack_(w, t)
-        for m in (2048, 8192):
+        for m in (2048, 8192, 16384):
             x = torch.from_numpy(synth.make_activation(m, k, 1400 + m, outliers=1e-3)).to(torch.bfloat16).to(dev)
             fn = lambda: linear.fused_mul_mat_gguf(x, w, t, None, packed)
             for _ in range(2):
@@ -505,11 +673,15 @@ def extra_prefill(dev, capture):
             e1.record()
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1) / 3
-            out.append({"type": tname, "m": m, "n": n, "k": k, "ms": round(ms, 3),
-                        "int8_TOPS": round(2.0 * m * n * k / (ms * 1e-3) / 1e12, 1)})
+            tops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+            rows.append({"type": tname, "m": m, "n": n, "k": k, "ms": round(ms, 3), "int8_TOPS": round(tops, 1),
+                         "frac_nominal": round(tops / NOMINAL_INT8_TOPS, 4),
+                         "frac_measured": round(tops / peak, 4) if peak else None})
             del x
         del w
-    return out
+    return {"int8_peak_nominal_TOPS": NOMINAL_INT8_TOPS, "int8_peak_measured_TOPS": peak,
+            "int8_peak_how": "torch._int_mm 8192^3, best of 5", "includes": "activation quantisation + GEMM per call",
+            "cells": rows}
 
 
 def extra_decode_stack(dev, capture, layers=64):
@@ -532,6 +704,7 @@ def extra_decode_stack(dev, capture, layers=64):
     stack = [{name: torch.roll(base[name], shifts=16 * (l + 1), dims=0) if l else base[name] for name, *_ in shapes}
              for l in range(layers)]
     bytes_step = layers * sum(base[name].numel() for name, *_ in shapes)
+    hbm = measured_peaks()[0]["hbm_gbs"]
     res = []
     for rows in (4, 8, 16, 32):
         x5 = torch.randn(rows, 5120, device=dev, dtype=torch.bfloat16)
@@ -553,54 +726,171 @@ def extra_decode_stack(dev, capture, layers=64):
             torch.cuda.synchronize()
             best = min(best, e0.elapsed_time(e1))
         res.append({"rows": rows, "ms_per_step": round(best, 3), "GBps": round(bytes_step / best / 1e6, 1),
-                    "floor_ms_at_measured_hbm": round(bytes_step / 6547.2e6, 3)})
-    return {"layers": layers, "weight_bytes_per_step": bytes_step, "steps": res}
+                    "floor_ms_at_measured_hbm": round(bytes_step / (hbm * 1e6), 3),
+                    "frac_of_measured_hbm": round(bytes_step / best / 1e6 / hbm, 4)})
+    # the same stack followed by the Q6_K output head 151936 x 5120 (the 1-GPU form of the tensor-parallel config)
+    head = torch.from_numpy(synth.make_weight(14, 151936, 5120, 3000)).to(dev)
+    res_head = []
+    for rows in (32,):
+        x5 = torch.randn(rows, 5120, device=dev, dtype=torch.bfloat16)
+        x17 = torch.randn(rows, 17408, device=dev, dtype=torch.bfloat16)
+
+        def step_head():
+            for lw in stack:
+                linear.fused_mul_mat_gguf(x5, lw["qkv"], 21, None, True)
+                linear.fused_mul_mat_gguf(x5, lw["o"], 21, None, True)
+                linear.fused_mul_mat_gguf(x5, lw["gate_up"], 21, None, True)
+                linear.fused_mul_mat_gguf(x17, lw["down"], 23, None, False)
+            linear.fused_mul_mat_gguf(x5, head, 14, None, False)
+        g = capture(step_head)
+        best = 1e30
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        b2 = bytes_step + head.numel()
+        res_head.append({"rows": rows, "ms_per_step": round(best, 3), "GBps": round(b2 / best / 1e6, 1),
+                         "floor_ms_at_measured_hbm": round(b2 / (hbm * 1e6), 3),
+                         "frac_of_measured_hbm": round(b2 / best / 1e6 / hbm, 4)})
+    return {"layers": layers, "weight_bytes_per_step": bytes_step, "steps": res,
+            "with_q6k_output_head": {"weight_bytes_per_step": bytes_step + head.numel(), "steps": res_head}}
 
 # --------------------------------------------------------------------------------------------------
 # CPU baseline / reference arm (the only places bench.py executes oracle/)
 
-def cpu_baseline(rows: int = 17408, k: int = 5120, m: int = 1):
+def _synth_module():
+    """gsq_b200/synth.py loaded by path: importing the package would load libgsq.so, which this arm never uses."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location(
+        "gsq_synth_standalone", os.path.join(ROOT, "vllm-gsqrco-exl3_b200", "gsq_b200", "synth.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _cpu_product(synth, t, rows, k, m, seed_w, seed_x, cores):
+    """One product on the host the way the reference's CPU model does it (tests/gpu/_refs.py:33-37,
+    tools/ggml_ref.py:48-56): dequantise W to fp32, then an fp32 matmul on all cores. -> (bytes, s_dequant, s_matmul)."""
     import numpy as np
     import torch
 
-    from gsq_b200 import synth
-    from oracle import product
+    raw = synth.make_weight(t, rows, k, seed_w)
+    x = synth.make_activation(m, k, seed_x)
+    t0 = time.perf_counter()
+    try:
+        import gguf
 
+        w = gguf.quants.dequantize(raw, gguf.GGMLQuantizationType(t))
+        kind = "reference"
+    except ImportError:
+        from oracle import blocks
+
+        w = blocks.dequantize(raw, t)
+        kind = "port"
+    t1 = time.perf_counter()
+    y = torch.from_numpy(np.asarray(x, dtype=np.float32)) @ torch.from_numpy(np.ascontiguousarray(w, dtype=np.float32)).T
+    t2 = time.perf_counter()
+    assert y.shape == (m, rows)
+    return raw.nbytes, t1 - t0, t2 - t1, kind
+
+
+def cpu_baseline(rows: int = 17408, k: int = 5120, m: int = 1):
+    """The single-layer CPU-runnable configuration in full: IQ3_S 17408 x 5120, one fp32 activation row."""
+    import torch
+
+    synth = _synth_module()
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    raw = synth.make_weight(21, rows, k, 1000)
-    x = synth.make_activation(m, k, 1001)
-    _, t_deq, t_mm = product.cpu_reference_linear(raw, 21, x, cores)
-    gbs = raw.nbytes / (t_deq + t_mm) / 1e9
-    return {"value": round(gbs, 4), "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": f"config 0: IQ3_S {rows}x{k}, M={m}, one product (dequantise {t_deq:.2f} s in numpy, "
-                      f"1 thread; fp32 matmul {t_mm:.3f} s, {cores} threads)"}
+    nbytes, t_deq, t_mm, kind = _cpu_product(synth, 21, rows, k, m, 1000, 1001, cores)
+    gbs = nbytes / (t_deq + t_mm) / 1e9
+    return {"value": round(gbs, 4), "unit": "GB/s", "cores": cores, "kind": kind,
+            "sample": f"IQ3_S {rows}x{k}, M={m}, one product: gguf-py dequantise {t_deq:.2f} s (numpy, 1 thread) + "
+                      f"fp32 matmul {t_mm:.3f} s ({cores} threads); the reference's tools/ggml_ref.py needs "
+                      f"libggml-base.so, absent here, and its tests pin gguf-py bit-identical to it"}
 
 
 def run_reference(args):
+    """The reference's CPU path on a bounded sample of the row sweep: per step the two corner cells (IQ3_S
+    17408 x 5120 at 1 row, which is also the single-layer configuration in full, and Q4_K 5120 x 5120 at 48 rows)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    import torch
+
+    synth = _synth_module()
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
     steps = max(1, args.steps)
-    vals = []
+    sample = [(21, 17408, 5120, 1), (12, 5120, 5120, 48)]
+
+    def one_step():
+        b = s = 0.0
+        kind = "reference"
+        for t, n, k, m in sample:
+            nb, t_deq, t_mm, kind = _cpu_product(synth, t, n, k, m, 1100, 1200 + m, cores)
+            b += nb
+            s += t_deq + t_mm
+        return b, s, kind
     for _ in range(max(0, min(args.warmup, 1))):
-        cpu_baseline(rows=2048)
+        one_step()
     t0 = time.perf_counter()
+    tot_b = tot_s = 0.0
     for _ in range(steps):
-        b = cpu_baseline(rows=4352)   # a quarter of config 0's rows per step keeps K steps within minutes
-        vals.append(b["value"])
+        b, sec, kind = one_step()
+        tot_b += b
+        tot_s += sec
     dt = time.perf_counter() - t0
-    v = statistics.mean(vals)
-    b["value"] = round(v, 4)
-    b["sample"] = "per step: IQ3_S 4352x5120 (a quarter of config 0), M=1; " + b["sample"].split(", one product ")[1]
+    v = round(tot_b / tot_s / 1e9, 4)
+    base = {"value": v, "unit": "GB/s", "cores": cores, "kind": kind,
+            "sample": "per step 2 of the 54 cells: IQ3_S 17408x5120 M=1 and Q4_K 5120x5120 M=48; per product gguf-py "
+                      "dequantise (numpy, 1 thread) + torch fp32 matmul (all threads)"}
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": round(v, 4), "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
         "warmup": min(args.warmup, 1), "ms_per_step": round(dt / steps * 1e3, 1), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "gemv_row_sweep", "note": "CPU path of the reference: dequantise + fp32 matmul"},
-        "cpu_baseline": b,
-        "e2e": {"value": round(v, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": {"workload": "gemv_row_sweep", "types": [t for t, _ in TYPES], "shapes": SHAPES, "rows": ROWS,
+                   "x_dtype": "fp16", "cells": len(TYPES) * len(SHAPES) * len(ROWS),
+                   "note": "CPU path of the reference (dequantise + fp32 matmul) on a bounded sample of these cells"},
+        "cpu_baseline": base,
+        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
+
+
+def run_cell(args):
+    """One product a few times on distinct weight copies, eager (for a profiler, or a quick number)."""
+    import torch
+
+    import gsq_b200  # noqa: F401
+    from gsq_b200 import synth
+    from gsq_b200.quantization import iq3_pack, linear
+
+    tname, n, k, m = args.cell[0], int(args.cell[1]), int(args.cell[2]), int(args.cell[3])
+    dev = "cuda:0"
+    t = synth.TYPE_IDS[tname]
+    w0 = torch.from_numpy(synth.make_weight(t, n, k, 1)).to(dev)
+    packed = tname == "IQ3_S" and not args.unpacked and n % 16 == 0
+    if packed:
+        iq3_pack.pack_(w0, t)
+    ws = [w0] + [w0.clone() for _ in range(3)]
+    dtype = torch.bfloat16 if m > 64 else torch.float16
+    x = synth.nudge_ties_torch(torch.from_numpy(synth.make_activation(m, k, 2)).to(dtype)).to(dev)
+    for i in range(2):
+        linear.fused_mul_mat_gguf(x, ws[i % len(ws)], t, None, packed)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.iters):
+        y = linear.fused_mul_mat_gguf(x, ws[(i + 2) % len(ws)], t, None, packed)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.iters
+    print(f"{tname} {n}x{k} m={m} packed={packed}: {us:.1f} us per call (eager, with launch overhead), "
+          f"{w0.numel() / us / 1e3:.0f} GB/s, {2.0 * m * n * k / us / 1e6:.1f} TOPS; op "
+          f"{linear._lcpp_op(m, t, n, k, packed)}; mean |y| {float(y.float().abs().mean()):.4f}")
 
 
 def main():
@@ -612,8 +902,15 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill-TOPS and decode-stack measurements")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
+    ap.add_argument("--no-check", action="store_true", help="skip the untimed parity / graph-replay check of every cell")
+    ap.add_argument("--no-ref-kernels", action="store_true", help="skip timing the reference's CUDA kernels (oracle/_ref)")
+    ap.add_argument("--cell", nargs=4, metavar=("TYPE", "N", "K", "M"), help="run one product only (for profilers)")
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--unpacked", action="store_true", help="--cell: keep IQ3_S in GGUF order")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.cell:
+        run_cell(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -142,7 +142,9 @@ int gsq_mul_mat_vec_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_
  *     32768 columns); anything larger returns GSQ_ERR_TOO_LARGE ("shape too large ...") and launches nothing.
  *   - Calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
- *     device current); make that first call before starting a stream capture.
+ *     device current); make that first call, and gsq_device_init for the device, before starting a stream
+ *     capture. On every call the device of `stream` must be the current device: the address used is the
+ *     current device's.
  *   - All calls on a device share the one array, which keeps what the last call wrote. Every call overwrites
  *     all the bytes it reads, so nothing needs clearing; but two calls that overlap on the GPU (different
  *     streams, no ordering) race on it. Order them, or use the two-call sequence with your own buffers.

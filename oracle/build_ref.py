@@ -26,11 +26,19 @@ OUT = os.path.join(OUT_DIR, "ref_C_gguf.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
 
+def reference_root() -> str | None:
+    """Where the reference tree is: $GSQ_REFERENCE, else a checkout named `reference` beside this repository."""
+    cand = os.environ.get("GSQ_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return cand if os.path.isdir(cand) else None
+
+
 def build(ref: str | None = None, force: bool = False) -> str:
     import torch
     from torch.utils import cpp_extension
 
-    ref = ref or os.environ.get("GSQ_REFERENCE", "/root/reference")
+    ref = ref or reference_root()
+    if ref is None:
+        raise FileNotFoundError("no reference tree: set GSQ_REFERENCE")
     csrc = os.path.join(ref, "plugin", "vllm_gguf_plugin", "csrc")
     if not os.path.isdir(csrc):
         raise FileNotFoundError(csrc)

@@ -4,8 +4,10 @@ torch.ops._C_gguf names as this repository, so the two never share a process).
 
     python oracle/ref_runner.py cases.pt results.pt
 
-cases.pt: list of dicts {"op": name, "args": [tensors / ints / bools / None ...], "time": bool}. Tensors are
-moved to cuda:0. results.pt: list of {"out": CPU tensor, "us": float or None}.
+cases.pt: list of dicts {"op": name, "args": [tensors / ints / bools / None ...], "time": bool, "copies": int,
+"no_out": bool}. Tensors are moved to cuda:0. results.pt: list of {"out": CPU tensor (None with no_out), "us": float
+or None}. Timing (the method of the reference's kit/micro_gguf.py:164-195): one call per weight copy in one CUDA
+graph, so that a copy is read again only after all the others, best of three replays.
 """
 
 import os
@@ -17,6 +19,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def graph_us(fn, reps=10):
+    reps = max(1, reps)
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
@@ -42,8 +45,19 @@ def main():
     torch.ops.load_library(os.path.join(HERE, "_ref", "ref_C_gguf.so"))
     cases = torch.load(sys.argv[1])
     out = []
+    on_device = {}   # a tensor shared by several cases is uploaded once
     for c in cases:
-        args = [a.to("cuda:0") if isinstance(a, torch.Tensor) else a for a in c["args"]]
+        args = []
+        for a in c["args"]:
+            if isinstance(a, torch.Tensor):
+                key = (a.data_ptr(), tuple(a.shape), a.dtype)
+                if key not in on_device:
+                    if a.numel() > (1 << 24):
+                        on_device.clear()
+                        torch.cuda.empty_cache()
+                    on_device[key] = a.to("cuda:0")
+                a = on_device[key]
+            args.append(a)
         op = getattr(torch.ops._C_gguf, c["op"])
         if c.get("copies"):  # timing on several copies of W so that L2 cannot serve it
             ws = [args[0]] + [args[0].clone() for _ in range(c["copies"] - 1)]
@@ -58,8 +72,9 @@ def main():
                 return op(*args)
         y = fn()
         torch.cuda.synchronize()
-        us = graph_us(fn) if c.get("time") else None
-        out.append({"out": y.cpu(), "us": us})
+        us = graph_us(fn, c.get("copies") or 10) if c.get("time") else None
+        out.append({"out": None if c.get("no_out") else y.cpu(), "us": us})
+        del args, y
     torch.save(out, sys.argv[2])
 
 

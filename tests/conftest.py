@@ -10,7 +10,7 @@ for p in (ROOT, PKG):
         sys.path.insert(0, p)
 
 GOLDEN = os.path.join(ROOT, "tests", "golden")
-REFERENCE = os.environ.get("GSQ_REFERENCE", "/root/reference")
+REFERENCE = os.environ.get("GSQ_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
 
 
 def pytest_configure(config):

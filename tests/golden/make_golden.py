@@ -127,7 +127,7 @@ def iq3_ref_packed(ref):
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ["GSQ_REFERENCE"]
     dequant_blocks()
     fixture_check(ref)
     routing(ref)

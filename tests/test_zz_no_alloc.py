@@ -52,6 +52,32 @@ def test_static_scratch_matches_two_call_path_twice(name, t, packed):
         assert torch.isfinite(y_static.float()).all() and float(y_static.float().abs().max()) > 0
 
 
+def test_static_entry_point_allocates_nothing():
+    """After one warm-up call (which resolves the array's address) the free device memory reported by the driver
+    is the same before and after a call, and a bad weight type is refused before anything is launched."""
+    from gsq_b200 import _cabi, synth
+
+    lib = _cabi.lib
+    rows, k, m = 64, 1024, 4
+    w = torch.from_numpy(synth.make_weight(12, rows, k, 5)).to(DEV)
+    x = torch.from_numpy(synth.make_activation(m, k, 6)).to(torch.float16).to(DEV)
+    y = torch.empty(m, rows, dtype=torch.float16, device=DEV)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def call(t=12):
+        return lib.gsq_linear_vec_static(w.data_ptr(), w.shape[1], rows, t, 0, x.data_ptr(), 1, m, k, k, y.data_ptr(), 1,
+                                         rows, st)
+    assert call() == 0
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        assert call() == 0
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0
+    assert call(t=2) == _cabi.ERR_UNSUPPORTED          # not a type with a kernel: refused, nothing queued
+
+
 def test_static_scratch_rejects_what_does_not_fit():
     from gsq_b200 import _cabi
 

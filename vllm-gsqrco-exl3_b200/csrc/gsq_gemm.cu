@@ -39,7 +39,8 @@ constexpr int SL_B = NT * 32 + 16;
 constexpr int TMEM_COLS = 512;
 
 __device__ const uint32_t g_iq3s_grid_gemm[512] = GSQ_IQ3S_GRID_INIT;
-__constant__ uint32_t c_iq4nl_words_gemm[4] = {0, 0, 0, 0};
+__constant__ __align__(16) int8_t c_iq4nl_bytes_gemm[16] = GSQ_IQ4NL_VALUES_INIT;  // statically initialised: no upload at run time
+#define c_iq4nl_words_gemm (reinterpret_cast<const uint32_t*>(c_iq4nl_bytes_gemm))
 __device__ int g_gemm_error = 0;
 
 struct GemmArgs {
@@ -902,15 +903,6 @@ static int launch_gemm(const GemmArgs& g, int sm_count, cudaStream_t st) {
                                       (int)gemm_smem_bytes<KIND>()));
     GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm_ws_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)gemm_ws_smem_bytes<KIND>()));
-    if (KIND == GK_IQ4XS) {
-      const int8_t vals[16] = GSQ_IQ4NL_VALUES_INIT;
-      uint32_t words[4];
-      for (int i = 0; i < 4; ++i) {
-        words[i] = 0;
-        for (int j = 0; j < 4; ++j) words[i] |= (uint32_t)(uint8_t)vals[4 * i + j] << (8 * j);
-      }
-      GSQ_CUDA_TRY(cudaMemcpyToSymbol(c_iq4nl_words_gemm, words, sizeof(words)));
-    }
     if (dev < 32) configured_mask |= 1 << dev;
   }
   const int n_items = g.n_row_tiles * g.n_tok_tiles;

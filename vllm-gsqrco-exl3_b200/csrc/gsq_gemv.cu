@@ -40,7 +40,9 @@ constexpr int GEMV_WARPS = 16;
 constexpr int GEMV_THREADS = GEMV_WARPS * 32;
 
 __device__ const uint32_t g_iq3s_grid[512] = GSQ_IQ3S_GRID_INIT;
-__constant__ uint32_t c_iq4nl_words[4] = {0, 0, 0, 0};  // filled at device init from GSQ_IQ4NL_VALUES_INIT
+// the 16 non-linear IQ4 values, read as four words of four bytes (statically initialised: no upload at run time)
+__constant__ __align__(16) int8_t c_iq4nl_bytes[16] = GSQ_IQ4NL_VALUES_INIT;
+#define c_iq4nl_words (reinterpret_cast<const uint32_t*>(c_iq4nl_bytes))
 
 constexpr int SEG_CAP = 4;  // most tiles one warp's chunk may touch in a round
 
@@ -816,18 +818,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
 
 static int g_force_direct = 0;
 static int g_force_cluster = 0;  // tests / experiments: 0 = choose, else 1, 2 or 4
-static int g_iq4_table_device_mask = 0;  // bit d set once device d has c_iq4nl_words
-
+// Nothing of this kernel family needs a per-device upload (the tables are statically initialised constants).
 int gemv_device_init(int device) {
-  if (device < 32 && (g_iq4_table_device_mask >> device) & 1) return GSQ_OK;
-  const int8_t vals[16] = GSQ_IQ4NL_VALUES_INIT;
-  uint32_t words[4];
-  for (int i = 0; i < 4; ++i) {
-    words[i] = 0;
-    for (int j = 0; j < 4; ++j) words[i] |= (uint32_t)(uint8_t)vals[4 * i + j] << (8 * j);
-  }
-  GSQ_CUDA_TRY(cudaMemcpyToSymbol(c_iq4nl_words, words, sizeof(words)));
-  if (device < 32) g_iq4_table_device_mask |= 1 << device;
+  (void)device;
   return GSQ_OK;
 }
 
@@ -948,6 +941,10 @@ bool mmv_early_trigger();
 int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* xq, int x_layout,
              int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump);
 
+static int gemv_host_dp4a(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_q8,
+                          int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump,
+                          int dump_m0);
+
 static int gemv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_q8,
                      int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump,
                      int dump_m0) {
@@ -957,6 +954,30 @@ static int gemv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_ty
     const int rc = mmv_host(w, row_bytes, rows, ggml_type, packed, x_q8, 0, m, k, y, y_dtype, y_row_stride, stream, d);
     if (rc != 1000) return rc;  // 1000: the shape does not fit that kernel
   }
+  if (m > 8 && m <= 48 && y && x_q8 && k > 0 && k % 32 == 0 &&
+      (y_dtype == GSQ_F32 || y_dtype == GSQ_F16 || y_dtype == GSQ_BF16)) {
+    // Row counts only the small-batch kernel takes in one launch, on a shape it declined (its staging area does
+    // not fit): the dp4a kernel below, eight rows per launch, so that every count up to
+    // gsq_mul_mat_vec_max_rows() is served whatever the shape.
+    const int64_t ysz = y_dtype == GSQ_F32 ? 4 : 2;
+    for (int64_t i = 0; i < m; i += 8) {
+      const int64_t c = m - i < 8 ? m - i : 8;
+      int* d = dump ? dump + (int64_t)(dump_m0 + i) * rows * (k / 32) : nullptr;
+      if (d) return GSQ_ERR_UNSUPPORTED;  // the dump instantiation takes one row per launch (gsq_debug_block_sums)
+      const int rc = gemv_host_dp4a(w, row_bytes, rows, ggml_type, packed, (const uint8_t*)x_q8 + i * (k / 32) * 36, c, k,
+                                    (uint8_t*)y + i * y_row_stride * ysz, y_dtype, y_row_stride, stream, nullptr, 0);
+      if (rc != GSQ_OK) return rc;
+    }
+    return GSQ_OK;
+  }
+  return gemv_host_dp4a(w, row_bytes, rows, ggml_type, packed, x_q8, m, k, y, y_dtype, y_row_stride, stream, dump, dump_m0);
+}
+
+// The dp4a kernel proper: 1..8 activation rows.
+static int gemv_host_dp4a(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_q8,
+                          int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump,
+                          int dump_m0) {
+  if (m == 0 || rows == 0) return GSQ_OK;
   if (m < 0 || m > 8 || rows < 0 || k <= 0 || k % 256 != 0 || !w || !x_q8 || !y) return GSQ_ERR_UNSUPPORTED;
   if (rows > INT32_MAX || k > INT32_MAX) return GSQ_ERR_TOO_LARGE;
   const int bs = block_bytes(ggml_type);

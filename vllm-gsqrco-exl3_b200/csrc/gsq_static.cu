@@ -48,6 +48,12 @@ extern "C" int gsq_linear_vec_static(const void* w, int64_t row_bytes, int64_t r
   if (m < 0 || k <= 0 || k % 256 != 0 || !x || !w || !y) return GSQ_ERR_UNSUPPORTED;
   // the fixed array is the limit: more rows or columns than it holds are refused, never truncated
   if (m > STATIC_MAX_ROWS || m * (k / 32) * 36 > STATIC_MAX_Q8_BYTES) return GSQ_ERR_TOO_LARGE;
+  // everything the product would refuse is refused here, before the quantiser is queued
+  const int bs = block_bytes(ggml_type);
+  if (bs == 0 || row_bytes != (k / 256) * bs || rows < 0 || rows > INT32_MAX || k > INT32_MAX) return GSQ_ERR_UNSUPPORTED;
+  if (y_dtype != GSQ_F32 && y_dtype != GSQ_F16 && y_dtype != GSQ_BF16) return GSQ_ERR_UNSUPPORTED;
+  if (x_dtype != GSQ_F32 && x_dtype != GSQ_F16 && x_dtype != GSQ_BF16) return GSQ_ERR_UNSUPPORTED;
+  if (ggml_type == GSQ_TYPE_IQ3_S && packed && rows % 16 != 0) return GSQ_ERR_UNSUPPORTED;
   void* q8 = nullptr;
   int rc = static_q8_address(&q8);
   if (rc != GSQ_OK) return rc;
