@@ -195,7 +195,7 @@ int gsq_q8_layout_for_type(int ggml_type);
  * sums[m][rows][k/32] (NULL switches it off). */
 int gsq_debug_swap_descriptor_strides(int on);
 int gsq_debug_gemm_dump_sums(int32_t* sums);
-int gsq_debug_gemm_variant(int v); /* 0 = lockstep kernel (default), 1 = warp-specialised kernel; returns previous */
+int gsq_debug_gemm_variant(int v); /* kernel behind gsq_linear above the small-batch row counts: 0 = prefill GEMM (default), 1 / 2 = the warp-specialised / lockstep kernels of gsq_mul_mat_q8; returns previous */
 int gsq_debug_gemm_ksplit(int ks); /* 0 = choose; 1, 2, 4 = CTAs per cluster that split K (experiments) */
 /* The register-operand tensor-core kernel that serves 1..48 activation rows behind gsq_mul_mat_vec_q8 and
  * gsq_mul_mat_q8 (experiments and tests; each returns the previous value). */
@@ -213,6 +213,20 @@ size_t gsq_mul_mat_scratch_bytes(int64_t rows, int64_t m, int64_t k, int ggml_ty
 int gsq_mul_mat_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,
                    const void* x_q8_mmq, int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride,
                    void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * The whole product from X as it is, any number of activation rows: quantises X into `scratch` in the layout of
+ * the kernel it then runs (the small-batch tensor-core kernel up to 48 rows, the warp-specialised tcgen05 GEMM
+ * above, the dp4a kernel for Q6_K and IQ3_S in GGUF order). Replaces what the reference's self-quantising ops do
+ * in one call: lcpp_mul_mat_q, lcpp_mul_mat_mma_k, lcpp_mul_mat_iq3_packed (lcpp_shim.cu:626-671, 753-909, whose
+ * scratch comes from torch's allocator, :250-263).
+ *   x            [m, k] in x_dtype, row stride x_row_stride elements
+ *   scratch      gsq_linear_scratch_bytes(...) bytes, 256-byte aligned; need not be initialised, not preserved
+ */
+size_t gsq_linear_scratch_bytes(int64_t rows, int64_t m, int64_t k, int ggml_type, int packed);
+int gsq_linear(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x, int x_dtype,
+               int64_t m, int64_t k, int64_t x_row_stride, void* y, int y_dtype, int64_t y_row_stride, void* scratch,
+               size_t scratch_bytes, void* stream);
 
 /*
  * IQ3_S load-time repack, in place, bijective: replaces iq3_pack.pack_ / unpack

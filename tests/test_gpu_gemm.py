@@ -59,11 +59,13 @@ CASES = [("IQ3_S", 128, 512), ("IQ3_S", 272, 5120), ("IQ3_S", 48, 1024), ("Q4_K"
          ("IQ4_XS", 128, 512), ("IQ4_XS", 202, 5120), ("IQ4_XS", 300, 17408)]
 
 
-@pytest.fixture(params=["specialised", "lockstep", "default"], autouse=True)
+@pytest.fixture(params=["prefill", "specialised", "lockstep", "default"], autouse=True)
 def gemm_variant(request):
-    """The tcgen05 GEMM kernels at every row count: warp-specialised (producer / MMA / consumer warps) and
-    all-warps-in-lockstep; and the library's own choice, which below 25 rows is the register-operand kernel."""
-    old = _cabi.lib.gsq_debug_gemm_variant(int(request.param == "specialised"))
+    """The tcgen05 GEMM kernels at every row count: the warp-specialised prefill GEMM on operand-ordered activation
+    tiles (weights decoded once per 256 tokens), the two older kernels on 128-value blocks (warp-specialised and
+    all-warps-in-lockstep); and the library's own choice, which up to 48 rows is the register-operand kernel."""
+    variant = {"prefill": 0, "specialised": 1, "lockstep": 2, "default": 0}[request.param]
+    old = _cabi.lib.gsq_debug_gemm_variant(variant)
     old_mode = _cabi.lib.gsq_debug_mmv_mode(0 if request.param == "default" else 1)
     yield request.param
     _cabi.lib.gsq_debug_gemm_variant(old)
@@ -89,7 +91,7 @@ def descriptor_strides():
 
 
 @pytest.mark.parametrize("name,rows,k", CASES)
-@pytest.mark.parametrize("m", [9, 16, 24, 33, 48, 64, 65, 200])
+@pytest.mark.parametrize("m", [9, 16, 24, 33, 48, 64, 65, 200, 300, 700])
 def test_gemm_fp32_vs_reference_model(name, rows, k, m):
     raw, w = _weights(name, rows, k, 300 + rows)
     x = _x(m, k, torch.float32, 400 + m)

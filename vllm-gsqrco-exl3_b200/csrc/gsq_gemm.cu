@@ -884,12 +884,21 @@ __global__ void __launch_bounds__(WS_THREADS, 1) gemm_ws_kernel(const GemmArgs g
 static int g_swap_lbo_sbo = 0;
 static int* g_gemm_dump = nullptr;
 static int g_gemm_ksplit = 0;  // experiments: 0 = choose, else 1, 2 or 4
-static int g_gemm_variant = 0;  // 0 = all warps in lockstep (default: faster on every measured shape), 1 = warp-specialised
+static int g_gemm_variant = 0;  // behind gsq_linear: 0 = the prefill GEMM of gsq_gemm2.cu; the kernels of this file: 1 = warp-specialised, else lockstep
+
+int gemm2_error_flag(int* flag);  // gsq_gemm2.cu
 
 int gemm_error_flag(int* flag) {
-  GSQ_CUDA_TRY(cudaMemcpyFromSymbol(flag, g_gemm_error, sizeof(int)));
+  int a = 0, b = 0;
+  GSQ_CUDA_TRY(cudaMemcpyFromSymbol(&a, g_gemm_error, sizeof(int)));
+  const int rc = gemm2_error_flag(&b);
+  if (rc != GSQ_OK) return rc;
+  *flag = a | b;
   return GSQ_OK;
 }
+
+int* gemm_dump_pointer() { return g_gemm_dump; }
+int gemm_variant() { return g_gemm_variant; }
 
 template <int KIND>
 static int launch_gemm(const GemmArgs& g, int sm_count, cudaStream_t st) {
@@ -945,7 +954,7 @@ extern "C" int gsq_debug_swap_descriptor_strides(int on) {
 
 extern "C" int gsq_debug_gemm_variant(int v) {
   const int old = gsq::g_gemm_variant;
-  gsq::g_gemm_variant = v ? 1 : 0;
+  gsq::g_gemm_variant = v == 1 ? 1 : v == 2 ? 2 : 0;
   return old;
 }
 

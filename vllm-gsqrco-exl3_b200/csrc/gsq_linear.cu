@@ -1,0 +1,82 @@
+// gsq_linear: the whole product for callers that hand over X as it is (fp32 / fp16 / bf16) -- what the reference's
+// ops that quantise for themselves do inside one call (lcpp_mul_mat_q, lcpp_mul_mat_mma_k, lcpp_mul_mat_iq3_packed:
+// plugin/vllm_gguf_plugin/csrc/lcpp_shim.cu:626-671, 753-909). The activation quantiser and its output layout are
+// chosen together with the kernel: 128-value blocks [K/128][M] for the small-batch tensor-core kernel and the
+// lockstep GEMM, operand-ordered tiles for the prefill GEMM, 36-byte blocks for the dp4a kernel.
+#include "gsq_common.cuh"
+
+namespace gsq {
+
+// gsq_mmv.cu
+bool mmv_applies(int ggml_type, int packed, int64_t rows, int64_t m);
+int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* xq, int x_layout,
+             int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump);
+// gsq_gemm2.cu
+bool gemm2_applies(int ggml_type, int packed, int64_t rows);
+size_t gemm2_tile_bytes(int64_t m, int64_t k, int ggml_type);
+int gemm2_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_tiles, int64_t m,
+               int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream);
+// gsq_quantize.cu
+int quantize_tiles_host(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride, int layout, void* out, void* stream);
+// gsq_gemm.cu
+int* gemm_dump_pointer();
+int gemm_variant();
+
+static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+}  // namespace gsq
+
+extern "C" size_t gsq_linear_scratch_bytes(int64_t rows, int64_t m, int64_t k, int ggml_type, int packed) {
+  (void)rows;
+  (void)packed;
+  if (m <= 0 || k <= 0) return 0;
+  const size_t mmq = (size_t)(k / 128) * (size_t)m * 144, tiles = gsq::gemm2_tile_bytes(m, k, ggml_type),
+               q81 = (size_t)(k / 32) * (size_t)m * 36;
+  size_t b = mmq > tiles ? mmq : tiles;
+  b = b > q81 ? b : q81;
+  return gsq::align256(b);
+}
+
+extern "C" int gsq_linear(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x,
+                          int x_dtype, int64_t m, int64_t k, int64_t x_row_stride, void* y, int y_dtype,
+                          int64_t y_row_stride, void* scratch, size_t scratch_bytes, void* stream) {
+  using namespace gsq;
+  if (m == 0 || rows == 0) return GSQ_OK;
+  if (m < 0 || rows < 0 || k <= 0 || k % 256 != 0 || !w || !x || !y) return GSQ_ERR_UNSUPPORTED;
+  const int bs = block_bytes(ggml_type);
+  if (bs == 0 || row_bytes != (k / 256) * bs) return GSQ_ERR_UNSUPPORTED;
+  if (y_dtype != GSQ_F32 && y_dtype != GSQ_F16 && y_dtype != GSQ_BF16) return GSQ_ERR_UNSUPPORTED;
+  if (!scratch || scratch_bytes < gsq_linear_scratch_bytes(rows, m, k, ggml_type, packed)) return GSQ_ERR_SCRATCH;
+  const int layout = gsq_q8_layout_for_type(ggml_type);
+  int rc;
+  // 1..48 rows: the small-batch tensor-core kernel on 128-value blocks, where it serves the type and the shape fits
+  if (mmv_applies(ggml_type, packed, rows, m)) {
+    rc = gsq_quantize_q8_1_mmq(x, x_dtype, m, k, x_row_stride, layout, scratch, stream);
+    if (rc != GSQ_OK) return rc;
+    rc = mmv_host(w, row_bytes, rows, ggml_type, packed, scratch, 1, m, k, y, y_dtype, y_row_stride, stream, gemm_dump_pointer());
+    if (rc != 1000) return rc;  // 1000: declined, the activations of this shape do not fit its staging area
+  }
+  // the prefill GEMM on operand-ordered tiles
+  if (gemm2_applies(ggml_type, packed, rows) && gemm_variant() == 0) {
+    rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, layout, scratch, stream);
+    if (rc != GSQ_OK) return rc;
+    return gemm2_host(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, stream);
+  }
+  if (gemm2_applies(ggml_type, packed, rows)) {
+    rc = gsq_quantize_q8_1_mmq(x, x_dtype, m, k, x_row_stride, layout, scratch, stream);
+    if (rc != GSQ_OK) return rc;
+    return gsq_mul_mat_q8(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, nullptr, 0, stream);
+  }
+  // Q6_K and IQ3_S in GGUF order: the dp4a kernel on 36-byte blocks, as many rows per launch as it takes
+  rc = gsq_quantize_q8_1(x, x_dtype, m, k, x_row_stride, scratch, stream);
+  if (rc != GSQ_OK) return rc;
+  const int step = gsq_mul_mat_vec_max_rows(ggml_type, packed);
+  const int64_t ysz = y_dtype == GSQ_F32 ? 4 : 2;
+  for (int64_t i = 0; i < m; i += step) {
+    const int64_t c = m - i < step ? m - i : step;
+    rc = gsq_mul_mat_vec_q8(w, row_bytes, rows, ggml_type, packed, (const uint8_t*)scratch + i * (k / 32) * 36, c, k,
+                            (uint8_t*)y + i * y_row_stride * ysz, y_dtype, y_row_stride, stream);
+    if (rc != GSQ_OK) return rc;
+  }
+  return GSQ_OK;
+}

@@ -165,6 +165,71 @@ __global__ void __launch_bounds__(256) quantize_q8_1_mmq_kernel(const T* __restr
   }
 }
 
+// Activation tiles of the prefill GEMM (gsq_gemm2.cu): the same quantisation as quantize_q8_1_mmq_kernel (32-value
+// blocks, d = 1 / (127 / amax), D4 or DS4 scales), written in the shared-memory layout of the tensor-core operand so
+// that one bulk copy brings a unit into place. Tiles of 64 tokens; per tile and superblock two units of 4 slices:
+//   unit = [4 slices][8 token groups][2 K chunks of 16][8 tokens][16 bytes] quants   (8192 bytes)
+//          [4 slices][64 tokens] float d                                              (1024 bytes)
+//          [4 slices][64 tokens] float(half(sum x))   (DS4 only)                      (1024 bytes)
+// Tokens past m (up to the end of the last tile) are written as zeros. One block = 64 tokens x one 32-value slice:
+// warp w holds token group w, lane = (token % 8) * 4 + 8-value piece, so a warp writes two whole 128-byte core
+// matrices.
+template <typename T, bool VEC, int LAYOUT>
+__global__ void __launch_bounds__(256) quantize_q8_1_tiles_kernel(const T* __restrict__ x, uint8_t* __restrict__ out,
+                                                                 int64_t m, int64_t k, int64_t stride) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  constexpr bool DS = LAYOUT == GSQ_Q8_LAYOUT_DS4;
+  constexpr int UB = 8192 + (DS ? 2048 : 1024);
+  const int slice = blockIdx.x;              // 32-value slice along k
+  const int64_t tt = blockIdx.y;             // token tile
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = 8 * warp + (lane >> 2), piece = lane & 3;
+  const int64_t row = tt * 64 + r;
+  const bool live = row < m;
+  float v[8];
+  if (live) {
+    load8<T, VEC>(x, row * stride + (int64_t)slice * 32 + piece * 8, v);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+  float sum = 0.0f;
+  if constexpr (DS) {
+    float pa = ((v[0] + v[1]) + v[2]) + v[3];
+    float pb = ((v[4] + v[5]) + v[6]) + v[7];
+    pa += __shfl_xor_sync(0xFFFFFFFFu, pa, 2);
+    pb += __shfl_xor_sync(0xFFFFFFFFu, pb, 2);
+    pa += __shfl_xor_sync(0xFFFFFFFFu, pa, 1);
+    pb += __shfl_xor_sync(0xFFFFFFFFu, pb, 1);
+    sum = pa + pb;
+  }
+  const float d_inv = div_approx(127.0f, amax);
+  float q[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) q[e] = live ? roundf(v[e] * d_inv) : 0.0f;
+  float d = live ? rcp_approx(d_inv) : 0.0f;
+  const int sb = slice >> 3, s = slice & 7, sl = s & 3;
+  uint8_t* unit = out + ((tt * (k >> 8) + sb) * 2 + (s >> 2)) * UB;
+  uint8_t* dst = unit + sl * 2048 + (r >> 3) * 256 + (piece >> 1) * 128 + (r & 7) * 16 + (piece & 1) * 8;
+  *reinterpret_cast<uint2*>(dst) = make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
+  if (piece == 0) {
+    float* sc = reinterpret_cast<float*>(unit + 8192);
+    if constexpr (DS) {
+      const float2 ds = __half22float2(__floats2half2_rn(d, sum));   // the reference keeps half2(d, sum)
+      sc[sl * 64 + r] = live ? ds.x : 0.0f;
+      sc[(4 + sl) * 64 + r] = live ? ds.y : 0.0f;
+    } else {
+      sc[sl * 64 + r] = d;
+    }
+  }
+}
+
 // launch with programmatic stream serialisation (see griddepcontrol.wait in the kernels)
 template <typename... KArgs, typename... Args>
 static int launch_pdl(void (*kern)(KArgs...), unsigned grid, cudaStream_t st, Args... args) {
@@ -200,6 +265,43 @@ static int launch_q8_1_mmq(const void* x, int64_t m, int64_t k, int64_t stride, 
   const bool vec = ((uintptr_t)x % 16 == 0) && ((stride * (int64_t)sizeof(T)) % 16 == 0);
   return vec ? launch_pdl(quantize_q8_1_mmq_kernel<T, true, LAYOUT>, grid, st, (const T*)x, (uint8_t*)out, m, k, stride)
              : launch_pdl(quantize_q8_1_mmq_kernel<T, false, LAYOUT>, grid, st, (const T*)x, (uint8_t*)out, m, k, stride);
+}
+
+template <typename T, int LAYOUT>
+static int launch_q8_1_tiles(const void* x, int64_t m, int64_t k, int64_t stride, void* out, cudaStream_t st) {
+  if (m == 0) return GSQ_OK;
+  const bool vec = ((uintptr_t)x % 16 == 0) && ((stride * (int64_t)sizeof(T)) % 16 == 0);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(k >> 5), (unsigned)((m + 63) / 64));
+  cfg.blockDim = dim3(256);
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (vec) {
+    GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, quantize_q8_1_tiles_kernel<T, true, LAYOUT>, (const T*)x, (uint8_t*)out, m, k, stride));
+  } else {
+    GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, quantize_q8_1_tiles_kernel<T, false, LAYOUT>, (const T*)x, (uint8_t*)out, m, k, stride));
+  }
+  return GSQ_OK;
+}
+
+// x [m, k] -> activation tiles for the prefill GEMM (see quantize_q8_1_tiles_kernel); k % 256 == 0.
+int quantize_tiles_host(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride, int layout, void* out, void* stream) {
+  if (m < 0 || k <= 0 || k % 256 != 0 || (m > 0 && (!x || !out)) || (m + 63) / 64 > 65535) return GSQ_ERR_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+#define GSQ_TILES_CASE(T)                                                                                  \
+  return layout == GSQ_Q8_LAYOUT_D4 ? launch_q8_1_tiles<T, GSQ_Q8_LAYOUT_D4>(x, m, k, stride, out, st) \
+                                    : launch_q8_1_tiles<T, GSQ_Q8_LAYOUT_DS4>(x, m, k, stride, out, st)
+  switch (x_dtype) {
+    case GSQ_F32: GSQ_TILES_CASE(float);
+    case GSQ_F16: GSQ_TILES_CASE(__half);
+    case GSQ_BF16: GSQ_TILES_CASE(__nv_bfloat16);
+    default: return GSQ_ERR_UNSUPPORTED;
+  }
+#undef GSQ_TILES_CASE
 }
 
 }  // namespace gsq

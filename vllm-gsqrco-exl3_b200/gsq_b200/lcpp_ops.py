@@ -7,9 +7,9 @@ op is registered for CUDA and for CPU: on CPU every guard runs and the call then
 What runs underneath an op name (lcpp_shim.cu:753-909 `run`):
   * the ops that read block_q8_1 activations (`x_q8` argument; vec_q, vec_iq3, vec_iq3_mma,
     vec_own, vec_iq3_mma_packed) -> gsq_quantize_q8_1 (unless x_q8 is given) + gsq_mul_mat_vec_q8,
-    8 activation rows per launch;
-  * the ops that quantise X themselves in 128-value blocks (mul_mat_q, mma_k, iq3_packed)
-    -> gsq_quantize_q8_1_mmq + gsq_mul_mat_q8 (tcgen05).
+    as many activation rows per launch as the kernel for the type takes (8 or 48);
+  * the ops that quantise X themselves (mul_mat_q, mma_k, iq3_packed) -> gsq_linear, which picks
+    the activation layout together with the kernel (small-batch tensor-core kernel, tcgen05 GEMM).
 Output and scratch come from torch's caching allocator on the current stream; the kernels write
 X's dtype directly, so no cast kernel follows.
 """
@@ -58,9 +58,6 @@ _DTYPES = {torch.float32: _cabi.F32, torch.float16: _cabi.F16, torch.bfloat16: _
 # K granularity the guards demand: 512 as in the reference (MATRIX_ROW_PADDING); the tensor-parallel
 # helpers lower it to 256 for K-sharded layers (gsq_b200.tp.relaxed_k).
 _k_multiple = 512
-# gsq_mul_mat_q8 covers Q4_K, IQ4_XS and packed IQ3_S; Q6_K and IQ3_S in GGUF order (and everything, if this
-# is switched off) run the dp4a kernel 8 rows at a time under the many-row op names
-_GEMM_READY = True
 
 
 def set_k_multiple(v: int) -> int:
@@ -148,22 +145,20 @@ def _run(op: str, W: torch.Tensor, X: torch.Tensor, type_: int, row: int, x_q8: 
     packed = bool(spec.get("packed", False))
     with torch.cuda.device(X.device):
         y = torch.empty((n, row), dtype=X.dtype, device=X.device)
-        gemm = (not spec["mmvq"]) and _GEMM_READY and (type_ in (Q4_K, IQ4_XS) or (type_ == IQ3_S and packed))
-        if not gemm:
+        if spec["mmvq"]:
             if x_q8 is None:
                 x_q8 = torch.empty(q8_bytes, dtype=torch.uint8, device=X.device)
                 quantize_q8_1_into(X, x_q8)
             _gemv(W, X, type_, row, x_q8, packed, y)
             return y
-        layout = _lib.gsq_q8_layout_for_type(type_)
-        xq = torch.empty(n * k // 128 * 144, dtype=torch.uint8, device=X.device)
-        quantize_q8_1_mmq_into(X, layout, xq)
-        sbytes = _lib.gsq_mul_mat_scratch_bytes(row, n, k, type_)
+        # the ops that quantise X themselves: one library call (quantiser + kernel chosen together)
+        sbytes = _lib.gsq_linear_scratch_bytes(row, n, k, type_, int(packed))
         scratch = torch.empty(max(sbytes, 1), dtype=torch.uint8, device=X.device)
+        stride = k if n == 1 else X.stride(0)
         _cabi.check(
-            _lib.gsq_mul_mat_q8(W.data_ptr(), W.shape[1], row, type_, int(packed), xq.data_ptr(), n, k, y.data_ptr(),
-                                _DTYPES[y.dtype], y.stride(0), scratch.data_ptr(), sbytes, _stream(X.device)),
-            "gsq_mul_mat_q8")
+            _lib.gsq_linear(W.data_ptr(), W.shape[1], row, type_, int(packed), X.data_ptr(), _DTYPES[X.dtype], n, k, stride,
+                            y.data_ptr(), _DTYPES[y.dtype], y.stride(0), scratch.data_ptr(), sbytes, _stream(X.device)),
+            "gsq_linear")
         return y
 
 
