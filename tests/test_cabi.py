@@ -1,4 +1,4 @@
-"""The C-ABI library loads and exports every function include/gsq.h declares (no compute calls)."""
+"""The C-ABI library loads and exports every function include/gsq.h and include/gsq_debug.h declare (no compute calls)."""
 
 import ctypes
 import os
@@ -10,7 +10,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _declared():
-    src = open(os.path.join(ROOT, "include", "gsq.h")).read()
+    src = open(os.path.join(ROOT, "include", "gsq.h")).read() + open(os.path.join(ROOT, "include", "gsq_debug.h")).read()
     src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
     return sorted(set(re.findall(r"\b(gsq_[a-z0-9_]+)\s*\(", src)))
 

@@ -32,6 +32,7 @@ def _sources():
 def _headers():
     hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     hs.append(os.path.join(os.path.dirname(HERE), "include", "gsq.h"))
+    hs.append(os.path.join(os.path.dirname(HERE), "include", "gsq_debug.h"))
     return hs
 
 

@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include "../../include/gsq.h"
+#include "../../include/gsq_debug.h"
 
 #define GSQ_WARP 32
 #define GSQ_QK_K 256

@@ -94,7 +94,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 // Bounded wait: gives up after 2^22 polls (or as soon as another thread of the CTA has given up) and raises the flags.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   uint32_t done = 0;
-  for (int spin = 0; spin < (1 << 22); ++spin) {
+  for (int spin = 0; spin < (1 << 21); ++spin) {
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
@@ -105,6 +105,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         : "r"(bar), "r"(parity)
         : "memory");
     if (done) return true;
+    __nanosleep(32);   // a waiting warp should not spend the issue slots of the working ones on polls
     if ((spin & 63) == 63 && *abort_flag) return false;
   }
   *abort_flag = 1;
@@ -195,6 +196,17 @@ __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
 }
 __device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// Bit pattern of the float 1.5 * 2^23 + c for an integer |c| < 2^22, in one logic instruction (not an integer add,
+// which the compiler may place on the fp32 pipe the scaling needs): the low 23 bits are those of c with bit 22
+// flipped (c + 2^22 never carries out of them), the rest those of the constant. Truth table of
+// f(c, mask, magic) = mask ? c ^ magic : magic, mask = 0x007FFFFF: 0x6A... computed below.
+__device__ __forceinline__ float biased_float(uint32_t c) {
+  uint32_t r;
+  // inputs a = c, b = mask, c = magic; LUT bit index = (a << 2) | (b << 1) | c: out = b ? a ^ c : c
+  //   a b c -> out : 000->0 001->1 010->0 011->1 100->0 101->1 110->1 111->0  => LUT = 0b01101010 = 0x6A
+  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(c), "r"(0x007FFFFFu), "r"((uint32_t)MAGIC));
+  return __uint_as_float(r);
 }
 __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   uint64_t r;
@@ -363,8 +375,8 @@ __device__ __forceinline__ void scale8(const uint32_t (&c)[8], float da, float d
 #pragma unroll
   for (int j4 = 0; j4 < 2; ++j4) {
     const float4 d = *reinterpret_cast<const float4*>(bd + 4 * j4);
-    const uint64_t t0 = fma2(pack2(__int_as_float((int)c[4 * j4] + MAGIC), __int_as_float((int)c[4 * j4 + 1] + MAGIC)), da2, nmda2);
-    const uint64_t t1 = fma2(pack2(__int_as_float((int)c[4 * j4 + 2] + MAGIC), __int_as_float((int)c[4 * j4 + 3] + MAGIC)), da2, nmda2);
+    const uint64_t t0 = fma2(pack2(biased_float(c[4 * j4]), biased_float(c[4 * j4 + 1])), da2, nmda2);
+    const uint64_t t1 = fma2(pack2(biased_float(c[4 * j4 + 2]), biased_float(c[4 * j4 + 3])), da2, nmda2);
     acc[2 * j4] = fma2(t0, pack2(d.x, d.y), acc[2 * j4]);
     acc[2 * j4 + 1] = fma2(t1, pack2(d.z, d.w), acc[2 * j4 + 1]);
     if (DS) {

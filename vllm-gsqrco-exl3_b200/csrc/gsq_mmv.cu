@@ -31,7 +31,6 @@
 #include <cooperative_groups.h>
 
 #include <cstdio>
-#include <cstdlib>
 
 #include "gsq_common.cuh"
 #include "gsq_tables.h"
@@ -917,6 +916,8 @@ static int g_mmv_cluster = 0;   // experiments: 0 = choose, else 1, 2, 4 or 8
 static unsigned long long* g_mmv_prof = nullptr;
 static int g_mmv_pdl = 2;       // programmatic stream serialisation: 0 off, 1 on, 2 + early start of the dependents where it pays, 3 + everywhere
 static int g_mmv_pf_first = 2;  // records requested from L2 ahead of the staging
+static int g_mmv_aligned = -1;  // experiments: -1 = choose, 0 / 1 = equal chunks / whole tiles per warp
+static int g_mmv_trace = 0;     // one line per launch plan on stderr
 
 // shared with the dp4a kernel: whether a product lets the next kernels of a programmatic-launch chain start early
 bool mmv_early_trigger() { return g_mmv_pdl >= 2; }
@@ -980,8 +981,7 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
   // combinations that fit, the one with the least estimated time.
   struct Plan { int cs, clusters, cap, round, bufs, per; double t; };
   Plan plans[2] = {{0, 0, 0, 0, 1, 0, 0.0}, {0, 0, 0, 0, 1, 0, 0.0}};
-  static const char* force_env = getenv("GSQ_MMV_ALIGNED");  // experiments: "0" / "1" forces the chunking
-  const int force_aligned = force_env ? atoi(force_env) : -1;
+  const int force_aligned = g_mmv_aligned;
   for (int aligned = 0; aligned <= 1; ++aligned) {
     if (force_aligned >= 0 && aligned != force_aligned) continue;
     const size_t fixed = MmvKind<KIND>::grid_bytes(NTL) + (aligned ? 0 : mmv_partial_bytes(MC));
@@ -1036,8 +1036,7 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
             best_round = plans[best_aligned].round, best_bufs = plans[best_aligned].bufs;
   const double best_t = plans[best_aligned].t;
   const size_t fixed = MmvKind<KIND>::grid_bytes(NTL) + (best_aligned ? 0 : mmv_partial_bytes(MC));
-  static const bool trace = getenv("GSQ_MMV_TRACE") != nullptr;  // one line per launch plan on stderr
-  if (trace) {
+  if (g_mmv_trace) {
     fprintf(stderr, "mmv plan kind=%d ntl=%d xl=%d m=%d rows=%d k=%d: cs=%d clusters=%d round=%d bufs=%d aligned=%d est=%.1f us%s\n",
             KIND, NTL, XL, a.m, a.nrows, a.k, best_cs, best_clusters, best_round, best_bufs, best_aligned, best_t,
             best_cs ? "" : " (declined)");
@@ -1196,6 +1195,18 @@ extern "C" int gsq_mul_mat_vec_max_rows(int ggml_type, int packed) {
 extern "C" int gsq_debug_mmv_prefetch_first(int n) {
   const int old = gsq::g_mmv_pf_first;
   gsq::g_mmv_pf_first = n < 0 ? 0 : n > 64 ? 64 : n;
+  return old;
+}
+
+extern "C" int gsq_debug_mmv_chunking(int mode) {
+  const int old = gsq::g_mmv_aligned;
+  gsq::g_mmv_aligned = (mode == 0 || mode == 1) ? mode : -1;
+  return old;
+}
+
+extern "C" int gsq_debug_mmv_trace(int on) {
+  const int old = gsq::g_mmv_trace;
+  gsq::g_mmv_trace = on ? 1 : 0;
   return old;
 }
 

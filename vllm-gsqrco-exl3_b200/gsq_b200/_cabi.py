@@ -23,7 +23,7 @@ EXPORTS = (
     "gsq_debug_block_sums", "gsq_debug_force_direct_loads", "gsq_device_error_flag", "gsq_debug_force_cluster_size",
     "gsq_debug_swap_descriptor_strides", "gsq_debug_gemm_dump_sums", "gsq_debug_gemm_ksplit", "gsq_debug_gemm_variant", "gsq_q8_layout_for_type", "gsq_mul_mat_scratch_bytes", "gsq_mul_mat_q8", "gsq_iq3s_repack", "gsq_route", "gsq_linear_vec_static", "gsq_linear_vec_static_max_q8_bytes",
     "gsq_debug_mmv_mode", "gsq_debug_mmv_min_rows", "gsq_debug_mmv_cluster_size", "gsq_mul_mat_vec_max_rows",
-    "gsq_debug_mmv_profile", "gsq_debug_mmv_max_rows", "gsq_debug_mmv_pdl", "gsq_debug_mmv_prefetch_first",
+    "gsq_debug_mmv_profile", "gsq_debug_mmv_max_rows", "gsq_debug_mmv_pdl", "gsq_debug_mmv_prefetch_first", "gsq_debug_mmv_chunking", "gsq_debug_mmv_trace",
     "gsq_linear", "gsq_linear_scratch_bytes",
 )
 
@@ -102,7 +102,7 @@ def _load() -> C.CDLL:
     lib.gsq_linear_vec_static_max_q8_bytes.restype = i64
     lib.gsq_debug_mmv_profile.restype = ci
     lib.gsq_debug_mmv_profile.argtypes = [vp]
-    for name in ("gsq_debug_mmv_mode", "gsq_debug_mmv_min_rows", "gsq_debug_mmv_max_rows", "gsq_debug_mmv_cluster_size", "gsq_debug_mmv_pdl", "gsq_debug_mmv_prefetch_first"):
+    for name in ("gsq_debug_mmv_mode", "gsq_debug_mmv_min_rows", "gsq_debug_mmv_max_rows", "gsq_debug_mmv_cluster_size", "gsq_debug_mmv_pdl", "gsq_debug_mmv_prefetch_first", "gsq_debug_mmv_chunking", "gsq_debug_mmv_trace"):
         getattr(lib, name).restype = ci
         getattr(lib, name).argtypes = [ci]
     lib.gsq_mul_mat_vec_max_rows.restype = ci
