@@ -38,6 +38,11 @@ int gsq_debug_block_sums(const void* w, int64_t row_bytes, int64_t rows, int ggm
 int gsq_debug_swap_descriptor_strides(int on);
 int gsq_debug_gemm_dump_sums(int32_t* sums);
 int gsq_debug_gemm_variant(int v); /* kernel behind gsq_linear above the small-batch row counts: 0 = prefill GEMM (default), 1 / 2 = the warp-specialised / lockstep kernels of gsq_mul_mat_q8; returns previous */
+/* device buffer of 16 uint64 per CTA that the prefill GEMM fills with clock counts of its roles' waits and work (a
+ * separate instantiation; NULL switches it off): [0] producer waits for a free stage, [1] decodes; MMA thread waits
+ * for [2] a weight tile, [3] a drained half of tensor memory, [4] an activation unit; consumer warp 4: [5] waits for
+ * the unit, [6] for the MMA, [7] scales, [8] waits for the scale planes; warps 7 and 19 likewise at [9..11], [12..14] */
+int gsq_debug_gemm_profile(unsigned long long* clocks);
 int gsq_debug_gemm_ksplit(int ks); /* 0 = choose; 1, 2, 4 = CTAs per cluster that split K (experiments) */
 /* The register-operand tensor-core kernel that serves 1..48 activation rows behind gsq_mul_mat_vec_q8 and
  * gsq_mul_mat_q8 (experiments and tests; each returns the previous value). */

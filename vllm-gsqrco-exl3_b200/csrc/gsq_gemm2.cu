@@ -64,6 +64,7 @@ struct Args {
   int64_t ldy;
   int n_row_tiles, n_tok_blocks;
   int* dump;           // debug: raw int32 slice sums [m][nrows][k / 32]
+  unsigned long long* prof;  // debug: per CTA 16 clock counts (see gsq_debug_gemm_profile)
 };
 
 // shared-memory map (byte offsets from the 1024-byte aligned base)
@@ -105,7 +106,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         : "r"(bar), "r"(parity)
         : "memory");
     if (done) return true;
-    __nanosleep(32);   // a waiting warp should not spend the issue slots of the working ones on polls
+    __nanosleep(100);  // a waiting warp should not spend the issue slots of the working ones on polls
     if ((spin & 63) == 63 && *abort_flag) return false;
   }
   *abort_flag = 1;
@@ -370,19 +371,21 @@ __device__ __forceinline__ void decode_iq4xs(const uint8_t* raw, uint8_t* a, flo
 // the result is the correctly rounded product. acc: the 4 register pairs of these 8 columns.
 template <bool DS>
 __device__ __forceinline__ void scale8(const uint32_t (&c)[8], float da, float dam, const float* bd, const float* bs,
-                                       uint64_t* acc) {
-  const uint64_t da2 = pack2(da, da), nmda2 = pack2(-MAGIC_F * da, -MAGIC_F * da), dam2 = pack2(dam, dam);
+                                       float2* acc) {
+  // packed fp32 FMAs (two elements per instruction; measured against scalar FMAs: the same pipe time, half the
+  // issue slots)
+  const float2 da2 = make_float2(da, da), nmda2 = make_float2(-MAGIC_F * da, -MAGIC_F * da), dam2 = make_float2(dam, dam);
 #pragma unroll
   for (int j4 = 0; j4 < 2; ++j4) {
     const float4 d = *reinterpret_cast<const float4*>(bd + 4 * j4);
-    const uint64_t t0 = fma2(pack2(biased_float(c[4 * j4]), biased_float(c[4 * j4 + 1])), da2, nmda2);
-    const uint64_t t1 = fma2(pack2(biased_float(c[4 * j4 + 2]), biased_float(c[4 * j4 + 3])), da2, nmda2);
-    acc[2 * j4] = fma2(t0, pack2(d.x, d.y), acc[2 * j4]);
-    acc[2 * j4 + 1] = fma2(t1, pack2(d.z, d.w), acc[2 * j4 + 1]);
+    const float2 t0 = __ffma2_rn(make_float2(biased_float(c[4 * j4]), biased_float(c[4 * j4 + 1])), da2, nmda2);
+    const float2 t1 = __ffma2_rn(make_float2(biased_float(c[4 * j4 + 2]), biased_float(c[4 * j4 + 3])), da2, nmda2);
+    acc[2 * j4] = __ffma2_rn(t0, make_float2(d.x, d.y), acc[2 * j4]);
+    acc[2 * j4 + 1] = __ffma2_rn(t1, make_float2(d.z, d.w), acc[2 * j4 + 1]);
     if (DS) {
       const float4 s = *reinterpret_cast<const float4*>(bs + 4 * j4);
-      acc[2 * j4] = fma2(dam2, pack2(s.x, s.y), acc[2 * j4]);
-      acc[2 * j4 + 1] = fma2(dam2, pack2(s.z, s.w), acc[2 * j4 + 1]);
+      acc[2 * j4] = __ffma2_rn(dam2, make_float2(s.x, s.y), acc[2 * j4]);
+      acc[2 * j4 + 1] = __ffma2_rn(dam2, make_float2(s.z, s.w), acc[2 * j4 + 1]);
     }
   }
 }
@@ -395,8 +398,11 @@ __device__ __forceinline__ void dump8(const Args& g, const uint32_t (&c)[8], int
   }
 }
 
-template <int KIND, bool DUMP>
+template <int KIND, int MODE>
 __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
+  constexpr bool DUMP = MODE == 1, PROF = MODE == 2;
+  unsigned long long pw[4] = {0ull, 0ull, 0ull, 0ull};   // debug (MODE 2): clocks spent in this thread's waits / work
+  auto tick = [&]() -> unsigned long long { return PROF ? (unsigned long long)clock64() : 0ull; };
   extern __shared__ __align__(1024) uint8_t smem[];
   using S = Smem<KIND>;
   constexpr bool DS = KIND == G2_Q4K;
@@ -476,7 +482,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
         asm volatile("bar.sync 1, %0;" ::"n"(PROD_THREADS) : "memory");   // everyone's have; everyone is done with n - 1
         fetch_next((int)n + 2);
         const uint32_t st = n & 1u;
+        const unsigned long long p0 = tick();
         alive = alive && mbar_wait(a_empty(st), ((n >> 1) & 1u) ^ 1u, abort_flag);
+        const unsigned long long p1 = tick();
+        pw[0] += p1 - p0;
         if (!alive) continue;
         const uint8_t* raw = smem + S::RAW + (n % RAW_STAGES) * RAWB;
         uint8_t* a = smem + S::A + st * (8 * SL_A);
@@ -490,7 +499,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> tensor-core reads
         mbar_arrive(a_full(st));
+        pw[1] += tick() - p1;
       }
+    }
+    if (PROF && tid == 0) {
+      g.prof[blockIdx.x * 16 + 0] = pw[0];   // producer: waiting for a free stage
+      g.prof[blockIdx.x * 16 + 1] = pw[1];   // producer: decoding
     }
     cp_async_wait<0>();
   } else if (warp == 3) {
@@ -523,16 +537,23 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
         const int nu = 2 * item_nsub(item);
         for (int sb = 0; sb < nsb && alive; ++sb, ++n) {
           const uint32_t st = n & 1u;
+          const unsigned long long m0 = tick();
           alive = mbar_wait(a_full(st), (n >> 1) & 1u, abort_flag);
+          pw[0] += tick() - m0;
           if (!alive) break;
           const uint32_t a_addr = saddr(smem + S::A + st * (8 * SL_A));
           for (int u = 0; u < nu; ++u, ++gu) {
             const uint32_t slot = gu & (B_SLOTS - 1), half = gu & 1u;
             // the consumers have drained this half of tensor memory (unit gu - 2) ...
+            const unsigned long long m1 = tick();
             alive = mbar_wait(d_empty(half), ((gu >> 1) & 1u) ^ 1u, abort_flag);
+            const unsigned long long m2 = tick();
+            pw[1] += m2 - m1;
             if (!alive) break;
             load_next();   // ... and with it released that unit's activation slot: the copy for unit gu + 6 goes there
+            const unsigned long long m3 = tick();
             alive = alive && mbar_wait(b_full(slot), (gu >> 3) & 1u, abort_flag);
+            pw[2] += tick() - m3;
             if (!alive) break;
             tc_fence_after();
             const uint32_t b_addr = saddr(smem + S::B + slot * UB);
@@ -544,6 +565,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
             mma_commit(d_full(half));
           }
         }
+      }
+      if (PROF) {
+        g.prof[blockIdx.x * 16 + 2] = pw[0];   // MMA thread: waiting for a decoded weight tile
+        g.prof[blockIdx.x * 16 + 3] = pw[1];   // MMA thread: waiting for a drained half of tensor memory
+        g.prof[blockIdx.x * 16 + 4] = pw[2];   // MMA thread: waiting for an activation unit
       }
       if (!alive) {
         // a wait gave up: let the copies already issued land (bounded) before the CTA's shared memory goes away
@@ -560,15 +586,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
     bool alive = true;
     for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
       const int rt = item_rt(item), tok0 = item_tb(item) * (NSUB * NT), nsub = item_nsub(item);
-      uint64_t acc[NSUB][8];
+      float2 acc[NSUB][8];
 #pragma unroll
       for (int j = 0; j < NSUB; ++j) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[j][i] = 0ull;
+        for (int i = 0; i < 8; ++i) acc[j][i] = make_float2(0.0f, 0.0f);
       }
       for (int sb = 0; sb < nsb && alive; ++sb, ++n) {
         const uint32_t st = n & 1u;
+        const unsigned long long c0t = tick();
         alive = mbar_wait(a_full(st), (n >> 1) & 1u, abort_flag);   // the producers' scale planes are visible
+        pw[0] += tick() - c0t;
         if (!alive) break;
         const float* sa = reinterpret_cast<const float*>(smem + S::SA + st * (scale_planes(KIND) * 8 * TR * 4));
         // One copy of the unit code per sub-tile (the accumulators of a sub-tile are fixed registers); the two units
@@ -580,8 +608,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
 #pragma unroll 1
             for (int h = 0; h < 2; ++h) {
               const uint32_t slot = gu & (B_SLOTS - 1);
-              alive = alive && mbar_wait(b_full(slot), (gu >> 3) & 1u, abort_flag) &&   // the unit's scales are visible
-                      mbar_wait(d_full(h), (gu >> 1) & 1u, abort_flag);
+              const unsigned long long c1t = tick();
+              alive = alive && mbar_wait(b_full(slot), (gu >> 3) & 1u, abort_flag);   // the unit's scales are visible
+              const unsigned long long c2t = tick();
+              alive = alive && mbar_wait(d_full(h), (gu >> 1) & 1u, abort_flag);
+              const unsigned long long c3t = tick();
+              pw[1] += c2t - c1t;
+              pw[2] += c3t - c2t;
               if (alive) {
                 tc_fence_after();
                 const float* bsc = reinterpret_cast<const float*>(smem + S::B + slot * UB + 4 * SL_B) + 16 * cg;
@@ -610,6 +643,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
                   mbar_arrive(b_empty(slot));
                   mbar_arrive(d_empty(h));
                 }
+                pw[3] += tick() - c3t;
               }
               ++gu;
             }
@@ -626,8 +660,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
           if (j < nsub) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              float v0, v1;
-              unpack2(acc[j][i], v0, v1);
+              const float v0 = acc[j][i].x, v1 = acc[j][i].y;
               const int tok = tok0 + j * NT + 16 * cg + 2 * i;
               if (tok < g.m) store_out_dyn(g.y, g.y_dtype, (int64_t)tok * g.ldy + row, v0);
               if (tok + 1 < g.m) store_out_dyn(g.y, g.y_dtype, (int64_t)(tok + 1) * g.ldy + row, v1);
@@ -636,6 +669,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
         }
       }
     }
+  }
+  if (PROF && warp >= 4 && lane == 0 && (warp == 4 || warp == 7 || warp == 19)) {
+    // three of the consumer warps (lane quarters 0, 3, 3; column groups 0, 0, 3): clocks waiting for scale planes,
+    // activation unit, MMA result; clocks scaling
+    const int o = warp == 4 ? 5 : warp == 7 ? 9 : 12;
+    g.prof[blockIdx.x * 16 + o] = pw[1];
+    g.prof[blockIdx.x * 16 + o + 1] = pw[2];
+    g.prof[blockIdx.x * 16 + o + 2] = pw[3];
+    if (warp == 4) g.prof[blockIdx.x * 16 + 8] = pw[0];
   }
   tc_fence_before();
   __syncthreads();
@@ -651,16 +693,19 @@ static int launch(const Args& g, int sm_count, cudaStream_t st) {
   static_assert(smem <= 227 * 1024, "shared memory budget");
   if (dev < 0 || dev >= 64) return GSQ_ERR_UNSUPPORTED;
   if (!configured[dev]) {
-    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm2_kernel<KIND, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm2_kernel<KIND, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm2_kernel<KIND, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm2_kernel<KIND, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm2_kernel<KIND, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured[dev] = true;
   }
   const int n_items = g.n_row_tiles * g.n_tok_blocks;
   const int grid = n_items < sm_count ? n_items : sm_count;
   if (g.dump) {
-    gemm2_kernel<KIND, true><<<grid, THREADS, smem, st>>>(g);
+    gemm2_kernel<KIND, 1><<<grid, THREADS, smem, st>>>(g);
+  } else if (g.prof) {
+    gemm2_kernel<KIND, 2><<<grid, THREADS, smem, st>>>(g);
   } else {
-    gemm2_kernel<KIND, false><<<grid, THREADS, smem, st>>>(g);
+    gemm2_kernel<KIND, 0><<<grid, THREADS, smem, st>>>(g);
   }
   GSQ_CUDA_TRY(cudaGetLastError());
   return GSQ_OK;
@@ -670,6 +715,8 @@ static int launch(const Args& g, int sm_count, cudaStream_t st) {
 
 // gsq_gemm.cu
 int* gemm_dump_pointer();
+
+static unsigned long long* g_prof = nullptr;
 
 int gemm2_error_flag(int* flag) {
   GSQ_CUDA_TRY(cudaMemcpyFromSymbol(flag, g2::g_error, sizeof(int)));
@@ -711,6 +758,7 @@ int gemm2_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
   g.n_row_tiles = (int)((rows + g2::TR - 1) / g2::TR);
   g.n_tok_blocks = (int)((m + g2::NSUB * g2::NT - 1) / (g2::NSUB * g2::NT));
   g.dump = gemm_dump_pointer();
+  g.prof = g_prof;
   cudaStream_t st = (cudaStream_t)stream;
   switch (ggml_type) {
     case GSQ_TYPE_IQ3_S: return g2::launch<G2_IQ3S>(g, di.sm_count, st);
@@ -720,3 +768,8 @@ int gemm2_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
 }
 
 }  // namespace gsq
+
+extern "C" int gsq_debug_gemm_profile(unsigned long long* clocks) {
+  gsq::g_prof = clocks;
+  return GSQ_OK;
+}
