@@ -127,20 +127,22 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(init));
 }
 
-// For IQ3_S from two column groups on, and for IQ4_XS always, the integer sub-scale is applied on the floating-point side: the tensor-core
-// instruction accumulates onto the bit pattern of 1.5 * 2^23, so its outputs, read as floats, only need that
-// constant subtracted (|sum| < 2^22), in place, as the two packed pairs they already are; the row's
-// d * sub-scale then joins the column scale in one packed multiply. Per slice and column group 6 packed
-// instructions instead of 4 integer multiply-adds, their moves into pairs and 6 packed instructions.
+// For IQ3_S from two column groups on, and for IQ4_XS always, the integer sub-scale is applied on the floating-point
+// side: the tensor-core instruction accumulates onto the bit pattern of 1.5 * 2^23, so its outputs, read as floats, are
+// 1.5 * 2^23 + sum (|sum| < 2^22), already the two packed pairs the fp32x2 instructions want. Per slice and column
+// group 4 packed instructions (see scale_acc) instead of 4 integer multiply-adds, their moves into pairs and 6
+// packed instructions.
 constexpr bool mmv_float_scale(int ntl) { return ntl >= 2; }
 
-__device__ __forceinline__ void scale_acc(const int (&c)[4], uint64_t dv2, uint64_t ds0, uint64_t ds1, uint64_t& a0,
-                                          uint64_t& a1) {
-  const uint64_t nm2 = pk2(-MAGIC_F, -MAGIC_F);
-  const uint64_t f01 = vadd2(pk2(__int_as_float(c[0]), __int_as_float(c[1])), nm2);
-  const uint64_t f23 = vadd2(pk2(__int_as_float(c[2]), __int_as_float(c[3])), nm2);
-  a0 = vfma2(f01, vmul2(dv2, ds0), a0);
-  a1 = vfma2(f23, vmul2(dv2, ds1), a1);
+__device__ __forceinline__ void scale_acc(const int (&c)[4], uint64_t dv2, uint64_t ds0, uint64_t ds1, uint64_t nm0,
+                                          uint64_t nm1, uint64_t& a0, uint64_t& a1) {
+  // c holds the bit patterns of 1.5 * 2^23 + sum. (1.5 * 2^23 + sum) * ds - 1.5 * 2^23 * ds in one fused operation is
+  // the correctly rounded sum * ds: ds = d * sub-scale has at most 17 significant bits, so the subtrahend nm =
+  // -1.5 * 2^23 * ds is exact. Two packed operations per pair of columns.
+  const uint64_t t01 = vfma2(pk2(__int_as_float(c[0]), __int_as_float(c[1])), ds0, nm0);
+  const uint64_t t23 = vfma2(pk2(__int_as_float(c[2]), __int_as_float(c[3])), ds1, nm1);
+  a0 = vfma2(t01, dv2, a0);
+  a1 = vfma2(t23, dv2, a1);
 }
 
 template <bool DUMP>
@@ -383,34 +385,56 @@ __device__ __forceinline__ void process(const RecQ4K& r, const MmvArgs& ar, int 
     uint32_t a[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) a[i] = ((s & 1) ? (w[i] >> 4) : w[i]) & 0x0F0F0F0Fu;
-    const int sc0 = (int)((scw[0][s >> 2] >> (8 * (s & 3))) & 0xFFu), sc1 = (int)((scw[1][s >> 2] >> (8 * (s & 3))) & 0xFFu);
     float m0 = byte_float(mnw[0][s >> 2], s & 3), m1 = byte_float(mnw[1][s >> 2], s & 3);
     if constexpr (!DEFER) {
       m0 *= ndm[0];
       m1 *= ndm[1];
     }
     const uint64_t m02 = pk2(m0, m0), m12 = pk2(m1, m1);
-#pragma unroll
-    for (int j = 0; j < NTL; ++j) {
-      const uint2 b = *reinterpret_cast<const uint2*>(xl.q + j * xl.q8 + s * 32);
-      const uint64_t dv2 = *reinterpret_cast<const uint64_t*>(xl.d + s * MC + 8 * j);
-      const uint64_t xs2 = *reinterpret_cast<const uint64_t*>(xl.s + s * MC + 8 * j);
+    if constexpr (NTL == 1) {
+      // one column group: the sub-scale as an integer multiply-add onto the magic pattern (measured faster here)
+      const int sc0 = (int)((scw[0][s >> 2] >> (8 * (s & 3))) & 0xFFu), sc1 = (int)((scw[1][s >> 2] >> (8 * (s & 3))) & 0xFFu);
+      const uint2 b = *reinterpret_cast<const uint2*>(xl.q + s * 32);
+      const uint64_t dv2 = *reinterpret_cast<const uint64_t*>(xl.d + s * MC);
+      const uint64_t xs2 = *reinterpret_cast<const uint64_t*>(xl.s + s * MC);
       int c[4];
-      {
-        mma_s8(c, a, b.x, b.y, 0);
-        dump_c<DUMP>(ar, c, 0, row0, lane, j, sb * 8 + s);
-        // (applying the sub-scale on the floating-point side, as the other two types do, measured slower here)
-        // |c * sc| <= 32 * 15 * 127 * 63 < 2^22: integer multiply-add onto the magic pattern, read as a float
-        const uint64_t f01 = vadd2(pk2(__int_as_float(c[0] * sc0 + MAGIC), __int_as_float(c[1] * sc0 + MAGIC)), nm2);
-        const uint64_t f23 = vadd2(pk2(__int_as_float(c[2] * sc1 + MAGIC), __int_as_float(c[3] * sc1 + MAGIC)), nm2);
+      mma_s8(c, a, b.x, b.y, 0);
+      dump_c<DUMP>(ar, c, 0, row0, lane, 0, sb * 8 + s);
+      // |c * sc| <= 32 * 15 * 127 * 63 < 2^22
+      const uint64_t f01 = vadd2(pk2(__int_as_float(c[0] * sc0 + MAGIC), __int_as_float(c[1] * sc0 + MAGIC)), nm2);
+      const uint64_t f23 = vadd2(pk2(__int_as_float(c[2] * sc1 + MAGIC), __int_as_float(c[3] * sc1 + MAGIC)), nm2);
+      tt[0][0] = vfma2(f01, dv2, tt[0][0]);
+      tt[0][1] = vfma2(f23, dv2, tt[0][1]);
+      uu[0][0] = vfma2(m02, xs2, uu[0][0]);
+      uu[0][1] = vfma2(m12, xs2, uu[0][1]);
+    } else {
+      // several column groups: the sub-scale on the floating-point side, two packed operations per pair of columns
+      // (scale_acc); the multiplier (sc, or d * sc where the record's sums are not deferred) has at most 17
+      // significant bits, so -1.5 * 2^23 times it is exact
+      float f0 = byte_float(scw[0][s >> 2], s & 3), f1 = byte_float(scw[1][s >> 2], s & 3);
+      if constexpr (!DEFER) {
+        f0 *= d[0];
+        f1 *= d[1];
+      }
+      const uint64_t ds0 = pk2(f0, f0), ds1 = pk2(f1, f1);
+      const float g0 = -MAGIC_F * f0, g1 = -MAGIC_F * f1;
+      const uint64_t nmA = pk2(g0, g0), nmB = pk2(g1, g1);
+#pragma unroll
+      for (int j = 0; j < NTL; ++j) {
+        const uint2 b = *reinterpret_cast<const uint2*>(xl.q + j * xl.q8 + s * 32);
+        const uint64_t dv2 = *reinterpret_cast<const uint64_t*>(xl.d + s * MC + 8 * j);
+        const uint64_t xs2 = *reinterpret_cast<const uint64_t*>(xl.s + s * MC + 8 * j);
+        int c[4];
+        mma_s8(c, a, b.x, b.y, MAGIC);
+        dump_c<DUMP>(ar, c, MAGIC, row0, lane, j, sb * 8 + s);
         if constexpr (DEFER) {
-          tt[j][0] = vfma2(f01, dv2, tt[j][0]);
-          tt[j][1] = vfma2(f23, dv2, tt[j][1]);
+          scale_acc(c, dv2, ds0, ds1, nmA, nmB, tt[j][0], tt[j][1]);
           uu[j][0] = vfma2(m02, xs2, uu[j][0]);
           uu[j][1] = vfma2(m12, xs2, uu[j][1]);
         } else {
-          acc[j][0] = vfma2(m02, xs2, vfma2(f01, vmul2(dv2, d02), acc[j][0]));
-          acc[j][1] = vfma2(m12, xs2, vfma2(f23, vmul2(dv2, d12), acc[j][1]));
+          scale_acc(c, dv2, ds0, ds1, nmA, nmB, acc[j][0], acc[j][1]);
+          acc[j][0] = vfma2(m02, xs2, acc[j][0]);
+          acc[j][1] = vfma2(m12, xs2, acc[j][1]);
         }
       }
     }
@@ -497,6 +521,8 @@ __device__ __forceinline__ void iq3_slice(const RecIQ3S& r, const MmvArgs& ar, i
     upk2(d2[1], h0, h1);
     const float f1 = h0 * byte_float(iscw[1][S & 1], S >> 1);
     const uint64_t ds0 = pk2(f0, f0), ds1 = pk2(f1, f1);
+    const float g0 = -MAGIC_F * f0, g1 = -MAGIC_F * f1;
+    const uint64_t nm0 = pk2(g0, g0), nm1 = pk2(g1, g1);
 #pragma unroll
     for (int j = 0; j < NTL; ++j) {
       const uint2 b = *reinterpret_cast<const uint2*>(xl.q + j * xl.q8 + S * 32);
@@ -504,7 +530,7 @@ __device__ __forceinline__ void iq3_slice(const RecIQ3S& r, const MmvArgs& ar, i
       int c[4];
       mma_s8(c, a, b.x, b.y, MAGIC);
       dump_c<DUMP>(ar, c, MAGIC, row0, lane, j, sb * 8 + S);
-      scale_acc(c, dv2, ds0, ds1, acc[j][0], acc[j][1]);
+      scale_acc(c, dv2, ds0, ds1, nm0, nm1, acc[j][0], acc[j][1]);
     }
   } else {
     const int sc0 = (int)((iscw[0][S & 1] >> (8 * (S >> 1))) & 0xFFu), sc1 = (int)((iscw[1][S & 1] >> (8 * (S >> 1))) & 0xFFu);
@@ -630,6 +656,8 @@ __device__ __forceinline__ void process(const RecIQ4XS& r, const MmvArgs& ar, in
     upk2(d2[1], h0, h1);
     const float f1 = h0 * (float)sc1;
     const uint64_t ds0 = pk2(f0, f0), ds1 = pk2(f1, f1);
+    const float g0 = -MAGIC_F * f0, g1 = -MAGIC_F * f1;
+    const uint64_t nm0 = pk2(g0, g0), nm1 = pk2(g1, g1);
 #pragma unroll
     for (int j = 0; j < NTL; ++j) {
       const uint2 b = *reinterpret_cast<const uint2*>(xl.q + j * xl.q8 + s * 32);
@@ -637,7 +665,7 @@ __device__ __forceinline__ void process(const RecIQ4XS& r, const MmvArgs& ar, in
       int c[4];
       mma_s8(c, a, b.x, b.y, MAGIC);
       dump_c<DUMP>(ar, c, MAGIC, row0, lane, j, sb * 8 + s);
-      scale_acc(c, dv2, ds0, ds1, acc[j][0], acc[j][1]);
+      scale_acc(c, dv2, ds0, ds1, nm0, nm1, acc[j][0], acc[j][1]);
     }
   }
 }
