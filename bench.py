@@ -730,6 +730,7 @@ def extra_decode_stack(dev, capture, layers=64):
                     "frac_of_measured_hbm": round(bytes_step / best / 1e6 / hbm, 4)})
     # the same stack followed by the Q6_K output head 151936 x 5120 (the 1-GPU form of the tensor-parallel config)
     head = torch.from_numpy(synth.make_weight(14, 151936, 5120, 3000)).to(dev)
+    iq3_pack.pack_(head, 14)    # repacked at load, as GGUFLinearMethod.process_weights_after_loading does
     res_head = []
     for rows in (32,):
         x5 = torch.randn(rows, 5120, device=dev, dtype=torch.bfloat16)
@@ -741,7 +742,7 @@ def extra_decode_stack(dev, capture, layers=64):
                 linear.fused_mul_mat_gguf(x5, lw["o"], 21, None, True)
                 linear.fused_mul_mat_gguf(x5, lw["gate_up"], 21, None, True)
                 linear.fused_mul_mat_gguf(x17, lw["down"], 23, None, False)
-            linear.fused_mul_mat_gguf(x5, head, 14, None, False)
+            linear.fused_mul_mat_gguf(x5, head, 14, None, True)
         g = capture(step_head)
         best = 1e30
         for _ in range(3):

@@ -203,6 +203,16 @@ int gsq_linear(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
 int gsq_iq3s_repack(void* w, int64_t rows, int64_t row_bytes, int direction, void* stream);
 
 /*
+ * Q6_K load-time repack, in place, bijective; no counterpart in the reference, which reads Q6_K in GGUF order
+ * with its vendored kernels. GGUF's 210-byte blocks are only 2-byte aligned; the repack is a byte permutation
+ * inside each 16-row tile into 3360-byte records (one per superblock) in which a lane's share of the int8
+ * tensor-core fragments is six 128-bit loads (layout in csrc/gsq_repack.cu). Arguments as gsq_iq3s_repack
+ * (row_bytes a multiple of 210). Repacked Q6_K is passed to the product entry points with packed != 0 and is
+ * served by the small-batch tensor-core kernel at every row count (48 rows per launch).
+ */
+int gsq_q6k_repack(void* w, int64_t rows, int64_t row_bytes, int direction, void* stream);
+
+/*
  * Kernel choice on B200 for (activation rows m, type, weight rows, k, packed): GSQ_KERNEL_*.
  * The op-level routing table of the reference (_lcpp_op, quantization/linear.py:85-114) stays in the
  * Python layer because its op names are API; this is the choice made underneath those names.

@@ -53,3 +53,43 @@ def pack_ref(w: np.ndarray) -> np.ndarray:
             off = t * ROWS * rb + j * REC
             out[off: off + REC] = rec
     return out.reshape(rows, rb)
+
+
+# ---------------------------------------------------------------------------------------------
+# Q6_K streaming layout (csrc/gsq_repack.cu): a byte permutation inside each 16-row tile, one 3360-byte record per
+# superblock. The reference does not repack Q6_K; the properties checked are the ones it checks for IQ3_S.
+
+BS6, REC6 = 210, 3360
+
+
+def pack_q6k_ref(w: np.ndarray) -> np.ndarray:
+    rows, rb = w.shape
+    assert rows % ROWS == 0 and rb % BS6 == 0
+    nb = rb // BS6
+    out = np.zeros_like(w).reshape(-1)
+    src = w.reshape(rows, nb, BS6)
+    for t in range(rows // ROWS):
+        for j in range(nb):
+            rec = np.zeros(REC6, dtype=np.uint8)
+            for lane in range(32):
+                g, tt = lane >> 2, lane & 3
+                for h in range(2):
+                    b = src[16 * t + g + 8 * h, j]
+                    for n in range(2):
+                        for qb in range(2):
+                            for i in range(2):       # is
+                                w8 = 4 * n + 2 * qb + i
+                                o = 64 * lane + 32 * h + 4 * w8
+                                rec[o: o + 4] = b[64 * n + 32 * qb + 16 * i + 4 * tt: 64 * n + 32 * qb + 16 * i + 4 * tt + 4]
+                        for i in range(2):
+                            w4 = 2 * n + i
+                            o = 2048 + 32 * lane + 16 * h + 4 * w4
+                            rec[o: o + 4] = b[128 + 32 * n + 16 * i + 4 * tt: 128 + 32 * n + 16 * i + 4 * tt + 4]
+            for g in range(8):
+                for h in range(2):
+                    b = src[16 * t + g + 8 * h, j]
+                    rec[3072 + 32 * g + 16 * h: 3088 + 32 * g + 16 * h] = b[192:208]
+                    rec[3328 + 4 * g + 2 * h: 3330 + 4 * g + 2 * h] = b[208:210]
+            off = t * ROWS * rb + j * REC6
+            out[off: off + REC6] = rec
+    return out.reshape(rows, rb)

@@ -56,7 +56,7 @@ def _x(m, k, dtype, seed, outliers=0.0):
 def _ours(raw, t, x):
     """apply()'s product on this library: IQ3_S repacked at load, the routed op of the row count."""
     w = raw.to(DEV)
-    packed = t == IQ3_S and w.shape[0] % 16 == 0
+    packed = t in (IQ3_S, Q6_K) and w.shape[0] % 16 == 0
     if packed:
         iq3_pack.pack_(w, t)
     return w, packed
@@ -128,13 +128,14 @@ def test_prefill_products_match_reference_kernels(tname, t, n, k, tmp_path):
 def test_q6k_output_head_matches_reference_kernels(tmp_path):
     n, k = 151936, 5120
     raw = torch.from_numpy(synth.make_weight(Q6_K, n, k, 3000))
-    w = raw.to(DEV)
+    w, packed = _ours(raw, Q6_K, None)          # repacked at load, as apply() does
+    assert packed
     cases, mine, ms = [], [], [1, 8, 32]
     for m in ms:
         x = _x(m, k, torch.float32, 3100 + m)
         op = linear._lcpp_op(m, Q6_K, n, k, False)
         cases.append({"op": op, "args": [raw, x, Q6_K, n] + ([] if op in linear._OWN_QUANTIZE_OPS else [None])})
-        mine.append(linear.fused_mul_mat_gguf(x.to(DEV), w, Q6_K, None, False).cpu())
+        mine.append(linear.fused_mul_mat_gguf(x.to(DEV), w, Q6_K, None, packed).cpu())
     res = run_reference(cases, tmp_path)
     for m, y, r in zip(ms, mine, res):
         err = product.rel_err(y.numpy(), r["out"].double().numpy())

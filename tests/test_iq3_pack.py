@@ -67,3 +67,36 @@ def test_rejects_bad_input():
         iq3_pack.pack(w, IQ3_S)
     with pytest.raises(AssertionError):
         iq3_pack.pack(torch.zeros(16, 144, dtype=torch.uint8), 12)
+
+
+# ---------------------------------------------------------------------------------------------
+# Q6_K: the same functions, a byte permutation per 16-row tile (no counterpart in the reference; the properties
+# are the ones it pins for IQ3_S)
+
+Q6_K = 14
+
+
+def test_q6k_matches_definition_and_round_trips():
+    w = synth.make_weight(Q6_K, 32, 1024, 6)
+    p = iq3_pack.pack(torch.from_numpy(w), Q6_K)
+    assert np.array_equal(p.numpy(), iq3_layout.pack_q6k_ref(w))
+    assert torch.equal(iq3_pack.unpack(p, Q6_K), torch.from_numpy(w))
+    assert not torch.equal(p, torch.from_numpy(w))
+    assert sorted(iq3_pack.q6k_record_source().tolist()) == list(range(3360))
+
+
+def test_q6k_tile_locality_and_in_place_view():
+    g = torch.Generator().manual_seed(2)
+    w = torch.randint(0, 256, (48, 210 * 3), dtype=torch.uint8, generator=g)
+    p = iq3_pack.pack(w, Q6_K)
+    w2 = w.clone()
+    w2[16:32] = torch.randint(0, 256, (16, 630), dtype=torch.uint8, generator=g)
+    p2 = iq3_pack.pack(w2, Q6_K)
+    assert torch.equal(p[:16], p2[:16]) and torch.equal(p[32:], p2[32:]) and not torch.equal(p[16:32], p2[16:32])
+    wide = torch.zeros(64, 210 * 3, dtype=torch.uint8)
+    wide[8:40].view(-1)[: 32 * 630].view(32, 630).copy_(w[:32])          # a run inside a wider buffer
+    view = wide[8:40].view(-1)[: 32 * 630].view(32, 630)
+    iq3_pack.pack_(view, Q6_K)
+    assert torch.equal(view, p[:32]) and not wide[:8].any() and not wide[40:].any()
+    with pytest.raises(AssertionError):
+        iq3_pack.pack(w[:24], Q6_K)

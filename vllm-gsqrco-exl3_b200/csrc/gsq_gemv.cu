@@ -954,6 +954,8 @@ static int gemv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_ty
     const int rc = mmv_host(w, row_bytes, rows, ggml_type, packed, x_q8, 0, m, k, y, y_dtype, y_row_stride, stream, d);
     if (rc != 1000) return rc;  // 1000: the shape does not fit that kernel
   }
+  // repacked Q6_K is read by the small-batch tensor-core kernel only
+  if (ggml_type == GSQ_TYPE_Q6_K && packed) return m > 48 ? GSQ_ERR_UNSUPPORTED : GSQ_ERR_TOO_LARGE;
   if (m > 8 && m <= 48 && y && x_q8 && k > 0 && k % 32 == 0 &&
       (y_dtype == GSQ_F32 || y_dtype == GSQ_F16 || y_dtype == GSQ_BF16)) {
     // Row counts only the small-batch kernel takes in one launch, on a shape it declined (its staging area does

@@ -67,6 +67,19 @@ extern "C" int gsq_linear(const void* w, int64_t row_bytes, int64_t rows, int gg
     if (rc != GSQ_OK) return rc;
     return gsq_mul_mat_q8(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, nullptr, 0, stream);
   }
+  if (ggml_type == GSQ_TYPE_Q6_K && packed) {
+    // repacked Q6_K above 48 rows: the small-batch kernel, 48 rows per launch, on 36-byte blocks of the whole X
+    rc = gsq_quantize_q8_1(x, x_dtype, m, k, x_row_stride, scratch, stream);
+    if (rc != GSQ_OK) return rc;
+    const int64_t ysz6 = y_dtype == GSQ_F32 ? 4 : 2;
+    for (int64_t i = 0; i < m; i += 48) {
+      const int64_t c = m - i < 48 ? m - i : 48;
+      rc = mmv_host(w, row_bytes, rows, ggml_type, packed, (const uint8_t*)scratch + i * (k / 32) * 36, 0, c, k,
+                    (uint8_t*)y + i * y_row_stride * ysz6, y_dtype, y_row_stride, stream, nullptr);
+      if (rc != GSQ_OK) return rc == 1000 ? GSQ_ERR_TOO_LARGE : rc;
+    }
+    return GSQ_OK;
+  }
   // Q6_K and IQ3_S in GGUF order: the dp4a kernel on 36-byte blocks, as many rows per launch as it takes
   rc = gsq_quantize_q8_1(x, x_dtype, m, k, x_row_stride, scratch, stream);
   if (rc != GSQ_OK) return rc;

@@ -39,7 +39,7 @@ namespace cg = cooperative_groups;
 
 namespace gsq {
 
-enum { MK_Q4K = 0, MK_IQ3S = 1, MK_IQ4XS = 2 };
+enum { MK_Q4K = 0, MK_IQ3S = 1, MK_IQ4XS = 2, MK_Q6K = 3 };
 enum { XL_Q81 = 0, XL_MMQ = 1 };
 
 constexpr int MMV_WARPS = 16;
@@ -671,10 +671,144 @@ __device__ __forceinline__ void process(const RecIQ4XS& r, const MmvArgs& ar, in
 }
 
 // ---------------------------------------------------------------------------------------------
+// Q6_K in the fragment-ordered layout of gsq_q6k_repack (see gsq_repack.cu): per lane and row the eight words of low
+// nibbles (n, qb, is), the four words of 2-bit high parts (n, is), and per row the 16 int8 sub-scales and d. A
+// sub-scale covers 16 values, so the products are m16n8k16 (one per 16-value group G = 8 n + 2 q + is, q = 0..3:
+// low nibbles of word (n, q & 1, is) for q < 2, its high nibbles for q >= 2; high parts from bits 2 q, 2 q + 1).
+// The two groups of a 32-value slice share the activation scale: their sums are combined as integers
+// (sum_a * sc_a + sum_b * sc_b, below 2^24 in magnitude) and converted once.
+
+struct RecQ6K {
+  uint4 ql[4];   // [2 h + n]: words (qb, is) = x y z w
+  uint4 qh[2];   // [h]: words (n, is)
+  uint4 sc[2];   // [h]: 16 int8
+  uint32_t dd;   // fp16 d of rows g, g + 8
+  __device__ __forceinline__ void load(const MmvArgs& a, int row0, int sb, int lane) {
+    const uint8_t* p = a.w + (int64_t)row0 * a.row_bytes + (int64_t)sb * 3360;
+    const int g = lane >> 2;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ql[i] = ldg_stream_v4(p + 64 * lane + 16 * i);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) qh[i] = ldg_stream_v4(p + 2048 + 32 * lane + 16 * i);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) sc[i] = ldg_stream_v4(p + 3072 + 32 * g + 16 * i);
+    dd = ldg_stream_u32(p + 3328 + 4 * g);
+  }
+  static __device__ __forceinline__ void prefetch(const MmvArgs& a, int row0, int sb, int lane) {
+    const uint8_t* p = a.w + (int64_t)row0 * a.row_bytes + (int64_t)sb * 3360;
+    if (lane < 27) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + min(128 * lane, 3359)));
+  }
+};
+
+// D = A (16 x 16, int8, row) * B (16 x 8, int8, col), accumulators starting at 0
+__device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%7, %7, %7, %7};"
+      : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+      : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+
+__device__ __forceinline__ uint32_t u4_get(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+// 4 six-bit values minus 32 as int8: lo = the 4 low nibbles (masked), hf = the high parts at bits 4, 5 of each byte
+// with bit 5 already inverted. With bit 5 inverted the byte is x = (v - 32) mod 64 plus, for v < 32, nothing in bits
+// 6, 7: adding 6 * (x & 0x20) sets them exactly then (two's complement of a negative value).
+__device__ __forceinline__ uint32_t q6_bytes(uint32_t lo, uint32_t hf) {
+  const uint32_t x = and_or(hf, 0x30303030u, lo);
+  return (x & 0x20202020u) * 6u + x;
+}
+
+// int8 byte b of w, sign-extended
+__device__ __forceinline__ int sbyte(uint32_t w, int b) {
+  return (int)mprmt(w, 0u, 0x8880u | (uint32_t)b | ((uint32_t)b << 4) | ((uint32_t)b << 8) | ((uint32_t)b << 12));
+}
+
+template <bool DUMP>
+__device__ __forceinline__ void dump_c16(const MmvArgs& ar, const int (&c)[4], int row0, int lane, int j, int group) {
+  if constexpr (DUMP) {
+    const int g = lane >> 2, t = lane & 3, col0 = 8 * j + 2 * t, nb16 = ar.k >> 4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int row = row0 + g + 8 * (e >> 1), col = col0 + (e & 1);
+      if (row < ar.nrows && col < ar.m) ar.dump[((int64_t)col * ar.nrows + row) * nb16 + group] = c[e];
+    }
+  }
+}
+
+template <int NTL, bool DUMP>
+__device__ __forceinline__ void process(const RecQ6K& r, const MmvArgs& ar, int row0, int sb, int lane, const XSmem& xl,
+                                        const uint8_t*, uint64_t (&acc)[NTL][2]) {
+  constexpr int MC = 8 * NTL;
+  const int t = lane & 3;
+  // the lane's view of the staged quants is set up for words 2t, 2t + 1 of a 32-byte block; here word t of each half
+  const uint8_t* xq = xl.q - 4 * t;
+  uint64_t tt[NTL][2];
+#pragma unroll
+  for (int j = 0; j < NTL; ++j) tt[j][0] = tt[j][1] = 0ull;
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+    // high parts of the two rows for is = 0, 1, the upper bit of every pair inverted once
+    uint32_t hf[2][2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      hf[h][0] = u4_get(r.qh[h], 2 * n) ^ 0xAAAAAAAAu;
+      hf[h][1] = u4_get(r.qh[h], 2 * n + 1) ^ 0xAAAAAAAAu;
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int s = 4 * n + q;   // slice of the superblock: groups 2 s (is = 0) and 2 s + 1 (is = 1)
+      uint32_t a[2][2];          // [is][h]
+#pragma unroll
+      for (int is = 0; is < 2; ++is) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t wl = u4_get(r.ql[2 * h + n], 2 * (q & 1) + is);
+          const uint32_t lo = (q < 2 ? wl : wl >> 4) & 0x0F0F0F0Fu;
+          const uint32_t hs = q == 0 ? hf[h][is] << 4 : q == 1 ? hf[h][is] << 2 : q == 2 ? hf[h][is] : hf[h][is] >> 2;
+          a[is][h] = q6_bytes(lo, hs);
+        }
+      }
+      const int G = 2 * s;
+      const int sa0 = sbyte(u4_get(r.sc[0], G >> 2), G & 3), sb0 = sbyte(u4_get(r.sc[0], G >> 2), (G & 3) + 1);
+      const int sa1 = sbyte(u4_get(r.sc[1], G >> 2), G & 3), sb1 = sbyte(u4_get(r.sc[1], G >> 2), (G & 3) + 1);
+#pragma unroll
+      for (int j = 0; j < NTL; ++j) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xq + j * xl.q8 + s * 32);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(xq + j * xl.q8 + s * 32 + 16);
+        const uint64_t dv2 = *reinterpret_cast<const uint64_t*>(xl.d + s * MC + 8 * j);
+        int ca[4], cb[4];
+        mma_s8_k16(ca, a[0][0], a[0][1], b0);
+        mma_s8_k16(cb, a[1][0], a[1][1], b1);
+        dump_c16<DUMP>(ar, ca, row0, lane, j, sb * 16 + G);
+        dump_c16<DUMP>(ar, cb, row0, lane, j, sb * 16 + G + 1);
+        // |sum * sc| <= 16 * 32 * 127 * 128 per group: the two together stay below 2^24, exact as a float
+        const float f0 = (float)(ca[0] * sa0 + cb[0] * sb0), f1 = (float)(ca[1] * sa0 + cb[1] * sb0);
+        const float f2 = (float)(ca[2] * sa1 + cb[2] * sb1), f3 = (float)(ca[3] * sa1 + cb[3] * sb1);
+        tt[j][0] = vfma2(pk2(f0, f1), dv2, tt[j][0]);
+        tt[j][1] = vfma2(pk2(f2, f3), dv2, tt[j][1]);
+      }
+    }
+  }
+  const float d0 = h2f(r.dd), d1 = h2f(r.dd >> 16);
+  const uint64_t d02 = pk2(d0, d0), d12 = pk2(d1, d1);
+#pragma unroll
+  for (int j = 0; j < NTL; ++j) {
+    acc[j][0] = vfma2(d02, tt[j][0], acc[j][0]);
+    acc[j][1] = vfma2(d12, tt[j][1], acc[j][1]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // The kernel.
 
 template <int KIND>
 struct MmvKind;
+template <>
+struct MmvKind<MK_Q6K> {
+  using Rec = RecQ6K;
+  static constexpr bool DS = false;
+  static constexpr int grid_bytes(int) { return 0; }
+  static constexpr bool PERM = false;
+};
 template <>
 struct MmvKind<MK_Q4K> {
   using Rec = RecQ4K;
@@ -1037,7 +1171,8 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
         if (round < cs) continue;
       }
       const int rounds = (per + round - 1) / round;
-      if (NTL >= 4 && rounds > 1) continue;  // measured: beyond 24 rows a second round costs more than the tcgen05 GEMM
+      // measured: beyond 24 rows a second round costs more than the tcgen05 GEMM (repacked Q6_K has no other kernel)
+      if (NTL >= 4 && rounds > 1 && KIND != MK_Q6K) continue;
       // estimated time (us): the stream of W at the rate the loop reaches, stretched by uneven clusters and idle
       // SMs; staging (36-byte blocks per thread, in batches of 4); per round a cluster barrier and the sums
       double balance = ((double)a.ntiles / (per * clusters)) * ((double)(clusters * cs) / sm_count);
@@ -1136,7 +1271,8 @@ static int mmv_launch_n(const MmvArgs& a, int sm_count, int max_smem, cudaStream
 
 // Whether (type, packed, m) may be served here (mmv_host can still decline a shape: MMV_DECLINED).
 bool mmv_applies(int ggml_type, int packed, int64_t rows, int64_t m) {
-  if (g_mmv_mode == 1 || m > g_mmv_max_rows) return false;
+  if ((g_mmv_mode == 1 && !(ggml_type == GSQ_TYPE_Q6_K && packed)) || m > 48 ||
+      (m > g_mmv_max_rows && !(ggml_type == GSQ_TYPE_Q6_K && packed))) return false;
   // Below these row counts the dp4a GEMV is faster on the measured shapes (its start-up is shorter: no staging of
   // the activations, no cluster-wide sum); packed IQ3_S has no faster kernel at any count.
   int min_rows;
@@ -1144,11 +1280,13 @@ bool mmv_applies(int ggml_type, int packed, int64_t rows, int64_t m) {
     case GSQ_TYPE_Q4_K: min_rows = 2; break;
     case GSQ_TYPE_IQ4_XS: min_rows = 4; break;
     case GSQ_TYPE_IQ3_S:
+    case GSQ_TYPE_Q6_K:   // (repacked Q6_K has no other kernel: served here at every count)
       if (!packed || rows % 16 != 0) return false;
       min_rows = 1;
       break;
     default: return false;
   }
+  if (ggml_type == GSQ_TYPE_Q6_K) return true;
   return m >= (g_mmv_min_rows > 0 ? g_mmv_min_rows : min_rows);
 }
 
@@ -1192,6 +1330,10 @@ int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int 
       if (!packed || rows % 16 != 0) return MMV_DECLINED;
       return x_layout == XL_Q81 ? mmv_launch_n<MK_IQ3S, XL_Q81>(a, di.sm_count, di.max_smem_optin, st)
                                 : mmv_launch_n<MK_IQ3S, XL_MMQ>(a, di.sm_count, di.max_smem_optin, st);
+    case GSQ_TYPE_Q6_K:
+      if (!packed || rows % 16 != 0) return MMV_DECLINED;
+      return x_layout == XL_Q81 ? mmv_launch_n<MK_Q6K, XL_Q81>(a, di.sm_count, di.max_smem_optin, st)
+                                : mmv_launch_n<MK_Q6K, XL_MMQ>(a, di.sm_count, di.max_smem_optin, st);
     default: return MMV_DECLINED;
   }
 }

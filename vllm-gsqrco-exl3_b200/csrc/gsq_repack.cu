@@ -1,4 +1,4 @@
-// IQ3_S load-time repack into the layout the sm_100a kernels read (in place, bijective).
+// Load-time repacks (in place, bijective) into the layouts the sm_100a kernels read: IQ3_S, and Q6_K further down.
 //
 // Takes the place of the reference's iq3_pack (plugin/vllm_gguf_plugin/quantization/iq3_pack.py:73-181).
 // As there, rows are grouped in tiles of 16 and tile t keeps the bytes rows 16t..16t+15 had, as one
@@ -124,7 +124,89 @@ __global__ void __launch_bounds__(256) iq3s_repack_kernel(uint8_t* __restrict__ 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Q6_K: 210-byte blocks are only 2-byte aligned in GGUF order (128 bytes of low nibbles, 64 bytes of 2-bit high
+// parts, 16 int8 sub-scales, fp16 d), which would force 16-bit loads. The repack is a pure byte permutation inside
+// each 16-row tile, one 3360-byte record per superblock j at  t * 16 * row_bytes + j * 3360  (a multiple of 16):
+//   [   0, 2048)  64 bytes per lane 4 g + t: row g, then row g + 8; per row the eight 4-byte words
+//                 (n, qb, is) = ql[64 n + 32 qb + 16 is + 4 t .. + 3]: the lane's 4 values of the 16-value groups
+//                 8 n + 2 qb + is (low nibbles) and 8 n + 2 (qb + 2) + is (high nibbles)
+//   [2048, 3072)  32 bytes per lane: row g, then row g + 8; per row the four words (n, is) =
+//                 qh[32 n + 16 is + 4 t .. + 3]: two bits for each of the four groups 8 n + 2 q + is, q = 0..3
+//   [3072, 3328)  32 bytes per g: the 16 sub-scales of row g, then of row g + 8
+//   [3328, 3360)   4 bytes per g: fp16 d of row g, then of row g + 8
+// With that a lane's share of the int8 tensor-core fragments (rows g, g + 8; values 4 t .. 4 t + 3 of every group) is
+// six 128-bit loads. No kernel reads GGUF-order bytes from a repacked tensor: direction 1 restores them.
+
+// byte o of a record comes from (row of the tile, byte of that row's 210-byte block)
+__host__ __device__ inline void q6k_source(int o, int* row, int* src) {
+  if (o < 2048) {
+    const int lane = o >> 6, w = (o & 63) >> 2, b = o & 3, g = lane >> 2, t = lane & 3, h = w >> 3, wi = w & 7;
+    *row = g + 8 * h;
+    *src = 64 * (wi >> 2) + 32 * ((wi >> 1) & 1) + 16 * (wi & 1) + 4 * t + b;
+  } else if (o < 3072) {
+    const int q = o - 2048, lane = q >> 5, w = (q & 31) >> 2, b = q & 3, g = lane >> 2, t = lane & 3, h = w >> 2, wi = w & 3;
+    *row = g + 8 * h;
+    *src = 128 + 32 * (wi >> 1) + 16 * (wi & 1) + 4 * t + b;
+  } else if (o < 3328) {
+    const int q = o - 3072;
+    *row = (q >> 5) + 8 * ((q >> 4) & 1);
+    *src = 192 + (q & 15);
+  } else {
+    const int q = o - 3328;
+    *row = (q >> 2) + 8 * ((q >> 1) & 1);
+    *src = 208 + (q & 1);
+  }
+}
+
+__global__ void __launch_bounds__(256) q6k_repack_kernel(uint8_t* __restrict__ w, int64_t row_bytes, int nb, int direction) {
+  extern __shared__ __align__(16) uint8_t tile[];
+  uint8_t* base = w + (int64_t)blockIdx.x * 16 * row_bytes;
+  const int tile_bytes = (int)(16 * row_bytes);
+  for (int i = threadIdx.x; i < tile_bytes / 16; i += blockDim.x) {
+    reinterpret_cast<uint4*>(tile)[i] = reinterpret_cast<const uint4*>(base)[i];
+  }
+  __syncthreads();
+  // two bytes per step: sources and destinations of even offsets are even and their partners follow them
+  for (int it = threadIdx.x; it < nb * 1680; it += blockDim.x) {
+    const int j = it / 1680, o = 2 * (it - j * 1680);
+    int row, src;
+    q6k_source(o, &row, &src);
+    const size_t raw = (size_t)row * row_bytes + (size_t)j * 210 + src, rec = (size_t)j * 3360 + o;
+    if (direction == 0) {
+      *reinterpret_cast<uint16_t*>(base + rec) = *reinterpret_cast<const uint16_t*>(tile + raw);
+    } else {
+      *reinterpret_cast<uint16_t*>(base + raw) = *reinterpret_cast<const uint16_t*>(tile + rec);
+    }
+  }
+}
+
 }  // namespace gsq
+
+extern "C" int gsq_q6k_repack(void* w, int64_t rows, int64_t row_bytes, int direction, void* stream) {
+  using namespace gsq;
+  if (rows == 0) return GSQ_OK;
+  if (!w || rows < 0 || rows % 16 != 0 || row_bytes <= 0 || row_bytes % 210 != 0 || (uintptr_t)w % 16 != 0 ||
+      (direction != 0 && direction != 1)) {
+    return GSQ_ERR_UNSUPPORTED;
+  }
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc != GSQ_OK) return rc;
+  const size_t smem = (size_t)16 * row_bytes;
+  if (smem > (size_t)di.max_smem_optin) return GSQ_ERR_TOO_LARGE;
+  static int configured_mask = 0;
+  int dev = 0;
+  GSQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 32 || !((configured_mask >> dev) & 1)) {
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(q6k_repack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    if (dev < 32) configured_mask |= 1 << dev;
+  }
+  q6k_repack_kernel<<<(unsigned)(rows / 16), 256, smem, (cudaStream_t)stream>>>((uint8_t*)w, row_bytes,
+                                                                               (int)(row_bytes / 210), direction);
+  GSQ_CUDA_TRY(cudaGetLastError());
+  return GSQ_OK;
+}
 
 extern "C" int gsq_iq3s_repack(void* w, int64_t rows, int64_t row_bytes, int direction, void* stream) {
   using namespace gsq;

@@ -39,6 +39,9 @@ _SCHEMAS = {
     "lcpp_mul_mat_vec_iq3_mma_packed": "(Tensor W, Tensor X, int type, SymInt row, Tensor? x_q8=None) -> Tensor",
     "lcpp_mul_mat_iq3_packed": "(Tensor W, Tensor X, int type, SymInt row) -> Tensor",
     "lcpp_quantize_q8_1": "(Tensor X, int type, bool mmq, bool vendored) -> Tensor",
+    # not in the reference: Q6_K repacked at load by this package (quantization/iq3_pack.py)
+    "gsq_mul_mat_vec_q6k_packed": "(Tensor W, Tensor X, int type, SymInt row, Tensor? x_q8=None) -> Tensor",
+    "gsq_mul_mat_q6k_packed": "(Tensor W, Tensor X, int type, SymInt row) -> Tensor",
 }
 
 # op -> (reads block_q8_1?, packed W?, IQ3 only?, Q4_K-own only?, mma_k types only?, is MMQ?, max X rows)
@@ -51,6 +54,8 @@ _OPS = {
     "lcpp_mul_mat_mma_k": dict(mmvq=False, need_mma_k=True, max_rows=MMA_K_MAX_COLS),
     "lcpp_mul_mat_vec_iq3_mma_packed": dict(mmvq=True, need_iq3=True, packed=True, max_rows=PACKED_VEC_MAX),
     "lcpp_mul_mat_iq3_packed": dict(mmvq=False, need_iq3=True, packed=True, max_rows=0),
+    "gsq_mul_mat_vec_q6k_packed": dict(mmvq=True, need_q6k=True, packed=True, max_rows=MMVQ_MAX_BATCH_SIZE),
+    "gsq_mul_mat_q6k_packed": dict(mmvq=False, need_q6k=True, packed=True, max_rows=0),
 }
 
 _DTYPES = {torch.float32: _cabi.F32, torch.float16: _cabi.F16, torch.bfloat16: _cabi.BF16}
@@ -130,6 +135,8 @@ def _gemv(W, X, type_, row, x_q8, packed, y):
 
 def _run(op: str, W: torch.Tensor, X: torch.Tensor, type_: int, row: int, x_q8: torch.Tensor | None = None):
     spec = _OPS[op]
+    if spec.get("need_q6k") and int(type_) != Q6_K:
+        raise RuntimeError(f"{op}: Q6_K only, got type {type_}")
     k = _guard(op, W, X, type_, row, spec)
     n = X.shape[0]
     q8_bytes = n * k // 32 * 36

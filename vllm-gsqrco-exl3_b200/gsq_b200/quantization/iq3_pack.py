@@ -1,4 +1,4 @@
-"""Lossless repack of IQ3_S weight bytes into the order the sm_100a kernels stream them.
+"""Lossless repack of IQ3_S (and Q6_K) weight bytes into the order the sm_100a kernels stream them.
 
 Same role and interface as the reference's quantization/iq3_pack.py (pack_ / pack / unpack, ROWS = 16,
 bijective, in place, tile t keeps the bytes of rows 16t..16t+15), a different layout: the reference's
@@ -17,6 +17,11 @@ its 32 fields are numbered f = 4s + 2h + e (row g + 8h, group 2t + e):
 CUDA tensors are repacked by gsq_iq3s_repack (one thread block per tile, staged in shared memory, no
 scratch); CPU tensors by the torch-op formulation below, which also serves as the layout's
 executable definition for the tests.
+
+Q6_K (type 14; not repacked by the reference, whose vendored kernels read GGUF order): GGUF's 210-byte blocks
+are only 2-byte aligned, so the same functions also take Q6_K and apply a byte permutation inside each 16-row
+tile into 3360-byte records (csrc/gsq_repack.cu, `q6k_record_source` below): per lane its words of low
+nibbles and of high parts, then the rows' sub-scales and d.
 """
 
 from __future__ import annotations
@@ -25,16 +30,61 @@ import torch
 
 from .. import _cabi
 
-IQ3_S = 21
+IQ3_S, Q6_K = 21, 14
 ROWS = 16  # rows per tile
 BS = 110   # bytes per IQ3_S superblock
 REC = ROWS * BS
+BS_Q6K = 210
+REC_Q6K = ROWS * BS_Q6K
+PACKABLE_TYPES = (IQ3_S, Q6_K)
 
 
 def _check(w: torch.Tensor, weight_type: int) -> None:
-    assert int(weight_type) == IQ3_S, weight_type
+    assert int(weight_type) in PACKABLE_TYPES, weight_type
+    bs = BS if int(weight_type) == IQ3_S else BS_Q6K
     assert w.dtype == torch.uint8 and w.dim() == 2, (w.shape, w.dtype)
-    assert w.shape[0] % ROWS == 0 and w.shape[1] % BS == 0, w.shape
+    assert w.shape[0] % ROWS == 0 and w.shape[1] % bs == 0, w.shape
+
+
+def q6k_record_source() -> torch.Tensor:
+    """int64 [3360]: byte o of a Q6_K record comes from byte (row * 210 + src) of the tile's 16 blocks of that
+    superblock (row = row of the tile). The layout's definition, as in csrc/gsq_repack.cu."""
+    o = torch.arange(REC_Q6K)
+    row = torch.zeros_like(o)
+    src = torch.zeros_like(o)
+    m = o < 2048
+    lane, w, b = o >> 6, (o & 63) >> 2, o & 3
+    g, t, h, wi = lane >> 2, lane & 3, w >> 3, w & 7
+    row = torch.where(m, g + 8 * h, row)
+    src = torch.where(m, 64 * (wi >> 2) + 32 * ((wi >> 1) & 1) + 16 * (wi & 1) + 4 * t + b, src)
+    m = (o >= 2048) & (o < 3072)
+    q = o - 2048
+    lane, w, b = q >> 5, (q & 31) >> 2, q & 3
+    g, t, h, wi = lane >> 2, lane & 3, w >> 2, w & 3
+    row = torch.where(m, g + 8 * h, row)
+    src = torch.where(m, 128 + 32 * (wi >> 1) + 16 * (wi & 1) + 4 * t + b, src)
+    m = (o >= 3072) & (o < 3328)
+    q = o - 3072
+    row = torch.where(m, (q >> 5) + 8 * ((q >> 4) & 1), row)
+    src = torch.where(m, 192 + (q & 15), src)
+    m = o >= 3328
+    q = o - 3328
+    row = torch.where(m, (q >> 2) + 8 * ((q >> 1) & 1), row)
+    src = torch.where(m, 208 + (q & 1), src)
+    return row * BS_Q6K + src
+
+
+def _q6k_tiles(w: torch.Tensor, inverse: bool) -> torch.Tensor:
+    rows, rb = w.shape
+    nb, t = rb // BS_Q6K, rows // ROWS
+    perm = q6k_record_source().to(w.device)
+    if not inverse:
+        blocks = w.reshape(t, ROWS, nb, BS_Q6K).permute(0, 2, 1, 3).reshape(t, nb, REC_Q6K)   # [tile, sb, row * 210 + byte]
+        return blocks[..., perm].reshape(rows, rb)
+    rec = w.reshape(t, nb, REC_Q6K)
+    blocks = torch.empty_like(rec)
+    blocks[..., perm] = rec
+    return blocks.reshape(t, nb, ROWS, BS_Q6K).permute(0, 2, 1, 3).reshape(rows, rb)
 
 
 def _bits(x: torch.Tensor, n: int) -> torch.Tensor:
@@ -105,21 +155,26 @@ def _unpack_tiles(p: torch.Tensor) -> torch.Tensor:
     return blocks.permute(0, 2, 3, 1, 4).reshape(rows, rb).to(torch.uint8)
 
 
-def _cuda_repack(w: torch.Tensor, direction: int) -> None:
+def _cuda_repack(w: torch.Tensor, direction: int, weight_type: int = IQ3_S) -> None:
     if w.stride(1) != 1 or w.stride(0) != w.shape[1]:
         raise RuntimeError("iq3_pack: rows must be contiguous")
     if w.data_ptr() % 16 != 0:
         raise RuntimeError("iq3_pack: data must be 16-byte aligned")
     with torch.cuda.device(w.device):
         st = torch.cuda.current_stream(w.device).cuda_stream
-        _cabi.check(_cabi.lib.gsq_iq3s_repack(w.data_ptr(), w.shape[0], w.shape[1], direction, st), "gsq_iq3s_repack")
+        if int(weight_type) == Q6_K:
+            _cabi.check(_cabi.lib.gsq_q6k_repack(w.data_ptr(), w.shape[0], w.shape[1], direction, st), "gsq_q6k_repack")
+        else:
+            _cabi.check(_cabi.lib.gsq_iq3s_repack(w.data_ptr(), w.shape[0], w.shape[1], direction, st), "gsq_iq3s_repack")
 
 
 def pack_(w: torch.Tensor, weight_type: int) -> None:
     """pack() in place."""
     _check(w, weight_type)
     if w.is_cuda:
-        _cuda_repack(w, 0)
+        _cuda_repack(w, 0, weight_type)
+    elif int(weight_type) == Q6_K:
+        w.copy_(_q6k_tiles(w, False))
     else:
         w.copy_(_pack_tiles(w))
 
@@ -136,6 +191,8 @@ def unpack(p: torch.Tensor, weight_type: int) -> torch.Tensor:
     _check(p, weight_type)
     if p.is_cuda:
         w = p.clone()
-        _cuda_repack(w, 1)
+        _cuda_repack(w, 1, weight_type)
         return w
+    if int(weight_type) == Q6_K:
+        return _q6k_tiles(p, True)
     return _unpack_tiles(p)

@@ -106,8 +106,12 @@ def _fused_mul_mat_gguf(
     name = _lcpp_op(n, weight_type, rows, x.shape[1], packed)
     if name is None:
         raise NotImplementedError(f"no kernel for ggml type {weight_type} at {n} activation rows")
+    if packed and weight_type == Q6_K:
+        # this package also repacks Q6_K at load (_pack_iq3); its two ops keep the split of the table's names: the
+        # vec op (reads the shared q8_1) where the table says lcpp_mul_mat_vec_q, the self-quantising one otherwise
+        name = "gsq_mul_mat_vec_q6k_packed" if name == "lcpp_mul_mat_vec_q" else "gsq_mul_mat_q6k_packed"
     op = getattr(torch.ops._C_gguf, name)
-    if name in _OWN_QUANTIZE_OPS:
+    if name in _OWN_QUANTIZE_OPS or name == "gsq_mul_mat_q6k_packed":
         return op(weight, x, weight_type, rows)
     per_call = 32 if name == "lcpp_mul_mat_vec_iq3_mma_packed" else 8
     if n > per_call:  # VLLM_GGUF_IQ3_TILED=0, or IQ1_M above 8 rows: several calls of the vec op
@@ -237,8 +241,8 @@ class GGUFLinearMethod:
             self._pack_iq3(layer)
 
     def _pack_iq3(self, layer: torch.nn.Module) -> None:
-        """Repack the layer's IQ3_S products in place and set weight.iq3_packed. All or nothing per
-        layer: only if every IQ3_S run has a multiple of 16 rows and 16-byte aligned bytes."""
+        """Repack the layer's IQ3_S (and, in this package, Q6_K) products in place and set weight.iq3_packed. All
+        or nothing per layer: only if every such run has a multiple of 16 rows and 16-byte aligned bytes."""
         weight = layer.weight
         if getattr(weight, "iq3_packed", False):
             return
@@ -248,7 +252,7 @@ class GGUFLinearMethod:
             runs = list(_shard_runs(weight, weight.shard_id, [types.get(i, fallback) for i in weight.shard_id]))
         else:
             runs = [(weight.data, layer.weight_type.weight_type)]
-        runs = [(w, t) for w, t in runs if t == IQ3_S]
+        runs = [(w, t) for w, t in runs if t in iq3_pack.PACKABLE_TYPES]
         if not runs or any(w.shape[0] % iq3_pack.ROWS or w.data_ptr() % 16 for w, _ in runs):
             return
         for w, t in runs:
