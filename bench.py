@@ -203,7 +203,6 @@ def run_ours(args):
     cells = build_cells(dev, world, rank, l2)
     xs_host = make_inputs(dev, cells, torch.float16)
     xs = {key: v.to(dev) for key, v in xs_host.items()}
-    xs_pinned = {key: v.pin_memory() for key, v in xs_host.items()}
     order = [(key, m) for key in cells for m in ROWS]
     launches = {"n": 0}
 
@@ -227,25 +226,23 @@ def run_ours(args):
         flat_k = torch.empty(max(off_k, 1), dtype=torch.float16, device=dev)
         gath_n = torch.empty(world * flat_n.numel(), dtype=torch.float16, device=dev)
 
-    def product(c, x, key_m=None):
-        """One cell: GGUFLinearMethod.apply() on this rank's shard."""
+    def product(c, x, key_m=None, sliced=False):
+        """One cell: GGUFLinearMethod.apply() on this rank's shard. sliced: x is already the K-shard's columns."""
         layer = c["layers"][c["use"] % len(c["layers"])]
         c["use"] += 1
-        xl = x if c["mode"] == "N" else x[:, c["a0"] * 256:(c["a0"] + c["cnt"]) * 256]
-        y = method.apply(layer, xl)
+        xl = x if (c["mode"] == "N" or sliced) else x[:, c["a0"] * 256:(c["a0"] + c["cnt"]) * 256]
         m = x.shape[0]
         launches["n"] += 1 + (m + 7) // 8
         if world > 1 and key_m is not None:
+            # the kernel writes the shard's result straight into its slot of the step's collective buffer
             kind, off, cnt = tp_slots[key_m]
-            tp_pending.append(((flat_n if kind == "N" else flat_k)[off:off + cnt].view_as(y), y))
-        return y
-
-    tp_pending = []   # (slot in a flat buffer, result): copied by one multi-tensor kernel at the end of a step
+            slot = (flat_n if kind == "N" else flat_k)[off:off + cnt].view(m, -1)
+            with lcpp_ops.output_into(slot):
+                return method.apply(layer, xl)
+        return method.apply(layer, xl)
 
     def tp_flush():
-        if tp_pending:
-            torch._foreach_copy_([d for d, _ in tp_pending], [y for _, y in tp_pending])
-            tp_pending.clear()
+        pass
 
     def collectives():
         if world > 1:
@@ -264,7 +261,13 @@ def run_ours(args):
     # End to end: uploads, products and downloads of a step are pipelined over three streams (upload stream ->
     # event per input -> product on the main stream -> event -> download stream), all inside the timed region.
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    x_dev = [torch.empty_like(xs[(key[2], m)]) for key, m in order]
+
+    def x_slice(key, m, t):
+        """The columns of the activation this rank needs: all of them for an N-shard, its K range for a K-shard."""
+        c = cells[key]
+        return t if c["mode"] == "N" else t[:, c["a0"] * 256:(c["a0"] + c["cnt"]) * 256]
+    xs_pinned = {(key, m): x_slice(key, m, xs_host[(key[2], m)]).contiguous().pin_memory() for key, m in order}
+    x_dev = [torch.empty_like(xs_pinned[(key, m)], device=dev) for key, m in order]
 
     def compute_e2e(outs):
         cur = torch.cuda.current_stream()
@@ -273,14 +276,14 @@ def run_ours(args):
         ready = []
         with torch.cuda.stream(s_in):
             for i, (key, m) in enumerate(order):
-                x_dev[i].copy_(xs_pinned[(key[2], m)], non_blocking=True)
+                x_dev[i].copy_(xs_pinned[(key, m)], non_blocking=True)
                 e = torch.cuda.Event()
                 e.record(s_in)
                 ready.append(e)
         keep = []   # results stay referenced until the streams have joined: their memory is not reused under a copy
         for i, (key, m) in enumerate(order):
             cur.wait_event(ready[i])
-            y = product(cells[key], x_dev[i], (key, m))
+            y = product(cells[key], x_dev[i], (key, m), sliced=True)
             if world == 1:
                 e = torch.cuda.Event()
                 e.record(cur)
@@ -384,7 +387,7 @@ def run_ours(args):
             run_e2e()
         ms_e2e = timed(run_e2e, args.steps)
     e2e = step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9
-    h2d = sum(m * key[2] * 2 for key, m in order)
+    h2d = sum(v.numel() * 2 for v in xs_pinned.values())
     d2h = sum(m * cells[key]["n"] * 2 for key, m in order)
 
     # per-cell table and the small-batch kernel's roofline (this rank's shard; kernel alone, x already quantised).
@@ -447,6 +450,11 @@ def run_ours(args):
             roof_launches += reps
         cell_rows.append(row)
 
+    tp_stack = None
+    if world > 1 and not args.no_extras:
+        del cells, xs
+        torch.cuda.empty_cache()
+        tp_stack = extra_tp_stack(dev, world, rank, capture)
     if rank == 0:
         achieved = roof_bytes / (roof_ms * 1e-3) / 1e9 if roof_ms else None
         out = {
@@ -487,7 +495,9 @@ def run_ours(args):
             out["graph_exact"] = "%d/%d" % (sum(1 for v in exact.values() if v), len(exact))
         else:
             out["parity_checked"] = False
-        raws = {key: c["raw"] for key, c in cells.items()}
+        if tp_stack is not None:
+            out["tp_decode_stack"] = tp_stack
+        raws = {key: c["raw"] for key, c in cells.items()} if world == 1 else {}
         if world == 1 and not args.no_extras:
             del cells, xs
             torch.cuda.empty_cache()
@@ -758,6 +768,106 @@ def extra_decode_stack(dev, capture, layers=64):
                          "frac_of_measured_hbm": round(b2 / best / 1e6 / hbm, 4)})
     return {"layers": layers, "weight_bytes_per_step": bytes_step, "steps": res,
             "with_q6k_output_head": {"weight_bytes_per_step": bytes_step + head.numel(), "steps": res_head}}
+
+def extra_tp_stack(dev, world, rank, capture, layers=64, rows=32):
+    """The 64-layer stack + Q6_K output head, tensor parallel over `world` GPUs, `rows` activation rows per step:
+    qkv and gate_up cut along N (gate_up's channels matched to down's K-shards, so nothing is gathered between them),
+    o_proj and down cut along K at 256-column granularity with an NCCL all-reduce of the partial [rows, 5120] results,
+    the head cut along N with an all-gather of the logits. One CUDA graph per step, collectives inside it. Reported:
+    the whole step, the products alone and the collectives alone (ms, max over ranks)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from gsq_b200 import lcpp_ops, synth, tp
+    from gsq_b200.quantization import iq3_pack, linear
+
+    H, I, QKV, V = 5120, 17408, 7168, 151936
+    with tp.relaxed_k():
+        p_qkv = tp.shard_plan(QKV, H, world, rank, "N")
+        p_o = tp.shard_plan(H, H, world, rank, "K")
+        up0, upc = tp.matched_up_rows(I, world, rank)
+        p_down = tp.shard_plan(H, I, world, rank, "K")
+        p_head = tp.shard_plan(V, H, world, rank, "N")
+
+        def up(raw, t, pack):
+            w = torch.from_numpy(np.ascontiguousarray(raw)).to(dev)
+            if pack:
+                iq3_pack.pack_(w, t)
+            return w
+        qkv = up(tp.shard_bytes(synth.make_weight(21, QKV, H, 2000), 21, p_qkv), 21, True)
+        o = up(tp.shard_bytes(synth.make_weight(21, H, H, 2001), 21, p_o), 21, True)
+        gu_full = synth.make_weight(21, 2 * I, H, 2002)
+        gate_up = up(np.concatenate([gu_full[up0:up0 + upc], gu_full[I + up0:I + up0 + upc]]), 21, True)
+        down = up(tp.shard_bytes(synth.make_weight(23, H, I, 2003), 23, p_down), 23, False)
+        head = up(tp.shard_bytes(synth.make_weight(14, V, H, 3000), 14, p_head), 14, True)
+        base = {"qkv": qkv, "o": o, "gate_up": gate_up, "down": down}
+        stack = [{n: torch.roll(w, shifts=16 * (l + 1), dims=0) if l else w for n, w in base.items()} for l in range(layers)]
+        local_bytes = layers * sum(w.numel() for w in base.values()) + head.numel()
+        ko, kd = p_o.count * 256, p_down.count * 256
+        x = torch.randn(rows, H, device=dev, dtype=torch.bfloat16)
+        h1 = torch.empty(rows, H, device=dev, dtype=torch.bfloat16)      # o_proj partial -> all-reduce
+        h2 = torch.empty(rows, H, device=dev, dtype=torch.bfloat16)      # down partial -> all-reduce
+        logits_local = torch.empty(rows, p_head.count, device=dev, dtype=torch.bfloat16)
+        # the head's N-shards are equal but for the last rank's remainder: the gather takes the largest, padded
+        hmax = max(tp.shard_plan(V, H, world, r, "N").count for r in range(world))
+        lg_in = torch.zeros(rows, hmax, device=dev, dtype=torch.bfloat16)
+        lg_out = torch.empty(world, rows, hmax, device=dev, dtype=torch.bfloat16)
+
+        def step(products=True, collectives=True):
+            cur = x
+            for lw in stack:
+                if products:
+                    a = linear.fused_mul_mat_gguf(cur, lw["qkv"], 21, None, True)          # [rows, 7168 / world]
+                    with lcpp_ops.output_into(h1):
+                        linear.fused_mul_mat_gguf(a[:, :ko], lw["o"], 21, None, True)      # attention stub: its columns
+                if collectives:
+                    dist.all_reduce(h1)
+                if products:
+                    g = linear.fused_mul_mat_gguf(h1, lw["gate_up"], 21, None, True)       # [rows, 2 * matched channels]
+                    with lcpp_ops.output_into(h2):
+                        linear.fused_mul_mat_gguf(g[:, :kd], lw["down"], 23, None, False)   # SwiGLU stub: gate's columns
+                if collectives:
+                    dist.all_reduce(h2)
+                cur = h2
+            if products:
+                with lcpp_ops.output_into(lg_in[:, :p_head.count]):
+                    linear.fused_mul_mat_gguf(cur, head, 14, None, True)
+            if collectives:
+                dist.all_gather_into_tensor(lg_out, lg_in)
+
+        def best_ms(fn):
+            g = capture(fn)
+            for _ in range(2):
+                g.replay()
+            torch.cuda.synchronize()
+            dist.barrier()
+            best = 1e30
+            for _ in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                best = min(best, e0.elapsed_time(e1))
+                dist.barrier()
+            t = torch.tensor([best], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        total = best_ms(lambda: step(True, True))
+        compute = best_ms(lambda: step(True, False))
+        coll = best_ms(lambda: step(False, True))
+    full_bytes = layers * 150978560 + V * (H // 256) * 210
+    return {"rows": rows, "layers": layers, "world": world, "ms_per_step": round(total, 3),
+            "products_only_ms": round(compute, 3), "collectives_only_ms": round(coll, 3),
+            "collectives_per_step": 2 * layers + 1,
+            "collective_us_each": round(coll * 1e3 / (2 * layers + 1), 1),
+            "weight_bytes_per_step_all_ranks": full_bytes, "weight_bytes_this_rank": local_bytes,
+            "GBps_all_ranks": round(full_bytes / total / 1e6, 1),
+            "sharding": "qkv / gate_up / head along N (gate_up matched to down's K-shards), o_proj / down along K "
+                        "(256-column granularity); all-reduce after o_proj and down, all-gather of the logits; "
+                        "collectives captured in the step's CUDA graph"}
+
 
 # --------------------------------------------------------------------------------------------------
 # CPU baseline / reference arm (the only places bench.py executes oracle/)

@@ -65,6 +65,36 @@ _DTYPES = {torch.float32: _cabi.F32, torch.float16: _cabi.F16, torch.bfloat16: _
 _k_multiple = 512
 
 
+# Where the next product writes its result, if set (see output_into): the kernels take any row stride, so a tensor-
+# parallel runtime can have a shard's result land in its slot of a collective's buffer instead of copying it there.
+_next_output: list = []
+
+
+class output_into:
+    """with output_into(t): the next op call of this module writes its [rows of X, row] result into `t` (same shape
+    and dtype as it would have returned, unit inner stride, any row stride) and returns `t`."""
+
+    def __init__(self, t: torch.Tensor):
+        self.t = t
+
+    def __enter__(self):
+        _next_output.append(self.t)
+        return self.t
+
+    def __exit__(self, *a):
+        if _next_output and _next_output[-1] is self.t:
+            _next_output.pop()
+
+
+def _result(n: int, row: int, X: torch.Tensor) -> torch.Tensor:
+    if _next_output:
+        y = _next_output.pop()
+        if y.shape != (n, row) or y.dtype != X.dtype or y.device != X.device or y.stride(1) != 1:
+            raise RuntimeError("output_into: the tensor does not match the result's shape, dtype, device or inner stride")
+        return y
+    return torch.empty((n, row), dtype=X.dtype, device=X.device)
+
+
 def set_k_multiple(v: int) -> int:
     global _k_multiple
     old, _k_multiple = _k_multiple, int(v)
@@ -151,7 +181,7 @@ def _run(op: str, W: torch.Tensor, X: torch.Tensor, type_: int, row: int, x_q8: 
         return X.new_empty((0, row))
     packed = bool(spec.get("packed", False))
     with torch.cuda.device(X.device):
-        y = torch.empty((n, row), dtype=X.dtype, device=X.device)
+        y = _result(n, row, X)
         if spec["mmvq"]:
             if x_q8 is None:
                 x_q8 = torch.empty(q8_bytes, dtype=torch.uint8, device=X.device)

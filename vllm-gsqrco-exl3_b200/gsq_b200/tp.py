@@ -44,6 +44,14 @@ def shard_plan(n: int, k: int, world: int, rank: int, mode: str | None = None) -
     return Shard("N", start, n - start if rank == world - 1 else per)
 
 
+def matched_up_rows(k_down: int, world: int, rank: int) -> tuple[int, int]:
+    """(first channel, channel count) of the gate / up projection that rank `rank` keeps so that its SwiGLU output
+    is exactly the column range of its K-shard of the down projection (k_down columns, cut at 256 granularity, the
+    first ranks one superblock more): at 8 ranks and 17408 columns {2304 x 4, 2048 x 4} channels, not 2176 each."""
+    s = shard_plan(1, k_down, world, rank, "K")
+    return s.start * 256, s.count * 256
+
+
 def shard_bytes(raw, ggml_type: int, s: Shard):
     """Rows / superblock columns of a [rows, row_bytes] byte matrix (numpy array or torch tensor) for a shard."""
     if s.mode == "N":
