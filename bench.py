@@ -814,22 +814,36 @@ def extra_tp_stack(dev, world, rank, capture, layers=64, rows=32):
         lg_in = torch.zeros(rows, hmax, device=dev, dtype=torch.bfloat16)
         lg_out = torch.empty(world, rows, hmax, device=dev, dtype=torch.bfloat16)
 
-        def step(products=True, collectives=True):
+        r1 = torch.empty(rows, H, device=dev, dtype=torch.bfloat16)      # sums (peer variant: the partials are elsewhere)
+        r2 = torch.empty(rows, H, device=dev, dtype=torch.bfloat16)
+
+        def step(products=True, collectives=True, peer=None):
+            """peer: a tp.PeerAllReduce -- the partials of o_proj / down are written into its symmetric buffers and
+            summed by one kernel per rank over peer memory instead of an NCCL all-reduce."""
+            p1 = peer.partial(0, (rows, H), torch.bfloat16) if peer else h1
+            p2 = peer.partial(1, (rows, H), torch.bfloat16) if peer else h2
+            s1, s2 = (r1, r2) if peer else (h1, h2)
             cur = x
             for lw in stack:
                 if products:
                     a = linear.fused_mul_mat_gguf(cur, lw["qkv"], 21, None, True)          # [rows, 7168 / world]
-                    with lcpp_ops.output_into(h1):
+                    with lcpp_ops.output_into(p1):
                         linear.fused_mul_mat_gguf(a[:, :ko], lw["o"], 21, None, True)      # attention stub: its columns
                 if collectives:
-                    dist.all_reduce(h1)
+                    if peer:
+                        peer.reduce(0, r1)
+                    else:
+                        dist.all_reduce(h1)
                 if products:
-                    g = linear.fused_mul_mat_gguf(h1, lw["gate_up"], 21, None, True)       # [rows, 2 * matched channels]
-                    with lcpp_ops.output_into(h2):
+                    g = linear.fused_mul_mat_gguf(s1, lw["gate_up"], 21, None, True)       # [rows, 2 * matched channels]
+                    with lcpp_ops.output_into(p2):
                         linear.fused_mul_mat_gguf(g[:, :kd], lw["down"], 23, None, False)   # SwiGLU stub: gate's columns
                 if collectives:
-                    dist.all_reduce(h2)
-                cur = h2
+                    if peer:
+                        peer.reduce(1, r2)
+                    else:
+                        dist.all_reduce(h2)
+                cur = s2
             if products:
                 with lcpp_ops.output_into(lg_in[:, :p_head.count]):
                     linear.fused_mul_mat_gguf(cur, head, 14, None, True)
@@ -851,12 +865,30 @@ def extra_tp_stack(dev, world, rank, capture, layers=64, rows=32):
                 torch.cuda.synchronize()
                 best = min(best, e0.elapsed_time(e1))
                 dist.barrier()
+            del g        # (a graph that holds NCCL collectives must be gone before the process group is destroyed)
             t = torch.tensor([best], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             return float(t.item())
         total = best_ms(lambda: step(True, True))
         compute = best_ms(lambda: step(True, False))
         coll = best_ms(lambda: step(False, True))
+        peer_res = None
+        try:
+            ar = tp.PeerAllReduce(rows * H * 2)
+            p_total = best_ms(lambda: step(True, True, ar))
+            p_coll = best_ms(lambda: step(False, True, ar))
+            flag = __import__("ctypes").c_int(-1)
+            _cabi_lib = __import__("gsq_b200")._cabi.lib
+            _cabi_lib.gsq_allreduce_error_flag(__import__("ctypes").byref(flag))
+            peer_res = {"ms_per_step": round(p_total, 3), "collectives_only_ms": round(p_coll, 3),
+                        "collective_us_each": round(p_coll * 1e3 / (2 * layers + 1), 1), "wait_gave_up": int(flag.value),
+                        "what": "the all-reduces replaced by gsq_allreduce_sum (one kernel per rank over symmetric "
+                                "memory: flag exchange + peer loads); the logits' all-gather stays NCCL"}
+            del ar
+        except Exception as e:  # noqa: BLE001  (symmetric memory unavailable: the NCCL variant stands alone)
+            peer_res = {"unavailable": str(e).splitlines()[0][:200]}
+        import gc
+        gc.collect()
     full_bytes = layers * 150978560 + V * (H // 256) * 210
     return {"rows": rows, "layers": layers, "world": world, "ms_per_step": round(total, 3),
             "products_only_ms": round(compute, 3), "collectives_only_ms": round(coll, 3),
@@ -864,6 +896,7 @@ def extra_tp_stack(dev, world, rank, capture, layers=64, rows=32):
             "collective_us_each": round(coll * 1e3 / (2 * layers + 1), 1),
             "weight_bytes_per_step_all_ranks": full_bytes, "weight_bytes_this_rank": local_bytes,
             "GBps_all_ranks": round(full_bytes / total / 1e6, 1),
+            "peer_memory_allreduce": peer_res,
             "sharding": "qkv / gate_up / head along N (gate_up matched to down's K-shards), o_proj / down along K "
                         "(256-column granularity); all-reduce after o_proj and down, all-gather of the logits; "
                         "collectives captured in the step's CUDA graph"}

@@ -213,6 +213,26 @@ int gsq_iq3s_repack(void* w, int64_t rows, int64_t row_bytes, int direction, voi
 int gsq_q6k_repack(void* w, int64_t rows, int64_t row_bytes, int direction, void* stream);
 
 /*
+ * Sum of the partial results of K-sharded products (o_proj / down style, one [m, rows] partial per GPU) over peer
+ * memory, one kernel per rank, no NCCL call and no host involvement (so it replays inside a CUDA graph). No
+ * counterpart in the reference, which leaves the reduction to vLLM's row-parallel layer (an NCCL all-reduce after
+ * apply()). Every rank must make the same sequence of calls.
+ *   peer_bufs    device array of `world` pointers: each rank's partial buffer of `count` elements, mapped into this
+ *                process (symmetric memory / CUDA IPC; entry `rank` is this rank's own); 16-byte aligned
+ *   peer_flags   device array of `world` pointers: each rank's flag pad of `world` uint32, zero before the first call
+ *   out          [count] in `dtype`, this rank's memory; receives the sum (fp32 accumulation, rank order: all
+ *                ranks get bit-identical results)
+ *   state        2 uint32 of this rank's device memory, zero before the first call (call counter, block ticket)
+ * Consecutive calls must use different partial buffers (alternate between two): a partial buffer may be rewritten
+ * once the call after the one that read it has returned. Waits on the peers are bounded (a fraction of a second):
+ * a wait that gives up leaves `out` unwritten and raises the flag read by gsq_allreduce_error_flag.
+ * count * element size must be a multiple of 16.
+ */
+int gsq_allreduce_sum(const void* const* peer_bufs, uint32_t* const* peer_flags, int rank, int world, int64_t count,
+                      int dtype, void* out, uint32_t* state, void* stream);
+int gsq_allreduce_error_flag(int* flag);
+
+/*
  * Kernel choice on B200 for (activation rows m, type, weight rows, k, packed): GSQ_KERNEL_*.
  * The op-level routing table of the reference (_lcpp_op, quantization/linear.py:85-114) stays in the
  * Python layer because its op names are API; this is the choice made underneath those names.

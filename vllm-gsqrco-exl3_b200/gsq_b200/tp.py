@@ -88,3 +88,60 @@ def combine(y, s: Shard, n: int, k: int, world: int, group=None):
              for r in range(world)]
     dist.all_gather(parts, y.contiguous(), group=group)
     return torch.cat(parts, dim=1)
+
+
+class PeerAllReduce:
+    """Sum of K-sharded partial results over peer memory (gsq_allreduce_sum): `slots` partial buffers of `nbytes`
+    each in symmetric memory (torch.distributed._symmetric_memory: the same allocation mapped into every rank of the
+    group) plus the flag pad. Usage per reduction, the same sequence on every rank:
+
+        part = ar.partial(i, (m, n), dtype)      # products write the rank's partial here (lcpp_ops.output_into)
+        ar.reduce(i, out)                        # out[...] = sum over ranks, bit-identical on all of them
+
+    with i alternating between slots from one reduction to the next. Launches one kernel on the current stream and
+    nothing else, so it can be captured in a CUDA graph."""
+
+    def __init__(self, nbytes: int, slots: int = 2, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from . import _cabi
+
+        assert slots >= 2
+        group = group or dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.dev = torch.device("cuda", torch.cuda.current_device())
+        self.nbytes = (int(nbytes) + 255) // 256 * 256
+        self.slots = slots
+        total = slots * self.nbytes + 256
+        self.buf = symm.empty(total, dtype=torch.uint8, device=self.dev)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self._bufs = [torch.tensor([p + i * self.nbytes for p in ptrs], dtype=torch.int64, device=self.dev) for i in range(slots)]
+        self._flags = torch.tensor([p + slots * self.nbytes for p in ptrs], dtype=torch.int64, device=self.dev)
+        self._state = torch.zeros(2, dtype=torch.int32, device=self.dev)
+        self._lib, self._check = _cabi.lib, _cabi.check
+        torch.cuda.synchronize()
+        dist.barrier(group)      # every rank's pad is zero before anyone signals
+
+    def partial(self, slot: int, shape, dtype):
+        import torch
+
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nb = n * torch.empty(0, dtype=dtype).element_size()
+        assert nb <= self.nbytes, (nb, self.nbytes)
+        return self.buf[slot * self.nbytes: slot * self.nbytes + nb].view(dtype).view(*shape)
+
+    def reduce(self, slot: int, out) -> None:
+        import torch
+
+        dt = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[out.dtype]
+        assert out.is_contiguous() and out.numel() * out.element_size() <= self.nbytes
+        st = torch.cuda.current_stream(self.dev).cuda_stream
+        self._check(self._lib.gsq_allreduce_sum(self._bufs[slot].data_ptr(), self._flags.data_ptr(), self.rank, self.world,
+                                                 out.numel(), dt, out.data_ptr(), self._state.data_ptr(), st),
+                    "gsq_allreduce_sum")
