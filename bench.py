@@ -1016,7 +1016,7 @@ def run_cell(args):
     dev = "cuda:0"
     t = synth.TYPE_IDS[tname]
     w0 = torch.from_numpy(synth.make_weight(t, n, k, 1)).to(dev)
-    packed = tname == "IQ3_S" and not args.unpacked and n % 16 == 0
+    packed = tname in ("IQ3_S", "Q6_K") and not args.unpacked and n % 16 == 0
     if packed:
         iq3_pack.pack_(w0, t)
     ws = [w0] + [w0.clone() for _ in range(3)]
@@ -1050,7 +1050,7 @@ def main():
     ap.add_argument("--no-ref-kernels", action="store_true", help="skip timing the reference's CUDA kernels (oracle/_ref)")
     ap.add_argument("--cell", nargs=4, metavar=("TYPE", "N", "K", "M"), help="run one product only (for profilers)")
     ap.add_argument("--iters", type=int, default=3)
-    ap.add_argument("--unpacked", action="store_true", help="--cell: keep IQ3_S in GGUF order")
+    ap.add_argument("--unpacked", action="store_true", help="--cell: keep IQ3_S / Q6_K in GGUF order")
     args = ap.parse_args()
     if args.cell:
         run_cell(args)

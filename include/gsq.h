@@ -50,8 +50,10 @@ extern "C" {
 
 /* kernel selectors returned by gsq_route / accepted by gsq_mul_mat */
 #define GSQ_KERNEL_NONE 0
-#define GSQ_KERNEL_GEMV 1 /* dp4a streaming GEMV, 1..8 activation rows, reads block_q8_1 */
-#define GSQ_KERNEL_GEMM 2 /* tcgen05 kind::i8 GEMM, any rows, reads 128-value q8_1 blocks */
+#define GSQ_KERNEL_GEMV 1 /* dp4a streaming GEMV, 1..8 activation rows per launch, reads block_q8_1 */
+#define GSQ_KERNEL_GEMM 2 /* tcgen05 kind::i8 GEMM, 64-token tiles in lockstep, reads 128-value q8_1 blocks */
+#define GSQ_KERNEL_MMV 3  /* register-operand tensor-core kernel, 1..48 activation rows per launch */
+#define GSQ_KERNEL_GEMM_PREFILL 4 /* warp-specialised tcgen05 kind::i8 GEMM, 256-token blocks, reads operand tiles */
 
 const char* gsq_strerror(int status);
 /* cudaError_t of the last failing CUDA call made by this library on this thread (0 if none). */
@@ -233,9 +235,10 @@ int gsq_allreduce_sum(const void* const* peer_bufs, uint32_t* const* peer_flags,
 int gsq_allreduce_error_flag(int* flag);
 
 /*
- * Kernel choice on B200 for (activation rows m, type, weight rows, k, packed): GSQ_KERNEL_*.
- * The op-level routing table of the reference (_lcpp_op, quantization/linear.py:85-114) stays in the
- * Python layer because its op names are API; this is the choice made underneath those names.
+ * Kernel family that serves (activation rows m, type, weight rows, k, packed) on B200: GSQ_KERNEL_*, the choice
+ * gsq_mul_mat_vec_q8 and gsq_linear make. The op-level routing table of the reference (_lcpp_op,
+ * quantization/linear.py:85-114) stays in the Python layer because its op names are API; this is the choice made
+ * underneath those names.
  */
 int gsq_route(int64_t m, int ggml_type, int64_t rows, int64_t k, int packed);
 

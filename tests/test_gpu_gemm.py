@@ -64,7 +64,7 @@ def gemm_variant(request):
     """The tcgen05 GEMM kernels at every row count: the warp-specialised prefill GEMM on operand-ordered activation
     tiles (weights decoded once per 256 tokens), the two older kernels on 128-value blocks (warp-specialised and
     all-warps-in-lockstep); and the library's own choice, which up to 48 rows is the register-operand kernel."""
-    variant = {"prefill": 0, "specialised": 1, "lockstep": 2, "default": 0}[request.param]
+    variant = {"prefill": 3, "specialised": 1, "lockstep": 2, "default": 0}[request.param]
     old = _cabi.lib.gsq_debug_gemm_variant(variant)
     old_mode = _cabi.lib.gsq_debug_mmv_mode(0 if request.param == "default" else 1)
     yield request.param

@@ -92,9 +92,19 @@ def test_zero_rows_return_before_routing():
 
 
 def test_c_route():
+    """gsq_route names the kernel family the library runs underneath the op names (what gsq_mul_mat_vec_q8 and
+    gsq_linear choose)."""
     from gsq_b200 import _cabi
 
-    assert _cabi.lib.gsq_route(1, IQ3_S, BIG, K, 1) == _cabi.KERNEL_GEMV
-    assert _cabi.lib.gsq_route(8, Q4_K, BIG, K, 0) == _cabi.KERNEL_GEMV
-    assert _cabi.lib.gsq_route(9, Q4_K, BIG, K, 0) == _cabi.KERNEL_GEMM
-    assert _cabi.lib.gsq_route(4, IQ2_S, BIG, K, 0) == _cabi.KERNEL_NONE
+    r = _cabi.lib.gsq_route
+    Q6_K, IQ4_XS = 14, 23
+    assert r(1, IQ3_S, BIG, K, 1) == _cabi.KERNEL_MMV          # repacked IQ3_S: the tensor-core kernel from 1 row
+    assert r(1, IQ3_S, BIG, K, 0) == _cabi.KERNEL_GEMV         # GGUF order: dp4a
+    assert r(1, Q4_K, BIG, K, 0) == _cabi.KERNEL_GEMV and r(2, Q4_K, BIG, K, 0) == _cabi.KERNEL_MMV
+    assert r(3, IQ4_XS, BIG, K, 0) == _cabi.KERNEL_GEMV and r(4, IQ4_XS, BIG, K, 0) == _cabi.KERNEL_MMV
+    assert r(48, Q4_K, BIG, K, 0) == _cabi.KERNEL_MMV and r(49, Q4_K, BIG, K, 0) == _cabi.KERNEL_GEMM
+    assert r(512, Q4_K, BIG, K, 0) == _cabi.KERNEL_GEMM_PREFILL
+    assert r(128, IQ3_S, 17408, K, 1) == _cabi.KERNEL_GEMM_PREFILL and r(128, IQ3_S, 5120, K, 1) == _cabi.KERNEL_GEMM
+    assert r(8192, Q6_K, 151936, K, 1) == _cabi.KERNEL_MMV     # repacked Q6_K: 48 rows per launch
+    assert r(33, Q6_K, BIG, K, 0) == _cabi.KERNEL_GEMV         # GGUF order: dp4a, 8 rows per launch
+    assert r(4, IQ2_S, BIG, K, 0) == _cabi.KERNEL_NONE

@@ -160,12 +160,24 @@ extern "C" int gsq_check_inputs(const gsq_guard_args* a, int64_t* k_out, char* m
   return GSQ_OK;
 }
 
+namespace gsq {
+bool mmv_applies(int ggml_type, int packed, int64_t rows, int64_t m);   // gsq_mmv.cu
+bool gemm2_applies(int ggml_type, int packed, int64_t rows);            // gsq_gemm2.cu
+}
+
+// The choice gsq_mul_mat_vec_q8 (m <= 8) and gsq_linear (any m) make, in the same order (a shape whose activations do
+// not fit the small-batch kernel's staging area falls through to the next family at launch).
 extern "C" int gsq_route(int64_t m, int ggml_type, int64_t rows, int64_t k, int packed) {
-  (void)rows;
   (void)k;
-  (void)packed;
-  if (gsq::block_bytes(ggml_type) == 0 || m <= 0) return GSQ_KERNEL_NONE;
-  return m <= 8 ? GSQ_KERNEL_GEMV : GSQ_KERNEL_GEMM;
+  if (gsq::block_bytes(ggml_type) == 0 || m <= 0 || rows <= 0) return GSQ_KERNEL_NONE;
+  if (ggml_type == GSQ_TYPE_Q6_K && packed && rows % 16 == 0) return GSQ_KERNEL_MMV;   // 48 rows per launch above 48
+  if (m <= 48 && gsq::mmv_applies(ggml_type, packed, rows, m)) return GSQ_KERNEL_MMV;
+  if (m <= 8) return GSQ_KERNEL_GEMV;
+  if (gsq::gemm2_applies(ggml_type, packed, rows)) {
+    const bool big = m >= 512 || (m >= 128 && (rows + 127) / 128 >= 74);
+    return big ? GSQ_KERNEL_GEMM_PREFILL : GSQ_KERNEL_GEMM;
+  }
+  return GSQ_KERNEL_GEMV;   // Q6_K / IQ3_S in GGUF order: the dp4a kernel, 8 rows per launch
 }
 
 extern "C" int gsq_q8_layout_for_type(int ggml_type) {

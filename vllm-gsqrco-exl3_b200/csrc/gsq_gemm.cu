@@ -884,7 +884,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) gemm_ws_kernel(const GemmArgs g
 static int g_swap_lbo_sbo = 0;
 static int* g_gemm_dump = nullptr;
 static int g_gemm_ksplit = 0;  // experiments: 0 = choose, else 1, 2 or 4
-static int g_gemm_variant = 0;  // behind gsq_linear: 0 = the prefill GEMM of gsq_gemm2.cu; the kernels of this file: 1 = warp-specialised, else lockstep
+static int g_gemm_variant = 0;  // behind gsq_linear: 0 = choose by shape, 3 = always the prefill GEMM of gsq_gemm2.cu; the kernels of this file: 1 = warp-specialised, 2 = lockstep
 
 int gemm2_error_flag(int* flag);  // gsq_gemm2.cu
 
@@ -905,7 +905,7 @@ static int launch_gemm(const GemmArgs& g, int sm_count, cudaStream_t st) {
   static int configured_mask = 0;
   int dev = 0;
   GSQ_CUDA_TRY(cudaGetDevice(&dev));
-  const bool ws = g_gemm_variant == 1;
+  const bool ws = g_gemm_variant == 1;   // (0 and 2: the lockstep kernel)
   const size_t smem = ws ? gemm_ws_smem_bytes<KIND>() : gemm_smem_bytes<KIND>();
   if (dev >= 32 || !((configured_mask >> dev) & 1)) {
     GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -954,7 +954,7 @@ extern "C" int gsq_debug_swap_descriptor_strides(int on) {
 
 extern "C" int gsq_debug_gemm_variant(int v) {
   const int old = gsq::g_gemm_variant;
-  gsq::g_gemm_variant = v == 1 ? 1 : v == 2 ? 2 : 0;
+  gsq::g_gemm_variant = (v >= 1 && v <= 3) ? v : 0;
   return old;
 }
 

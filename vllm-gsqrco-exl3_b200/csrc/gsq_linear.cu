@@ -56,8 +56,12 @@ extern "C" int gsq_linear(const void* w, int64_t row_bytes, int64_t rows, int gg
     rc = mmv_host(w, row_bytes, rows, ggml_type, packed, scratch, 1, m, k, y, y_dtype, y_row_stride, stream, gemm_dump_pointer());
     if (rc != 1000) return rc;  // 1000: declined, the activations of this shape do not fit its staging area
   }
-  // the prefill GEMM on operand-ordered tiles
-  if (gemm2_applies(ggml_type, packed, rows) && gemm_variant() == 0) {
+  // The prefill GEMM on operand-ordered tiles, where its 128-row x 256-token items can occupy the GPU: measured
+  // against the lockstep kernel (64-token tiles, K split over a cluster when tiles are few) it wins from 512 tokens
+  // on, and from 128 tokens where the weight alone gives half an SM count of row tiles.
+  const int variant = gemm_variant();
+  const bool big = m >= 512 || (m >= 128 && (rows + 127) / 128 >= 74);
+  if (gemm2_applies(ggml_type, packed, rows) && (variant == 3 || (variant == 0 && big))) {
     rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, layout, scratch, stream);
     if (rc != GSQ_OK) return rc;
     return gemm2_host(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, stream);

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libgsq.so")
 OK, ERR_GUARD, ERR_CUDA, ERR_UNSUPPORTED, ERR_SCRATCH, ERR_TOO_LARGE, ERR_DEVICE = 0, -1, -2, -3, -4, -5, -6
 F32, F16, BF16, DTYPE_OTHER = 0, 1, 2, 99
 LAYOUT_D4, LAYOUT_DS4 = 0, 1
-KERNEL_NONE, KERNEL_GEMV, KERNEL_GEMM = 0, 1, 2
+KERNEL_NONE, KERNEL_GEMV, KERNEL_GEMM, KERNEL_MMV, KERNEL_GEMM_PREFILL = 0, 1, 2, 3, 4
 
 EXPORTS = (
     "gsq_strerror", "gsq_last_cuda_error", "gsq_abi_version", "gsq_type_block_bytes", "gsq_check_inputs",
