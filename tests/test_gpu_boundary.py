@@ -82,7 +82,9 @@ _CAPTURE_FIRST = textwrap.dedent("""
     ("IQ4_XS", IQ4_XS, "lcpp_mul_mat_mma_k", 16, False),
     ("IQ4_XS", IQ4_XS, "lcpp_mul_mat_q", 200, False),
     ("IQ3_S", IQ3_S, "lcpp_mul_mat_iq3_packed", 130, True),
+    ("IQ3_S", IQ3_S, "lcpp_mul_mat_iq3_packed", 512, True),
     ("Q6_K", Q6_K, "lcpp_mul_mat_vec_q", 3, False),
+    ("Q6_K", Q6_K, "gsq_mul_mat_q6k_packed", 20, True),
 ])
 def test_first_call_of_a_process_inside_a_capture(name, t, op, m, packed):
     code = _CAPTURE_FIRST.format(root=ROOT, pkg=os.path.join(ROOT, "vllm-gsqrco-exl3_b200"), name=name, t=t, op=op, m=m,

@@ -37,6 +37,22 @@ def test_uneven_k_shards_of_the_survey():
     assert [tp.shard_plan(5120, 5120, 8, r, "K").count for r in range(8)] == [3, 3, 3, 3, 2, 2, 2, 2]
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_gate_up_channels_match_the_k_shards_of_down(world):
+    """A rank's SwiGLU output must be exactly the columns its K-shard of the down projection multiplies: the gate /
+    up channels are cut where down's superblocks are cut (uneven at 8 ranks: 2304 x 4, 2048 x 4), not evenly."""
+    inter = 17408
+    got = [tp.matched_up_rows(inter, world, r) for r in range(world)]
+    assert got[0][0] == 0 and sum(c for _, c in got) == inter
+    for r in range(world):
+        s = tp.shard_plan(5120, inter, world, r, "K")
+        assert got[r] == (s.start * 256, s.count * 256) and got[r][1] % 16 == 0
+        if r:
+            assert got[r][0] == got[r - 1][0] + got[r - 1][1]
+    if world == 8:
+        assert [c for _, c in got] == [2304] * 4 + [2048] * 4
+
+
 @pytest.mark.parametrize("t", [21, 12])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_sharded_products_equal_unsharded(t, world):

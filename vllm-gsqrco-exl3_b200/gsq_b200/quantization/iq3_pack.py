@@ -1,9 +1,9 @@
 """Lossless repack of IQ3_S (and Q6_K) weight bytes into the order the sm_100a kernels stream them.
 
 Same role and interface as the reference's quantization/iq3_pack.py (pack_ / pack / unpack, ROWS = 16,
-bijective, in place, tile t keeps the bytes of rows 16t..16t+15), a different layout: the reference's
-differs in how the bits of a lane are laid out: this one is cut for 128-bit coalesced loads and a decode of
-shifts, one table load and one byte permute per four values.
+bijective, in place, tile t keeps the bytes of rows 16t..16t+15), but a different bit layout inside a
+record: this one is cut for 128-bit coalesced loads and a decode of shifts, one table load and one byte
+permute per four values.
 The layout is documented in csrc/gsq_repack.cu; in short, per 16-row x 256-column record (1760 B)
 lane l = 4g + t owns rows g and g + 8 and, of every 32-value slice s, the 4-value groups 2t and 2t + 1;
 its 32 fields are numbered f = 4s + 2h + e (row g + 8h, group 2t + e):
