@@ -59,12 +59,17 @@ CASES = [("IQ3_S", 128, 512), ("IQ3_S", 272, 5120), ("IQ3_S", 48, 1024), ("Q4_K"
          ("IQ4_XS", 128, 512), ("IQ4_XS", 202, 5120), ("IQ4_XS", 300, 17408)]
 
 
-@pytest.fixture(params=["prefill", "specialised", "lockstep", "default"], autouse=True)
+@pytest.fixture(params=["prefill", "prefill_int8", "specialised", "lockstep", "default"], autouse=True)
 def gemm_variant(request):
-    """The tcgen05 GEMM kernels at every row count: the warp-specialised prefill GEMM on operand-ordered activation
-    tiles (weights decoded once per 256 tokens), the two older kernels on 128-value blocks (warp-specialised and
-    all-warps-in-lockstep); and the library's own choice, which up to 48 rows is the register-operand kernel."""
-    variant = {"prefill": 3, "specialised": 1, "lockstep": 2, "default": 0}[request.param]
+    """The tcgen05 GEMM kernels at every row count: the warp-specialised prefill GEMMs on operand-ordered activation
+    tiles (weights decoded once per 256 tokens; for repacked IQ3_S "prefill" is the kernel with fp16 operands that
+    carry the sub-scales and "prefill_int8" the int8 one, for the other types both names are the int8 kernel), the
+    two older kernels on 128-value blocks (warp-specialised and all-warps-in-lockstep); and the library's own choice,
+    which up to 48 rows is the register-operand kernel."""
+    callspec = getattr(request.node, "callspec", None)
+    if request.param == "prefill_int8" and callspec is not None and callspec.params.get("name", "IQ3_S") != "IQ3_S":
+        pytest.skip("the same kernel as 'prefill' for this type")
+    variant = {"prefill": 3, "prefill_int8": 4, "specialised": 1, "lockstep": 2, "default": 0}[request.param]
     old = _cabi.lib.gsq_debug_gemm_variant(variant)
     old_mode = _cabi.lib.gsq_debug_mmv_mode(0 if request.param == "default" else 1)
     yield request.param

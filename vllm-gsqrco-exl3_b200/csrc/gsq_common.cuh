@@ -22,6 +22,9 @@ int record_cuda_error(cudaError_t e);
     if (_e != cudaSuccess) return gsq::record_cuda_error(_e); \
   } while (0)
 
+// activation tiles of the prefill GEMMs: besides GSQ_Q8_LAYOUT_D4 / _DS4, the quants as fp16 with fp32 d (gsq_gemm3.cu)
+constexpr int Q8_TILES_H16 = 2;
+
 struct DeviceInfo {
   int sm_count;
   int max_smem_optin;

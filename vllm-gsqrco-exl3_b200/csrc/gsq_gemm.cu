@@ -884,16 +884,19 @@ __global__ void __launch_bounds__(WS_THREADS, 1) gemm_ws_kernel(const GemmArgs g
 static int g_swap_lbo_sbo = 0;
 static int* g_gemm_dump = nullptr;
 static int g_gemm_ksplit = 0;  // experiments: 0 = choose, else 1, 2 or 4
-static int g_gemm_variant = 0;  // behind gsq_linear: 0 = choose by shape, 3 = always the prefill GEMM of gsq_gemm2.cu; the kernels of this file: 1 = warp-specialised, 2 = lockstep
+static int g_gemm_variant = 0;  // behind gsq_linear: 0 = choose by shape, 3 = always a prefill GEMM (gsq_gemm3.cu for repacked IQ3_S, else gsq_gemm2.cu), 4 = always gsq_gemm2.cu; the kernels of this file: 1 = warp-specialised, 2 = lockstep
 
 int gemm2_error_flag(int* flag);  // gsq_gemm2.cu
+int gemm3_error_flag(int* flag);  // gsq_gemm3.cu
 
 int gemm_error_flag(int* flag) {
-  int a = 0, b = 0;
+  int a = 0, b = 0, c = 0;
   GSQ_CUDA_TRY(cudaMemcpyFromSymbol(&a, g_gemm_error, sizeof(int)));
-  const int rc = gemm2_error_flag(&b);
+  int rc = gemm2_error_flag(&b);
   if (rc != GSQ_OK) return rc;
-  *flag = a | b;
+  rc = gemm3_error_flag(&c);
+  if (rc != GSQ_OK) return rc;
+  *flag = a | b | c;
   return GSQ_OK;
 }
 
@@ -954,7 +957,7 @@ extern "C" int gsq_debug_swap_descriptor_strides(int on) {
 
 extern "C" int gsq_debug_gemm_variant(int v) {
   const int old = gsq::g_gemm_variant;
-  gsq::g_gemm_variant = (v >= 1 && v <= 3) ? v : 0;
+  gsq::g_gemm_variant = (v >= 1 && v <= 4) ? v : 0;
   return old;
 }
 

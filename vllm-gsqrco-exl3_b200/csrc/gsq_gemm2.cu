@@ -23,6 +23,7 @@
 // warpgroup to the four consumer warpgroups.
 #include "gsq_common.cuh"
 #include "gsq_tables.h"
+#include "gsq_tc.cuh"
 
 namespace gsq {
 
@@ -43,8 +44,6 @@ constexpr int A_STAGES = 2;
 constexpr int B_SLOTS = 8;
 constexpr int RAW_STAGES = 3;
 constexpr int TMEM_COLS = 512;
-constexpr int MAGIC = 0x4B400000;       // bit pattern of 1.5 * 2^23
-constexpr float MAGIC_F = 12582912.0f;
 
 // bytes of one unit (4 slices of a 64-token sub-tile) of the activation tiles: quants, d (+ sum for Q4_K)
 __host__ __device__ constexpr int unit_bytes(bool ds) { return 4 * SL_B + 4 * NT * 4 * (ds ? 2 : 1); }
@@ -81,103 +80,11 @@ struct Smem {
 
 __device__ int g_error = 0;
 
-__device__ __forceinline__ uint32_t saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+using namespace tc;
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Bounded wait: gives up after 2^22 polls (or as soon as another thread of the CTA has given up) and raises the flags.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  uint32_t done = 0;
-  for (int spin = 0; spin < (1 << 21); ++spin) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-    __nanosleep(100);  // a waiting warp should not spend the issue slots of the working ones on polls
-    if ((spin & 63) == 63 && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  atomicExch(&g_error, 1);
-  return false;
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
-               "r"(bytes), "r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-// D[tmem] = A[smem] * B[smem], int8 x int8 -> int32, K = 32, D overwritten
-__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, 0, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-               : "r"(taddr)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major int8 operand stored as core matrices of 8 rows x 16 bytes: the two
-// core matrices of a row group (K bytes 0-15, 16-31) 128 bytes apart, consecutive 8-row groups 256 bytes apart; no
-// swizzle; descriptor version 1.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-  uint64_t d = (uint64_t)((addr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)(128 >> 4) << 16;
-  d |= (uint64_t)(256 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  return d;
-}
+// K-major int8 operand: the two core matrices of a row group (K bytes 0-15, 16-31) 128 bytes apart, consecutive 8-row
+// groups 256 bytes apart
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) { return tc::smem_desc(addr, 128, 256); }
 // Instruction descriptor: D = s32, A = B = s8, both K-major, N = 64, M = 128, dense.
 __host__ __device__ constexpr uint32_t idesc() {
   return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(TR >> 4) << 24);
@@ -185,35 +92,6 @@ __host__ __device__ constexpr uint32_t idesc() {
 // byte offset of (row r, 16-byte K chunk c16) inside one slice of a K-major core-matrix tile
 __device__ __forceinline__ int core_off(int r, int c16) { return (r >> 3) * 256 + c16 * 128 + (r & 7) * 16; }
 
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-  uint32_t r;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
-  return r;
-}
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-// Bit pattern of the float 1.5 * 2^23 + c for an integer |c| < 2^22, in one logic instruction (not an integer add,
-// which the compiler may place on the fp32 pipe the scaling needs): the low 23 bits are those of c with bit 22
-// flipped (c + 2^22 never carries out of them), the rest those of the constant. Truth table of
-// f(c, mask, magic) = mask ? c ^ magic : magic, mask = 0x007FFFFF: 0x6A... computed below.
-__device__ __forceinline__ float biased_float(uint32_t c) {
-  uint32_t r;
-  // inputs a = c, b = mask, c = magic; LUT bit index = (a << 2) | (b << 1) | c: out = b ? a ^ c : c
-  //   a b c -> out : 000->0 001->1 010->0 011->1 100->0 101->1 110->1 111->0  => LUT = 0b01101010 = 0x6A
-  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(c), "r"(0x007FFFFFu), "r"((uint32_t)MAGIC));
-  return __uint_as_float(r);
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
 
 __device__ const uint32_t g_iq3s_grid[512] = GSQ_IQ3S_GRID_INIT;
 __constant__ __align__(16) int8_t c_iq4nl[16] = GSQ_IQ4NL_VALUES_INIT;
@@ -483,7 +361,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
         fetch_next((int)n + 2);
         const uint32_t st = n & 1u;
         const unsigned long long p0 = tick();
-        alive = alive && mbar_wait(a_empty(st), ((n >> 1) & 1u) ^ 1u, abort_flag);
+        alive = alive && mbar_wait(a_empty(st), ((n >> 1) & 1u) ^ 1u, abort_flag, &g_error);
         const unsigned long long p1 = tick();
         pw[0] += p1 - p0;
         if (!alive) continue;
@@ -519,7 +397,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
       auto load_next = [&]() {
         if (l_item >= n_items || !alive) return;
         const uint32_t slot = l_g & (B_SLOTS - 1);
-        alive = mbar_wait(b_empty(slot), ((l_g >> 3) & 1u) ^ 1u, abort_flag);
+        alive = mbar_wait(b_empty(slot), ((l_g >> 3) & 1u) ^ 1u, abort_flag, &g_error);
         if (!alive) return;
         const int tt = item_tb(l_item) * NSUB + (l_u >> 1);
         const uint8_t* src = g.xt + (((int64_t)tt * nsb + l_sb) * 2 + (l_u & 1)) * UB;
@@ -538,7 +416,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
         for (int sb = 0; sb < nsb && alive; ++sb, ++n) {
           const uint32_t st = n & 1u;
           const unsigned long long m0 = tick();
-          alive = mbar_wait(a_full(st), (n >> 1) & 1u, abort_flag);
+          alive = mbar_wait(a_full(st), (n >> 1) & 1u, abort_flag, &g_error);
           pw[0] += tick() - m0;
           if (!alive) break;
           const uint32_t a_addr = saddr(smem + S::A + st * (8 * SL_A));
@@ -546,13 +424,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
             const uint32_t slot = gu & (B_SLOTS - 1), half = gu & 1u;
             // the consumers have drained this half of tensor memory (unit gu - 2) ...
             const unsigned long long m1 = tick();
-            alive = mbar_wait(d_empty(half), ((gu >> 1) & 1u) ^ 1u, abort_flag);
+            alive = mbar_wait(d_empty(half), ((gu >> 1) & 1u) ^ 1u, abort_flag, &g_error);
             const unsigned long long m2 = tick();
             pw[1] += m2 - m1;
             if (!alive) break;
             load_next();   // ... and with it released that unit's activation slot: the copy for unit gu + 6 goes there
             const unsigned long long m3 = tick();
-            alive = alive && mbar_wait(b_full(slot), (gu >> 3) & 1u, abort_flag);
+            alive = alive && mbar_wait(b_full(slot), (gu >> 3) & 1u, abort_flag, &g_error);
             pw[2] += tick() - m3;
             if (!alive) break;
             tc_fence_after();
@@ -573,7 +451,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
       }
       if (!alive) {
         // a wait gave up: let the copies already issued land (bounded) before the CTA's shared memory goes away
-        for (uint32_t q = gu; q < l_g; ++q) mbar_wait(b_full(q & (B_SLOTS - 1)), (q >> 3) & 1u, abort_flag);
+        for (uint32_t q = gu; q < l_g; ++q) mbar_wait(b_full(q & (B_SLOTS - 1)), (q >> 3) & 1u, abort_flag, &g_error);
       }
     }
   } else {
@@ -595,7 +473,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
       for (int sb = 0; sb < nsb && alive; ++sb, ++n) {
         const uint32_t st = n & 1u;
         const unsigned long long c0t = tick();
-        alive = mbar_wait(a_full(st), (n >> 1) & 1u, abort_flag);   // the producers' scale planes are visible
+        alive = mbar_wait(a_full(st), (n >> 1) & 1u, abort_flag, &g_error);   // the producers' scale planes are visible
         pw[0] += tick() - c0t;
         if (!alive) break;
         const float* sa = reinterpret_cast<const float*>(smem + S::SA + st * (scale_planes(KIND) * 8 * TR * 4));
@@ -609,9 +487,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
             for (int h = 0; h < 2; ++h) {
               const uint32_t slot = gu & (B_SLOTS - 1);
               const unsigned long long c1t = tick();
-              alive = alive && mbar_wait(b_full(slot), (gu >> 3) & 1u, abort_flag);   // the unit's scales are visible
+              alive = alive && mbar_wait(b_full(slot), (gu >> 3) & 1u, abort_flag, &g_error);   // the unit's scales are visible
               const unsigned long long c2t = tick();
-              alive = alive && mbar_wait(d_full(h), (gu >> 1) & 1u, abort_flag);
+              alive = alive && mbar_wait(d_full(h), (gu >> 1) & 1u, abort_flag, &g_error);
               const unsigned long long c3t = tick();
               pw[1] += c2t - c1t;
               pw[2] += c3t - c2t;
@@ -717,6 +595,7 @@ static int launch(const Args& g, int sm_count, cudaStream_t st) {
 int* gemm_dump_pointer();
 
 static unsigned long long* g_prof = nullptr;
+unsigned long long* gemm_profile_pointer() { return g_prof; }
 
 int gemm2_error_flag(int* flag) {
   GSQ_CUDA_TRY(cudaMemcpyFromSymbol(flag, g2::g_error, sizeof(int)));

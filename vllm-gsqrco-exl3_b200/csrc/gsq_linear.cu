@@ -16,6 +16,11 @@ bool gemm2_applies(int ggml_type, int packed, int64_t rows);
 size_t gemm2_tile_bytes(int64_t m, int64_t k, int ggml_type);
 int gemm2_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_tiles, int64_t m,
                int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream);
+// gsq_gemm3.cu
+bool gemm3_applies(int ggml_type, int packed, int64_t rows);
+size_t gemm3_tile_bytes(int64_t m, int64_t k);
+int gemm3_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_tiles, int64_t m,
+               int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream);
 // gsq_quantize.cu
 int quantize_tiles_host(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride, int layout, void* out, void* stream);
 // gsq_gemm.cu
@@ -27,11 +32,9 @@ static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 }  // namespace gsq
 
 extern "C" size_t gsq_linear_scratch_bytes(int64_t rows, int64_t m, int64_t k, int ggml_type, int packed) {
-  (void)rows;
-  (void)packed;
   if (m <= 0 || k <= 0) return 0;
-  const size_t mmq = (size_t)(k / 128) * (size_t)m * 144, tiles = gsq::gemm2_tile_bytes(m, k, ggml_type),
-               q81 = (size_t)(k / 32) * (size_t)m * 36;
+  const size_t mmq = (size_t)(k / 128) * (size_t)m * 144, q81 = (size_t)(k / 32) * (size_t)m * 36;
+  const size_t tiles = gsq::gemm3_applies(ggml_type, packed, rows) ? gsq::gemm3_tile_bytes(m, k) : gsq::gemm2_tile_bytes(m, k, ggml_type);
   size_t b = mmq > tiles ? mmq : tiles;
   b = b > q81 ? b : q81;
   return gsq::align256(b);
@@ -61,6 +64,17 @@ extern "C" int gsq_linear(const void* w, int64_t row_bytes, int64_t rows, int gg
   // on, and from 128 tokens where the weight alone gives half an SM count of row tiles.
   const int variant = gemm_variant();
   const bool big = m >= 512 || (m >= 128 && (rows + 127) / 128 >= 74);
+  // repacked IQ3_S: the kernel with the sub-scales folded into fp16 operands (variant 4 keeps the int8 kernel for it)
+  if (gemm3_applies(ggml_type, packed, rows) && (variant == 3 || (variant == 0 && big))) {
+    rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, Q8_TILES_H16, scratch, stream);
+    if (rc != GSQ_OK) return rc;
+    return gemm3_host(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, stream);
+  }
+  if (gemm2_applies(ggml_type, packed, rows) && variant == 4) {
+    rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, layout, scratch, stream);
+    if (rc != GSQ_OK) return rc;
+    return gemm2_host(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, stream);
+  }
   if (gemm2_applies(ggml_type, packed, rows) && (variant == 3 || (variant == 0 && big))) {
     rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, layout, scratch, stream);
     if (rc != GSQ_OK) return rc;

@@ -171,6 +171,11 @@ __global__ void __launch_bounds__(256) quantize_q8_1_mmq_kernel(const T* __restr
 //   unit = [4 slices][8 token groups][2 K chunks of 16][8 tokens][16 bytes] quants   (8192 bytes)
 //          [4 slices][64 tokens] float d                                              (1024 bytes)
 //          [4 slices][64 tokens] float(half(sum x))   (DS4 only)                      (1024 bytes)
+// and, for the kernel whose operands are fp16 (gsq_gemm3.cu; LAYOUT = Q8_TILES_H16), the same quants as fp16 numbers
+// in units of one slice x 256 tokens, [token block of 256][superblock][slice][unit]:
+//   unit = [32 token groups][4 K chunks of 8][8 tokens][8 fp16] quants                 (16384 bytes)
+//          [256 tokens] float d                                                       (1024 bytes)
+// (the grid then covers whole blocks of 256 tokens).
 // Tokens past m (up to the end of the last tile) are written as zeros. One block = 64 tokens x one 32-value slice:
 // warp w holds token group w, lane = (token % 8) * 4 + 8-value piece, so a warp writes two whole 128-byte core
 // matrices.
@@ -179,8 +184,8 @@ __global__ void __launch_bounds__(256) quantize_q8_1_tiles_kernel(const T* __res
                                                                  int64_t m, int64_t k, int64_t stride) {
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  constexpr bool DS = LAYOUT == GSQ_Q8_LAYOUT_DS4;
-  constexpr int UB = 8192 + (DS ? 2048 : 1024);
+  constexpr bool DS = LAYOUT == GSQ_Q8_LAYOUT_DS4, H16 = LAYOUT == Q8_TILES_H16;
+  constexpr int UB = H16 ? 16384 + 1024 : 8192 + (DS ? 2048 : 1024);
   const int slice = blockIdx.x;              // 32-value slice along k
   const int64_t tt = blockIdx.y;             // token tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -215,9 +220,23 @@ __global__ void __launch_bounds__(256) quantize_q8_1_tiles_kernel(const T* __res
   for (int e = 0; e < 8; ++e) q[e] = live ? roundf(v[e] * d_inv) : 0.0f;
   float d = live ? rcp_approx(d_inv) : 0.0f;
   const int sb = slice >> 3, s = slice & 7, sl = s & 3;
+  if constexpr (H16) {
+    // the lane's 8 values are one 16-byte row of a core matrix (integers up to 127 in magnitude: exact in fp16)
+    const int rb = (int)(tt & 3) * 64 + r;   // token within its block of 256
+    uint8_t* unit = out + (((tt >> 2) * (k >> 8) + sb) * 8 + s) * UB;
+    uint8_t* dst = unit + (rb >> 3) * 512 + piece * 128 + (rb & 7) * 16;
+    __half2 h[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(q[2 * e], q[2 * e + 1]);
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(h);
+    if (piece == 0) reinterpret_cast<float*>(unit + 16384)[rb] = d;
+    return;
+  }
   uint8_t* unit = out + ((tt * (k >> 8) + sb) * 2 + (s >> 2)) * UB;
-  uint8_t* dst = unit + sl * 2048 + (r >> 3) * 256 + (piece >> 1) * 128 + (r & 7) * 16 + (piece & 1) * 8;
-  *reinterpret_cast<uint2*>(dst) = make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
+  {
+    uint8_t* dst = unit + sl * 2048 + (r >> 3) * 256 + (piece >> 1) * 128 + (r & 7) * 16 + (piece & 1) * 8;
+    *reinterpret_cast<uint2*>(dst) = make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
+  }
   if (piece == 0) {
     float* sc = reinterpret_cast<float*>(unit + 8192);
     if constexpr (DS) {
@@ -272,7 +291,7 @@ static int launch_q8_1_tiles(const void* x, int64_t m, int64_t k, int64_t stride
   if (m == 0) return GSQ_OK;
   const bool vec = ((uintptr_t)x % 16 == 0) && ((stride * (int64_t)sizeof(T)) % 16 == 0);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(k >> 5), (unsigned)((m + 63) / 64));
+  cfg.gridDim = dim3((unsigned)(k >> 5), LAYOUT == Q8_TILES_H16 ? (unsigned)((m + 255) / 256 * 4) : (unsigned)((m + 63) / 64));
   cfg.blockDim = dim3(256);
   cfg.stream = st;
   cudaLaunchAttribute attr;
@@ -293,8 +312,9 @@ int quantize_tiles_host(const void* x, int x_dtype, int64_t m, int64_t k, int64_
   if (m < 0 || k <= 0 || k % 256 != 0 || (m > 0 && (!x || !out)) || (m + 63) / 64 > 65535) return GSQ_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
 #define GSQ_TILES_CASE(T)                                                                                  \
-  return layout == GSQ_Q8_LAYOUT_D4 ? launch_q8_1_tiles<T, GSQ_Q8_LAYOUT_D4>(x, m, k, stride, out, st) \
-                                    : launch_q8_1_tiles<T, GSQ_Q8_LAYOUT_DS4>(x, m, k, stride, out, st)
+  return layout == Q8_TILES_H16      ? launch_q8_1_tiles<T, Q8_TILES_H16>(x, m, k, stride, out, st)     \
+         : layout == GSQ_Q8_LAYOUT_D4 ? launch_q8_1_tiles<T, GSQ_Q8_LAYOUT_D4>(x, m, k, stride, out, st) \
+                                      : launch_q8_1_tiles<T, GSQ_Q8_LAYOUT_DS4>(x, m, k, stride, out, st)
   switch (x_dtype) {
     case GSQ_F32: GSQ_TILES_CASE(float);
     case GSQ_F16: GSQ_TILES_CASE(__half);

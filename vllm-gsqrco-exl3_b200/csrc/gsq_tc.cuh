@@ -1,0 +1,181 @@
+// PTX wrappers shared by the tcgen05 GEMM kernels (sm_100a): mbarriers with bounded waits, bulk and cp.async copies,
+// tensor-memory allocation and loads, MMA commit, fences, byte permutes and packed fp32 arithmetic.
+#pragma once
+#include "gsq_common.cuh"
+
+namespace gsq {
+namespace tc {
+
+constexpr int MAGIC = 0x4B400000;       // bit pattern of 1.5 * 2^23
+constexpr float MAGIC_F = 12582912.0f;
+
+__device__ __forceinline__ uint32_t saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: gives up after 2^22 polls (or as soon as another thread of the CTA has given up) and raises the flags.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* sticky) {
+  uint32_t done = 0;
+  for (int spin = 0; spin < (1 << 21); ++spin) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    __nanosleep(100);  // a waiting warp should not spend the issue slots of the working ones on polls
+    if ((spin & 63) == 63 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(sticky, 1);
+  return false;
+}
+// The same with the hardware doing the waiting: try_wait suspends the thread until the phase completes or `hint_ns`
+// have passed, so a waiting warp issues an instruction per `hint_ns` instead of polling. Bounded by time: gives up
+// 0.1 s after the first failed try (read from the global timer every 16 tries), or when the CTA's abort flag is up.
+__device__ __forceinline__ bool mbar_wait_hw(uint32_t bar, uint32_t parity, uint32_t hint_ns, volatile int* abort_flag, int* sticky) {
+  uint32_t done = 0;
+  unsigned long long t0 = 0ull;
+  for (int spin = 0; spin < (1 << 24); ++spin) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    if (done) return true;
+    if ((spin & 15) == 0) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      if (spin == 0) t0 = t;
+      if (t - t0 > 100000000ull) break;
+      if (*abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  atomicExch(sticky, 1);
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// D[tmem] = A[smem] * B[smem], int8 x int8 -> int32, K = 32, D overwritten
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, 0, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major operand stored as core matrices of 8 rows x 16 bytes, no swizzle,
+// descriptor version 1: `kstep` = bytes between the core matrices of one row group that are neighbours along K,
+// `rstep` = bytes between consecutive 8-row groups.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t kstep, uint32_t rstep) {
+  uint64_t d = (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(kstep >> 4) << 16;
+  d |= (uint64_t)(rstep >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+// D[tmem] (+)= A[smem] * B[smem], fp16 x fp16 -> fp32, K = 16; `accumulate` = 0 overwrites D
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// Bit pattern of the float 1.5 * 2^23 + c for an integer |c| < 2^22, in one logic instruction (not an integer add,
+// which the compiler may place on the fp32 pipe the scaling needs): the low 23 bits are those of c with bit 22
+// flipped (c + 2^22 never carries out of them), the rest those of the constant. Truth table of
+// f(c, mask, magic) = mask ? c ^ magic : magic, mask = 0x007FFFFF: 0x6A... computed below.
+__device__ __forceinline__ float biased_float(uint32_t c) {
+  uint32_t r;
+  // inputs a = c, b = mask, c = magic; LUT bit index = (a << 2) | (b << 1) | c: out = b ? a ^ c : c
+  //   a b c -> out : 000->0 001->1 010->0 011->1 100->0 101->1 110->1 111->0  => LUT = 0b01101010 = 0x6A
+  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(c), "r"(0x007FFFFFu), "r"((uint32_t)MAGIC));
+  return __uint_as_float(r);
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
+}  // namespace tc
+}  // namespace gsq

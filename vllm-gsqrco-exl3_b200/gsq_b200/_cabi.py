@@ -21,7 +21,7 @@ EXPORTS = (
     "gsq_strerror", "gsq_last_cuda_error", "gsq_abi_version", "gsq_type_block_bytes", "gsq_check_inputs",
     "gsq_device_init", "gsq_quantize_q8_1", "gsq_quantize_q8_1_mmq", "gsq_mul_mat_vec_q8",
     "gsq_debug_block_sums", "gsq_debug_force_direct_loads", "gsq_device_error_flag", "gsq_debug_force_cluster_size",
-    "gsq_debug_swap_descriptor_strides", "gsq_debug_gemm_dump_sums", "gsq_debug_gemm_ksplit", "gsq_debug_gemm_variant", "gsq_q8_layout_for_type", "gsq_mul_mat_scratch_bytes", "gsq_mul_mat_q8", "gsq_iq3s_repack", "gsq_route", "gsq_linear_vec_static", "gsq_linear_vec_static_max_q8_bytes",
+    "gsq_debug_swap_descriptor_strides", "gsq_debug_gemm_dump_sums", "gsq_debug_gemm_ksplit", "gsq_debug_gemm_variant", "gsq_debug_gemm_wait_hint", "gsq_q8_layout_for_type", "gsq_mul_mat_scratch_bytes", "gsq_mul_mat_q8", "gsq_iq3s_repack", "gsq_route", "gsq_linear_vec_static", "gsq_linear_vec_static_max_q8_bytes",
     "gsq_debug_mmv_mode", "gsq_debug_mmv_min_rows", "gsq_debug_mmv_cluster_size", "gsq_mul_mat_vec_max_rows",
     "gsq_debug_mmv_profile", "gsq_debug_mmv_max_rows", "gsq_debug_mmv_pdl", "gsq_debug_mmv_prefetch_first", "gsq_debug_mmv_chunking", "gsq_debug_mmv_trace",
     "gsq_linear", "gsq_linear_scratch_bytes", "gsq_debug_gemm_profile", "gsq_q6k_repack", "gsq_allreduce_sum", "gsq_allreduce_error_flag",
@@ -78,6 +78,8 @@ def _load() -> C.CDLL:
     lib.gsq_debug_swap_descriptor_strides.restype = ci
     lib.gsq_debug_swap_descriptor_strides.argtypes = [ci]
     lib.gsq_debug_gemm_variant.restype = ci
+    lib.gsq_debug_gemm_wait_hint.restype = ci
+    lib.gsq_debug_gemm_wait_hint.argtypes = [ci]
     lib.gsq_debug_gemm_variant.argtypes = [ci]
     lib.gsq_debug_gemm_ksplit.restype = ci
     lib.gsq_debug_gemm_ksplit.argtypes = [ci]
