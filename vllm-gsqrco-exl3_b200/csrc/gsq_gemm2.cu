@@ -10,14 +10,14 @@
 // A CTA owns a tile of 128 weight rows x 256 tokens and walks K one superblock (256 values = 8 slices) at a time:
 //   * 3 producer warps fetch the raw superblocks of the 128 rows (cp.async into a 3-deep ring) and decode them ONCE
 //     into an int8 tile in shared memory, in the K-major core-matrix layout the MMA descriptors describe, plus the
-//     per-row slice scales; the tile then serves all 256 tokens (4 sub-tiles of 64);
-//   * one thread streams the activation sub-tiles -- already in that same layout in global memory, written so by
-//     quantize_q8_1_tiles_kernel (gsq_quantize.cu) -- with one bulk copy per unit into an 8-deep ring, and issues the
-//     MMAs: a unit is 4 slices x 64 tokens, i.e. 4 instructions of 128 x 64 x 32 into one half of tensor memory
-//     (256 columns), the other half being drained meanwhile;
-//   * 16 consumer warps (4 per tensor-memory lane quarter, 16 columns each) read the int32 sums with tcgen05.ld,
-//     scale them (2 integer adds + 2 packed fp32 FMAs per pair of elements) and accumulate 64 fp32 values per thread
-//     (row = lane of tensor memory, 4 sub-tiles x 16 tokens) in registers over the whole of K.
+//     per-row slice scales;
+//   * one thread streams the activation units (one slice x 256 tokens, already in that same layout in global memory,
+//     written so by quantize_q8_1_tiles_kernel, gsq_quantize.cu) with one bulk copy per unit into an 8-deep ring, and
+//     issues one MMA of 128 x 256 x 32 per unit into one half of tensor memory (256 columns), the other half being
+//     drained meanwhile (N = 256: the weight slice is read from shared memory once per 256 tokens);
+//   * 16 consumer warps (4 per tensor-memory lane quarter, 64 columns each) read the int32 sums with tcgen05.ld,
+//     scale them (one logic instruction + 2 packed fp32 FMAs per pair of elements) and accumulate 64 fp32 values per
+//     thread (row = lane of tensor memory) in registers over the whole of K.
 // All hand-offs are mbarriers; every wait is bounded and raises a CTA-wide abort flag (and the sticky device flag
 // read by gsq_device_error_flag) instead of hanging. Register budget: setmaxnreg moves registers from the producer
 // warpgroup to the four consumer warpgroups.
@@ -32,21 +32,21 @@ enum { G2_IQ3S = 0, G2_Q4K = 1, G2_IQ4XS = 2 };
 namespace g2 {
 
 constexpr int TR = 128;                 // weight rows per tile (MMA M)
-constexpr int NT = 64;                  // tokens per sub-tile (MMA N)
-constexpr int NSUB = 4;                 // sub-tiles per token block
+constexpr int NT = 256;                 // tokens per tile (MMA N)
 constexpr int PROD_WARPS = 3;
 constexpr int PROD_THREADS = PROD_WARPS * 32;
 constexpr int CONS_WARPS = 16;
 constexpr int THREADS = 128 + CONS_WARPS * 32;   // warps 0-2 producers, warp 3 MMA + bulk copies, warps 4-19 consumers
 constexpr int SL_A = 4096;              // bytes of one slice of the decoded weight tile (128 rows x 32)
-constexpr int SL_B = 2048;              // bytes of one slice of an activation sub-tile (64 tokens x 32)
+constexpr int SL_B = 8192;              // bytes of the quants of one activation unit (256 tokens x 32)
 constexpr int A_STAGES = 2;
 constexpr int B_SLOTS = 8;
+constexpr int B_AHEAD = 6;              // units the bulk copies run ahead of the MMAs
 constexpr int RAW_STAGES = 3;
 constexpr int TMEM_COLS = 512;
 
-// bytes of one unit (4 slices of a 64-token sub-tile) of the activation tiles: quants, d (+ sum for Q4_K)
-__host__ __device__ constexpr int unit_bytes(bool ds) { return 4 * SL_B + 4 * NT * 4 * (ds ? 2 : 1); }
+// bytes of one unit (one slice of a 256-token block) of the activation tiles: quants, d (+ sum for Q4_K)
+__host__ __device__ constexpr int unit_bytes(bool ds) { return SL_B + NT * 4 * (ds ? 2 : 1); }
 __host__ __device__ constexpr int raw_bytes(int kind) { return kind == G2_IQ3S ? 8 * 1760 : kind == G2_Q4K ? 128 * 144 : 128 * 136; }
 __host__ __device__ constexpr int grid_bytes(int kind) { return kind == G2_IQ3S ? 512 * 64 : 0; }  // (g, -g) x 8 replicas
 __host__ __device__ constexpr int scale_planes(int kind) { return kind == G2_Q4K ? 2 : 1; }
@@ -56,7 +56,7 @@ struct Args {
   int64_t row_bytes;
   int nrows;
   int k;
-  const uint8_t* xt;   // activation tiles: [token tile of 64][superblock][2 units][unit_bytes]
+  const uint8_t* xt;   // activation units: [token block of 256][superblock][slice][unit_bytes]
   int m;
   void* y;
   int y_dtype;
@@ -85,7 +85,7 @@ using namespace tc;
 // K-major int8 operand: the two core matrices of a row group (K bytes 0-15, 16-31) 128 bytes apart, consecutive 8-row
 // groups 256 bytes apart
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) { return tc::smem_desc(addr, 128, 256); }
-// Instruction descriptor: D = s32, A = B = s8, both K-major, N = 64, M = 128, dense.
+// Instruction descriptor: D = s32, A = B = s8, both K-major, N = 256, M = 128, dense.
 __host__ __device__ constexpr uint32_t idesc() {
   return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(TR >> 4) << 24);
 }
@@ -276,6 +276,14 @@ __device__ __forceinline__ void dump8(const Args& g, const uint32_t (&c)[8], int
   }
 }
 
+// ring cursor: position and phase parity of an n-deep ring of mbarriers 8 bytes apart
+struct Ring {
+  uint32_t i, ph;
+  __device__ __forceinline__ void next(uint32_t n) {
+    if (++i == n) { i = 0; ph ^= 1u; }
+  }
+};
+
 template <int KIND, int MODE>
 __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
   constexpr bool DUMP = MODE == 1, PROF = MODE == 2;
@@ -286,30 +294,28 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
   constexpr bool DS = KIND == G2_Q4K;
   constexpr int UB = unit_bytes(DS);
   constexpr int RAWB = (raw_bytes(KIND) + 127) / 128 * 128;
+  constexpr int STAGE_A = 8 * SL_A, STAGE_SA = scale_planes(KIND) * 8 * TR * 4;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // barriers (8 bytes each): a_full[2] a_empty[2] b_full[8] b_empty[8] d_full[2] d_empty[2]
   const uint32_t bar0 = saddr(smem + S::BAR);
-  auto a_full = [&](int i) { return bar0 + 8 * i; };
-  auto a_empty = [&](int i) { return bar0 + 8 * (2 + i); };
-  auto b_full = [&](int i) { return bar0 + 8 * (4 + i); };
-  auto b_empty = [&](int i) { return bar0 + 8 * (12 + i); };
-  auto d_full = [&](int i) { return bar0 + 8 * (20 + i); };
-  auto d_empty = [&](int i) { return bar0 + 8 * (22 + i); };
+  const uint32_t a_full = bar0, a_empty = bar0 + 16, b_full = bar0 + 32, b_empty = b_full + 8 * B_SLOTS,
+                 d_full = b_empty + 8 * B_SLOTS, d_empty = d_full + 16;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::BAR + 256);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + S::BAR + 260);
+  auto wait = [&](uint32_t bar, uint32_t parity) -> bool { return mbar_wait(bar, parity, abort_flag, &g_error); };
 
   if (tid == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 2; ++i) {
-      mbar_init(a_full(i), PROD_THREADS);
-      mbar_init(a_empty(i), CONS_WARPS);
-      mbar_init(d_full(i), 1);
-      mbar_init(d_empty(i), CONS_WARPS);
+      mbar_init(a_full + 8 * i, PROD_THREADS);
+      mbar_init(a_empty + 8 * i, CONS_WARPS);
+      mbar_init(d_full + 8 * i, 1);
+      mbar_init(d_empty + 8 * i, CONS_WARPS);
     }
     for (int i = 0; i < B_SLOTS; ++i) {
-      mbar_init(b_full(i), 1);
-      mbar_init(b_empty(i), CONS_WARPS);
+      mbar_init(b_full + 8 * i, 1);
+      mbar_init(b_empty + 8 * i, CONS_WARPS);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -332,7 +338,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
   // items of this CTA: row tiles fastest, so that the CTAs running at one time share a token block's activations in L2
   auto item_rt = [&](int item) { return item % g.n_row_tiles; };
   auto item_tb = [&](int item) { return item / g.n_row_tiles; };
-  auto item_nsub = [&](int item) { return min(NSUB, (g.m - item_tb(item) * (NSUB * NT) + NT - 1) / NT); };
 
   if (warp < PROD_WARPS) {
     // ------------------------------------------------------------------------------------ producers
@@ -350,6 +355,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
     fetch_next(0);
     fetch_next(1);
     uint32_t n = 0;
+    Ring ra = {0u, 0u};
     bool alive = true;
     // (after a wait has given up the loop still runs to its end, without work: every producer thread passes the
     // same number of named barriers)
@@ -359,25 +365,26 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
         cp_async_wait<1>();                                  // this thread's pieces of stream position n have landed
         asm volatile("bar.sync 1, %0;" ::"n"(PROD_THREADS) : "memory");   // everyone's have; everyone is done with n - 1
         fetch_next((int)n + 2);
-        const uint32_t st = n & 1u;
         const unsigned long long p0 = tick();
-        alive = alive && mbar_wait(a_empty(st), ((n >> 1) & 1u) ^ 1u, abort_flag, &g_error);
+        alive = alive && wait(a_empty + 8 * ra.i, ra.ph ^ 1u);
         const unsigned long long p1 = tick();
         pw[0] += p1 - p0;
-        if (!alive) continue;
-        const uint8_t* raw = smem + S::RAW + (n % RAW_STAGES) * RAWB;
-        uint8_t* a = smem + S::A + st * (8 * SL_A);
-        float* sa = reinterpret_cast<float*>(smem + S::SA + st * (scale_planes(KIND) * 8 * TR * 4));
-        if (KIND == G2_IQ3S) {
-          decode_iq3s(raw, a, sa, smem + S::GRID, g.nrows - rt * TR, warp, lane);
-        } else if (KIND == G2_Q4K) {
-          decode_q4k(raw, a, sa, sa + 8 * TR, ptid);
-        } else {
-          decode_iq4xs(raw, a, sa, ptid);
+        if (alive) {
+          const uint8_t* raw = smem + S::RAW + (n % RAW_STAGES) * RAWB;
+          uint8_t* a = smem + S::A + ra.i * STAGE_A;
+          float* sa = reinterpret_cast<float*>(smem + S::SA + ra.i * STAGE_SA);
+          if (KIND == G2_IQ3S) {
+            decode_iq3s(raw, a, sa, smem + S::GRID, g.nrows - rt * TR, warp, lane);
+          } else if (KIND == G2_Q4K) {
+            decode_q4k(raw, a, sa, sa + 8 * TR, ptid);
+          } else {
+            decode_iq4xs(raw, a, sa, ptid);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> tensor-core reads
+          mbar_arrive(a_full + 8 * ra.i);
+          pw[1] += tick() - p1;
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> tensor-core reads
-        mbar_arrive(a_full(st));
-        pw[1] += tick() - p1;
+        ra.next(A_STAGES);
       }
     }
     if (PROF && tid == 0) {
@@ -389,59 +396,69 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
     // ------------------------------------------------------------------------------------ bulk copies + MMA issue
     asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
     if (lane == 0) {
+      // This one thread is on every unit's critical path: everything it does per unit is kept to a few dozen
+      // instructions (no divisions, descriptors and source addresses by increments).
       const uint32_t id = idesc();
-      // load cursor over the stream of units (item, superblock, unit), 6 units ahead of the MMA cursor
-      int l_item = blockIdx.x, l_sb = 0, l_u = 0;
-      uint32_t l_g = 0;
+      const uint64_t desc_hi = smem_desc(0u) & 0xFFFFFFFF00000000ull;
+      const uint32_t a_lo0 = (uint32_t)smem_desc(saddr(smem + S::A)), b_lo0 = (uint32_t)smem_desc(saddr(smem + S::B));
+      auto desc = [&](uint32_t lo) { return desc_hi | (uint64_t)lo; };
+      const uint32_t b_smem0 = saddr(smem + S::B);
+      // load cursor over the stream of units (item, superblock, slice), B_AHEAD ahead of the MMAs; the units of a
+      // token block are contiguous in global memory
+      int l_item = blockIdx.x, l_u = 0;
+      const int units_item = 8 * nsb;
+      const uint8_t* l_base = nullptr;
+      auto load_item = [&]() {
+        if (l_item < n_items) l_base = g.xt + (int64_t)item_tb(l_item) * units_item * UB;
+      };
+      load_item();
+      Ring rl = {0u, 0u};
+      uint32_t n_loaded = 0;
       bool alive = true;
       auto load_next = [&]() {
         if (l_item >= n_items || !alive) return;
-        const uint32_t slot = l_g & (B_SLOTS - 1);
-        alive = mbar_wait(b_empty(slot), ((l_g >> 3) & 1u) ^ 1u, abort_flag, &g_error);
+        alive = wait(b_empty + 8 * rl.i, rl.ph ^ 1u);
         if (!alive) return;
-        const int tt = item_tb(l_item) * NSUB + (l_u >> 1);
-        const uint8_t* src = g.xt + (((int64_t)tt * nsb + l_sb) * 2 + (l_u & 1)) * UB;
-        mbar_expect_tx(b_full(slot), UB);
-        bulk_g2s(saddr(smem + S::B + slot * UB), src, UB, b_full(slot));
-        ++l_g;
-        if (++l_u == 2 * item_nsub(l_item)) {
+        mbar_expect_tx(b_full + 8 * rl.i, UB);
+        bulk_g2s(b_smem0 + rl.i * UB, l_base + (int64_t)l_u * UB, UB, b_full + 8 * rl.i);
+        rl.next(B_SLOTS);
+        ++n_loaded;
+        if (++l_u == units_item) {
           l_u = 0;
-          if (++l_sb == nsb) { l_sb = 0; l_item += gridDim.x; }
+          l_item += gridDim.x;
+          load_item();
         }
       };
-      for (int i = 0; i < 6; ++i) load_next();
-      uint32_t n = 0, gu = 0;
+      for (int i = 0; i < B_AHEAD; ++i) load_next();
+      Ring ra = {0u, 0u}, rb = {0u, 0u}, rd = {0u, 0u};
+      uint32_t n_used = 0;
       for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
-        const int nu = 2 * item_nsub(item);
-        for (int sb = 0; sb < nsb && alive; ++sb, ++n) {
-          const uint32_t st = n & 1u;
+        for (int sb = 0; sb < nsb && alive; ++sb) {
           const unsigned long long m0 = tick();
-          alive = mbar_wait(a_full(st), (n >> 1) & 1u, abort_flag, &g_error);
+          alive = wait(a_full + 8 * ra.i, ra.ph);
           pw[0] += tick() - m0;
           if (!alive) break;
-          const uint32_t a_addr = saddr(smem + S::A + st * (8 * SL_A));
-          for (int u = 0; u < nu; ++u, ++gu) {
-            const uint32_t slot = gu & (B_SLOTS - 1), half = gu & 1u;
-            // the consumers have drained this half of tensor memory (unit gu - 2) ...
+          const uint32_t a_lo = a_lo0 + ra.i * (STAGE_A >> 4);
+#pragma unroll 1
+          for (int sl = 0; sl < 8; ++sl) {
+            // the consumers have drained this half of tensor memory (two units ago)
             const unsigned long long m1 = tick();
-            alive = mbar_wait(d_empty(half), ((gu >> 1) & 1u) ^ 1u, abort_flag, &g_error);
-            const unsigned long long m2 = tick();
-            pw[1] += m2 - m1;
+            alive = wait(d_empty + 8 * rd.i, rd.ph ^ 1u);
+            pw[1] += tick() - m1;
             if (!alive) break;
-            load_next();   // ... and with it released that unit's activation slot: the copy for unit gu + 6 goes there
             const unsigned long long m3 = tick();
-            alive = alive && mbar_wait(b_full(slot), (gu >> 3) & 1u, abort_flag, &g_error);
+            alive = wait(b_full + 8 * rb.i, rb.ph);
             pw[2] += tick() - m3;
             if (!alive) break;
             tc_fence_after();
-            const uint32_t b_addr = saddr(smem + S::B + slot * UB);
-            const int sl0 = 4 * (u & 1);
-#pragma unroll
-            for (int sl = 0; sl < 4; ++sl) {
-              mma_i8(tmem_base + half * 256 + sl * NT, smem_desc(a_addr + (sl0 + sl) * SL_A), smem_desc(b_addr + sl * SL_B), id);
-            }
-            mma_commit(d_full(half));
+            mma_i8(tmem_base + rd.i * 256, desc(a_lo + sl * (SL_A >> 4)), desc(b_lo0 + rb.i * (UB >> 4)), id);
+            mma_commit(d_full + 8 * rd.i);
+            rb.next(B_SLOTS);
+            rd.next(2);
+            ++n_used;
+            load_next();   // after the MMA is on its way: the copy for B_AHEAD units further on
           }
+          ra.next(A_STAGES);
         }
       }
       if (PROF) {
@@ -451,7 +468,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
       }
       if (!alive) {
         // a wait gave up: let the copies already issued land (bounded) before the CTA's shared memory goes away
-        for (uint32_t q = gu; q < l_g; ++q) mbar_wait(b_full(q & (B_SLOTS - 1)), (q >> 3) & 1u, abort_flag, &g_error);
+        for (; n_used < n_loaded; ++n_used) {
+          wait(b_full + 8 * rb.i, rb.ph);
+          rb.next(B_SLOTS);
+        }
       }
     }
   } else {
@@ -459,91 +479,73 @@ __global__ void __launch_bounds__(THREADS, 1) gemm2_kernel(const Args g) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     const int cw = warp - 4, q4 = warp & 3, cg = cw >> 2;   // tensor-memory lane quarter = warp id mod 4
     const int r_in = 32 * q4 + lane;
-    const uint32_t t_warp = tmem_base + ((uint32_t)(32 * q4) << 16) + (uint32_t)(16 * cg);
-    uint32_t n = 0, gu = 0;
+    const uint32_t t_warp = tmem_base + ((uint32_t)(32 * q4) << 16) + (uint32_t)(64 * cg);
+    Ring ra = {0u, 0u}, rb = {0u, 0u}, rd = {0u, 0u};
     bool alive = true;
     for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
-      const int rt = item_rt(item), tok0 = item_tb(item) * (NSUB * NT), nsub = item_nsub(item);
-      float2 acc[NSUB][8];
+      const int rt = item_rt(item), tok0 = item_tb(item) * NT + 64 * cg;
+      float2 acc[32];   // this thread's row x 64 tokens
 #pragma unroll
-      for (int j = 0; j < NSUB; ++j) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[j][i] = make_float2(0.0f, 0.0f);
-      }
-      for (int sb = 0; sb < nsb && alive; ++sb, ++n) {
-        const uint32_t st = n & 1u;
+      for (int i = 0; i < 32; ++i) acc[i] = make_float2(0.0f, 0.0f);
+      for (int sb = 0; sb < nsb && alive; ++sb) {
         const unsigned long long c0t = tick();
-        alive = mbar_wait(a_full(st), (n >> 1) & 1u, abort_flag, &g_error);   // the producers' scale planes are visible
+        alive = wait(a_full + 8 * ra.i, ra.ph);   // the producers' scale planes are visible
         pw[0] += tick() - c0t;
         if (!alive) break;
-        const float* sa = reinterpret_cast<const float*>(smem + S::SA + st * (scale_planes(KIND) * 8 * TR * 4));
-        // One copy of the unit code per sub-tile (the accumulators of a sub-tile are fixed registers); the two units
-        // and the four slices of a unit are real loops, so that the consumers' code stays small enough for the
-        // instruction caches.
+        const float* sap = reinterpret_cast<const float*>(smem + S::SA + ra.i * STAGE_SA) + r_in;
+#pragma unroll 1
+        for (int sl = 0; sl < 8; ++sl) {
+          const unsigned long long c1t = tick();
+          alive = alive && wait(b_full + 8 * rb.i, rb.ph);   // the unit's scales are visible
+          const unsigned long long c2t = tick();
+          alive = alive && wait(d_full + 8 * rd.i, rd.ph);
+          const unsigned long long c3t = tick();
+          pw[1] += c2t - c1t;
+          pw[2] += c3t - c2t;
+          if (alive) {
+            tc_fence_after();
+            const float* bd = reinterpret_cast<const float*>(smem + S::B + rb.i * UB + SL_B) + 64 * cg;
+            const float* bs = bd + NT;
+            const float da = sap[sl * TR], dam = DS ? sap[(8 + sl) * TR] : 0.0f;
+            const uint32_t t_unit = t_warp + rd.i * 256;
+            const int slice = sb * 8 + sl;
+            // chunks of 8 columns, the next chunk's load in flight while one is scaled
+            uint32_t c0[8], c1[8];
+            tmem_ld8(t_unit, c0);
 #pragma unroll
-        for (int j = 0; j < NSUB; ++j) {
-          if (j < nsub) {
-#pragma unroll 1
-            for (int h = 0; h < 2; ++h) {
-              const uint32_t slot = gu & (B_SLOTS - 1);
-              const unsigned long long c1t = tick();
-              alive = alive && mbar_wait(b_full(slot), (gu >> 3) & 1u, abort_flag, &g_error);   // the unit's scales are visible
-              const unsigned long long c2t = tick();
-              alive = alive && mbar_wait(d_full(h), (gu >> 1) & 1u, abort_flag, &g_error);
-              const unsigned long long c3t = tick();
-              pw[1] += c2t - c1t;
-              pw[2] += c3t - c2t;
-              if (alive) {
-                tc_fence_after();
-                const float* bsc = reinterpret_cast<const float*>(smem + S::B + slot * UB + 4 * SL_B) + 16 * cg;
-                const float* sap = sa + (4 * h) * TR + r_in;
-                const uint32_t t_unit = t_warp + h * 256;
-                // per slice two chunks of 8 columns, the next chunk's load in flight while one is scaled
-                uint32_t c0[8], c1[8];
-                tmem_ld8(t_unit, c0);
-#pragma unroll 1
-                for (int sl = 0; sl < 4; ++sl) {
-                  const float da = sap[sl * TR], dam = DS ? sap[(8 + sl) * TR] : 0.0f;
-                  const float* bd = bsc + sl * NT;
-                  const float* bs = bsc + (4 + sl) * NT;
-                  tmem_ld_wait();
-                  tmem_ld8(t_unit + sl * NT + 8, c1);
-                  if (DUMP) dump8(g, c0, rt * TR + r_in, tok0 + j * NT + 16 * cg, sb * 8 + 4 * h + sl);
-                  scale8<DS>(c0, da, dam, bd, bs, &acc[j][0]);
-                  tmem_ld_wait();
-                  if (sl < 3) tmem_ld8(t_unit + (sl + 1) * NT, c0);
-                  if (DUMP) dump8(g, c1, rt * TR + r_in, tok0 + j * NT + 16 * cg + 8, sb * 8 + 4 * h + sl);
-                  scale8<DS>(c1, da, dam, bd + 8, bs + 8, &acc[j][4]);
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                  mbar_arrive(b_empty(slot));
-                  mbar_arrive(d_empty(h));
-                }
-                pw[3] += tick() - c3t;
-              }
-              ++gu;
+            for (int ch = 0; ch < 8; ch += 2) {
+              tmem_ld_wait();
+              tmem_ld8(t_unit + 8 * (ch + 1), c1);
+              if (DUMP) dump8(g, c0, rt * TR + r_in, tok0 + 8 * ch, slice);
+              scale8<DS>(c0, da, dam, bd + 8 * ch, bs + 8 * ch, &acc[4 * ch]);
+              tmem_ld_wait();
+              if (ch < 6) tmem_ld8(t_unit + 8 * (ch + 2), c0);
+              if (DUMP) dump8(g, c1, rt * TR + r_in, tok0 + 8 * (ch + 1), slice);
+              scale8<DS>(c1, da, dam, bd + 8 * (ch + 1), bs + 8 * (ch + 1), &acc[4 * (ch + 1)]);
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive(b_empty + 8 * rb.i);
+              mbar_arrive(d_empty + 8 * rd.i);
+            }
+            pw[3] += tick() - c3t;
           }
+          rb.next(B_SLOTS);
+          rd.next(2);
         }
         __syncwarp();
-        if (lane == 0 && alive) mbar_arrive(a_empty(st));   // the stage's scale planes (and, the MMAs done, its tile) are free
+        if (lane == 0 && alive) mbar_arrive(a_empty + 8 * ra.i);   // the stage's scale planes (and, the MMAs done, its tile) are free
+        ra.next(A_STAGES);
       }
-      // results of the item: thread = weight row, 16 tokens per sub-tile
+      // results of the item: thread = weight row, 64 tokens
       const int row = rt * TR + r_in;
       if (alive && row < g.nrows) {
 #pragma unroll
-        for (int j = 0; j < NSUB; ++j) {
-          if (j < nsub) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float v0 = acc[j][i].x, v1 = acc[j][i].y;
-              const int tok = tok0 + j * NT + 16 * cg + 2 * i;
-              if (tok < g.m) store_out_dyn(g.y, g.y_dtype, (int64_t)tok * g.ldy + row, v0);
-              if (tok + 1 < g.m) store_out_dyn(g.y, g.y_dtype, (int64_t)(tok + 1) * g.ldy + row, v1);
-            }
-          }
+        for (int i = 0; i < 32; ++i) {
+          const int tok = tok0 + 2 * i;
+          if (tok < g.m) store_out_dyn(g.y, g.y_dtype, (int64_t)tok * g.ldy + row, acc[i].x);
+          if (tok + 1 < g.m) store_out_dyn(g.y, g.y_dtype, (int64_t)(tok + 1) * g.ldy + row, acc[i].y);
         }
       }
     }
@@ -602,10 +604,10 @@ int gemm2_error_flag(int* flag) {
   return GSQ_OK;
 }
 
-// bytes of the activation tiles of m tokens x k columns (tokens padded to whole sub-tiles of 64)
+// bytes of the activation units of m tokens x k columns (tokens padded to whole blocks of 256)
 size_t gemm2_tile_bytes(int64_t m, int64_t k, int ggml_type) {
-  const int64_t tt = (m + g2::NT - 1) / g2::NT;
-  return (size_t)(tt * (k / 256) * 2 * g2::unit_bytes(ggml_type == GSQ_TYPE_Q4_K));
+  const int64_t tb = (m + g2::NT - 1) / g2::NT;
+  return (size_t)(tb * (k / 256) * 8 * g2::unit_bytes(ggml_type == GSQ_TYPE_Q4_K));
 }
 
 bool gemm2_applies(int ggml_type, int packed, int64_t rows) {
@@ -635,7 +637,7 @@ int gemm2_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
   g.y_dtype = y_dtype;
   g.ldy = y_row_stride;
   g.n_row_tiles = (int)((rows + g2::TR - 1) / g2::TR);
-  g.n_tok_blocks = (int)((m + g2::NSUB * g2::NT - 1) / (g2::NSUB * g2::NT));
+  g.n_tok_blocks = (int)((m + g2::NT - 1) / g2::NT);
   g.dump = gemm_dump_pointer();
   g.prof = g_prof;
   cudaStream_t st = (cudaStream_t)stream;

@@ -165,20 +165,18 @@ __global__ void __launch_bounds__(256) quantize_q8_1_mmq_kernel(const T* __restr
   }
 }
 
-// Activation tiles of the prefill GEMM (gsq_gemm2.cu): the same quantisation as quantize_q8_1_mmq_kernel (32-value
-// blocks, d = 1 / (127 / amax), D4 or DS4 scales), written in the shared-memory layout of the tensor-core operand so
-// that one bulk copy brings a unit into place. Tiles of 64 tokens; per tile and superblock two units of 4 slices:
-//   unit = [4 slices][8 token groups][2 K chunks of 16][8 tokens][16 bytes] quants   (8192 bytes)
-//          [4 slices][64 tokens] float d                                              (1024 bytes)
-//          [4 slices][64 tokens] float(half(sum x))   (DS4 only)                      (1024 bytes)
-// and, for the kernel whose operands are fp16 (gsq_gemm3.cu; LAYOUT = Q8_TILES_H16), the same quants as fp16 numbers
-// in units of one slice x 256 tokens, [token block of 256][superblock][slice][unit]:
-//   unit = [32 token groups][4 K chunks of 8][8 tokens][8 fp16] quants                 (16384 bytes)
-//          [256 tokens] float d                                                       (1024 bytes)
-// (the grid then covers whole blocks of 256 tokens).
-// Tokens past m (up to the end of the last tile) are written as zeros. One block = 64 tokens x one 32-value slice:
-// warp w holds token group w, lane = (token % 8) * 4 + 8-value piece, so a warp writes two whole 128-byte core
-// matrices.
+// Activation units of the prefill GEMMs (gsq_gemm2.cu, gsq_gemm3.cu): the same quantisation as
+// quantize_q8_1_mmq_kernel (32-value blocks, d = 1 / (127 / amax), D4 or DS4 scales), written in the shared-memory layout
+// of the tensor-core operand so that one bulk copy brings a unit into place. A unit is one 32-value slice of a block
+// of 256 tokens, [token block][superblock][slice][unit]:
+//   int8 operands:  [32 token groups][2 K chunks of 16][8 tokens][16 bytes] quants       (8192 bytes)
+//                   [256 tokens] float d                                                 (1024 bytes)
+//                   [256 tokens] float(half(sum x))   (DS4 only)                         (1024 bytes)
+//   fp16 operands (LAYOUT = Q8_TILES_H16): the same quants as fp16 numbers
+//                   [32 token groups][4 K chunks of 8][8 tokens][8 fp16] quants          (16384 bytes)
+//                   [256 tokens] float d                                                 (1024 bytes)
+// Tokens past m (up to the end of the last block) are written as zeros. One CUDA block = 64 tokens x one slice:
+// warp w holds token group w of the 64, lane = (token % 8) * 4 + 8-value piece, so a warp writes whole core matrices.
 template <typename T, bool VEC, int LAYOUT>
 __global__ void __launch_bounds__(256) quantize_q8_1_tiles_kernel(const T* __restrict__ x, uint8_t* __restrict__ out,
                                                                  int64_t m, int64_t k, int64_t stride) {
@@ -219,11 +217,11 @@ __global__ void __launch_bounds__(256) quantize_q8_1_tiles_kernel(const T* __res
 #pragma unroll
   for (int e = 0; e < 8; ++e) q[e] = live ? roundf(v[e] * d_inv) : 0.0f;
   float d = live ? rcp_approx(d_inv) : 0.0f;
-  const int sb = slice >> 3, s = slice & 7, sl = s & 3;
+  const int sb = slice >> 3, s = slice & 7;
+  const int rb = (int)(tt & 3) * 64 + r;   // token within its block of 256
+  uint8_t* unit = out + (((tt >> 2) * (k >> 8) + sb) * 8 + s) * UB;
   if constexpr (H16) {
     // the lane's 8 values are one 16-byte row of a core matrix (integers up to 127 in magnitude: exact in fp16)
-    const int rb = (int)(tt & 3) * 64 + r;   // token within its block of 256
-    uint8_t* unit = out + (((tt >> 2) * (k >> 8) + sb) * 8 + s) * UB;
     uint8_t* dst = unit + (rb >> 3) * 512 + piece * 128 + (rb & 7) * 16;
     __half2 h[4];
 #pragma unroll
@@ -232,19 +230,16 @@ __global__ void __launch_bounds__(256) quantize_q8_1_tiles_kernel(const T* __res
     if (piece == 0) reinterpret_cast<float*>(unit + 16384)[rb] = d;
     return;
   }
-  uint8_t* unit = out + ((tt * (k >> 8) + sb) * 2 + (s >> 2)) * UB;
-  {
-    uint8_t* dst = unit + sl * 2048 + (r >> 3) * 256 + (piece >> 1) * 128 + (r & 7) * 16 + (piece & 1) * 8;
-    *reinterpret_cast<uint2*>(dst) = make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
-  }
+  uint8_t* dst = unit + (rb >> 3) * 256 + (piece >> 1) * 128 + (rb & 7) * 16 + (piece & 1) * 8;
+  *reinterpret_cast<uint2*>(dst) = make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
   if (piece == 0) {
     float* sc = reinterpret_cast<float*>(unit + 8192);
     if constexpr (DS) {
       const float2 ds = __half22float2(__floats2half2_rn(d, sum));   // the reference keeps half2(d, sum)
-      sc[sl * 64 + r] = live ? ds.x : 0.0f;
-      sc[(4 + sl) * 64 + r] = live ? ds.y : 0.0f;
+      sc[rb] = live ? ds.x : 0.0f;
+      sc[256 + rb] = live ? ds.y : 0.0f;
     } else {
-      sc[sl * 64 + r] = d;
+      sc[rb] = d;
     }
   }
 }
@@ -291,7 +286,7 @@ static int launch_q8_1_tiles(const void* x, int64_t m, int64_t k, int64_t stride
   if (m == 0) return GSQ_OK;
   const bool vec = ((uintptr_t)x % 16 == 0) && ((stride * (int64_t)sizeof(T)) % 16 == 0);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(k >> 5), LAYOUT == Q8_TILES_H16 ? (unsigned)((m + 255) / 256 * 4) : (unsigned)((m + 63) / 64));
+  cfg.gridDim = dim3((unsigned)(k >> 5), (unsigned)((m + 255) / 256 * 4));   // whole blocks of 256 tokens
   cfg.blockDim = dim3(256);
   cfg.stream = st;
   cudaLaunchAttribute attr;
@@ -309,7 +304,7 @@ static int launch_q8_1_tiles(const void* x, int64_t m, int64_t k, int64_t stride
 
 // x [m, k] -> activation tiles for the prefill GEMM (see quantize_q8_1_tiles_kernel); k % 256 == 0.
 int quantize_tiles_host(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride, int layout, void* out, void* stream) {
-  if (m < 0 || k <= 0 || k % 256 != 0 || (m > 0 && (!x || !out)) || (m + 63) / 64 > 65535) return GSQ_ERR_UNSUPPORTED;
+  if (m < 0 || k <= 0 || k % 256 != 0 || (m > 0 && (!x || !out)) || (m + 255) / 256 * 4 > 65535) return GSQ_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
 #define GSQ_TILES_CASE(T)                                                                                  \
   return layout == Q8_TILES_H16      ? launch_q8_1_tiles<T, Q8_TILES_H16>(x, m, k, stride, out, st)     \
