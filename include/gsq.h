@@ -27,6 +27,13 @@ extern "C" {
 #define GSQ_TYPE_Q6_K 14
 #define GSQ_TYPE_IQ3_S 21
 #define GSQ_TYPE_IQ4_XS 23
+/* the low-bit types a model file mixes with those four: served in GGUF order by the dp4a kernel, 8 rows per launch */
+#define GSQ_TYPE_Q2_K 10
+#define GSQ_TYPE_IQ2_XXS 16
+#define GSQ_TYPE_IQ2_XS 17
+#define GSQ_TYPE_IQ3_XXS 18
+#define GSQ_TYPE_IQ2_S 22
+#define GSQ_TYPE_IQ1_M 29
 
 /* element types of X / Y */
 #define GSQ_F32 0

@@ -15,6 +15,9 @@ Writes
                         (tests/fixtures/dequant/*.npz): sha256 of the raw bytes, of the stored gguf-py
                         output, and whether oracle.blocks.dequantize reproduced it bit for bit when
                         this script ran
+  dequant_blocks_f1.npz, fixture_check_f1.json
+                        the same two for the six low-bit types of the model file (Q2_K, IQ2_XXS, IQ2_XS,
+                        IQ2_S, IQ3_XXS, IQ1_M) and oracle.blocks_f1
   iq3_ref_packed.npz    a seeded IQ3_S weight (64 rows x 1024 columns) and the reference's own load-time
                         repack of it (plugin/vllm_gguf_plugin/quantization/iq3_pack.py:134-138), the
                         input its packed kernels read; lets a GPU box run those kernels without the
@@ -85,6 +88,42 @@ def dequant_blocks():
     print("dequant_blocks.npz written; gguf", getattr(gguf, "__version__", "?"))
 
 
+def dequant_blocks_f1():
+    import gguf
+    from gguf import quants
+
+    from gsq_b200 import synth
+
+    out = {}
+    for name, t in synth.LOW_BIT_TYPE_IDS.items():
+        raw = synth.make_weight(t, 4, 512, 4242 + t)
+        out[f"{name}_raw"] = raw
+        out[f"{name}_ref"] = quants.dequantize(raw, gguf.GGMLQuantizationType(t)).astype(np.float32)
+    np.savez_compressed(os.path.join(HERE, "dequant_blocks_f1.npz"), **out)
+    print("dequant_blocks_f1.npz written")
+
+
+def fixture_check_f1(ref):
+    from oracle import blocks_f1
+
+    import glob
+
+    rec = []
+    for f in sorted(glob.glob(os.path.join(ref, "tests", "fixtures", "dequant", "*.npz"))):
+        z = np.load(f)
+        t = int(z["ggml_type"])
+        if t not in blocks_f1.BLOCK_BYTES:
+            continue
+        mine = blocks_f1.dequantize(z["raw"], t)[0]
+        rec.append({"file": os.path.basename(f), "type": t,
+                    "raw_sha256": hashlib.sha256(np.ascontiguousarray(z["raw"]).tobytes()).hexdigest(),
+                    "ref_sha256": hashlib.sha256(np.ascontiguousarray(z["ref"]).tobytes()).hexdigest(),
+                    "oracle_bit_exact": bool(np.array_equal(mine.view(np.uint32), z["ref"].view(np.uint32)))})
+    with open(os.path.join(HERE, "fixture_check_f1.json"), "w") as fo:
+        json.dump({"source": "tests/fixtures/dequant/*.npz", "fixtures": rec}, fo, indent=1)
+    print("fixture_check_f1.json:", len(rec), "fixtures,", sum(r["oracle_bit_exact"] for r in rec), "bit exact")
+
+
 def fixture_check(ref):
     from oracle import blocks
 
@@ -130,5 +169,7 @@ if __name__ == "__main__":
     ref = sys.argv[1] if len(sys.argv) > 1 else os.environ["GSQ_REFERENCE"]
     dequant_blocks()
     fixture_check(ref)
+    dequant_blocks_f1()
+    fixture_check_f1(ref)
     routing(ref)
     iq3_ref_packed(ref)

@@ -107,4 +107,5 @@ def test_c_route():
     assert r(128, IQ3_S, 17408, K, 1) == _cabi.KERNEL_GEMM_PREFILL and r(128, IQ3_S, 5120, K, 1) == _cabi.KERNEL_GEMM
     assert r(8192, Q6_K, 151936, K, 1) == _cabi.KERNEL_MMV     # repacked Q6_K: 48 rows per launch
     assert r(33, Q6_K, BIG, K, 0) == _cabi.KERNEL_GEMV         # GGUF order: dp4a, 8 rows per launch
-    assert r(4, IQ2_S, BIG, K, 0) == _cabi.KERNEL_NONE
+    assert r(4, IQ2_S, BIG, K, 0) == _cabi.KERNEL_GEMV and r(300, IQ2_S, BIG, K, 0) == _cabi.KERNEL_GEMV   # low-bit types: dp4a
+    assert r(4, 8, BIG, K, 0) == _cabi.KERNEL_NONE             # Q8_0: not a type of this route

@@ -154,8 +154,7 @@ extern "C" int gsq_check_inputs(const gsq_guard_args* a, int64_t* k_out, char* m
   if (!(a->w_is_cuda && a->x_is_cuda)) return guard_fail(msg, n, "%s: W and X must be CUDA tensors", op);
   if (!a->same_device) return guard_fail(msg, n, "%s: W and X must be on the same device", op);
   if (gsq::block_bytes((int)type) == 0)
-    return guard_fail(msg, n, "%s: ggml type %lld has no sm_100a kernel in this build (IQ3_S, IQ4_XS, Q4_K, Q6_K)", op,
-                      type);
+    return guard_fail(msg, n, "%s: ggml type %lld has no sm_100a kernel in this build", op, type);
   if (k_out) *k_out = k;
   return GSQ_OK;
 }

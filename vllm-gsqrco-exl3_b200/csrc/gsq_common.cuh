@@ -34,7 +34,17 @@ struct DeviceInfo {
 int device_info(DeviceInfo* out);
 
 __host__ __device__ constexpr int block_bytes(int t) {
-  return t == GSQ_TYPE_Q4_K ? 144 : t == GSQ_TYPE_Q6_K ? 210 : t == GSQ_TYPE_IQ3_S ? 110 : t == GSQ_TYPE_IQ4_XS ? 136 : 0;
+  return t == GSQ_TYPE_Q4_K     ? 144
+         : t == GSQ_TYPE_Q6_K   ? 210
+         : t == GSQ_TYPE_IQ3_S  ? 110
+         : t == GSQ_TYPE_IQ4_XS ? 136
+         : t == GSQ_TYPE_Q2_K   ? 84
+         : t == GSQ_TYPE_IQ2_XXS ? 66
+         : t == GSQ_TYPE_IQ2_XS ? 74
+         : t == GSQ_TYPE_IQ3_XXS ? 98
+         : t == GSQ_TYPE_IQ2_S  ? 82
+         : t == GSQ_TYPE_IQ1_M  ? 56
+                                : 0;
 }
 
 __device__ __forceinline__ float h2f(uint32_t bits16) {

@@ -945,10 +945,29 @@ static int gemv_host_dp4a(const void* w, int64_t row_bytes, int64_t rows, int gg
                           int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump,
                           int dump_m0);
 
+// gsq_gemv_f1.cu
+bool gemv_f1_applies(int ggml_type);
+int gemv_f1_group(int ggml_type);
+int gemv_f1_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, const void* x_q8, int64_t m, int64_t k,
+                 void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump, int dump_m0);
+
 static int gemv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_q8,
                      int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump,
                      int dump_m0) {
   if (m == 0 || rows == 0) return GSQ_OK;
+  if (gemv_f1_applies(ggml_type)) {
+    // the low-bit types: their own dp4a kernel, eight activation rows per launch
+    if (packed || m < 0 || m > 48 || !y || !x_q8 || k <= 0 || k % 32 != 0) return GSQ_ERR_UNSUPPORTED;
+    if (y_dtype != GSQ_F32 && y_dtype != GSQ_F16 && y_dtype != GSQ_BF16) return GSQ_ERR_UNSUPPORTED;
+    const int64_t ysz = y_dtype == GSQ_F32 ? 4 : 2;
+    for (int64_t i = 0; i < m; i += 8) {
+      const int64_t c = m - i < 8 ? m - i : 8;
+      const int rc = gemv_f1_host(w, row_bytes, rows, ggml_type, (const uint8_t*)x_q8 + i * (k / 32) * 36, c, k,
+                                  (uint8_t*)y + i * y_row_stride * ysz, y_dtype, y_row_stride, stream, dump, dump_m0 + (int)i);
+      if (rc != GSQ_OK) return rc;
+    }
+    return GSQ_OK;
+  }
   if (mmv_applies(ggml_type, packed, rows, m)) {
     int* d = dump ? dump + (int64_t)dump_m0 * rows * (k / 32) : nullptr;
     const int rc = mmv_host(w, row_bytes, rows, ggml_type, packed, x_q8, 0, m, k, y, y_dtype, y_row_stride, stream, d);

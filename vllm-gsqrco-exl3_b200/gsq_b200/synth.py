@@ -11,6 +11,9 @@ value distributions are the stated ones:
   Q4_K    d, dmin = f16(|N(0,1)| * 1e-2); 8 six-bit sc and 8 six-bit m uniform 0..63 packed into
           12 bytes; 128 bytes of nibbles uniform
   Q6_K    ql[128], qh[64] uniform; 16 int8 sub-scales uniform; d = f16(|N(0,1)| * 1e-2)
+  Q2_K, IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS, IQ1_M (the other types of the model file): every index, sign and
+          sub-scale byte uniform; d (and Q2_K's dmin) = f16(|N(0,1)| * 5e-3); IQ1_M's d is spread over the top
+          nibbles of its four scale words as the format has it
 
 Everything is numpy on the host; callers move the bytes to the GPU.
 """
@@ -20,8 +23,11 @@ from __future__ import annotations
 import numpy as np
 
 Q4_K, Q6_K, IQ3_S, IQ4_XS = 12, 14, 21, 23
-BLOCK_BYTES = {Q4_K: 144, Q6_K: 210, IQ3_S: 110, IQ4_XS: 136}
+Q2_K, IQ2_XXS, IQ2_XS, IQ3_XXS, IQ2_S, IQ1_M = 10, 16, 17, 18, 22, 29
+BLOCK_BYTES = {Q4_K: 144, Q6_K: 210, IQ3_S: 110, IQ4_XS: 136, Q2_K: 84, IQ2_XXS: 66, IQ2_XS: 74, IQ3_XXS: 98, IQ2_S: 82,
+               IQ1_M: 56}
 TYPE_IDS = {"Q4_K": Q4_K, "Q6_K": Q6_K, "IQ3_S": IQ3_S, "IQ4_XS": IQ4_XS}
+LOW_BIT_TYPE_IDS = {"Q2_K": Q2_K, "IQ2_XXS": IQ2_XXS, "IQ2_XS": IQ2_XS, "IQ3_XXS": IQ3_XXS, "IQ2_S": IQ2_S, "IQ1_M": IQ1_M}
 
 
 def _f16_scale(rng, shape, mult):
@@ -66,6 +72,20 @@ def make_weight(ggml_type: int, rows: int, k: int, seed: int) -> np.ndarray:
         out[..., 0:192] = rng.integers(0, 256, size=(rows, nb, 192), dtype=np.uint8)
         out[..., 192:208] = rng.integers(-128, 128, size=(rows, nb, 16), dtype=np.int8).view(np.uint8)
         out[..., 208:210] = _f16_scale(rng, (rows, nb, 1), 1e-2).view(np.uint8)
+    elif ggml_type in (IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS):
+        out[...] = rng.integers(0, 256, size=(rows, nb, bs), dtype=np.uint8)
+        out[..., 0:2] = _f16_scale(rng, (rows, nb, 1), 5e-3).view(np.uint8)
+    elif ggml_type == Q2_K:
+        out[...] = rng.integers(0, 256, size=(rows, nb, bs), dtype=np.uint8)
+        out[..., 80:82] = _f16_scale(rng, (rows, nb, 1), 5e-3).view(np.uint8)
+        out[..., 82:84] = _f16_scale(rng, (rows, nb, 1), 5e-3).view(np.uint8)
+    elif ggml_type == IQ1_M:
+        out[...] = rng.integers(0, 256, size=(rows, nb, bs), dtype=np.uint8)
+        d = _f16_scale(rng, (rows, nb, 1), 5e-3).view(np.uint16).astype(np.uint32)[..., 0]
+        sc = out[..., 48:56].copy().view(np.uint16).astype(np.uint32) & 0x0FFF
+        for j in range(4):   # nibble j of d sits in the top nibble of scale word j
+            sc[..., j] |= ((d >> (4 * j)) & 0xF) << 12
+        out[..., 48:56] = sc.astype(np.uint16).view(np.uint8)
     else:
         raise ValueError(f"unsupported ggml type {ggml_type}")
     return out.reshape(rows, nb * bs)
