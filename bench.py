@@ -503,6 +503,7 @@ def run_ours(args):
             torch.cuda.empty_cache()
             out["prefill"] = extra_prefill(dev, capture)
             out["decode_stack"] = extra_decode_stack(dev, capture)
+            out["low_bit_types"] = extra_low_bit(dev, capture, l2)
         if world == 1 and not args.no_ref_kernels:
             out["ref_kernels"] = ref_kernels(cell_rows, raws, l2)
         if world == 1 and not args.no_cpu_baseline:
@@ -569,7 +570,7 @@ def check_cells(cells, xs, xs_host, order, product, capture):
     return parity, exact
 
 
-def ref_kernels(cell_rows, raws, l2_bytes):
+def ref_kernels(cell_rows, raws, l2_bytes, types=None):
     """The reference's own CUDA kernels (oracle/_ref/ref_C_gguf.so, the routed op of each cell on GGUF-order bytes;
     for IQ3_S also its packed route, timed on the same bytes: same traffic, meaningless values) in a process of
     their own, timed like the cells above: one call per weight copy in one graph, best of 3 replays."""
@@ -586,7 +587,7 @@ def ref_kernels(cell_rows, raws, l2_bytes):
     xs, cases, tags = {}, [], []
     for row in cell_rows:
         key = (row["type"], row["n"], row["k"])
-        t = dict(TYPES)[row["type"]]
+        t = (types or dict(TYPES))[row["type"]]
         m, n, k = row["m"], row["n"], row["k"]
         if (k, m) not in xs:
             from gsq_b200 import synth
@@ -692,6 +693,51 @@ def extra_prefill(dev, capture):
     return {"int8_peak_nominal_TOPS": NOMINAL_INT8_TOPS, "int8_peak_measured_TOPS": peak,
             "int8_peak_how": "torch._int_mm 8192^3, best of 5", "includes": "activation quantisation + GEMM per call",
             "cells": rows}
+
+
+LOW_BIT_TYPES = [("Q2_K", 10), ("IQ2_XXS", 16), ("IQ2_XS", 17), ("IQ3_XXS", 18), ("IQ2_S", 22), ("IQ1_M", 29)]
+
+
+def extra_low_bit(dev, capture, l2_bytes):
+    """The six low-bit types the model file mixes with the main four (GGUF order, dp4a kernel): 17408 x 5120 at 1 and
+    8 activation rows, quantise + product per call, one graph over weight copies cycled beyond 3 x L2, best of 3
+    replays; and the reference's own kernel for the same cells (its stock MMVQ route) where oracle/_ref is built."""
+    import torch
+
+    from gsq_b200 import synth
+    from gsq_b200.quantization import linear
+
+    n, k = 17408, 5120
+    rows, raws = [], {}
+    for tname, t in LOW_BIT_TYPES:
+        raw = synth.make_weight(t, n, k, 1700 + t)
+        raws[(tname, n, k)] = raw
+        w0 = torch.from_numpy(raw).to(dev)
+        copies = max(2, -(-3 * l2_bytes // w0.numel()) + 1)
+        ws = [w0] + [w0.clone() for _ in range(copies - 1)]
+        for m in (1, 8):
+            x = synth.nudge_ties_torch(torch.from_numpy(synth.make_activation(m, k, 1200 + m)).half()).to(dev)
+
+            def many():
+                for w in ws:
+                    linear.fused_mul_mat_gguf(x, w, t, None, False)
+            g = capture(many)
+            best = 1e30
+            for _ in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                best = min(best, e0.elapsed_time(e1) * 1e3 / len(ws))
+            rows.append({"type": tname, "n": n, "k": k, "m": m, "us": round(best, 2), "GBps": round(w0.numel() / best / 1e3, 1)})
+            del g
+        del ws, w0
+        torch.cuda.empty_cache()
+    ref = ref_kernels(rows, raws, l2_bytes, dict(LOW_BIT_TYPES))
+    return {"what": "GGUF-order dp4a kernel, 8 activation rows per launch; weight GB/s = weight bytes / time", "cells": rows,
+            "ref_kernels": {k2: v for k2, v in ref.items() if k2 != "cells"} if "cells" in ref else ref,
+            "ref_cells": ref.get("cells")}
 
 
 def extra_decode_stack(dev, capture, layers=64):
