@@ -8,7 +8,7 @@
 // integer dot product of the signed codebook bytes with the q8_1 quants, the integer sub-scale applied with the same
 // truncating divisions, then one fp32 product with d_w * d_x.
 //
-// Work split: a warp owns 4 weight rows; per step its 32 lanes cover 4 superblocks x 8 slices of 32 values, each lane
+// Work split: a warp owns 4 weight rows (2 at one or two activation rows); per step its 32 lanes cover 4 superblocks x 8 slices of 32 values, each lane
 // decoding its slice of the 4 rows once and dotting it with every activation row (the 36-byte q8_1 blocks come through
 // L1: every warp of the SM reads the same ones). Blocks of these types are only 2-byte aligned (66, 74, 82, 98 bytes),
 // so weights come in as halfwords. Codebooks are device tables read through the cache hierarchy.
@@ -201,17 +201,21 @@ struct Slice {
 
 constexpr int F1_WARPS = 4;
 
+// weight rows per warp: 4 amortise the activation loads; at 1 and 2 activation rows there is little to amortise and
+// twice the warps hide more of the load latency
+__host__ __device__ constexpr int f1_rows(int m) { return m <= 2 ? 2 : 4; }
+
 template <int KIND, int M, bool DUMP>
 __global__ void __launch_bounds__(F1_WARPS * 32) gemv_f1_kernel(const F1Args a) {
-  constexpr int BS = f1_block_bytes(KIND), G = f1_group(KIND);
+  constexpr int BS = f1_block_bytes(KIND), G = f1_group(KIND), R = f1_rows(M);
   const int lane = threadIdx.x & 31;
-  const int row0 = (blockIdx.x * F1_WARPS + (threadIdx.x >> 5)) * 4;
+  const int row0 = (blockIdx.x * F1_WARPS + (threadIdx.x >> 5)) * R;
   if (row0 >= a.nrows) return;
   const int nsb = a.k >> 8, nb32 = a.k >> 5;
   const int sbl = lane >> 3, s = lane & 7;
-  float acc[4][M];
+  float acc[R][M];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < R; ++i) {
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[i][m] = 0.0f;
   }
@@ -219,8 +223,10 @@ __global__ void __launch_bounds__(F1_WARPS * 32) gemv_f1_kernel(const F1Args a) 
     const int sb = sb0 + sbl;
     if (sb < nsb) {
       const int blk = sb * 8 + s;
+      // row by row: decode the lane's slice, dot it with every activation block (the blocks of the step stay in L1;
+      // holding all rows' slices to load each block once measured slower: registers)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < R; ++i) {
         const int r = min(row0 + i, a.nrows - 1);
         Slice<KIND> sl;
         sl.load(a.w + (int64_t)r * a.row_bytes + (int64_t)sb * BS, s);
@@ -247,7 +253,7 @@ __global__ void __launch_bounds__(F1_WARPS * 32) gemv_f1_kernel(const F1Args a) 
     }
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < R; ++i) {
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       float v = acc[i][m];
@@ -260,7 +266,8 @@ __global__ void __launch_bounds__(F1_WARPS * 32) gemv_f1_kernel(const F1Args a) 
 
 template <int KIND, bool DUMP>
 static int launch_f1(const F1Args& a, int m, cudaStream_t st) {
-  const unsigned grid = (unsigned)((a.nrows + 4 * F1_WARPS - 1) / (4 * F1_WARPS));
+  const int per_block = f1_rows(m) * F1_WARPS;
+  const unsigned grid = (unsigned)((a.nrows + per_block - 1) / per_block);
   switch (m) {
 #define GSQ_F1_CASE(MM) \
   case MM: gemv_f1_kernel<KIND, MM, DUMP><<<grid, F1_WARPS * 32, 0, st>>>(a); break;
