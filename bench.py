@@ -1051,36 +1051,58 @@ def run_reference(args):
 
 
 def run_cell(args):
-    """One product a few times on distinct weight copies, eager (for a profiler, or a quick number)."""
+    """One product (or the same product at several row counts: M may be a comma-separated list) a few times on distinct
+    weight copies: eager for a profiler, or as a CUDA graph for a number without launch overhead."""
     import torch
 
     import gsq_b200  # noqa: F401
-    from gsq_b200 import synth
+    from gsq_b200 import _cabi, synth
     from gsq_b200.quantization import iq3_pack, linear
 
-    tname, n, k, m = args.cell[0], int(args.cell[1]), int(args.cell[2]), int(args.cell[3])
+    tname, n, k = args.cell[0], int(args.cell[1]), int(args.cell[2])
+    ms = [int(v) for v in args.cell[3].split(",")]
     dev = "cuda:0"
-    t = synth.TYPE_IDS[tname]
+    t = {**synth.TYPE_IDS, **synth.LOW_BIT_TYPE_IDS}[tname]
     w0 = torch.from_numpy(synth.make_weight(t, n, k, 1)).to(dev)
     packed = tname in ("IQ3_S", "Q6_K") and not args.unpacked and n % 16 == 0
     if packed:
         iq3_pack.pack_(w0, t)
-    ws = [w0] + [w0.clone() for _ in range(3)]
-    dtype = torch.bfloat16 if m > 64 else torch.float16
-    x = synth.nudge_ties_torch(torch.from_numpy(synth.make_activation(m, k, 2)).to(dtype)).to(dev)
-    for i in range(2):
-        linear.fused_mul_mat_gguf(x, ws[i % len(ws)], t, None, packed)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.iters):
-        y = linear.fused_mul_mat_gguf(x, ws[(i + 2) % len(ws)], t, None, packed)
-    e1.record()
-    torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / args.iters
-    print(f"{tname} {n}x{k} m={m} packed={packed}: {us:.1f} us per call (eager, with launch overhead), "
-          f"{w0.numel() / us / 1e3:.0f} GB/s, {2.0 * m * n * k / us / 1e6:.1f} TOPS; op "
-          f"{linear._lcpp_op(m, t, n, k, packed)}; mean |y| {float(y.float().abs().mean()):.4f}")
+    ws = [w0] + [w0.clone() for _ in range(15 if args.graph else 3)]
+    for m in ms:
+        dtype = torch.bfloat16 if m > 64 else torch.float16
+        x = synth.nudge_ties_torch(torch.from_numpy(synth.make_activation(m, k, 2)).to(dtype)).to(dev)
+        for kernel in (["default", "tcgen05"] if args.kernel == "both" else [args.kernel]):
+            old = _cabi.lib.gsq_debug_mmv_mode(1 if kernel == "tcgen05" else 0)
+            for i in range(2):
+                y = linear.fused_mul_mat_gguf(x, ws[i % len(ws)], t, None, packed)
+            torch.cuda.synchronize()
+            if args.graph:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for w in ws:
+                        linear.fused_mul_mat_gguf(x, w, t, None, packed)
+                us = 1e30
+                for _ in range(3):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    g.replay()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    us = min(us, e0.elapsed_time(e1) * 1e3 / len(ws))
+                del g
+            else:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(args.iters):
+                    y = linear.fused_mul_mat_gguf(x, ws[(i + 2) % len(ws)], t, None, packed)
+                e1.record()
+                torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / args.iters
+            _cabi.lib.gsq_debug_mmv_mode(old)
+            how = "graph replay over 16 weight copies" if args.graph else "eager, with launch overhead"
+            print(f"{tname} {n}x{k} m={m} packed={packed} kernel={kernel}: {us:.1f} us per call ({how}), "
+                  f"{w0.numel() / us / 1e3:.0f} GB/s, {2.0 * m * n * k / us / 1e6:.1f} TOPS; op "
+                  f"{linear._lcpp_op(m, t, n, k, packed)}; mean |y| {float(y.float().abs().mean()):.4f}", flush=True)
 
 
 def main():
@@ -1097,6 +1119,10 @@ def main():
     ap.add_argument("--cell", nargs=4, metavar=("TYPE", "N", "K", "M"), help="run one product only (for profilers)")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--unpacked", action="store_true", help="--cell: keep IQ3_S / Q6_K in GGUF order")
+    ap.add_argument("--kernel", default="default", choices=["default", "tcgen05", "both"],
+                    help="--cell: 'tcgen05' switches the register-operand small-batch kernel off, so that 9..48 rows run on "
+                         "the tcgen05 GEMM instead; 'both' times one after the other")
+    ap.add_argument("--graph", action="store_true", help="--cell: time a CUDA graph of the calls (no launch overhead), best of 3 replays")
     args = ap.parse_args()
     if args.cell:
         run_cell(args)
