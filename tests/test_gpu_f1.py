@@ -105,3 +105,38 @@ def test_against_reference_kernels(name, tmp_path):
     res = torch.load(cout)
     for y, r in zip(mine, res):
         assert product.rel_err(y.numpy(), r["out"].double().numpy()) <= 1e-3
+
+
+@pytest.mark.parametrize("m", [1, 8, 20])
+def test_apply_fused_layer_mixing_main_and_low_bit_types(m):
+    """A fused layer as the model file has them: a repacked IQ3_S run beside IQ3_XXS (which stays in GGUF order here,
+    though the layer carries the packed flag), IQ2_XS and Q2_K runs, through GGUFLinearMethod.apply()."""
+    from oracle import blocks
+
+    k = 1024
+    main = {"IQ3_S": 21}
+    shards = [("a", "IQ3_S", 128), ("b", "IQ3_XXS", 64), ("c", "IQ2_XS", 64), ("d", "Q2_K", 48)]
+    layer = torch.nn.Module()
+    method = linear.GGUFLinearMethod(None)
+    method.create_weights(layer, k, [r for _, _, r in shards], k, sum(r for _, _, r in shards), torch.float16)
+    raws = {}
+    for i, (sid, name, rows) in enumerate(shards):
+        t = main.get(name) or TYPES[name]
+        raws[sid] = synth.make_weight(t, rows, k, 950 + i)
+        layer.weight.load_shard(torch.from_numpy(raws[sid]).to(DEV), sid)
+        layer.weight_type.shard_weight_type[sid] = t
+    layer.weight_type.weight_type = 21
+    method.process_weights_after_loading(layer)
+    assert layer.weight.iq3_packed
+    x = _x(m, k, torch.float16, 960 + m)
+    y = method.apply(layer, x.to(DEV))
+    q, d, _ = q8_1.quantize_q8_1(x.float().numpy())
+    refs = []
+    for sid, name, rows in shards:
+        if name in main:
+            refs.append(product.product_q81(blocks.decode(raws[sid], main[name]), q, d.astype(np.float32)))
+        else:
+            refs.append(blocks_f1.product_q81(blocks_f1.decode(raws[sid], TYPES[name]), q, d.astype(np.float32)))
+    ref = np.concatenate(refs, axis=1)
+    assert y.shape == ref.shape
+    assert product.rel_err(y.float().cpu().numpy(), ref) <= 2e-3

@@ -20,8 +20,9 @@ LCPP_QUANT_TYPES = frozenset({
     GGML_TYPE_Q2_K, GGML_TYPE_Q4_K, GGML_TYPE_Q6_K, GGML_TYPE_IQ2_XXS, GGML_TYPE_IQ2_XS, GGML_TYPE_IQ2_S,
     GGML_TYPE_IQ3_XXS, GGML_TYPE_IQ3_S, GGML_TYPE_IQ4_XS, GGML_TYPE_IQ1_M,
 })
-# ... and the ones that have an sm_100a kernel here
-B200_QUANT_TYPES = frozenset({GGML_TYPE_Q4_K, GGML_TYPE_Q6_K, GGML_TYPE_IQ3_S, GGML_TYPE_IQ4_XS})
+# ... and the ones that have an sm_100a kernel here: all of them (tensor-core kernels for Q4_K, Q6_K, IQ3_S, IQ4_XS; the
+# dp4a kernel of gsq_gemv_f1.cu for the rest)
+B200_QUANT_TYPES = LCPP_QUANT_TYPES
 UNQUANTIZED_TYPES = frozenset({GGML_TYPE_F32, GGML_TYPE_F16, GGML_TYPE_BF16})
 
 # (values per block, bytes per block)

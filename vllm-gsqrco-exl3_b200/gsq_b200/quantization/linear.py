@@ -103,6 +103,9 @@ def _fused_mul_mat_gguf(
     _require_route()
     if weight_type not in ops.LCPP_QUANT_TYPES:
         raise NotImplementedError(f"Unsupported GGUF quantization type: {weight_type}")
+    # the layer's flag says its IQ3_S / Q6_K runs are repacked; this package leaves IQ3_XXS (which the reference
+    # repacks too) in GGUF order, so such a run of a packed layer routes as unpacked
+    packed = packed and weight_type in iq3_pack.PACKABLE_TYPES
     name = _lcpp_op(n, weight_type, rows, x.shape[1], packed)
     if name is None:
         raise NotImplementedError(f"no kernel for ggml type {weight_type} at {n} activation rows")
