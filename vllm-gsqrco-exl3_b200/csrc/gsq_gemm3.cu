@@ -201,7 +201,8 @@ __device__ __forceinline__ void decode_half(const uint8_t* raw, uint8_t* a, floa
 // ---------------------------------------------------------------------------------------------
 // Consumers.
 
-// 8 columns of one slice: y += (S * d_w) * d_x (packed fp32 instructions: measured faster than scalar ones here)
+// 8 columns of one slice: y += (S * d_w) * d_x. Packed fp32 instructions: measured against scalar ones and against
+// packed multiplies with scalar FMAs (to use both fp32 pipes), all-packed is fastest: issue slots count for more.
 __device__ __forceinline__ void scale8(const uint32_t (&c)[8], const float* bd, float dw, float2* acc) {
   const float2 dw2 = make_float2(dw, dw);
 #pragma unroll
