@@ -242,6 +242,33 @@ int gsq_allreduce_sum(const void* const* peer_bufs, uint32_t* const* peer_flags,
 int gsq_allreduce_error_flag(int* flag);
 
 /*
+ * The same sum fused into the product: gsq_linear whose kernel, after forming this rank's partial [m, rows] of a
+ * K-sharded product, stores it into a slot on every GPU, signals, waits (bounded) for the other ranks' partials and
+ * writes their sum to y -- one kernel per rank for product + all-reduce, no collective call, replayable in a CUDA
+ * graph. Served by the small-batch tensor-core kernel only (1..48 rows of the types and shapes it takes; any other
+ * call returns GSQ_ERR_UNSUPPORTED with only the activation quantiser queued, and the caller uses gsq_linear +
+ * gsq_allreduce_sum). Every rank must make the same sequence of calls with the same shapes.
+ *   slots   device array of `world` pointers: each rank's slot area of 2 * world * slot_bytes bytes (symmetric memory /
+ *           CUDA IPC; entry `rank` is this rank's own), 16-byte aligned
+ *   flags   device array of `world` pointers: each rank's flag area of `world` uint32, zero before the first call
+ *   state   3 uint32 of this rank's device memory, zero before the first call
+ *   slot_bytes  >= ((m - 1) * y_row_stride + rows) * element size of y, a multiple of 16
+ * y is written in y_dtype with fp32 accumulation of the ranks' partials (rounded to y_dtype) in rank order: all ranks
+ * get bit-identical results. A wait that gives up leaves y unwritten and raises gsq_peer_reduce_error_flag.
+ */
+typedef struct gsq_peer_reduce {
+  void* const* slots;
+  uint32_t* const* flags;
+  uint32_t* state;
+  int rank, world;
+  int64_t slot_bytes;
+} gsq_peer_reduce;
+int gsq_linear_allreduce(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x,
+                         int x_dtype, int64_t m, int64_t k, int64_t x_row_stride, void* y, int y_dtype,
+                         int64_t y_row_stride, void* scratch, size_t scratch_bytes, const gsq_peer_reduce* pr, void* stream);
+int gsq_peer_reduce_error_flag(int* flag);
+
+/*
  * Kernel family that serves (activation rows m, type, weight rows, k, packed) on B200: GSQ_KERNEL_*, the choice
  * gsq_mul_mat_vec_q8 and gsq_linear make. The op-level routing table of the reference (_lcpp_op,
  * quantization/linear.py:85-114) stays in the Python layer because its op names are API; this is the choice made

@@ -75,3 +75,17 @@ def test_ranks_on_separate_gpus():
                        timeout=300, env=env)
     assert p.returncode == 0 and "peer all-reduce ok" in p.stdout, (p.stdout[-1500:], p.stderr[-3000:])
     print(p.stdout.strip().splitlines()[-1])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_product_fused_with_its_sum():
+    """gsq_linear_allreduce: the K-sharded product and the sum of its result over the GPUs in one kernel per rank,
+    bit for bit against product + gathered sum in rank order, eagerly and in a CUDA graph."""
+    n = min(4, torch.cuda.device_count())
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", "29535",
+                        os.path.join(ROOT, "tests", "_fused_allreduce_worker.py")], capture_output=True, text=True,
+                       timeout=400, env=env)
+    assert p.returncode == 0 and "fused product + sum ok" in p.stdout, (p.stdout[-1500:], p.stderr[-3000:])
+    print(p.stdout.strip().splitlines()[-1])

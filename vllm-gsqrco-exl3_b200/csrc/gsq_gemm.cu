@@ -981,7 +981,8 @@ namespace gsq {
 // gsq_mmv.cu: the register-operand tensor-core kernel for 1..48 rows
 bool mmv_applies(int ggml_type, int packed, int64_t rows, int64_t m);
 int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* xq, int x_layout,
-             int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump);
+             int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump,
+             const gsq_peer_reduce* pr = nullptr);
 }  // namespace gsq
 
 extern "C" int gsq_mul_mat_q8(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed,

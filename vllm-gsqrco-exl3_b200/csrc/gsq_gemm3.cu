@@ -144,8 +144,6 @@ __device__ __forceinline__ void decode_pair(const uint8_t* p, uint8_t* a, float*
   const uint32_t dd = *reinterpret_cast<const uint32_t*>(p + 1728 + 4 * gq);
 #pragma unroll
   for (int sl = 0; sl < 2; ++sl) {
-    constexpr int dummy = 0;
-    (void)dummy;
     const int s_half = 2 * SP + sl;        // slice within the half = slice of the stage
     const int s = 4 * HF + s_half;         // slice within the superblock
 #pragma unroll

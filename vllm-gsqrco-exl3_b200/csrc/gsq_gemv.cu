@@ -939,7 +939,8 @@ static int launch_gemv_m(int m, const GemvArgs& a, int sm_count, int max_smem, c
 bool mmv_applies(int ggml_type, int packed, int64_t rows, int64_t m);
 bool mmv_early_trigger();
 int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* xq, int x_layout,
-             int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump);
+             int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump,
+             const gsq_peer_reduce* pr = nullptr);
 
 static int gemv_host_dp4a(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_q8,
                           int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump,

@@ -10,7 +10,8 @@ namespace gsq {
 // gsq_mmv.cu
 bool mmv_applies(int ggml_type, int packed, int64_t rows, int64_t m);
 int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* xq, int x_layout,
-             int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump);
+             int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump,
+             const gsq_peer_reduce* pr = nullptr);
 // gsq_gemm2.cu
 bool gemm2_applies(int ggml_type, int packed, int64_t rows);
 size_t gemm2_tile_bytes(int64_t m, int64_t k, int ggml_type);
@@ -110,4 +111,21 @@ extern "C" int gsq_linear(const void* w, int64_t row_bytes, int64_t rows, int gg
     if (rc != GSQ_OK) return rc;
   }
   return GSQ_OK;
+}
+
+extern "C" int gsq_linear_allreduce(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x,
+                                    int x_dtype, int64_t m, int64_t k, int64_t x_row_stride, void* y, int y_dtype,
+                                    int64_t y_row_stride, void* scratch, size_t scratch_bytes, const gsq_peer_reduce* pr,
+                                    void* stream) {
+  using namespace gsq;
+  if (!pr || m <= 0 || m > 48 || rows <= 0 || k <= 0 || k % 256 != 0 || !w || !x || !y) return GSQ_ERR_UNSUPPORTED;
+  const int bs = block_bytes(ggml_type);
+  if (bs == 0 || row_bytes != (k / 256) * bs) return GSQ_ERR_UNSUPPORTED;
+  if (y_dtype != GSQ_F32 && y_dtype != GSQ_F16 && y_dtype != GSQ_BF16) return GSQ_ERR_UNSUPPORTED;
+  if (!scratch || scratch_bytes < gsq_linear_scratch_bytes(rows, m, k, ggml_type, packed)) return GSQ_ERR_SCRATCH;
+  if (!mmv_applies(ggml_type, packed, rows, m)) return GSQ_ERR_UNSUPPORTED;
+  int rc = gsq_quantize_q8_1_mmq(x, x_dtype, m, k, x_row_stride, gsq_q8_layout_for_type(ggml_type), scratch, stream);
+  if (rc != GSQ_OK) return rc;
+  rc = mmv_host(w, row_bytes, rows, ggml_type, packed, scratch, 1, m, k, y, y_dtype, y_row_stride, stream, nullptr, pr);
+  return rc == 1000 ? GSQ_ERR_UNSUPPORTED : rc;   // 1000: the shape does not fit the kernel's staging area
 }

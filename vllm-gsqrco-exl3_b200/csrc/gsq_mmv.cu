@@ -72,7 +72,32 @@ struct MmvArgs {
   int nsr_lo;
   uint32_t inv_gpc[2], inv_nkb[2], inv_per;
   unsigned long long* prof;  // debug: per CTA 8 time stamps (ns) at the phase boundaries
+  // Sum over GPUs of the partial results of a K-sharded product, inside this kernel (pr_world > 1; see the end of
+  // mmv_kernel): every rank's slot area [2][world][pr_slot_bytes] and flag area [world], the same offsets on every
+  // GPU (peer pointers; entry pr_rank is this GPU's own), and this rank's call counter + two tickets.
+  void* const* pr_slots;
+  uint32_t* const* pr_flags;
+  uint32_t* pr_state;
+  int pr_rank, pr_world;
+  int64_t pr_slot_bytes;
 };
+
+__device__ int g_mmv_peer_error = 0;
+
+__device__ __forceinline__ void mmv_st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t mmv_ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// one element of a partial result in another rank's slot of this GPU's memory: never from L1 (a peer wrote it)
+__device__ __forceinline__ float mmv_load_partial(const void* base, int y_dtype, int64_t idx) {
+  if (y_dtype == GSQ_F32) return __ldcv(reinterpret_cast<const float*>(base) + idx);
+  const unsigned short b = __ldcv(reinterpret_cast<const unsigned short*>(base) + idx);
+  return y_dtype == GSQ_F16 ? __half2float(__ushort_as_half(b)) : __uint_as_float((uint32_t)b << 16);
+}
 
 __device__ __forceinline__ void mmv_stamp(const MmvArgs& a, int phase) {
   if (a.prof && threadIdx.x == 0) {
@@ -923,6 +948,11 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
     for (int r2 = 0; r2 < GRID / 512 / 16; ++r2) dst[r2] = make_uint4(gv, ~gv + 0x01010101u, gv, ~gv + 0x01010101u);
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // fused sum over GPUs: this call's number (the same in every CTA and on every rank) picks the slot pair. Read after
+  // the wait: the kernel before this one in a programmatic-launch chain may be the call that publishes it.
+  const bool fused = a.pr_world > 1;
+  const uint32_t epoch = fused ? *reinterpret_cast<volatile uint32_t*>(a.pr_state) + 1u : 0u;
+  const int64_t push_off = fused ? (int64_t)((epoch & 1u) * a.pr_world + a.pr_rank) * a.pr_slot_bytes : 0;
   auto nothing = []() {};
   if (XL == XL_Q81) {
     stage_x_q81<MC, DS, MmvKind<KIND>::PERM>(a, sb0 * 8, nkb, colb, xq, xd, xs, tid, nothing);
@@ -1056,7 +1086,15 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
             const float o[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              if (4 * c4 + e < a.m) store_out_dyn(a.y, a.y_dtype, (int64_t)(4 * c4 + e) * a.ldy + row, o[e]);
+              if (4 * c4 + e < a.m) {
+                const int64_t yi = (int64_t)(4 * c4 + e) * a.ldy + row;
+                if (!fused) {
+                  store_out_dyn(a.y, a.y_dtype, yi, o[e]);
+                } else {
+                  // this rank's partial goes into its slot on every GPU (plain stores over peer pointers)
+                  for (int p = 0; p < a.pr_world; ++p) store_out_dyn(reinterpret_cast<char*>(a.pr_slots[p]) + push_off, a.y_dtype, yi, o[e]);
+                }
+              }
             }
           }
         }
@@ -1065,6 +1103,69 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
     if (t0 == 0) mmv_stamp(a, 4);
     __syncthreads();  // the parked sums are reused by the next round
     if (t0 == 0) mmv_stamp(a, 5);
+  }
+  if (fused) {
+    // Sum over GPUs, in this kernel: (1) this CTA's partials are in every GPU's slot of this rank (pushed above); the
+    // last CTA of this rank to get here tells every rank "rank r's partial of this call is complete" (the ranks'
+    // launch plans may differ -- uneven K shards -- so the hand-off is per rank, not per CTA); (2) every CTA waits
+    // (bounded) until every rank has said so; (3) it adds the world's partials of its own tiles, from this GPU's
+    // memory, in rank order (bit-identical on all ranks) and stores Y.
+    // (the verdict of the wait is kept in the activations' staging area, free by now: the launch plan hands all of
+    // the shared memory to the dynamic part, so the kernel must not declare any of its own)
+    __threadfence_system();
+    __syncthreads();
+    volatile int* s_peer_ok = reinterpret_cast<volatile int*>(xq);
+    if (tid == 0) *s_peer_ok = 1;
+    __syncthreads();
+    if (tid == 0 && atomicAdd(a.pr_state + 2, 1u) == gridDim.x - 1) {
+      a.pr_state[2] = 0u;
+      __threadfence_system();
+      for (int p = 0; p < a.pr_world; ++p) mmv_st_release_sys(a.pr_flags[p] + a.pr_rank, epoch);
+    }
+    if (tid < a.pr_world) {
+      const uint32_t* f = a.pr_flags[a.pr_rank] + tid;
+      bool ok = false;
+      unsigned long long t0c, t1c;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0c));
+      for (int spin = 0; spin < (1 << 24); ++spin) {       // bounded twice: by polls and by time (0.2 s)
+        if ((int32_t)(mmv_ld_acquire_sys(f) - epoch) >= 0) { ok = true; break; }
+        __nanosleep(20);
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1c));
+        if (t1c - t0c > 200000000ull) break;
+      }
+      if (!ok) {
+        *s_peer_ok = 0;
+        atomicExch(&g_mmv_peer_error, 1);
+      }
+    }
+    __syncthreads();
+    if (*s_peer_ok) {
+      const char* mine = reinterpret_cast<const char*>(a.pr_slots[a.pr_rank]) + (int64_t)((epoch & 1u) * a.pr_world) * a.pr_slot_bytes;
+      for (int t0 = 0; t0 < tile_cnt; t0 += a.tiles_round) {
+        const int tiles_r = min(a.tiles_round, tile_cnt - t0);
+        const int own_tiles = max(0, min(a.share_cap, tiles_r - crank * a.share_cap));
+        for (int r2 = tid; r2 < own_tiles * MMV_TR; r2 += MMV_THREADS) {
+          const int row = (tile_begin + t0 + crank * a.share_cap) * MMV_TR + r2;
+          if (row < a.nrows) {
+            for (int c = 0; c < a.m; ++c) {
+              const int64_t yi = (int64_t)c * a.ldy + row;
+              float v = 0.0f;
+              for (int p = 0; p < a.pr_world; ++p) v += mmv_load_partial(mine + (int64_t)p * a.pr_slot_bytes, a.y_dtype, yi);
+              store_out_dyn(a.y, a.y_dtype, yi, v);
+            }
+          }
+        }
+      }
+    }
+    // the last CTA to finish publishes the call number for the next call
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      if (atomicAdd(a.pr_state + 1, 1u) == gridDim.x - 1) {
+        a.pr_state[1] = 0u;
+        *reinterpret_cast<volatile uint32_t*>(a.pr_state) = epoch;
+      }
+    }
   }
 }
 
@@ -1292,7 +1393,9 @@ bool mmv_applies(int ggml_type, int packed, int64_t rows, int64_t m) {
 
 // x_layout: 0 = block_q8_1, 1 = block_q8_1_mmq. Returns MMV_DECLINED when the shape does not fit.
 int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* xq, int x_layout,
-             int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump) {
+             int64_t m, int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream, int* dump,
+             const gsq_peer_reduce* pr) {
+  if (pr && (m == 0 || rows == 0)) return GSQ_ERR_UNSUPPORTED;   // every rank must launch: nothing to skip
   if (m == 0 || rows == 0) return GSQ_OK;
   if (m < 0 || m > 48 || rows < 0 || k <= 0 || k % 256 != 0 || !w || !xq || !y) return GSQ_ERR_UNSUPPORTED;
   if (rows > INT32_MAX || k > INT32_MAX) return GSQ_ERR_TOO_LARGE;
@@ -1318,6 +1421,24 @@ int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int 
   a.xcap_kb = 0;
   a.dump = dump;
   a.prof = g_mmv_prof;
+  a.pr_slots = nullptr;
+  a.pr_flags = nullptr;
+  a.pr_state = nullptr;
+  a.pr_rank = 0;
+  a.pr_world = 1;
+  a.pr_slot_bytes = 0;
+  if (pr) {
+    const int64_t esz = y_dtype == GSQ_F32 ? 4 : 2;
+    if (!pr->slots || !pr->flags || !pr->state || pr->world < 2 || pr->world > 8 || pr->rank < 0 || pr->rank >= pr->world ||
+        pr->slot_bytes < ((m - 1) * y_row_stride + rows) * esz || pr->slot_bytes % 16 != 0 || dump)
+      return GSQ_ERR_UNSUPPORTED;
+    a.pr_slots = pr->slots;
+    a.pr_flags = pr->flags;
+    a.pr_state = pr->state;
+    a.pr_rank = pr->rank;
+    a.pr_world = pr->world;
+    a.pr_slot_bytes = pr->slot_bytes;
+  }
   cudaStream_t st = (cudaStream_t)stream;
   switch (ggml_type) {
     case GSQ_TYPE_Q4_K:
@@ -1339,6 +1460,12 @@ int mmv_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int 
 }
 
 }  // namespace gsq
+
+extern "C" int gsq_peer_reduce_error_flag(int* flag) {
+  if (!flag) return GSQ_ERR_UNSUPPORTED;
+  GSQ_CUDA_TRY(cudaMemcpyFromSymbol(flag, gsq::g_mmv_peer_error, sizeof(int)));
+  return GSQ_OK;
+}
 
 extern "C" int gsq_debug_mmv_mode(int mode) {
   const int old = gsq::g_mmv_mode;

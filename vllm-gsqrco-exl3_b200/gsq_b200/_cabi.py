@@ -24,8 +24,14 @@ EXPORTS = (
     "gsq_debug_swap_descriptor_strides", "gsq_debug_gemm_dump_sums", "gsq_debug_gemm_ksplit", "gsq_debug_gemm_variant", "gsq_debug_gemm_wait_hint", "gsq_q8_layout_for_type", "gsq_mul_mat_scratch_bytes", "gsq_mul_mat_q8", "gsq_iq3s_repack", "gsq_route", "gsq_linear_vec_static", "gsq_linear_vec_static_max_q8_bytes",
     "gsq_debug_mmv_mode", "gsq_debug_mmv_min_rows", "gsq_debug_mmv_cluster_size", "gsq_mul_mat_vec_max_rows",
     "gsq_debug_mmv_profile", "gsq_debug_mmv_max_rows", "gsq_debug_mmv_pdl", "gsq_debug_mmv_prefetch_first", "gsq_debug_mmv_chunking", "gsq_debug_mmv_trace",
-    "gsq_linear", "gsq_linear_scratch_bytes", "gsq_debug_gemm_profile", "gsq_q6k_repack", "gsq_allreduce_sum", "gsq_allreduce_error_flag",
+    "gsq_linear", "gsq_linear_scratch_bytes", "gsq_debug_gemm_profile", "gsq_q6k_repack", "gsq_allreduce_sum", "gsq_allreduce_error_flag", "gsq_linear_allreduce", "gsq_peer_reduce_error_flag",
 )
+
+
+class PeerReduce(C.Structure):
+    """gsq_peer_reduce (include/gsq.h)."""
+    _fields_ = [("slots", C.c_void_p), ("flags", C.c_void_p), ("state", C.c_void_p), ("rank", C.c_int), ("world", C.c_int),
+                ("slot_bytes", C.c_int64)]
 
 
 class GuardArgs(C.Structure):
@@ -103,6 +109,11 @@ def _load() -> C.CDLL:
     lib.gsq_allreduce_sum.argtypes = [vp, vp, ci, ci, i64, ci, vp, vp, vp]
     lib.gsq_allreduce_error_flag.restype = ci
     lib.gsq_allreduce_error_flag.argtypes = [C.POINTER(ci)]
+    lib.gsq_linear_allreduce.restype = ci
+    lib.gsq_linear_allreduce.argtypes = [vp, i64, i64, ci, ci, vp, ci, i64, i64, i64, vp, ci, i64, vp, C.c_size_t,
+                                         C.POINTER(PeerReduce), vp]
+    lib.gsq_peer_reduce_error_flag.restype = ci
+    lib.gsq_peer_reduce_error_flag.argtypes = [C.POINTER(ci)]
     lib.gsq_q6k_repack.restype = ci
     lib.gsq_q6k_repack.argtypes = [vp, i64, i64, ci, vp]
     lib.gsq_linear_vec_static.restype = ci

@@ -86,6 +86,28 @@ class output_into:
             _next_output.pop()
 
 
+# Set by tp.PeerAllReduce.fused(): the next self-quantising op call sums its result over the ranks inside its kernel
+# (gsq_linear_allreduce) instead of returning this rank's partial.
+_next_peer: list = []
+
+
+class peer_reduce:
+    """with peer_reduce(ctx): the next self-quantising op call of this module (lcpp_mul_mat_q, lcpp_mul_mat_mma_k,
+    lcpp_mul_mat_iq3_packed, gsq_mul_mat_q6k_packed) is the product AND the sum of its result over the ranks of `ctx`
+    (a _cabi.PeerReduce), one kernel. Raises if the shape is not one the small-batch kernel serves."""
+
+    def __init__(self, ctx):
+        self.ctx = ctx
+
+    def __enter__(self):
+        _next_peer.append(self.ctx)
+        return self
+
+    def __exit__(self, *a):
+        if _next_peer and _next_peer[-1] is self.ctx:
+            _next_peer.pop()
+
+
 def _result(n: int, row: int, X: torch.Tensor) -> torch.Tensor:
     if _next_output:
         y = _next_output.pop()
@@ -192,6 +214,14 @@ def _run(op: str, W: torch.Tensor, X: torch.Tensor, type_: int, row: int, x_q8: 
         sbytes = _lib.gsq_linear_scratch_bytes(row, n, k, type_, int(packed))
         scratch = torch.empty(max(sbytes, 1), dtype=torch.uint8, device=X.device)
         stride = k if n == 1 else X.stride(0)
+        if _next_peer:
+            ctx = _next_peer.pop()
+            _cabi.check(
+                _lib.gsq_linear_allreduce(W.data_ptr(), W.shape[1], row, type_, int(packed), X.data_ptr(), _DTYPES[X.dtype], n,
+                                          k, stride, y.data_ptr(), _DTYPES[y.dtype], y.stride(0), scratch.data_ptr(), sbytes,
+                                          C.byref(ctx), _stream(X.device)),
+                "gsq_linear_allreduce")
+            return y
         _cabi.check(
             _lib.gsq_linear(W.data_ptr(), W.shape[1], row, type_, int(packed), X.data_ptr(), _DTYPES[X.dtype], n, k, stride,
                             y.data_ptr(), _DTYPES[y.dtype], y.stride(0), scratch.data_ptr(), sbytes, _stream(X.device)),

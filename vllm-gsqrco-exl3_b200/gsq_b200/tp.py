@@ -126,6 +126,34 @@ class PeerAllReduce:
         torch.cuda.synchronize()
         dist.barrier(group)      # every rank's pad is zero before anyone signals
 
+    def fused(self, slot_bytes: int):
+        """Resources of the sum fused into the product kernel (gsq_linear_allreduce): a second symmetric allocation of
+        2 * world slots of `slot_bytes` plus `world` flag words per rank. Returns the context manager
+        to wrap each K-sharded product call in: `with ar.fused(nbytes): y = op(W, X, type, rows)` -- y is the sum."""
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from . import _cabi, lcpp_ops
+
+        if getattr(self, "_fused", None) is None or self._fused_slot < slot_bytes:
+            sb = (int(slot_bytes) + 255) // 256 * 256
+            total = 2 * self.world * sb + 256
+            self._fbuf = symm.empty(total, dtype=torch.uint8, device=self.dev)
+            self._fbuf.zero_()
+            self._fhandle = symm.rendezvous(self._fbuf, dist.group.WORLD)
+            ptrs = [int(p) for p in self._fhandle.buffer_ptrs]
+            self._fslots = torch.tensor(ptrs, dtype=torch.int64, device=self.dev)
+            self._fflags = torch.tensor([p + 2 * self.world * sb for p in ptrs], dtype=torch.int64, device=self.dev)
+            self._fstate = torch.zeros(4, dtype=torch.int32, device=self.dev)
+            ctx = _cabi.PeerReduce()
+            ctx.slots, ctx.flags, ctx.state = self._fslots.data_ptr(), self._fflags.data_ptr(), self._fstate.data_ptr()
+            ctx.rank, ctx.world, ctx.slot_bytes = self.rank, self.world, sb
+            self._fused, self._fused_slot = ctx, sb
+            torch.cuda.synchronize()
+            dist.barrier()       # every rank's flags are zero before anyone signals
+        return lcpp_ops.peer_reduce(self._fused)
+
     def partial(self, slot: int, shape, dtype):
         import torch
 
