@@ -863,6 +863,24 @@ def extra_tp_stack(dev, world, rank, capture, layers=64, rows=32):
         r1 = torch.empty(rows, H, device=dev, dtype=torch.bfloat16)      # sums (peer variant: the partials are elsewhere)
         r2 = torch.empty(rows, H, device=dev, dtype=torch.bfloat16)
 
+        def step_fused(peer):
+            """o_proj and down as gsq_linear_allreduce: the product kernel itself pushes its partial to every rank, waits
+            for the others' and writes the sum -- no collective call and no extra kernel for the two sums of a layer."""
+            nb = rows * H * 2
+            cur = x
+            with tp.relaxed_k():
+                for lw in stack:
+                    a = linear.fused_mul_mat_gguf(cur, lw["qkv"], 21, None, True)
+                    with peer.fused(nb), lcpp_ops.output_into(r1):
+                        linear.fused_mul_mat_gguf(a[:, :ko], lw["o"], 21, None, True)
+                    g = linear.fused_mul_mat_gguf(r1, lw["gate_up"], 21, None, True)
+                    with peer.fused(nb), lcpp_ops.output_into(r2):
+                        linear.fused_mul_mat_gguf(g[:, :kd], lw["down"], 23, None, False)
+                    cur = r2
+                with lcpp_ops.output_into(lg_in[:, :p_head.count]):
+                    linear.fused_mul_mat_gguf(cur, head, 14, None, True)
+            dist.all_gather_into_tensor(lg_out, lg_in)
+
         def step(products=True, collectives=True, peer=None):
             """peer: a tp.PeerAllReduce -- the partials of o_proj / down are written into its symmetric buffers and
             summed by one kernel per rank over peer memory instead of an NCCL all-reduce."""
@@ -930,6 +948,16 @@ def extra_tp_stack(dev, world, rank, capture, layers=64, rows=32):
                         "collective_us_each": round(p_coll * 1e3 / (2 * layers + 1), 1), "wait_gave_up": int(flag.value),
                         "what": "the all-reduces replaced by gsq_allreduce_sum (one kernel per rank over symmetric "
                                 "memory: flag exchange + peer loads); the logits' all-gather stays NCCL"}
+            try:
+                ar.fused(rows * H * 2)      # allocate before the capture
+                f_total = best_ms(lambda: step_fused(ar))
+                _cabi_lib.gsq_peer_reduce_error_flag(__import__("ctypes").byref(flag))
+                peer_res["fused_into_the_product"] = {
+                    "ms_per_step": round(f_total, 3), "wait_gave_up": int(flag.value),
+                    "what": "o_proj and down through gsq_linear_allreduce: one kernel per rank forms the partial, stores it "
+                            "into every rank's slot over peer pointers, waits for the others and sums in rank order"}
+            except Exception as e:  # noqa: BLE001
+                peer_res["fused_into_the_product"] = {"unavailable": str(e).splitlines()[0][:200]}
             del ar
         except Exception as e:  # noqa: BLE001  (symmetric memory unavailable: the NCCL variant stands alone)
             peer_res = {"unavailable": str(e).splitlines()[0][:200]}

@@ -877,7 +877,9 @@ __host__ __device__ inline void mmv_k_range(int nsb, int cs, int rank, int* firs
   *last = (int)((int64_t)nsb * (rank + 1) / cs);
 }
 
-template <int KIND, int NTL, int XL, bool DUMP>
+// FUSED: the instantiation that also sums the result over the GPUs (see the end of the kernel); the plain product is
+// a separate instantiation so that it carries none of that code or of its registers.
+template <int KIND, int NTL, int XL, bool DUMP, bool FUSED = false>
 __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   using Rec = typename MmvKind<KIND>::Rec;
@@ -950,7 +952,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // fused sum over GPUs: this call's number (the same in every CTA and on every rank) picks the slot pair. Read after
   // the wait: the kernel before this one in a programmatic-launch chain may be the call that publishes it.
-  const bool fused = a.pr_world > 1;
+  constexpr bool fused = FUSED;
   const uint32_t epoch = fused ? *reinterpret_cast<volatile uint32_t*>(a.pr_state) + 1u : 0u;
   const int64_t push_off = fused ? (int64_t)((epoch & 1u) * a.pr_world + a.pr_rank) * a.pr_slot_bytes : 0;
   auto nothing = []() {};
@@ -1069,32 +1071,52 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
     // next round writes the other gather area, and a CTA that has passed the last barrier only reads locally.
     const int own_tiles = max(0, min(a.share_cap, tiles_r - crank * a.share_cap));
     const float* g0 = gath + (size_t)buf * cs * a.share_cap * SEGF;
-    for (int r2 = tid; r2 < own_tiles * MMV_TR; r2 += MMV_THREADS) {
-      const int row = (tile_begin + t0 + crank * a.share_cap) * MMV_TR + r2;
-      if (row < a.nrows) {
+    if constexpr (!fused) {
+      for (int r2 = tid; r2 < own_tiles * MMV_TR; r2 += MMV_THREADS) {
+        const int row = (tile_begin + t0 + crank * a.share_cap) * MMV_TR + r2;
+        if (row < a.nrows) {
 #pragma unroll
-        for (int c4 = 0; c4 < MC / 4; ++c4) {
-          if (4 * c4 < a.m) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int c4 = 0; c4 < MC / 4; ++c4) {
+            if (4 * c4 < a.m) {
+              float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-              if (r < cs) {
-                const float4 p = *reinterpret_cast<const float4*>(g0 + (size_t)r * a.share_cap * SEGF + r2 * MC + 4 * c4);
-                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
-              }
-            }
-            const float o[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              if (4 * c4 + e < a.m) {
-                const int64_t yi = (int64_t)(4 * c4 + e) * a.ldy + row;
-                if (!fused) {
-                  store_out_dyn(a.y, a.y_dtype, yi, o[e]);
-                } else {
-                  // this rank's partial goes into its slot on every GPU (plain stores over peer pointers)
-                  for (int p = 0; p < a.pr_world; ++p) store_out_dyn(reinterpret_cast<char*>(a.pr_slots[p]) + push_off, a.y_dtype, yi, o[e]);
+              for (int r = 0; r < 8; ++r) {
+                if (r < cs) {
+                  const float4 p = *reinterpret_cast<const float4*>(g0 + (size_t)r * a.share_cap * SEGF + r2 * MC + 4 * c4);
+                  v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
                 }
               }
+              const float o[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                if (4 * c4 + e < a.m) store_out_dyn(a.y, a.y_dtype, (int64_t)(4 * c4 + e) * a.ldy + row, o[e]);
+              }
+            }
+          }
+        }
+      }
+    } else {
+      // this rank's partial goes into its slot on every GPU (plain stores over peer pointers); one item = one row
+      // x four columns, rows fastest, so that all threads of the CTA store and a warp's stores are contiguous
+      const int own_rows = own_tiles * MMV_TR;
+      for (int it = tid; it < own_rows * (MC / 4); it += MMV_THREADS) {
+        const int c4 = it / own_rows, r2 = it - c4 * own_rows;
+        const int row = (tile_begin + t0 + crank * a.share_cap) * MMV_TR + r2;
+        if (row < a.nrows && 4 * c4 < a.m) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            if (r < cs) {
+              const float4 p = *reinterpret_cast<const float4*>(g0 + (size_t)r * a.share_cap * SEGF + r2 * MC + 4 * c4);
+              v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+            }
+          }
+          const float o[4] = {v.x, v.y, v.z, v.w};
+          for (int p = 0; p < a.pr_world; ++p) {
+            char* dst = reinterpret_cast<char*>(a.pr_slots[p]) + push_off;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (4 * c4 + e < a.m) store_out_dyn(dst, a.y_dtype, (int64_t)(4 * c4 + e) * a.ldy + row, o[e]);
             }
           }
         }
@@ -1104,7 +1126,7 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
     __syncthreads();  // the parked sums are reused by the next round
     if (t0 == 0) mmv_stamp(a, 5);
   }
-  if (fused) {
+  if constexpr (fused) {
     // Sum over GPUs, in this kernel: (1) this CTA's partials are in every GPU's slot of this rank (pushed above); the
     // last CTA of this rank to get here tells every rank "rank r's partial of this call is complete" (the ranks'
     // launch plans may differ -- uneven K shards -- so the hand-off is per rank, not per CTA); (2) every CTA waits
@@ -1144,15 +1166,23 @@ __global__ void __launch_bounds__(MMV_THREADS, 1) mmv_kernel(const MmvArgs a) {
       for (int t0 = 0; t0 < tile_cnt; t0 += a.tiles_round) {
         const int tiles_r = min(a.tiles_round, tile_cnt - t0);
         const int own_tiles = max(0, min(a.share_cap, tiles_r - crank * a.share_cap));
-        for (int r2 = tid; r2 < own_tiles * MMV_TR; r2 += MMV_THREADS) {
+        const int own_rows = own_tiles * MMV_TR;
+        for (int it = tid; it < own_rows * a.m; it += MMV_THREADS) {       // one item = one result, rows fastest
+          const int c = it / own_rows, r2 = it - c * own_rows;
           const int row = (tile_begin + t0 + crank * a.share_cap) * MMV_TR + r2;
           if (row < a.nrows) {
-            for (int c = 0; c < a.m; ++c) {
-              const int64_t yi = (int64_t)c * a.ldy + row;
-              float v = 0.0f;
-              for (int p = 0; p < a.pr_world; ++p) v += mmv_load_partial(mine + (int64_t)p * a.pr_slot_bytes, a.y_dtype, yi);
-              store_out_dyn(a.y, a.y_dtype, yi, v);
+            const int64_t yi = (int64_t)c * a.ldy + row;
+            float part[8];
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {                                   // independent loads, then the sum in rank order
+              if (p < a.pr_world) part[p] = mmv_load_partial(mine + (int64_t)p * a.pr_slot_bytes, a.y_dtype, yi);
             }
+            float v = 0.0f;
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+              if (p < a.pr_world) v += part[p];
+            }
+            store_out_dyn(a.y, a.y_dtype, yi, v);
           }
         }
       }
@@ -1341,6 +1371,23 @@ static int mmv_launch_t(MmvArgs a, int sm_count, int max_smem, cudaStream_t st) 
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = g_mmv_pdl ? 2 : 1;
+  if (a.pr_world > 1) {
+    if constexpr (DUMP) {
+      return GSQ_ERR_UNSUPPORTED;
+    } else {
+      static bool configured[32];
+      int dev = 0;
+      GSQ_CUDA_TRY(cudaGetDevice(&dev));
+      auto kern = mmv_kernel<KIND, NTL, XL, false, true>;
+      if (dev >= 32 || !configured[dev]) {
+        GSQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        GSQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 0));
+        if (dev < 32) configured[dev] = true;
+      }
+      GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a));
+      return GSQ_OK;
+    }
+  }
   GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, mmv_kernel<KIND, NTL, XL, DUMP>, a));
   return GSQ_OK;
 }
