@@ -57,6 +57,49 @@ __device__ __forceinline__ int apply_signs4(uint32_t g, uint32_t bits) {
 // C integer division by a power of two (truncation toward zero)
 __device__ __forceinline__ int tdiv(int a, int sh) { return (a + ((a >> 31) & ((1 << sh) - 1))) >> sh; }
 
+// The raw words of one lane's slice of one row, as loaded (fetch), before any table look-up: fetched one step ahead
+// of their use so that the load latency is behind the arithmetic of the step before.
+template <int KIND>
+struct Raw {
+  uint32_t r[KIND == F1_Q2K ? 10 : KIND == F1_IQ2S ? 5 : 4];
+
+  __device__ __forceinline__ void fetch(const uint8_t* b, int s) {
+    if (KIND == F1_IQ2XXS) {
+      r[0] = ldg_stream_u16(b);
+      r[1] = ld32_h(b + 2 + 8 * s);
+      r[2] = ld32_h(b + 6 + 8 * s);
+    } else if (KIND == F1_IQ2XS) {
+      r[0] = ldg_stream_u16(b);
+      r[1] = ld32_h(b + 2 + 8 * s);
+      r[2] = ld32_h(b + 6 + 8 * s);
+      r[3] = ldg_stream_u8(b + 66 + s);
+    } else if (KIND == F1_IQ2S) {
+      r[0] = ldg_stream_u16(b);
+      r[1] = ld32_h(b + 2 + 4 * s);
+      r[2] = ld32_h(b + 34 + 4 * s);
+      r[3] = ldg_stream_u8(b + 66 + s);
+      r[4] = ldg_stream_u8(b + 74 + s);
+    } else if (KIND == F1_IQ3XXS) {
+      r[0] = ldg_stream_u16(b);
+      r[1] = ld32_h(b + 2 + 8 * s);
+      r[2] = ld32_h(b + 6 + 8 * s);
+      r[3] = ld32_h(b + 66 + 4 * s);
+    } else if (KIND == F1_Q2K) {
+      const int h = s >> 2;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) r[e] = ldg_stream_u32(b + 16 + 32 * h + 4 * e);
+      r[8] = ldg_stream_u16(b + 2 * s);
+      r[9] = ldg_stream_u32(b + 80);
+    } else {  // IQ1_M
+      r[0] = ldg_stream_u32(b + 4 * s);
+      r[1] = ldg_stream_u16(b + 32 + 2 * s);
+      const uint2 sa = ldg_stream_v2(b + 48);
+      r[2] = sa.x;
+      r[3] = sa.y;
+    }
+  }
+};
+
 // One lane's slice of one row: the 8 int8x4 words of its 32 values and what scales them.
 template <int KIND>
 struct Slice {
@@ -64,10 +107,10 @@ struct Slice {
   int p0, p1, p2, p3;   // per kind: sub-scales (and mins)
   float d, dmin;
 
-  __device__ __forceinline__ void load(const uint8_t* b, int s) {
+  __device__ __forceinline__ void decode(const Raw<KIND>& w, int s) {
     if (KIND == F1_IQ2XXS) {
-      d = h2f(ldg_stream_u16(b));
-      const uint32_t q = ld32_h(b + 2 + 8 * s), aux = ld32_h(b + 6 + 8 * s);
+      d = h2f(w.r[0]);
+      const uint32_t q = w.r[1], aux = w.r[2];
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         const uint64_t gv = g_iq2xxs_grid[(q >> (8 * g)) & 0xFFu];
@@ -77,21 +120,20 @@ struct Slice {
       }
       p0 = (int)(aux >> 28);
     } else if (KIND == F1_IQ2XS) {
-      d = h2f(ldg_stream_u16(b));
+      d = h2f(w.r[0]);
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
-        const uint32_t q = ldg_stream_u16(b + 2 + 8 * s + 2 * g);
+        const uint32_t q = (w.r[1 + (g >> 1)] >> (16 * (g & 1))) & 0xFFFFu;
         const uint64_t gv = g_iq2xs_grid[q & 511u];
         const uint32_t sg = g_ksigns[q >> 9];
         wv[2 * g] = apply_signs4((uint32_t)gv, sg);
         wv[2 * g + 1] = apply_signs4((uint32_t)(gv >> 32), sg >> 4);
       }
-      const uint32_t sc = ldg_stream_u8(b + 66 + s);
-      p0 = (int)(sc & 0xFu);
-      p1 = (int)(sc >> 4);
+      p0 = (int)(w.r[3] & 0xFu);
+      p1 = (int)(w.r[3] >> 4);
     } else if (KIND == F1_IQ2S) {
-      d = h2f(ldg_stream_u16(b));
-      const uint32_t qs = ld32_h(b + 2 + 4 * s), sgs = ld32_h(b + 34 + 4 * s), qh = ldg_stream_u8(b + 66 + s);
+      d = h2f(w.r[0]);
+      const uint32_t qs = w.r[1], sgs = w.r[2], qh = w.r[3];
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         const uint64_t gv = g_iq2s_grid[((qs >> (8 * g)) & 0xFFu) | (((qh >> (2 * g)) & 3u) << 8)];
@@ -99,12 +141,11 @@ struct Slice {
         wv[2 * g] = apply_signs4((uint32_t)gv, sg);
         wv[2 * g + 1] = apply_signs4((uint32_t)(gv >> 32), sg >> 4);
       }
-      const uint32_t sc = ldg_stream_u8(b + 74 + s);
-      p0 = (int)(sc & 0xFu);
-      p1 = (int)(sc >> 4);
+      p0 = (int)(w.r[4] & 0xFu);
+      p1 = (int)(w.r[4] >> 4);
     } else if (KIND == F1_IQ3XXS) {
-      d = h2f(ldg_stream_u16(b));
-      const uint32_t qa = ld32_h(b + 2 + 8 * s), qb = ld32_h(b + 6 + 8 * s), aux = ld32_h(b + 66 + 4 * s);
+      d = h2f(w.r[0]);
+      const uint32_t qa = w.r[1], qb = w.r[2], aux = w.r[3];
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         const uint32_t q = g < 2 ? qa >> (16 * g) : qb >> (16 * (g - 2));
@@ -115,20 +156,19 @@ struct Slice {
       p0 = (int)(aux >> 28);
     } else if (KIND == F1_Q2K) {
       // slice s = 4 h + j: bits 2j, 2j + 1 of the 32 bytes qs[32 h ..]
-      const int h = s >> 2, j = s & 3;
+      const int j = s & 3;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) wv[e] = (int)((ldg_stream_u32(b + 16 + 32 * h + 4 * e) >> (2 * j)) & 0x03030303u);
-      const uint32_t sc = ldg_stream_u16(b + 2 * s);
+      for (int e = 0; e < 8; ++e) wv[e] = (int)((w.r[e] >> (2 * j)) & 0x03030303u);
+      const uint32_t sc = w.r[8];
       p0 = (int)(sc & 0xFu);
       p1 = (int)((sc >> 8) & 0xFu);
       p2 = (int)((sc >> 4) & 0xFu);
       p3 = (int)(sc >> 12);
-      const uint32_t dm = ldg_stream_u32(b + 80);
-      d = h2f(dm);
-      dmin = h2f(dm >> 16);
+      d = h2f(w.r[9]);
+      dmin = h2f(w.r[9] >> 16);
     } else {  // IQ1_M
-      const uint32_t qs = ldg_stream_u32(b + 4 * s), qh = ldg_stream_u16(b + 32 + 2 * s);
-      const uint2 sa = ldg_stream_v2(b + 48);
+      const uint32_t qs = w.r[0], qh = w.r[1];
+      const uint2 sa = make_uint2(w.r[2], w.r[3]);
       const uint32_t dbits = ((sa.x >> 12) & 0x000Fu) | ((sa.x >> 24) & 0x00F0u) | ((sa.y >> 4) & 0x0F00u) | ((sa.y >> 16) & 0xF000u);
       d = h2f(dbits);
       p2 = 0;
@@ -219,17 +259,32 @@ __global__ void __launch_bounds__(F1_WARPS * 32) gemv_f1_kernel(const F1Args a) 
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[i][m] = 0.0f;
   }
-  for (int sb0 = 0; sb0 < nsb; sb0 += 4) {
-    const int sb = sb0 + sbl;
+  // raw words of the next step are fetched while this step's are decoded and multiplied
+  Raw<KIND> nxt[R];
+  auto fetch_step = [&](int sb) {
     if (sb < nsb) {
-      const int blk = sb * 8 + s;
-      // row by row: decode the lane's slice, dot it with every activation block (the blocks of the step stay in L1;
-      // holding all rows' slices to load each block once measured slower: registers)
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         const int r = min(row0 + i, a.nrows - 1);
+        nxt[i].fetch(a.w + (int64_t)r * a.row_bytes + (int64_t)sb * BS, s);
+      }
+    }
+  };
+  fetch_step(sbl);
+  for (int sb0 = 0; sb0 < nsb; sb0 += 4) {
+    const int sb = sb0 + sbl;
+    Raw<KIND> cur[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) cur[i] = nxt[i];
+    fetch_step(sb + 4);
+    if (sb < nsb) {
+      const int blk = sb * 8 + s;
+      // row by row: decode the lane's slice, dot it with every activation block (the blocks of the step stay in L1;
+      // holding all rows' decoded slices to load each block once measured slower: registers)
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
         Slice<KIND> sl;
-        sl.load(a.w + (int64_t)r * a.row_bytes + (int64_t)sb * BS, s);
+        sl.decode(cur[i], s);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
           const uint32_t* xb = reinterpret_cast<const uint32_t*>(a.xq8 + ((int64_t)m * nb32 + blk) * 36);
