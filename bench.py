@@ -504,6 +504,7 @@ def run_ours(args):
             out["prefill"] = extra_prefill(dev, capture)
             out["decode_stack"] = extra_decode_stack(dev, capture)
             out["low_bit_types"] = extra_low_bit(dev, capture, l2)
+            out["fused_steps"] = extra_fused_steps(dev, capture)
         if world == 1 and not args.no_ref_kernels:
             out["ref_kernels"] = ref_kernels(cell_rows, raws, l2)
         if world == 1 and not args.no_cpu_baseline:
@@ -738,6 +739,70 @@ def extra_low_bit(dev, capture, l2_bytes):
     return {"what": "GGUF-order dp4a kernel, 8 activation rows per launch; weight GB/s = weight bytes / time", "cells": rows,
             "ref_kernels": {k2: v for k2, v in ref.items() if k2 != "cells"} if "cells" in ref else ref,
             "ref_cells": ref.get("cells")}
+
+
+def extra_fused_steps(dev, capture):
+    """The element-wise step in front of a quantised linear, separate (torch's RMSNorm arithmetic / silu * up as eager
+    torch ops, then this library's q8_1 quantiser) against fused with the quantiser (gsq_b200.fused), each followed by
+    the product that consumes the q8_1 bytes, 64 times in one CUDA graph; microseconds per (step + product)."""
+    import torch
+
+    from gsq_b200 import fused, synth
+    from gsq_b200.quantization import iq3_pack
+
+    H, I, eps = 5120, 17408, 1e-6
+    out = []
+    w_qkv = torch.from_numpy(synth.make_weight(21, 7168, H, 2100)).to(dev)
+    iq3_pack.pack_(w_qkv, 21)
+    w_down = torch.from_numpy(synth.make_weight(23, H, I, 2101)).to(dev)
+    gamma = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    op_qkv = torch.ops._C_gguf.lcpp_mul_mat_vec_iq3_mma_packed
+    op_down = torch.ops._C_gguf.lcpp_mul_mat_vec_q
+
+    def timed(fn, reps=64):
+        def many():
+            for _ in range(reps):
+                fn()
+        g = capture(many)
+        best = 1e30
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) * 1e3 / reps)
+        del g
+        return round(best, 2)
+    for m in (4, 8):
+        x = torch.randn(m, H, device=dev, dtype=torch.bfloat16)
+        res = torch.randn(m, H, device=dev, dtype=torch.bfloat16)
+        gu = torch.randn(m, 2 * I, device=dev, dtype=torch.bfloat16)
+
+        def norm_separate():
+            z = x + res
+            y = (z.float() * torch.rsqrt(z.float().pow(2).mean(-1, keepdim=True) + eps)).to(torch.bfloat16) * gamma
+            xq = torch.ops._C_gguf.lcpp_quantize_q8_1(y, 21, False, False)
+            op_qkv(w_qkv, y, 21, 7168, xq)
+
+        def norm_fused():
+            r = res.clone()
+            xq, y = fused.rmsnorm_quantize_q8_1(x, gamma, eps, r, want_y=True)
+            op_qkv(w_qkv, y, 21, 7168, xq)
+
+        def act_separate():
+            y = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+            xq = torch.ops._C_gguf.lcpp_quantize_q8_1(y, 23, False, False)
+            op_down(w_down, y, 23, H, xq)
+
+        def act_fused():
+            xq, y = fused.silu_mul_quantize_q8_1(gu, want_y=True)
+            op_down(w_down, y, 23, H, xq)
+        out.append({"rows": m, "add_rmsnorm_quantize_qkv_us": {"separate": timed(norm_separate), "fused": timed(norm_fused)},
+                    "silu_mul_quantize_down_us": {"separate": timed(act_separate), "fused": timed(act_fused)}})
+    return {"what": "residual add + RMSNorm -> q8_1 -> qkv product (IQ3_S 7168 x 5120) and SwiGLU -> q8_1 -> down product "
+                    "(IQ4_XS 5120 x 17408); 'separate' = eager torch ops for the step + gsq quantiser, 'fused' = one gsq kernel "
+                    "for step + quantiser (the fused norm also clones the residual per call)", "cells": out}
 
 
 def extra_decode_stack(dev, capture, layers=64):

@@ -120,6 +120,23 @@ int gsq_quantize_q8_1(const void* x, int x_dtype, int64_t m, int64_t k, int64_t 
                       void* stream);
 
 /*
+ * The element-wise step in front of a quantised linear fused with its q8_1 quantiser (block_q8_1 layout, as
+ * gsq_quantize_q8_1 writes it). Not in the reference, whose layers run vLLM's rms_norm / silu_and_mul kernels and
+ * then quantise inside apply(); the arithmetic here is theirs (every intermediate rounded to X's type where the
+ * separate kernels store it), so the q8_1 bytes equal gsq_quantize_q8_1 of the y_out of the same call bit for bit.
+ *
+ * gsq_rmsnorm_quantize_q8_1: x [m, k] (row stride x_row_stride); residual: NULL, or [m, k] contiguous, read and
+ *   overwritten with x + residual (the "fused add" form); gamma [k] in X's type; out_q8: m * k/32 blocks; y_out: NULL or
+ *   [m, k] contiguous, receives the normalised activations in X's type. k % 32 == 0, k <= 40960.
+ * gsq_silu_mul_quantize_q8_1: gate_up [m, 2 * inter] (gate columns first; row stride row_stride) -> q8_1 of
+ *   silu(gate) * up over the `inter` columns; y_out: NULL or [m, inter] contiguous. inter % 32 == 0.
+ */
+int gsq_rmsnorm_quantize_q8_1(const void* x, int x_dtype, int64_t m, int64_t k, int64_t x_row_stride, void* residual,
+                              const void* gamma, float eps, void* out_q8, void* y_out, void* stream);
+int gsq_silu_mul_quantize_q8_1(const void* gate_up, int x_dtype, int64_t m, int64_t inter, int64_t row_stride,
+                               void* out_q8, void* y_out, void* stream);
+
+/*
  * q8_1 quantisation, 128-value blocks: replaces quantize_mmq_q8_1_x (lcpp_shim.cu:298-355).
  * out: k/128 * m blocks of 144 bytes (16 scale bytes in `layout`, then 128 x int8); block (kb, row)
  * sits at (kb * m + row) * 144. k % 128 == 0.

@@ -59,6 +59,34 @@ __device__ __forceinline__ uint32_t pack4(float a, float b, float c, float d) {
   return (uint32_t)(ia & 0xFF) | ((uint32_t)(ib & 0xFF) << 8) | ((uint32_t)(ic & 0xFF) << 16) | ((uint32_t)(id & 0xFF) << 24);
 }
 
+// This thread's 8 consecutive values (piece `piece` of the 32-value block its 4 adjacent lanes share) -> block_q8_1 at
+// `b`. All 32 lanes of the warp must call it (shuffles); dead lanes pass zeros and live = false.
+__device__ __forceinline__ void q8_1_store8(const float (&v)[8], bool live, uint8_t* b, int piece) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+  float s[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) s[e] = v[e] + __shfl_xor_sync(0xFFFFFFFFu, v[e], 2);  // lane offset 16
+#pragma unroll
+  for (int e = 0; e < 8; ++e) s[e] = s[e] + __shfl_xor_sync(0xFFFFFFFFu, s[e], 1);  // lane offset 8
+  const float s0 = s[0] + s[4], s1 = s[1] + s[5], s2 = s[2] + s[6], s3 = s[3] + s[7];  // offset 4
+  const float sum = (s0 + s2) + (s1 + s3);                                              // offsets 2, 1
+  if (!live) return;
+  const float d = div_approx(amax, 127.0f);
+  float q[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) q[e] = amax == 0.0f ? 0.0f : roundf(div_approx(v[e], d));
+  uint32_t* q32 = reinterpret_cast<uint32_t*>(b + 4 + piece * 8);  // the quants follow the (d, sum) pair
+  q32[0] = pack4(q[0], q[1], q[2], q[3]);
+  q32[1] = pack4(q[4], q[5], q[6], q[7]);
+  if (piece == 0) {
+    *reinterpret_cast<__half2*>(b) = __floats2half2_rn(d, sum);
+  }
+}
+
 // MMVQ layout: block_q8_1 = half d, half sum, 32 x int8 (36 bytes).
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict__ x, uint8_t* __restrict__ out,
@@ -83,31 +111,7 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = 0.0f;
   }
-  float amax = 0.0f;
-#pragma unroll
-  for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
-  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-  float s[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) s[e] = v[e] + __shfl_xor_sync(0xFFFFFFFFu, v[e], 2);  // lane offset 16
-#pragma unroll
-  for (int e = 0; e < 8; ++e) s[e] = s[e] + __shfl_xor_sync(0xFFFFFFFFu, s[e], 1);  // lane offset 8
-  const float s0 = s[0] + s[4], s1 = s[1] + s[5], s2 = s[2] + s[6], s3 = s[3] + s[7];  // offset 4
-  const float sum = (s0 + s2) + (s1 + s3);                                              // offsets 2, 1
-  if (!live) return;
-  const float d = div_approx(amax, 127.0f);
-  float q[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) q[e] = amax == 0.0f ? 0.0f : roundf(div_approx(v[e], d));
-  const int64_t blk = row * (k >> 5) + (c8 >> 2);
-  uint8_t* b = out + blk * 36;
-  uint32_t* q32 = reinterpret_cast<uint32_t*>(b + 4 + (c8 & 3) * 8);  // the quants follow the (d, sum) pair
-  q32[0] = pack4(q[0], q[1], q[2], q[3]);
-  q32[1] = pack4(q[4], q[5], q[6], q[7]);
-  if ((c8 & 3) == 0) {
-    *reinterpret_cast<__half2*>(b) = __floats2half2_rn(d, sum);
-  }
+  q8_1_store8(v, live, out + (row * (k >> 5) + (c8 >> 2)) * 36, (int)(c8 & 3));
 }
 
 // 128-value blocks: 16 scale bytes + 128 x int8, block (kb, row) at (kb * m + row) * 144.
@@ -244,6 +248,116 @@ __global__ void __launch_bounds__(256) quantize_q8_1_tiles_kernel(const T* __res
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The two element-wise steps that stand in front of a quantised linear in a decoder layer, fused with its q8_1
+// quantiser (block_q8_1 layout), so that the step costs one launch and the normalised / activated values never make
+// a round trip through memory on their way to the quantiser. The arithmetic between the steps is the unfused one:
+// every intermediate is rounded to X's type where the separate kernels would have stored it, and the quantiser part
+// is q8_1_store8 above, so the q8_1 bytes equal quantising the (optional) y_out of the same call bit for bit.
+
+template <typename T>
+__device__ __forceinline__ float round_to(float v);
+template <>
+__device__ __forceinline__ float round_to<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float round_to<__half>(float v) { return __half2float(__float2half_rn(v)); }
+template <>
+__device__ __forceinline__ float round_to<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&v)[8]) {
+#pragma unroll
+  for (int e = 0; e < 8; ++e) store_out<T>(p + e, v[e]);
+}
+
+// RMSNorm (optionally with the residual add in front of it) -> q8_1. One CTA per row:
+//   z = T(x + residual)          (residual updated in place; z = x without one)
+//   var = sum z^2 / k            (fp32: each thread adds its items in order, lanes by the 16-8-4-2-1 xor tree, the
+//                                 eight warps' sums in warp order)
+//   y = T(T(z * rsqrt(var + eps)) * gamma)
+// which is vLLM's rms_norm / fused_add_rms_norm arithmetic (csrc/layernorm_kernels.cu: the scaled value is converted
+// to the tensor's type before the multiplication by the weight), then quantised.
+template <typename T>
+__global__ void __launch_bounds__(256) rmsnorm_q8_1_kernel(const T* __restrict__ x, int64_t stride, T* __restrict__ residual,
+                                                          const T* __restrict__ gamma, float eps, uint8_t* __restrict__ out,
+                                                          T* __restrict__ y_out, int64_t k) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  extern __shared__ float zrow[];          // the row after the residual add, as fp32
+  __shared__ float wsum[8];
+  const int64_t row = blockIdx.x;
+  const int tid = threadIdx.x, per_row = (int)(k >> 3);
+  float ss = 0.0f;
+  for (int it = tid; it < per_row; it += 256) {
+    float v[8];
+    load8<T, false>(x, row * stride + (int64_t)it * 8, v);
+    if (residual) {
+      float r[8];
+      load8<T, false>(residual, row * k + (int64_t)it * 8, r);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = round_to<T>(v[e] + r[e]);
+      store8<T>(residual + row * k + (int64_t)it * 8, v);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      zrow[it * 8 + e] = v[e];
+      ss = fmaf(v[e], v[e], ss);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+  if ((tid & 31) == 0) wsum[tid >> 5] = ss;
+  __syncthreads();
+  float tot = wsum[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) tot += wsum[w];
+  const float rs = rsqrtf(tot / (float)k + eps);
+  // whole warps pass q8_1_store8 together: the loop bound is rounded up to the warp
+  for (int it0 = 0; it0 < per_row; it0 += 256) {
+    const int it = it0 + tid;
+    const bool live = it < per_row;
+    float v[8];
+    if (live) {
+      float g[8];
+      load8<T, false>(gamma, (int64_t)it * 8, g);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = round_to<T>(round_to<T>(zrow[it * 8 + e] * rs) * g[e]);
+      if (y_out) store8<T>(y_out + row * k + (int64_t)it * 8, v);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+    }
+    q8_1_store8(v, live, out + (row * (k >> 5) + (it >> 2)) * 36, it & 3);
+  }
+}
+
+// SwiGLU -> q8_1: gate_up [m, 2 * inter] (gate = the first `inter` columns, up = the rest), as vLLM's silu_and_mul
+// (csrc/activation_kernels.cu): y = T(g / (1 + exp(-g))) * u in T arithmetic, then quantised over the `inter` columns.
+template <typename T>
+__global__ void __launch_bounds__(256) silu_mul_q8_1_kernel(const T* __restrict__ gu, int64_t stride, uint8_t* __restrict__ out,
+                                                           T* __restrict__ y_out, int64_t m, int64_t inter) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 8 values
+  const int64_t per_row = inter >> 3;
+  const bool live = t < m * per_row;
+  const int64_t row = live ? t / per_row : 0;
+  const int64_t c8 = live ? t - row * per_row : 0;
+  float v[8];
+  if (live) {
+    float g[8], u[8];
+    load8<T, false>(gu, row * stride + c8 * 8, g);
+    load8<T, false>(gu, row * stride + inter + c8 * 8, u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = round_to<T>(round_to<T>(g[e] / (1.0f + expf(-g[e]))) * u[e]);
+    if (y_out) store8<T>(y_out + row * inter + c8 * 8, v);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+  }
+  q8_1_store8(v, live, out + (row * (inter >> 5) + (c8 >> 2)) * 36, (int)(c8 & 3));
+}
+
 // launch with programmatic stream serialisation (see griddepcontrol.wait in the kernels)
 template <typename... KArgs, typename... Args>
 static int launch_pdl(void (*kern)(KArgs...), unsigned grid, cudaStream_t st, Args... args) {
@@ -348,4 +462,69 @@ extern "C" int gsq_quantize_q8_1_mmq(const void* x, int x_dtype, int64_t m, int6
     default: return GSQ_ERR_UNSUPPORTED;
   }
 #undef GSQ_MMQ_CASE
+}
+
+namespace gsq {
+
+template <typename T>
+static int launch_rmsnorm_q8_1(const void* x, int64_t m, int64_t k, int64_t stride, void* residual, const void* gamma, float eps,
+                               void* out, void* y_out, cudaStream_t st) {
+  static bool configured[64];
+  int dev = 0;
+  GSQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return GSQ_ERR_UNSUPPORTED;
+  if (!configured[dev]) {
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(rmsnorm_q8_1_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)m);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = (size_t)k * 4;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, rmsnorm_q8_1_kernel<T>, (const T*)x, stride, (T*)residual, (const T*)gamma, eps,
+                                  (uint8_t*)out, (T*)y_out, k));
+  return GSQ_OK;
+}
+
+}  // namespace gsq
+
+extern "C" int gsq_rmsnorm_quantize_q8_1(const void* x, int x_dtype, int64_t m, int64_t k, int64_t x_row_stride,
+                                         void* residual, const void* gamma, float eps, void* out_q8, void* y_out,
+                                         void* stream) {
+  if (m == 0) return GSQ_OK;
+  if (m < 0 || m > 65535 || k <= 0 || k % 32 != 0 || k > 40960 || !x || !gamma || !out_q8) return GSQ_ERR_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (x_dtype) {
+    case GSQ_F32: return gsq::launch_rmsnorm_q8_1<float>(x, m, k, x_row_stride, residual, gamma, eps, out_q8, y_out, st);
+    case GSQ_F16: return gsq::launch_rmsnorm_q8_1<__half>(x, m, k, x_row_stride, residual, gamma, eps, out_q8, y_out, st);
+    case GSQ_BF16: return gsq::launch_rmsnorm_q8_1<__nv_bfloat16>(x, m, k, x_row_stride, residual, gamma, eps, out_q8, y_out, st);
+    default: return GSQ_ERR_UNSUPPORTED;
+  }
+}
+
+extern "C" int gsq_silu_mul_quantize_q8_1(const void* gate_up, int x_dtype, int64_t m, int64_t inter, int64_t row_stride,
+                                          void* out_q8, void* y_out, void* stream) {
+  if (m == 0) return GSQ_OK;
+  if (m < 0 || inter <= 0 || inter % 32 != 0 || !gate_up || !out_q8) return GSQ_ERR_UNSUPPORTED;
+  const int64_t threads = m * (inter >> 3);
+  const unsigned grid = (unsigned)((threads + 255) / 256);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (x_dtype) {
+    case GSQ_F32:
+      return gsq::launch_pdl(gsq::silu_mul_q8_1_kernel<float>, grid, st, (const float*)gate_up, row_stride, (uint8_t*)out_q8,
+                             (float*)y_out, m, inter);
+    case GSQ_F16:
+      return gsq::launch_pdl(gsq::silu_mul_q8_1_kernel<__half>, grid, st, (const __half*)gate_up, row_stride, (uint8_t*)out_q8,
+                             (__half*)y_out, m, inter);
+    case GSQ_BF16:
+      return gsq::launch_pdl(gsq::silu_mul_q8_1_kernel<__nv_bfloat16>, grid, st, (const __nv_bfloat16*)gate_up, row_stride,
+                             (uint8_t*)out_q8, (__nv_bfloat16*)y_out, m, inter);
+    default: return GSQ_ERR_UNSUPPORTED;
+  }
 }
