@@ -60,13 +60,16 @@ extern "C" int gsq_linear(const void* w, int64_t row_bytes, int64_t rows, int gg
     rc = mmv_host(w, row_bytes, rows, ggml_type, packed, scratch, 1, m, k, y, y_dtype, y_row_stride, stream, gemm_dump_pointer());
     if (rc != 1000) return rc;  // 1000: declined, the activations of this shape do not fit its staging area
   }
-  // The prefill GEMM on operand-ordered tiles, where its 128-row x 256-token items can occupy the GPU: measured
-  // against the lockstep kernel (64-token tiles, K split over a cluster when tiles are few) it wins from 512 tokens
-  // on, and from 128 tokens where the weight alone gives half an SM count of row tiles.
+  // The prefill GEMMs on operand-ordered units, where their 128-row x 256-token items can occupy the GPU. Measured
+  // against the lockstep kernel (64-token tiles, K split over a cluster when tiles are few) on 17408 x 5120,
+  // 5120 x 5120 and 5120 x 17408: the fp16-operand kernel wins from 256 tokens on, and from 128 where the weight
+  // alone gives half an SM count of row tiles; the int8 one from 512, and from 192 on the tall weights.
   const int variant = gemm_variant();
-  const bool big = m >= 512 || (m >= 128 && (rows + 127) / 128 >= 74);
+  const bool tall = (rows + 127) / 128 >= 74;
+  const bool big3 = m >= 256 || (m >= 128 && tall);
+  const bool big = m >= 512 || (m >= 192 && tall);
   // repacked IQ3_S: the kernel with the sub-scales folded into fp16 operands (variant 4 keeps the int8 kernel for it)
-  if (gemm3_applies(ggml_type, packed, rows) && (variant == 3 || (variant == 0 && big))) {
+  if (gemm3_applies(ggml_type, packed, rows) && (variant == 3 || (variant == 0 && big3))) {
     rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, Q8_TILES_H16, scratch, stream);
     if (rc != GSQ_OK) return rc;
     return gemm3_host(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, stream);
