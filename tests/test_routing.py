@@ -109,3 +109,16 @@ def test_c_route():
     assert r(33, Q6_K, BIG, K, 0) == _cabi.KERNEL_GEMV         # GGUF order: dp4a, 8 rows per launch
     assert r(4, IQ2_S, BIG, K, 0) == _cabi.KERNEL_GEMV and r(300, IQ2_S, BIG, K, 0) == _cabi.KERNEL_GEMV   # low-bit types: dp4a
     assert r(4, 8, BIG, K, 0) == _cabi.KERNEL_NONE             # Q8_0: not a type of this route
+
+
+def test_route_switch_keys_the_compile_cache():
+    """The switch that changes apply()'s traced graph is registered where vLLM hashes its compile factors
+    (plugin.py:156-161 of the reference does the same)."""
+    reg = {}
+    assert linear.register_compile_factor(reg) and callable(reg["VLLM_GGUF_LCPP"])
+    import os
+
+    assert reg["VLLM_GGUF_LCPP"]() == os.environ.get("VLLM_GGUF_LCPP")
+    keep = reg["VLLM_GGUF_LCPP"]
+    linear.register_compile_factor(reg)                # a second registration keeps the first entry
+    assert reg["VLLM_GGUF_LCPP"] is keep

@@ -326,6 +326,24 @@ class GGUFLinearMethod:
         return out
 
 
+def register_compile_factor(registry: dict | None = None) -> bool:
+    """VLLM_GGUF_LCPP changes the traced graph of apply() and the weight layout, so it has to key vLLM's torch.compile
+    caches: the reference adds it to vllm.envs.environment_variables, which vLLM hashes into its compile factors
+    (plugin/vllm_gguf_plugin/plugin.py:156-161). Same here; `registry` stands in for that dict in tests. Returns
+    whether the entry is present afterwards."""
+    import os
+
+    if registry is None:
+        try:
+            import vllm.envs as envs
+
+            registry = envs.environment_variables
+        except Exception:  # no vLLM, or one without that registry
+            return False
+    registry.setdefault("VLLM_GGUF_LCPP", lambda: os.environ.get("VLLM_GGUF_LCPP"))
+    return "VLLM_GGUF_LCPP" in registry
+
+
 def _register_with_vllm() -> None:
     """Inside a vLLM process, make the class a LinearMethodBase and list it as weight-loader-v2 capable
     (the reference's decorator keys on the class name, linear.py:330, 347). Outside vLLM nothing is
@@ -334,6 +352,7 @@ def _register_with_vllm() -> None:
 
     if "vllm" not in sys.modules:
         return
+    register_compile_factor()
     try:
         from vllm.model_executor.layers.linear import LinearMethodBase, register_weight_loader_v2_supported_method
 
