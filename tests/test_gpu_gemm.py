@@ -171,3 +171,24 @@ def test_gemm_no_bounded_wait_gave_up():
     flag = ctypes.c_int(-1)
     assert _cabi.lib.gsq_device_error_flag(ctypes.byref(flag)) == 0
     assert flag.value == 0
+
+
+def test_prefill_waits_suspended_by_the_hardware_give_the_same_result():
+    """The fp16-operand prefill GEMM with its mbarrier waits in the time-limited try_wait form (gsq_debug_gemm_wait_hint)
+    instead of polls with short sleeps: bit-identical results, no wait gives up."""
+    raw, w = _weights("IQ3_S", 272, 5120, 77)
+    x = _x(600, 5120, torch.bfloat16, 78).to(DEV)
+    old_v = _cabi.lib.gsq_debug_gemm_variant(3)
+    try:
+        a = torch.ops._C_gguf.lcpp_mul_mat_iq3_packed(w, x, IQ3_S, 272)
+        old_h = _cabi.lib.gsq_debug_gemm_wait_hint(2000)
+        try:
+            b = torch.ops._C_gguf.lcpp_mul_mat_iq3_packed(w, x, IQ3_S, 272)
+        finally:
+            _cabi.lib.gsq_debug_gemm_wait_hint(old_h)
+        torch.cuda.synchronize()
+    finally:
+        _cabi.lib.gsq_debug_gemm_variant(old_v)
+    assert torch.equal(a, b)
+    flag = ctypes.c_int(-1)
+    assert _cabi.lib.gsq_device_error_flag(ctypes.byref(flag)) == 0 and flag.value == 0

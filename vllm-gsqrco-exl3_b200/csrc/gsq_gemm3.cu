@@ -21,7 +21,7 @@
 //     quantize_q8_1_tiles_kernel, fp16 layout) with one bulk copy per unit into a 5-deep ring and issues the MMAs:
 //     2 instructions of 128 x 256 x 16 per unit into one half of tensor memory, the other half being drained
 //     meanwhile. (N = 256 reads the weight slice from shared memory once per 256 tokens; with four N = 64 sub-tiles
-//     the operand reads alone took a third of the shared-memory bandwidth, which is what bounds this kernel.)
+//     the operand reads alone took a third of the shared-memory bandwidth.)
 //   * 16 consumer warps (4 per tensor-memory lane quarter, 64 columns each) read the sums with tcgen05.ld and
 //     accumulate y += (S * d_w) * d_x in 64 fp32 registers per thread over the whole of K.
 // All hand-offs are mbarriers; every wait is bounded and raises a CTA-wide abort flag (and the sticky device flag read
