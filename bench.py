@@ -505,6 +505,7 @@ def run_ours(args):
             out["decode_stack"] = extra_decode_stack(dev, capture)
             out["low_bit_types"] = extra_low_bit(dev, capture, l2)
             out["fused_steps"] = extra_fused_steps(dev, capture)
+            out["embedding"] = extra_embedding(dev, capture)
         if world == 1 and not args.no_ref_kernels:
             out["ref_kernels"] = ref_kernels(cell_rows, raws, l2)
         if world == 1 and not args.no_cpu_baseline:
@@ -739,6 +740,40 @@ def extra_low_bit(dev, capture, l2_bytes):
     return {"what": "GGUF-order dp4a kernel, 8 activation rows per launch; weight GB/s = weight bytes / time", "cells": rows,
             "ref_kernels": {k2: v for k2, v in ref.items() if k2 != "cells"} if "cells" in ref else ref,
             "ref_cells": ref.get("cells")}
+
+
+def extra_embedding(dev, capture):
+    """Quantised embedding look-up: 2048 and 8 token ids into a [151936, 5120] table (Q6_K and IQ2_S, the two types the
+    model file uses for it), bf16 output; one kernel gathers and dequantises (gsq_dequantize_rows)."""
+    import torch
+
+    from gsq_b200 import synth
+    from gsq_b200.quantization import vocab_embeds
+
+    vocab, k = 151936, 5120
+    rows = []
+    for tname, t in (("Q6_K", 14), ("IQ2_S", 22)):
+        small = torch.from_numpy(synth.make_weight(t, 4096, k, 3300 + t)).to(dev)
+        table = small.repeat(vocab // 4096 + 1, 1)[:vocab].contiguous()      # seeded blocks, tiled to the table's size
+        del small
+        for n in (8, 2048):
+            ids = torch.randint(0, vocab, (n,), device=dev)
+            fn = lambda: vocab_embeds.apply_gguf_embedding(ids, table, t, k, torch.bfloat16)
+            g = capture(lambda: [fn() for _ in range(8)])
+            best = 1e30
+            for _ in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                best = min(best, e0.elapsed_time(e1) * 1e3 / 8)
+            del g
+            moved = n * (table.shape[1] + k * 2)
+            rows.append({"type": tname, "tokens": n, "us": round(best, 2), "GBps_read_plus_written": round(moved / best / 1e3, 1)})
+        del table
+        torch.cuda.empty_cache()
+    return {"what": "ids -> [tokens, 5120] bf16 from a 151936-row quantised table, gather + dequantise in one kernel", "cells": rows}
 
 
 def extra_fused_steps(dev, capture):

@@ -120,6 +120,19 @@ int gsq_quantize_q8_1(const void* x, int x_dtype, int64_t m, int64_t k, int64_t 
                       void* stream);
 
 /*
+ * Row gather + dequantisation (the quantised embedding look-up): out[i, :] = dequantise(w[ids[i], :]) for the ten types
+ * above. Replaces torch.index_select + _C_gguf::ggml_dequantize (quantization/vocal_embeds.py:79-98,
+ * csrc/gguf/gguf_kernel.cu:87-103). fp32 arithmetic in the operation order of llama.cpp's C dequantiser / gguf-py
+ * (bit-identical to the reference's dequantisation fixtures in fp32); fp16 / bf16 outputs are that value rounded once.
+ *   w [w_rows, row_bytes] in GGUF order (not repacked); ids: n int64 row indices on the device, or NULL for rows 0..n-1;
+ *   out [n, k] with row stride out_row_stride elements. An index outside [0, w_rows) writes a row of zeros and raises
+ *   the flag read by gsq_dequantize_bad_index_flag (nothing out of bounds is read).
+ */
+int gsq_dequantize_rows(const void* w, int64_t row_bytes, int64_t w_rows, int ggml_type, const int64_t* ids, int64_t n,
+                        int64_t k, void* out, int out_dtype, int64_t out_row_stride, void* stream);
+int gsq_dequantize_bad_index_flag(int* flag);
+
+/*
  * The element-wise step in front of a quantised linear fused with its q8_1 quantiser (block_q8_1 layout, as
  * gsq_quantize_q8_1 writes it). Not in the reference, whose layers run vLLM's rms_norm / silu_and_mul kernels and
  * then quantise inside apply(); the arithmetic here is theirs (every intermediate rounded to X's type where the
