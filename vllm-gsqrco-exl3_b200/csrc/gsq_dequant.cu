@@ -124,10 +124,39 @@ __device__ __forceinline__ void dequant_slice(const uint8_t* b, int s, float (&o
   }
 }
 
+// 32 consecutive values as 16-byte stores (dst 16-byte aligned)
+template <typename T>
+__device__ __forceinline__ void store32(T* dst, const float (&o)[32]);
+template <>
+__device__ __forceinline__ void store32<float>(float* dst, const float (&o)[32]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) reinterpret_cast<float4*>(dst)[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+}
+template <>
+__device__ __forceinline__ void store32<__half>(__half* dst, const float (&o)[32]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __half2 h[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(o[8 * i + 2 * e], o[8 * i + 2 * e + 1]);
+    reinterpret_cast<uint4*>(dst)[i] = *reinterpret_cast<const uint4*>(h);
+  }
+}
+template <>
+__device__ __forceinline__ void store32<__nv_bfloat16>(__nv_bfloat16* dst, const float (&o)[32]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 h[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(o[8 * i + 2 * e], o[8 * i + 2 * e + 1]);
+    reinterpret_cast<uint4*>(dst)[i] = *reinterpret_cast<const uint4*>(h);
+  }
+}
+
 template <int KIND, typename T>
 __global__ void __launch_bounds__(256) dequant_rows_kernel(const uint8_t* __restrict__ w, int64_t row_bytes, int64_t w_rows,
                                                           const int64_t* __restrict__ ids, int nsb, T* __restrict__ out,
-                                                          int64_t ldo, int* __restrict__ bad_id) {
+                                                          int64_t ldo, int* __restrict__ bad_id, bool vec) {
   const int64_t orow = blockIdx.x;
   int64_t src = ids ? ids[orow] : orow;
   if (src < 0 || src >= w_rows) {          // an index outside the table: flagged, the row is written as zeros
@@ -144,8 +173,12 @@ __global__ void __launch_bounds__(256) dequant_rows_kernel(const uint8_t* __rest
       for (int i = 0; i < 32; ++i) o[i] = 0.0f;
     }
     T* dst = out + orow * ldo + (int64_t)sb * 256 + s * 32;
+    if (vec) {
+      store32<T>(dst, o);
+    } else {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) store_out<T>(dst + i, o[i]);
+      for (int i = 0; i < 32; ++i) store_out<T>(dst + i, o[i]);
+    }
   }
 }
 
@@ -158,16 +191,17 @@ static int launch_dequant(const void* w, int64_t row_bytes, int64_t w_rows, cons
   GSQ_CUDA_TRY(cudaGetSymbolAddress((void**)&bad, g_dequant_bad_id));
   const int nsb = (int)(k >> 8);
   const unsigned grid = (unsigned)n;
+  const bool vec = (uintptr_t)out % 16 == 0 && (ldo * (out_dtype == GSQ_F32 ? 4 : 2)) % 16 == 0;
   switch (out_dtype) {
     case GSQ_F32:
-      dequant_rows_kernel<KIND, float><<<grid, 256, 0, st>>>((const uint8_t*)w, row_bytes, w_rows, ids, nsb, (float*)out, ldo, bad);
+      dequant_rows_kernel<KIND, float><<<grid, 256, 0, st>>>((const uint8_t*)w, row_bytes, w_rows, ids, nsb, (float*)out, ldo, bad, vec);
       break;
     case GSQ_F16:
-      dequant_rows_kernel<KIND, __half><<<grid, 256, 0, st>>>((const uint8_t*)w, row_bytes, w_rows, ids, nsb, (__half*)out, ldo, bad);
+      dequant_rows_kernel<KIND, __half><<<grid, 256, 0, st>>>((const uint8_t*)w, row_bytes, w_rows, ids, nsb, (__half*)out, ldo, bad, vec);
       break;
     case GSQ_BF16:
       dequant_rows_kernel<KIND, __nv_bfloat16><<<grid, 256, 0, st>>>((const uint8_t*)w, row_bytes, w_rows, ids, nsb,
-                                                                    (__nv_bfloat16*)out, ldo, bad);
+                                                                    (__nv_bfloat16*)out, ldo, bad, vec);
       break;
     default: return GSQ_ERR_UNSUPPORTED;
   }

@@ -81,6 +81,15 @@ def _lcpp_op(n: int, weight_type: int, rows: int, k: int, packed: bool = False) 
     return "lcpp_mul_mat_q" if n >= 8 else "lcpp_mul_mat_vec_q"
 
 
+def _unquantized_gemm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """x @ weight.T (+ bias) for an F32 / F16 / BF16 tensor of the file. Up to 8 activation rows times a weight of at
+    most 128 rows run as a batched gemv, as in the reference (linear.py:281-291: the library GEMM picked for that shape
+    is several times slower than reading the small weight once per row)."""
+    if x.shape[0] <= 8 and weight.shape[0] <= 128 and bias is None:
+        return torch.bmm(x.unsqueeze(1), weight.T.expand(x.shape[0], -1, -1)).squeeze(1)
+    return torch.nn.functional.linear(x, weight, bias)
+
+
 def _require_route() -> None:
     if not ops.LCPP_ENABLED:
         raise RuntimeError("VLLM_GGUF_LCPP=0: this package only implements that route and has no other path")
@@ -99,7 +108,7 @@ def _fused_mul_mat_gguf(
     if n == 0:
         return torch.empty(0, rows, dtype=x.dtype, device=x.device)
     if weight_type in ops.UNQUANTIZED_TYPES:
-        return x @ weight.T
+        return _unquantized_gemm(x, weight)
     _require_route()
     if weight_type not in ops.LCPP_QUANT_TYPES:
         raise NotImplementedError(f"Unsupported GGUF quantization type: {weight_type}")
