@@ -506,6 +506,7 @@ def run_ours(args):
             out["low_bit_types"] = extra_low_bit(dev, capture, l2)
             out["fused_steps"] = extra_fused_steps(dev, capture)
             out["embedding"] = extra_embedding(dev, capture)
+            out["gguf_load"] = extra_gguf_load(dev)
         if world == 1 and not args.no_ref_kernels:
             out["ref_kernels"] = ref_kernels(cell_rows, raws, l2)
         if world == 1 and not args.no_cpu_baseline:
@@ -774,6 +775,52 @@ def extra_embedding(dev, capture):
         del table
         torch.cuda.empty_cache()
     return {"what": "ids -> [tokens, 5120] bf16 from a 151936-row quantised table, gather + dequantise in one kernel", "cells": rows}
+
+
+def extra_gguf_load(dev):
+    """GGUF file -> GPU layers (gsq_b200.gguf_load): a synthetic file of 8 IQ3_S [17408, 5120] and 2 Q6_K [16384, 5120]
+    tensors written to the local temp directory, then loaded as single-tensor layers (memory-mapped read, pinned staging,
+    device copy, in-place GPU repack); seconds and GB/s of file bytes."""
+    import tempfile
+
+    import numpy as np
+    import torch
+
+    try:
+        import gguf
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": "gguf python package: " + str(e)[:100]}
+    from gsq_b200 import gguf_load, synth
+
+    with tempfile.TemporaryDirectory() as td:
+        path = os.path.join(td, "synthetic.gguf")
+        w = gguf.GGUFWriter(path, "gsq-synthetic")
+        names, total = [], 0
+        base3 = synth.make_weight(21, 17408, 5120, 3400)
+        base6 = synth.make_weight(14, 16384, 5120, 3401)
+        for i in range(8):
+            names.append(f"blk.{i}.ffn_gate.weight")
+            w.add_tensor(names[-1], np.roll(base3, 16 * i, axis=0), raw_dtype=gguf.GGMLQuantizationType(21))
+            total += base3.nbytes
+        for i in range(2):
+            names.append(f"blk.{i}.attn_output.weight")
+            w.add_tensor(names[-1], np.roll(base6, 16 * i, axis=0), raw_dtype=gguf.GGMLQuantizationType(14))
+            total += base6.nbytes
+        w.write_header_to_file()
+        w.write_kv_data_to_file()
+        w.write_tensors_to_file()
+        w.close()
+        tens = gguf_load.tensors(path)
+        stager = gguf_load._Stager(dev)
+        gguf_load.load_linear(tens, [names[0]], dev, torch.bfloat16, stager)      # warm-up: kernels, pinned buffer
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        layers = [gguf_load.load_linear(tens, [n], dev, torch.bfloat16, stager) for n in names]
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        packed = sum(1 for l, _ in layers if getattr(l.weight, "iq3_packed", False))
+    return {"what": "10 tensors (8 IQ3_S 17408 x 5120, 2 Q6_K 16384 x 5120) from a GGUF file in the page cache to repacked GPU "
+                    "layers", "file_bytes": total, "seconds": round(dt, 4), "GBps": round(total / dt / 1e9, 2), "layers_repacked": packed}
 
 
 def extra_fused_steps(dev, capture):
