@@ -669,6 +669,20 @@ def extra_prefill(dev, capture):
 
     peak = int8_peak(dev)
     rows = []
+    from gsq_b200 import lcpp_ops
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 3
+
     for tname, t, n, k in (("IQ3_S", 21, 17408, 5120), ("IQ4_XS", 23, 5120, 17408)):
         w = torch.from_numpy(synth.make_weight(t, n, k, 1300)).to(dev)
         packed = t == 21
@@ -677,20 +691,36 @@ def extra_prefill(dev, capture):
         for m in (2048, 8192, 16384):
             x = torch.from_numpy(synth.make_activation(m, k, 1400 + m, outliers=1e-3)).to(torch.bfloat16).to(dev)
             fn = lambda: linear.fused_mul_mat_gguf(x, w, t, None, packed)
-            for _ in range(2):
-                fn()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(3):
-                fn()
-            e1.record()
-            torch.cuda.synchronize()
-            ms = e0.elapsed_time(e1) / 3
+            ms = timed(fn)
             tops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
-            rows.append({"type": tname, "m": m, "n": n, "k": k, "ms": round(ms, 3), "int8_TOPS": round(tops, 1),
-                         "frac_nominal": round(tops / NOMINAL_INT8_TOPS, 4),
-                         "frac_measured": round(tops / peak, 4) if peak else None})
+            row = {"type": tname, "m": m, "n": n, "k": k, "ms": round(ms, 3), "int8_TOPS": round(tops, 1),
+                   "frac_nominal": round(tops / NOMINAL_INT8_TOPS, 4),
+                   "frac_measured": round(tops / peak, 4) if peak else None}
+            if packed:
+                # the other two forms of this product (gsq_prefill_precision), and how far the default is from the one
+                # that keeps the reference's exact integer slice sums, relative to the result's norm
+                row["form"] = "rounded (default)"
+                xf = x.float() if m == 2048 else None        # fp32 in, fp32 out: no output rounding in the comparison
+                cmp_fn = lambda: linear.fused_mul_mat_gguf(xf, w, t, None, packed)
+                y0 = cmp_fn() if m == 2048 else None
+                for name, mode in (("split", lcpp_ops.PREFILL_SPLIT), ("integer", lcpp_ops.PREFILL_INTEGER)):
+                    lcpp_ops.set_prefill_precision(mode)
+                    try:
+                        row[name + "_TOPS"] = round(2.0 * m * n * k / (timed(fn) * 1e-3) / 1e12, 1)
+                        if m == 2048:
+                            y1 = cmp_fn()
+                            row["rounded_vs_" + name] = float(((y0 - y1).norm() / y1.norm()).item())
+                            if name == "integer":
+                                yi = y1
+                            else:
+                                ys = y1
+                    finally:
+                        lcpp_ops.set_prefill_precision(lcpp_ops.PREFILL_ROUNDED)
+                if m == 2048:
+                    row["split_vs_integer"] = float(((ys - yi).norm() / yi.norm()).item())
+                    del y1, ys, yi
+                del y0, xf
+            rows.append(row)
             del x
         del w
     return {"int8_peak_nominal_TOPS": NOMINAL_INT8_TOPS, "int8_peak_measured_TOPS": peak,

@@ -59,17 +59,22 @@ CASES = [("IQ3_S", 128, 512), ("IQ3_S", 272, 5120), ("IQ3_S", 48, 1024), ("Q4_K"
          ("IQ4_XS", 128, 512), ("IQ4_XS", 202, 5120), ("IQ4_XS", 300, 17408)]
 
 
-@pytest.fixture(params=["prefill", "prefill_int8", "specialised", "lockstep", "default"], autouse=True)
+@pytest.fixture(params=["prefill", "prefill_split", "prefill_integer", "prefill_int8", "specialised", "lockstep", "default"],
+                autouse=True)
 def gemm_variant(request):
     """The tcgen05 GEMM kernels at every row count: the warp-specialised prefill GEMMs on operand-ordered activation
-    tiles (weights decoded once per 256 tokens; for repacked IQ3_S "prefill" is the kernel with fp16 operands that
-    carry the sub-scales and "prefill_int8" the int8 one, for the other types both names are the int8 kernel), the
-    two older kernels on 128-value blocks (warp-specialised and all-warps-in-lockstep); and the library's own choice,
-    which up to 48 rows is the register-operand kernel."""
+    tiles (weights decoded once per 256 tokens; for repacked IQ3_S "prefill" is the kernel with fp16 operands in its
+    default form -- sub-scales and rounded activation products in the operands, sums over a superblock --,
+    "prefill_split" the same with the products as fp16 pairs, "prefill_integer" the form with exact integer slice sums
+    and "prefill_int8" the int8 kernel; for the other types all these names are the int8 kernel), the two older
+    kernels on 128-value blocks (warp-specialised and all-warps-in-lockstep); and the library's own choice, which up
+    to 48 rows is the register-operand kernel."""
     callspec = getattr(request.node, "callspec", None)
-    if request.param == "prefill_int8" and callspec is not None and callspec.params.get("name", "IQ3_S") != "IQ3_S":
+    if request.param in ("prefill_int8", "prefill_split", "prefill_integer") and callspec is not None \
+            and callspec.params.get("name", "IQ3_S") != "IQ3_S":
         pytest.skip("the same kernel as 'prefill' for this type")
-    variant = {"prefill": 3, "prefill_int8": 4, "specialised": 1, "lockstep": 2, "default": 0}[request.param]
+    variant = {"prefill": 3, "prefill_split": 5, "prefill_integer": 7, "prefill_int8": 4, "specialised": 1, "lockstep": 2,
+               "default": 0}[request.param]
     old = _cabi.lib.gsq_debug_gemm_variant(variant)
     old_mode = _cabi.lib.gsq_debug_mmv_mode(0 if request.param == "default" else 1)
     yield request.param
@@ -173,12 +178,13 @@ def test_gemm_no_bounded_wait_gave_up():
     assert flag.value == 0
 
 
-def test_prefill_waits_suspended_by_the_hardware_give_the_same_result():
-    """The fp16-operand prefill GEMM with its mbarrier waits in the time-limited try_wait form (gsq_debug_gemm_wait_hint)
-    instead of polls with short sleeps: bit-identical results, no wait gives up."""
+@pytest.mark.parametrize("form", [6, 5, 7])
+def test_prefill_waits_suspended_by_the_hardware_give_the_same_result(form):
+    """The fp16-operand prefill GEMM (its rounded, split and integer forms) with its mbarrier waits in the time-limited
+    try_wait form (gsq_debug_gemm_wait_hint) instead of polls with short sleeps: bit-identical results, no wait gives up."""
     raw, w = _weights("IQ3_S", 272, 5120, 77)
     x = _x(600, 5120, torch.bfloat16, 78).to(DEV)
-    old_v = _cabi.lib.gsq_debug_gemm_variant(3)
+    old_v = _cabi.lib.gsq_debug_gemm_variant(form)
     try:
         a = torch.ops._C_gguf.lcpp_mul_mat_iq3_packed(w, x, IQ3_S, 272)
         old_h = _cabi.lib.gsq_debug_gemm_wait_hint(2000)

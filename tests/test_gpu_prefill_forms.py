@@ -1,0 +1,116 @@
+"""The three forms of the prefill product of repacked IQ3_S (gsq_prefill_precision) against the reference kernels'
+arithmetic (exact integer slice sums scaled in fp32: lcpp_owned_iq3_mma.cu:768-970), restated in float64 by the oracle:
+
+  integer  the same arithmetic: <= 2e-6 of the row norm (fp32 accumulation order)
+  split    d_x * q as an fp16 pair, sums over a superblock in tensor memory: <= 5e-6
+  rounded  d_x * q as one fp16 number (the default): <= 1e-3, the bound stated for this path; about 3e-4 measured
+
+on inputs that stress the per-token power-of-two scaling of the fp16 operands: blocks and whole tokens of zeros,
+an outlier channel, activations from 1e-30 to 3e4, token counts that do not fill a block of 256, row counts that do
+not fill a tile of 128."""
+
+import ctypes
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import gsq_b200  # noqa: F401
+from gsq_b200 import _cabi, lcpp_ops, synth
+from gsq_b200.quantization import iq3_pack
+from oracle import blocks, product, q8_1
+
+pytestmark = pytest.mark.gpu
+IQ3_S = 21
+DEV = "cuda:0"
+FORMS = {"rounded": (6, 1e-3), "split": (5, 5e-6), "integer": (7, 2e-6)}
+
+
+def _case(rows, k, m, scale, seed, dtype=torch.float32):
+    raw = synth.make_weight(IQ3_S, rows, k, seed)
+    w = torch.from_numpy(raw).to(DEV)
+    iq3_pack.pack_(w, IQ3_S)
+    xa = synth.make_activation(m, k, seed + 1).astype(np.float64) * scale
+    xa[min(3, m - 1), :64] = 0.0                      # two blocks of zeros
+    if m > 100:
+        xa[100, :] = 0.0                              # a token of zeros
+    xa[min(5, m - 1), 7] = 40.0 * scale               # an outlier channel
+    # values a 16-bit type holds, off the quantiser's rounding ties (bf16 for the fp32 cases: the range)
+    x = synth.nudge_ties_torch(torch.from_numpy(xa.astype(np.float32)).to(torch.bfloat16 if dtype == torch.float32 else dtype)).to(dtype)
+    q, d, _ = q8_1.quantize_mmq(x.float().numpy(), q8_1.LAYOUT_D4)
+    return raw, w, x, product.product_q81(blocks.decode(raw, IQ3_S), q, d)
+
+
+def _run(form, w, x, rows):
+    old = _cabi.lib.gsq_debug_gemm_variant(form)
+    old_mode = _cabi.lib.gsq_debug_mmv_mode(1)          # the prefill kernel at every token count, also below 49
+    try:
+        y = torch.ops._C_gguf.lcpp_mul_mat_iq3_packed(w, x.to(DEV), IQ3_S, rows)
+        torch.cuda.synchronize()
+    finally:
+        _cabi.lib.gsq_debug_gemm_variant(old)
+        _cabi.lib.gsq_debug_mmv_mode(old_mode)
+    return y
+
+
+@pytest.mark.parametrize("rows,k,m,scale", [(144, 1024, 70, 1.0), (128, 512, 300, 1e-3), (272, 5120, 700, 300.0),
+                                            (256, 2048, 257, 3e4), (128, 1024, 512, 1e-30), (16, 512, 1, 1.0)])
+def test_forms_against_the_reference_arithmetic(rows, k, m, scale):
+    raw, w, x, ref = _case(rows, k, m, scale, 900 + rows + m)
+    errs = {}
+    for name, (form, tol) in FORMS.items():
+        y = _run(form, w, x, rows)
+        assert y.shape == (m, rows) and y.dtype == torch.float32
+        got = y.cpu().numpy()
+        assert np.isfinite(got).all(), name
+        errs[name] = product.rel_err(got, ref)
+        assert errs[name] <= tol, (name, errs)
+        if m > 100:
+            assert not got[100].any(), name           # a token of zeros gives zeros in every form
+    print(f"{rows}x{k} m={m} scale {scale}:", {n: f"{e:.2e}" for n, e in errs.items()})
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, 1e-3), (torch.bfloat16, 5e-3)])
+def test_forms_16bit(dtype, tol):
+    raw, w, x, ref = _case(256, 1024, 300, 1.0, 77, dtype)
+    for name, (form, _) in FORMS.items():
+        y = _run(form, w, x, 256)
+        assert y.dtype == dtype
+        assert product.rel_err(y.float().cpu().numpy(), ref) <= tol, name
+
+
+def test_default_route_and_the_setting():
+    """The library's own choice from 256 tokens on is the rounded form; gsq_prefill_precision switches it, and a form is
+    reproducible bit for bit from call to call."""
+    raw, w, x, ref = _case(272, 2048, 300, 1.0, 55)
+    lib = _cabi.lib
+    forced = {name: _run(form, w, x, 272) for name, (form, _) in FORMS.items()}
+    assert lib.gsq_debug_gemm_variant(0) == 0
+    modes = {"rounded": lcpp_ops.PREFILL_ROUNDED, "split": lcpp_ops.PREFILL_SPLIT, "integer": lcpp_ops.PREFILL_INTEGER}
+    assert lcpp_ops.set_prefill_precision(lcpp_ops.PREFILL_ROUNDED) == lcpp_ops.PREFILL_ROUNDED      # the default
+    try:
+        for name, mode in modes.items():
+            lcpp_ops.set_prefill_precision(mode)
+            y = torch.ops._C_gguf.lcpp_mul_mat_iq3_packed(w, x.to(DEV), IQ3_S, 272)
+            assert torch.equal(y, forced[name]), name
+        assert lcpp_ops.set_prefill_precision(17) == lcpp_ops.PREFILL_INTEGER                        # ignored
+        assert lcpp_ops.set_prefill_precision(lcpp_ops.PREFILL_ROUNDED) == lcpp_ops.PREFILL_INTEGER
+    finally:
+        lcpp_ops.set_prefill_precision(lcpp_ops.PREFILL_ROUNDED)
+    assert not torch.equal(forced["rounded"], forced["integer"])
+    flag = ctypes.c_int(-1)
+    assert lib.gsq_device_error_flag(ctypes.byref(flag)) == 0 and flag.value == 0
+
+
+def test_environment_variable_sets_the_form():
+    code = ("import gsq_b200, sys\nfrom gsq_b200 import lcpp_ops\n"
+            "sys.exit(10 + lcpp_ops.set_prefill_precision(lcpp_ops.PREFILL_ROUNDED))")
+    env = dict(os.environ, GSQ_PREFILL_PRECISION="split")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env["PYTHONPATH"] = os.pathsep.join([os.path.join(root, "vllm-gsqrco-exl3_b200"), root, env.get("PYTHONPATH", "")])
+    assert subprocess.run([sys.executable, "-c", code], env=env).returncode == 10 + lcpp_ops.PREFILL_SPLIT
+    env["GSQ_PREFILL_PRECISION"] = "nonsense"
+    assert subprocess.run([sys.executable, "-c", code], env=env, stderr=subprocess.DEVNULL).returncode not in (10, 11, 12)

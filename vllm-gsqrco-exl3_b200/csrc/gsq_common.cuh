@@ -24,6 +24,9 @@ int record_cuda_error(cudaError_t e);
 
 // activation tiles of the prefill GEMMs: besides GSQ_Q8_LAYOUT_D4 / _DS4, the quants as fp16 with fp32 d (gsq_gemm3.cu)
 constexpr int Q8_TILES_H16 = 2;
+// the products d * q themselves as fp16, scaled by a power of two per token: the rounded product alone (16 KB per unit)
+// or with the rounding's remainder as a second fp16 plane (2 x 16 KB per unit); see gemm3_acc_kernel
+constexpr int Q8_TILES_F16S = 3, Q8_TILES_F16S2 = 4;
 
 struct DeviceInfo {
   int sm_count;

@@ -75,6 +75,7 @@ struct Args {
   int* dump;           // debug: raw int32 slice sums [m][nrows][k / 32]
   unsigned long long* prof;  // debug: per CTA 16 clock counts (see gsq_debug_gemm_profile)
   uint32_t wait_hint;  // 0: poll the mbarriers with short sleeps; else nanoseconds the hardware suspends a waiting thread per try
+  const float* inv_scale;  // gemm3_acc_kernel: 2^-e per token of the padded range (behind the last unit)
 };
 
 struct Smem {
@@ -185,7 +186,9 @@ __device__ __forceinline__ void decode_pair(const uint8_t* p, uint8_t* a, float*
 template <int HF>
 __device__ __forceinline__ void decode_half(const uint8_t* raw, uint8_t* a, float* sa, const uint8_t* grid, int nrows_left,
                                             int pwarp, int lane) {
-  for (int u = pwarp; u < 16; u += PROD_WARPS) {
+  // 16 pieces over 7 warps: the two halves of a superblock start at different warps, so that over a superblock the
+  // warps get 5, 5, 5, 5, 4, 4, 4 pieces (the warps meet at a barrier once per superblock)
+  for (int u = HF ? (pwarp + PROD_WARPS - 2) % PROD_WARPS : pwarp; u < 16; u += PROD_WARPS) {
     const int rec = u >> 1;
     if (16 * rec >= nrows_left) continue;
     if (u & 1) {
@@ -508,14 +511,321 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_kernel(const Args g) {
   if (warp == MMA_WARP) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-static int launch(const Args& g, int sm_count, cudaStream_t st) {
+// ---------------------------------------------------------------------------------------------
+// The same product with the activation scale inside the operand as well, so that tensor memory accumulates over a whole
+// superblock and the sums are read once per 256 values of K instead of once per 32.
+//
+// Operands: the weight tile as above ((1 + 2 ls) * g, exact); the activation tile holds p = d_x * q * 2^e[token]
+// as fp16, either rounded (HU = 1: relative error of an element up to 2^-11, of a result about 2e-4 of its row norm) or
+// as the pair hi = fp16(p), lo = fp16(p - hi) multiplied one after the other into the same accumulator (HU = 2: 22 bits
+// of every p, the fp32 accumulation's own rounding is what is left). 2^e[token] keeps every p below 2^14 whatever
+// the activations' range (quantize_q8_1_tiles_kernel, scaled products). Per superblock and result the consumers do one
+// FMA, y' += C * d_w, and at the end of K y = y' * 2^-e[token].
+//
+// Against the kernel above: the activation slots are released by the MMAs' completion (tcgen05.commit), not by the
+// consumers, and so are the weight stages; the consumers take d_w from the record in global memory (2 bytes per
+// thread and superblock, fetched one superblock ahead), so nothing but tensor memory couples them to the rest.
+constexpr int HB = 16384;               // one fp16 plane of one slice: 256 tokens x 32 values
+constexpr int UBA = 2 * HB;             // one copy and one turn of the MMA thread: two slices (HU = 1) or hi + lo of one (HU = 2)
+constexpr int ACC_B_SLOTS = 3;
+constexpr int ACC_B_AHEAD = 2;
+
+struct SmemAcc {
+  static constexpr int BAR = 0;
+  static constexpr int GRID = 1024;
+  static constexpr int RAW = GRID + GRIDB;
+  static constexpr int A = RAW + RAW_STAGES * RAWB;
+  static constexpr int B = A + A_STAGES * STAGE_A;
+  static constexpr int SAX = B + ACC_B_SLOTS * UBA;      // scratch the shared decoder writes its scale planes to (unused here)
+  static constexpr int TOTAL = SAX + SA_STAGE;
+};
+static_assert(SmemAcc::A % 128 == 0 && SmemAcc::B % 128 == 0, "operand alignment");
+
+template <int HU, bool PROF>
+__global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
+  unsigned long long pw[4] = {0ull, 0ull, 0ull, 0ull};
+  auto tick = [&]() -> unsigned long long { return PROF ? (unsigned long long)clock64() : 0ull; };
+  extern __shared__ __align__(1024) uint8_t smem[];
+  using S = SmemAcc;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // barriers (8 bytes each): a_full[2] a_empty[2] b_full[6] b_empty[6] d_full[2] d_empty[2]
+  const uint32_t bar0 = saddr(smem + S::BAR);
+  const uint32_t a_full = bar0, a_empty = bar0 + 16, b_full = bar0 + 32, b_empty = b_full + 8 * ACC_B_SLOTS,
+                 d_full = b_empty + 8 * ACC_B_SLOTS, d_empty = d_full + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::BAR + 256);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + S::BAR + 260);
+  const uint32_t hint = g.wait_hint;
+  auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
+    return hint ? mbar_wait_hw(bar, parity, hint, abort_flag, &g_error) : mbar_wait(bar, parity, abort_flag, &g_error);
+  };
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(a_full + 8 * i, PROD_THREADS);
+      mbar_init(a_empty + 8 * i, 1);          // the MMAs that read the stage have completed
+      mbar_init(d_full + 8 * i, 1);
+      mbar_init(d_empty + 8 * i, CONS_WARPS);
+    }
+    for (int i = 0; i < ACC_B_SLOTS; ++i) {
+      mbar_init(b_full + 8 * i, 1);
+      mbar_init(b_empty + 8 * i, 1);          // the MMAs that read the slot have completed
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == MMA_WARP) tmem_alloc(saddr(tmem_slot), TMEM_COLS);
+  for (int i = tid; i < 512; i += THREADS) {
+    const uint32_t gv = g_iq3s_grid3[i];
+    const uint32_t pos = gv ^ 0x80808080u, neg = (~gv + 0x01010101u) ^ 0x80808080u;
+    uint4* dst = reinterpret_cast<uint4*>(smem + S::GRID + i * 64);
+#pragma unroll
+    for (int r2 = 0; r2 < 4; ++r2) dst[r2] = make_uint4(pos, neg, pos, neg);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int nsb = g.k >> 8;
+  const int n_items = g.n_row_tiles * g.n_tok_blocks;
+  auto item_rt = [&](int item) { return item % g.n_row_tiles; };
+  auto item_tb = [&](int item) { return item / g.n_row_tiles; };
+
+  if (warp < PROD_WARPS) {
+    // ------------------------------------------------------------------------------------ producers
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PROD_REGS));
+    const int ptid = tid;
+    int f_item = blockIdx.x, f_sb = 0;
+    auto fetch_next = [&](uint32_t n_fetch) {
+      if (f_item < n_items) {
+        fetch_raw(g, item_rt(f_item), f_sb, smem + S::RAW + (n_fetch & 1u) * RAWB, ptid);
+        if (++f_sb == nsb) { f_sb = 0; f_item += gridDim.x; }
+      }
+      cp_async_commit();
+    };
+    fetch_next(0);
+    uint32_t ns = 0;
+    Ring ra = {0u, 0u};
+    bool alive = true;
+    float* sa = reinterpret_cast<float*>(smem + S::SAX);
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      const int rt = item_rt(item);
+      for (int sb = 0; sb < nsb; ++sb, ++ns) {
+        cp_async_wait<0>();
+        asm volatile("bar.sync 1, %0;" ::"n"(PROD_THREADS) : "memory");
+        fetch_next(ns + 1);
+        const uint8_t* raw = smem + S::RAW + (ns & 1u) * RAWB;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const unsigned long long p0 = tick();
+          alive = alive && wait(a_empty + 8 * ra.i, ra.ph ^ 1u);
+          const unsigned long long p1 = tick();
+          pw[0] += p1 - p0;
+          if (alive) {
+            uint8_t* a = smem + S::A + ra.i * STAGE_A;
+            if (hf == 0) {
+              decode_half<0>(raw, a, sa, smem + S::GRID, g.nrows - rt * TR, warp, lane);
+            } else {
+              decode_half<1>(raw, a, sa, smem + S::GRID, g.nrows - rt * TR, warp, lane);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(a_full + 8 * ra.i);
+            pw[1] += tick() - p1;
+          }
+          ra.next(A_STAGES);
+        }
+      }
+    }
+    if (PROF && tid == 0) {
+      g.prof[blockIdx.x * 16 + 0] = pw[0];   // producer: waiting for a free stage
+      g.prof[blockIdx.x * 16 + 1] = pw[1];   // producer: decoding
+    }
+    cp_async_wait<0>();
+  } else if (warp == MMA_WARP) {
+    // ------------------------------------------------------------------------------------ bulk copies + MMA issue
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PROD_REGS));
+    if (lane == 0) {
+      const uint32_t id = idesc();
+      const uint64_t desc_hi = desc16(0u) & 0xFFFFFFFF00000000ull;
+      const uint32_t a_lo0 = (uint32_t)desc16(saddr(smem + S::A)), b_lo0 = (uint32_t)desc16(saddr(smem + S::B));
+      auto desc = [&](uint32_t lo) { return desc_hi | (uint64_t)lo; };
+      const uint32_t b_smem0 = saddr(smem + S::B);
+      // load cursor over the stream of half-units (item, superblock, slice, hi / lo), ACC_B_AHEAD ahead of the MMAs
+      int l_item = blockIdx.x, l_u = 0;
+      const int units_item = 4 * HU * nsb;
+      const uint8_t* l_base = nullptr;
+      auto load_item = [&]() {
+        if (l_item < n_items) l_base = g.xt + (int64_t)item_tb(l_item) * units_item * UBA;
+      };
+      load_item();
+      Ring rl = {0u, 0u};
+      uint32_t n_loaded = 0;
+      bool alive = true;
+      auto load_next = [&]() {
+        if (l_item >= n_items || !alive) return;
+        const unsigned long long l0 = tick();
+        alive = wait(b_empty + 8 * rl.i, rl.ph ^ 1u);
+        pw[3] += tick() - l0;
+        if (!alive) return;
+        mbar_expect_tx(b_full + 8 * rl.i, UBA);
+        bulk_g2s(b_smem0 + rl.i * UBA, l_base + (int64_t)l_u * UBA, UBA, b_full + 8 * rl.i);
+        rl.next(ACC_B_SLOTS);
+        ++n_loaded;
+        if (++l_u == units_item) {
+          l_u = 0;
+          l_item += gridDim.x;
+          load_item();
+        }
+      };
+      for (int i = 0; i < ACC_B_AHEAD; ++i) load_next();
+      Ring ra = {0u, 0u}, rb = {0u, 0u}, rd = {0u, 0u};
+      uint32_t n_used = 0;
+      for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+        for (int st2 = 0; st2 < 2 * nsb && alive; ++st2) {
+          const unsigned long long m0 = tick();
+          alive = wait(a_full + 8 * ra.i, ra.ph);
+          pw[0] += tick() - m0;
+          if (!alive) break;
+          if ((st2 & 1) == 0) {
+            // a new superblock starts a new sum: the consumers have drained this half of tensor memory
+            const unsigned long long m1 = tick();
+            alive = wait(d_empty + 8 * rd.i, rd.ph ^ 1u);
+            pw[1] += tick() - m1;
+            if (!alive) break;
+          }
+          const uint32_t a_lo = a_lo0 + ra.i * (STAGE_A >> 4);
+          const uint32_t d_addr = tmem_base + rd.i * 256;
+#pragma unroll 1
+          for (int u2 = 0; u2 < 2 * HU && alive; ++u2) {
+            const unsigned long long m3 = tick();
+            alive = wait(b_full + 8 * rb.i, rb.ph);
+            pw[2] += tick() - m3;
+            if (!alive) break;
+            tc_fence_after();
+            const uint32_t b_lo = b_lo0 + rb.i * (UBA >> 4);
+            // HU = 1: slices 2 u2, 2 u2 + 1 against the unit's two planes; HU = 2: slice u2 against hi, then lo
+            const uint32_t as0 = a_lo + (HU == 1 ? 2 * u2 : u2) * (SL_A >> 4), as1 = HU == 1 ? as0 + (SL_A >> 4) : as0;
+            mma_f16(d_addr, desc(as0), desc(b_lo), id, ((st2 & 1) == 0 && u2 == 0) ? 0u : 1u);
+            mma_f16(d_addr, desc(as0 + (256 >> 4)), desc(b_lo + (256 >> 4)), id, 1u);
+            mma_f16(d_addr, desc(as1), desc(b_lo + (HB >> 4)), id, 1u);
+            mma_f16(d_addr, desc(as1 + (256 >> 4)), desc(b_lo + ((HB + 256) >> 4)), id, 1u);
+            mma_commit(b_empty + 8 * rb.i);
+            rb.next(ACC_B_SLOTS);
+            ++n_used;
+            load_next();
+          }
+          if (!alive) break;
+          mma_commit(a_empty + 8 * ra.i);
+          ra.next(A_STAGES);
+          if (st2 & 1) {
+            mma_commit(d_full + 8 * rd.i);
+            rd.next(2);
+          }
+        }
+      }
+      if (PROF) {
+        g.prof[blockIdx.x * 16 + 2] = pw[0];   // MMA thread: waiting for a decoded weight tile
+        g.prof[blockIdx.x * 16 + 3] = pw[1];   // MMA thread: waiting for a drained half of tensor memory
+        g.prof[blockIdx.x * 16 + 4] = pw[2];   // MMA thread: waiting for an activation half-unit to land
+        g.prof[blockIdx.x * 16 + 5] = pw[3];   // MMA thread: waiting for a free activation slot
+
+      }
+      if (!alive) {
+        // a wait gave up: let the copies already issued land (bounded) before the CTA's shared memory goes away
+        for (; n_used < n_loaded; ++n_used) {
+          wait(b_full + 8 * rb.i, rb.ph);
+          rb.next(ACC_B_SLOTS);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------------------------ consumers
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(CONS_REGS));
+    const int cw = warp - CONS_WARP0, q4 = warp & 3, cg = cw >> 2;
+    const int r_in = 32 * q4 + lane;
+    const uint32_t t_warp = tmem_base + ((uint32_t)(32 * q4) << 16) + (uint32_t)(64 * cg);
+    Ring rd = {0u, 0u};
+    bool alive = true;
+    for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+      const int rt = item_rt(item), tok0 = item_tb(item) * NT + 64 * cg;
+      const int row = rt * TR + r_in;
+      const bool row_ok = row < g.nrows;
+      // fp16 d of this thread's row: halfword (row % 16) / 8 of word row % 8 at byte 1728 of its 16-row record
+      const uint8_t* dwp = g.w + (int64_t)(row & ~15) * g.row_bytes + 1728 + 4 * (row & 7) + 2 * ((row >> 3) & 1);
+      auto load_dw = [&](int sb) -> float {
+        return row_ok ? h2f(*reinterpret_cast<const uint16_t*>(dwp + (int64_t)sb * 1760)) : 0.0f;
+      };
+      float2 acc[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) acc[i] = make_float2(0.0f, 0.0f);
+      float dw_next = load_dw(0);
+      for (int sb = 0; sb < nsb && alive; ++sb) {
+        const float dw = dw_next;
+        if (sb + 1 < nsb) dw_next = load_dw(sb + 1);
+        const unsigned long long c2t = tick();
+        alive = wait(d_full + 8 * rd.i, rd.ph);
+        const unsigned long long c3t = tick();
+        pw[2] += c3t - c2t;
+        if (!alive) break;
+        tc_fence_after();
+        const uint32_t t_unit = t_warp + rd.i * 256;
+        const float2 dw2 = make_float2(dw, dw);
+        uint32_t c0[8], c1[8];
+        tmem_ld8(t_unit, c0);
+#pragma unroll
+        for (int ch = 0; ch < 8; ch += 2) {
+          tmem_ld_wait();
+          tmem_ld8(t_unit + 8 * (ch + 1), c1);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            acc[4 * ch + j] = __ffma2_rn(make_float2(__uint_as_float(c0[2 * j]), __uint_as_float(c0[2 * j + 1])), dw2, acc[4 * ch + j]);
+          tmem_ld_wait();
+          if (ch < 6) tmem_ld8(t_unit + 8 * (ch + 2), c0);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            acc[4 * (ch + 1) + j] = __ffma2_rn(make_float2(__uint_as_float(c1[2 * j]), __uint_as_float(c1[2 * j + 1])), dw2, acc[4 * (ch + 1) + j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(d_empty + 8 * rd.i);
+        pw[3] += tick() - c3t;
+        rd.next(2);
+      }
+      if (alive && row_ok) {
+        const float* inv = g.inv_scale + tok0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int tok = tok0 + 2 * i;
+          const float2 is = *reinterpret_cast<const float2*>(inv + 2 * i);   // (the padded range: always readable)
+          if (tok < g.m) store_out_dyn(g.y, g.y_dtype, (int64_t)tok * g.ldy + row, acc[i].x * is.x);
+          if (tok + 1 < g.m) store_out_dyn(g.y, g.y_dtype, (int64_t)(tok + 1) * g.ldy + row, acc[i].y * is.y);
+        }
+      }
+    }
+  }
+  if (PROF && lane == 0 && (warp == CONS_WARP0 || warp == CONS_WARP0 + 3 || warp == CONS_WARP0 + 15)) {
+    const int o = warp == CONS_WARP0 ? 6 : warp == CONS_WARP0 + 3 ? 9 : 12;
+    g.prof[blockIdx.x * 16 + o + 1] = pw[2];   // consumer: waiting for a superblock's sums
+    g.prof[blockIdx.x * 16 + o + 2] = pw[3];   // consumer: reading and scaling them
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+static int launch(const Args& g, int sm_count, int acc, cudaStream_t st) {
   static bool configured[64];
   int dev = 0;
   GSQ_CUDA_TRY(cudaGetDevice(&dev));
-  constexpr int smem = Smem::TOTAL;
-  static_assert(smem <= 227 * 1024, "shared memory budget");
+  constexpr int smem = Smem::TOTAL, smem_acc = SmemAcc::TOTAL;
+  static_assert(smem <= 227 * 1024 && smem_acc <= 227 * 1024, "shared memory budget");
   if (dev < 0 || dev >= 64) return GSQ_ERR_UNSUPPORTED;
   if (!configured[dev]) {
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm3_acc_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_acc));
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm3_acc_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_acc));
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm3_acc_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_acc));
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm3_acc_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_acc));
     GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm3_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm3_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm3_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -523,7 +833,16 @@ static int launch(const Args& g, int sm_count, cudaStream_t st) {
   }
   const int n_items = g.n_row_tiles * g.n_tok_blocks;
   const int grid = n_items < sm_count ? n_items : sm_count;
-  if (g.dump) {
+  if (acc) {
+    if (g.dump) return GSQ_ERR_UNSUPPORTED;   // no per-slice integer sums exist in this form
+    if (acc == 1) {
+      if (g.prof) gemm3_acc_kernel<1, true><<<grid, THREADS, smem_acc, st>>>(g);
+      else gemm3_acc_kernel<1, false><<<grid, THREADS, smem_acc, st>>>(g);
+    } else {
+      if (g.prof) gemm3_acc_kernel<2, true><<<grid, THREADS, smem_acc, st>>>(g);
+      else gemm3_acc_kernel<2, false><<<grid, THREADS, smem_acc, st>>>(g);
+    }
+  } else if (g.dump) {
     gemm3_kernel<1><<<grid, THREADS, smem, st>>>(g);
   } else if (g.prof) {
     gemm3_kernel<2><<<grid, THREADS, smem, st>>>(g);
@@ -547,17 +866,19 @@ int gemm3_error_flag(int* flag) {
   return GSQ_OK;
 }
 
-// bytes of the fp16 activation units of m tokens x k columns (tokens padded to whole blocks of 256)
-size_t gemm3_tile_bytes(int64_t m, int64_t k) {
+// bytes of the fp16 activation units of m tokens x k columns (tokens padded to whole blocks of 256). acc: 0 = quants
+// and d per slice, 1 / 2 = scaled products in one / two fp16 planes, then one float per token
+size_t gemm3_tile_bytes(int64_t m, int64_t k, int acc) {
   const int64_t tb = (m + g3::NT - 1) / g3::NT;
+  if (acc) return (size_t)(tb * (k / 256) * 8 * acc * g3::HB + tb * g3::NT * 4);
   return (size_t)(tb * (k / 256) * 8 * g3::UB);
 }
 
 bool gemm3_applies(int ggml_type, int packed, int64_t rows) { return ggml_type == GSQ_TYPE_IQ3_S && packed && rows % 16 == 0; }
 
-// x_tiles: the output of quantize_tiles_host in the fp16 layout
+// x_tiles: the output of quantize_tiles_host in the fp16 layout that goes with acc (Q8_TILES_H16, _F16S, _F16S2)
 int gemm3_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_tiles, int64_t m,
-               int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream) {
+               int64_t k, void* y, int y_dtype, int64_t y_row_stride, int acc, void* stream) {
   if (m == 0 || rows == 0) return GSQ_OK;
   if (m < 0 || rows < 0 || k <= 0 || k % 256 != 0 || !w || !x_tiles || !y) return GSQ_ERR_UNSUPPORTED;
   if (rows > INT32_MAX || k > INT32_MAX || m > INT32_MAX) return GSQ_ERR_TOO_LARGE;
@@ -581,7 +902,9 @@ int gemm3_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
   g.dump = gemm_dump_pointer();
   g.prof = gemm_profile_pointer();
   g.wait_hint = (uint32_t)g_wait_hint;
-  return g3::launch(g, di.sm_count, (cudaStream_t)stream);
+  g.inv_scale = acc ? reinterpret_cast<const float*>((const uint8_t*)x_tiles + (size_t)g.n_tok_blocks * (k / 256) * 8 * acc * g3::HB) : nullptr;
+  if (acc < 0 || acc > 2) return GSQ_ERR_UNSUPPORTED;
+  return g3::launch(g, di.sm_count, acc, (cudaStream_t)stream);
 }
 
 }  // namespace gsq

@@ -19,9 +19,9 @@ int gemm2_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
                int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream);
 // gsq_gemm3.cu
 bool gemm3_applies(int ggml_type, int packed, int64_t rows);
-size_t gemm3_tile_bytes(int64_t m, int64_t k);
+size_t gemm3_tile_bytes(int64_t m, int64_t k, int acc);
 int gemm3_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_tiles, int64_t m,
-               int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream);
+               int64_t k, void* y, int y_dtype, int64_t y_row_stride, int acc, void* stream);
 // gsq_quantize.cu
 int quantize_tiles_host(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride, int layout, void* out, void* stream);
 // gsq_gemm.cu
@@ -30,12 +30,20 @@ int gemm_variant();
 
 static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
+static int g_prefill_precision = GSQ_PREFILL_ROUNDED;
+
 }  // namespace gsq
+
+extern "C" int gsq_prefill_precision(int mode) {
+  const int old = gsq::g_prefill_precision;
+  if (mode >= GSQ_PREFILL_ROUNDED && mode <= GSQ_PREFILL_INTEGER) gsq::g_prefill_precision = mode;
+  return old;
+}
 
 extern "C" size_t gsq_linear_scratch_bytes(int64_t rows, int64_t m, int64_t k, int ggml_type, int packed) {
   if (m <= 0 || k <= 0) return 0;
   const size_t mmq = (size_t)(k / 128) * (size_t)m * 144, q81 = (size_t)(k / 32) * (size_t)m * 36;
-  const size_t tiles = gsq::gemm3_applies(ggml_type, packed, rows) ? gsq::gemm3_tile_bytes(m, k) : gsq::gemm2_tile_bytes(m, k, ggml_type);
+  const size_t tiles = gsq::gemm3_applies(ggml_type, packed, rows) ? gsq::gemm3_tile_bytes(m, k, 2) : gsq::gemm2_tile_bytes(m, k, ggml_type);
   size_t b = mmq > tiles ? mmq : tiles;
   b = b > q81 ? b : q81;
   return gsq::align256(b);
@@ -69,10 +77,17 @@ extern "C" int gsq_linear(const void* w, int64_t row_bytes, int64_t rows, int gg
   const bool big3 = m >= 256 || (m >= 128 && tall);
   const bool big = m >= 512 || (m >= 192 && tall);
   // repacked IQ3_S: the kernel with the sub-scales folded into fp16 operands (variant 4 keeps the int8 kernel for it)
-  if (gemm3_applies(ggml_type, packed, rows) && (variant == 3 || (variant == 0 && big3))) {
-    rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, Q8_TILES_H16, scratch, stream);
+  if (gemm3_applies(ggml_type, packed, rows) && (variant == 3 || variant >= 5 || (variant == 0 && big3))) {
+    // the form that accumulates over a superblock in tensor memory, on one or two fp16 planes of scaled products, or the
+    // one with integer slice sums (also whenever the debug dump of those sums is on); variants 5 / 6 / 7 force one
+    int acc = g_prefill_precision == GSQ_PREFILL_ROUNDED ? 1 : g_prefill_precision == GSQ_PREFILL_SPLIT ? 2 : 0;
+    if (variant == 5) acc = 2;
+    if (variant == 6) acc = 1;
+    if (variant == 7 || gemm_dump_pointer()) acc = 0;
+    rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, acc == 2 ? Q8_TILES_F16S2 : acc == 1 ? Q8_TILES_F16S : Q8_TILES_H16,
+                             scratch, stream);
     if (rc != GSQ_OK) return rc;
-    return gemm3_host(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, stream);
+    return gemm3_host(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, acc, stream);
   }
   if (gemm2_applies(ggml_type, packed, rows) && variant == 4) {
     rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, layout, scratch, stream);

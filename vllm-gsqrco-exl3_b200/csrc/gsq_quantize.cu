@@ -169,6 +169,41 @@ __global__ void __launch_bounds__(256) quantize_q8_1_mmq_kernel(const T* __restr
   }
 }
 
+// Per token (one warp each) the power of two that brings its largest magnitude over all of k to [2^13, 2^14), stored as
+// its reciprocal; tokens past m get 0, a token of zeros 1. For the scaled-product units below.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256) row_scale_kernel(const T* __restrict__ x, float* __restrict__ inv_scale, int64_t m,
+                                                       int64_t mpad, int64_t k, int64_t stride) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= mpad) return;
+  if (row >= m) {
+    if (lane == 0) inv_scale[row] = 0.0f;
+    return;
+  }
+  float amax = 0.0f;
+  for (int64_t c = 8 * lane; c < k; c += 256) {
+    float v[8];
+    load8<T, VEC>(x, row * stride + c, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+  if (lane == 0) {
+    float inv = 1.0f;
+    if (amax > 0.0f && amax <= 3.0e38f) {
+      int e;
+      frexpf(amax, &e);                        // amax = f * 2^e, f in [0.5, 1)
+      const int up = min(max(14 - e, -100), 100);
+      inv = ldexpf(1.0f, -up);
+    }
+    inv_scale[row] = inv;
+  }
+}
+
 // Activation units of the prefill GEMMs (gsq_gemm2.cu, gsq_gemm3.cu): the same quantisation as
 // quantize_q8_1_mmq_kernel (32-value blocks, d = 1 / (127 / amax), D4 or DS4 scales), written in the shared-memory layout
 // of the tensor-core operand so that one bulk copy brings a unit into place. A unit is one 32-value slice of a block
@@ -179,6 +214,10 @@ __global__ void __launch_bounds__(256) quantize_q8_1_mmq_kernel(const T* __restr
 //   fp16 operands (LAYOUT = Q8_TILES_H16): the same quants as fp16 numbers
 //                   [32 token groups][4 K chunks of 8][8 tokens][8 fp16] quants          (16384 bytes)
 //                   [256 tokens] float d                                                 (1024 bytes)
+//   scaled products (LAYOUT = Q8_TILES_F16S / _F16S2): in the fp16 operand order, hi = fp16(d * q * 2^e[token]) (16384
+//                   bytes) and, for _F16S2, lo = fp16(d * q * 2^e - hi) (16384 more); after the last unit one float
+//                   per token of the padded range, 2^-e[token] (row_scale_kernel: 2^e brings the token's largest
+//                   magnitude to [2^13, 2^14), so no product overflows fp16 and hi + lo carries 22 bits of each)
 // Tokens past m (up to the end of the last block) are written as zeros. One CUDA block = 64 tokens x one slice:
 // warp w holds token group w of the 64, lane = (token % 8) * 4 + 8-value piece, so a warp writes whole core matrices.
 template <typename T, bool VEC, int LAYOUT>
@@ -187,7 +226,8 @@ __global__ void __launch_bounds__(256) quantize_q8_1_tiles_kernel(const T* __res
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr bool DS = LAYOUT == GSQ_Q8_LAYOUT_DS4, H16 = LAYOUT == Q8_TILES_H16;
-  constexpr int UB = H16 ? 16384 + 1024 : 8192 + (DS ? 2048 : 1024);
+  constexpr bool F16S = LAYOUT == Q8_TILES_F16S || LAYOUT == Q8_TILES_F16S2, LO = LAYOUT == Q8_TILES_F16S2;
+  constexpr int UB = F16S ? (LO ? 32768 : 16384) : H16 ? 16384 + 1024 : 8192 + (DS ? 2048 : 1024);
   const int slice = blockIdx.x;              // 32-value slice along k
   const int64_t tt = blockIdx.y;             // token tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -219,11 +259,27 @@ __global__ void __launch_bounds__(256) quantize_q8_1_tiles_kernel(const T* __res
   const float d_inv = div_approx(127.0f, amax);
   float q[8];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) q[e] = live ? roundf(v[e] * d_inv) : 0.0f;
+  for (int e = 0; e < 8; ++e) q[e] = live && amax > 0.0f ? roundf(v[e] * d_inv) : 0.0f;   // (a block of zeros: 0 * inf)
   float d = live ? rcp_approx(d_inv) : 0.0f;
   const int sb = slice >> 3, s = slice & 7;
   const int rb = (int)(tt & 3) * 64 + r;   // token within its block of 256
   uint8_t* unit = out + (((tt >> 2) * (k >> 8) + sb) * 8 + s) * UB;
+  if constexpr (F16S) {
+    const float* inv_scale = reinterpret_cast<const float*>(out + (int64_t)gridDim.y / 4 * (k >> 8) * 8 * UB);
+    const float ds = live ? d * (1.0f / inv_scale[row]) : 0.0f;   // a power of two: exact
+    uint8_t* dst = unit + (rb >> 3) * 512 + piece * 128 + (rb & 7) * 16;
+    __half2 hi[4], lo[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float p0 = ds * q[2 * e], p1 = ds * q[2 * e + 1];
+      hi[e] = __floats2half2_rn(p0, p1);
+      const float2 back = __half22float2(hi[e]);
+      lo[e] = __floats2half2_rn(p0 - back.x, p1 - back.y);
+    }
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(hi);
+    if constexpr (LO) *reinterpret_cast<uint4*>(dst + 16384) = *reinterpret_cast<const uint4*>(lo);
+    return;
+  }
   if constexpr (H16) {
     // the lane's 8 values are one 16-byte row of a core matrix (integers up to 127 in magnitude: exact in fp16)
     uint8_t* dst = unit + (rb >> 3) * 512 + piece * 128 + (rb & 7) * 16;
@@ -399,6 +455,15 @@ template <typename T, int LAYOUT>
 static int launch_q8_1_tiles(const void* x, int64_t m, int64_t k, int64_t stride, void* out, cudaStream_t st) {
   if (m == 0) return GSQ_OK;
   const bool vec = ((uintptr_t)x % 16 == 0) && ((stride * (int64_t)sizeof(T)) % 16 == 0);
+  if constexpr (LAYOUT == Q8_TILES_F16S || LAYOUT == Q8_TILES_F16S2) {
+    // first the per-token scales, behind the last unit
+    const int64_t mpad = (m + 255) / 256 * 256;
+    float* inv_scale = reinterpret_cast<float*>((uint8_t*)out + mpad / 256 * (k >> 8) * 8 * (LAYOUT == Q8_TILES_F16S2 ? 32768 : 16384));
+    const unsigned grid = (unsigned)(mpad / 8);
+    const int rc = vec ? launch_pdl(row_scale_kernel<T, true>, grid, st, (const T*)x, inv_scale, m, mpad, k, stride)
+                       : launch_pdl(row_scale_kernel<T, false>, grid, st, (const T*)x, inv_scale, m, mpad, k, stride);
+    if (rc != GSQ_OK) return rc;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(k >> 5), (unsigned)((m + 255) / 256 * 4));   // whole blocks of 256 tokens
   cfg.blockDim = dim3(256);
@@ -422,6 +487,8 @@ int quantize_tiles_host(const void* x, int x_dtype, int64_t m, int64_t k, int64_
   cudaStream_t st = (cudaStream_t)stream;
 #define GSQ_TILES_CASE(T)                                                                                  \
   return layout == Q8_TILES_H16      ? launch_q8_1_tiles<T, Q8_TILES_H16>(x, m, k, stride, out, st)     \
+         : layout == Q8_TILES_F16S   ? launch_q8_1_tiles<T, Q8_TILES_F16S>(x, m, k, stride, out, st)    \
+         : layout == Q8_TILES_F16S2  ? launch_q8_1_tiles<T, Q8_TILES_F16S2>(x, m, k, stride, out, st)   \
          : layout == GSQ_Q8_LAYOUT_D4 ? launch_q8_1_tiles<T, GSQ_Q8_LAYOUT_D4>(x, m, k, stride, out, st) \
                                       : launch_q8_1_tiles<T, GSQ_Q8_LAYOUT_DS4>(x, m, k, stride, out, st)
   switch (x_dtype) {

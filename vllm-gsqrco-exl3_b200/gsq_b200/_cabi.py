@@ -24,7 +24,7 @@ EXPORTS = (
     "gsq_debug_swap_descriptor_strides", "gsq_debug_gemm_dump_sums", "gsq_debug_gemm_ksplit", "gsq_debug_gemm_variant", "gsq_debug_gemm_wait_hint", "gsq_q8_layout_for_type", "gsq_mul_mat_scratch_bytes", "gsq_mul_mat_q8", "gsq_iq3s_repack", "gsq_route", "gsq_linear_vec_static", "gsq_linear_vec_static_max_q8_bytes",
     "gsq_debug_mmv_mode", "gsq_debug_mmv_min_rows", "gsq_debug_mmv_cluster_size", "gsq_mul_mat_vec_max_rows",
     "gsq_debug_mmv_profile", "gsq_debug_mmv_max_rows", "gsq_debug_mmv_pdl", "gsq_debug_mmv_prefetch_first", "gsq_debug_mmv_chunking", "gsq_debug_mmv_trace",
-    "gsq_linear", "gsq_linear_scratch_bytes", "gsq_debug_gemm_profile", "gsq_q6k_repack", "gsq_allreduce_sum", "gsq_allreduce_error_flag", "gsq_linear_allreduce", "gsq_peer_reduce_error_flag", "gsq_rmsnorm_quantize_q8_1", "gsq_silu_mul_quantize_q8_1", "gsq_dequantize_rows", "gsq_dequantize_bad_index_flag",
+    "gsq_linear", "gsq_linear_scratch_bytes", "gsq_debug_gemm_profile", "gsq_q6k_repack", "gsq_allreduce_sum", "gsq_allreduce_error_flag", "gsq_linear_allreduce", "gsq_peer_reduce_error_flag", "gsq_rmsnorm_quantize_q8_1", "gsq_silu_mul_quantize_q8_1", "gsq_dequantize_rows", "gsq_dequantize_bad_index_flag", "gsq_prefill_precision",
 )
 
 
@@ -101,6 +101,8 @@ def _load() -> C.CDLL:
     lib.gsq_mul_mat_q8.argtypes = [vp, i64, i64, ci, ci, vp, i64, i64, vp, ci, i64, vp, sz, vp]
     lib.gsq_linear_scratch_bytes.restype = sz
     lib.gsq_linear_scratch_bytes.argtypes = [i64, i64, i64, ci, ci]
+    lib.gsq_prefill_precision.restype = ci
+    lib.gsq_prefill_precision.argtypes = [ci]
     lib.gsq_linear.restype = ci
     lib.gsq_linear.argtypes = [vp, i64, i64, ci, ci, vp, ci, i64, i64, i64, vp, ci, i64, vp, sz, vp]
     lib.gsq_iq3s_repack.restype = ci

@@ -123,6 +123,17 @@ def set_k_multiple(v: int) -> int:
     return old
 
 
+PREFILL_ROUNDED, PREFILL_SPLIT, PREFILL_INTEGER = 0, 1, 2
+
+
+def set_prefill_precision(mode: int) -> int:
+    """How the prefill product of repacked IQ3_S is formed (gsq_prefill_precision): PREFILL_ROUNDED (default; within
+    about 3e-4 of a row's norm of the reference kernels' result), PREFILL_SPLIT (about 1e-6), PREFILL_INTEGER (the
+    reference's exact integer slice sums). Returns the previous mode. The environment variable GSQ_PREFILL_PRECISION
+    (rounded / split / integer) sets it at import."""
+    return int(_cabi.lib.gsq_prefill_precision(int(mode)))
+
+
 def _stream(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
@@ -283,6 +294,14 @@ def register() -> list[str]:
     global _LIBRARY
     if _LIBRARY is not None:
         return registered
+    import os
+
+    want = os.environ.get("GSQ_PREFILL_PRECISION", "").strip().lower()
+    if want:
+        modes = {"rounded": PREFILL_ROUNDED, "split": PREFILL_SPLIT, "integer": PREFILL_INTEGER}
+        if want not in modes:
+            raise ValueError(f"GSQ_PREFILL_PRECISION={want!r}: expected one of {sorted(modes)}")
+        set_prefill_precision(modes[want])
     _LIBRARY = torch.library.Library("_C_gguf", "FRAGMENT")
     for name, schema in _SCHEMAS.items():
         try:
