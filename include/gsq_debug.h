@@ -38,7 +38,7 @@ int gsq_debug_block_sums(const void* w, int64_t row_bytes, int64_t rows, int ggm
 int gsq_debug_swap_descriptor_strides(int on);
 int gsq_debug_gemm_dump_sums(int32_t* sums);
 int gsq_debug_gemm_wait_hint(int ns); /* fp16-operand prefill GEMM: 0 = poll the mbarriers with short sleeps, else the nanoseconds a waiting thread is suspended per try; returns previous */
-int gsq_debug_gemm_variant(int v); /* kernel behind gsq_linear above the small-batch row counts: 0 = by shape (default), 3 = always a prefill GEMM (fp16 operands for repacked IQ3_S in the form gsq_prefill_precision selects, int8 otherwise), 5 / 6 / 7 = the same with the split / rounded / integer form forced, 4 = always the int8 prefill GEMM, 1 / 2 = the warp-specialised / lockstep kernels of gsq_mul_mat_q8; returns previous */
+int gsq_debug_gemm_variant(int v); /* kernel behind gsq_linear above the small-batch row counts: 0 = by shape (default), 3 = always a prefill GEMM (fp16 operands for repacked IQ3_S in the form gsq_prefill_precision selects, int8 otherwise), 5 / 6 / 7 = the same with the split / rounded / integer form forced, 9 / 8 = the split / rounded form on pairs of CTAs (cta_group::2), 4 = always the int8 prefill GEMM, 1 / 2 = the warp-specialised / lockstep kernels of gsq_mul_mat_q8; returns previous */
 /* device buffer of 16 uint64 per CTA that the prefill GEMM fills with clock counts of its roles' waits and work (a
  * separate instantiation; NULL switches it off): [0] producer waits for a free stage, [1] decodes; MMA thread waits
  * for [2] a weight tile, [3] a drained half of tensor memory, [4] an activation unit; consumer warp 4: [5] waits for

@@ -114,3 +114,17 @@ def test_environment_variable_sets_the_form():
     assert subprocess.run([sys.executable, "-c", code], env=env).returncode == 10 + lcpp_ops.PREFILL_SPLIT
     env["GSQ_PREFILL_PRECISION"] = "nonsense"
     assert subprocess.run([sys.executable, "-c", code], env=env, stderr=subprocess.DEVNULL).returncode not in (10, 11, 12)
+
+
+@pytest.mark.parametrize("rows,k,m", [(272, 5120, 700), (128, 512, 40), (1024, 1024, 1000)])
+def test_two_cta_form_is_bit_identical(rows, k, m):
+    """The same sums formed by pairs of CTAs (tcgen05 cta_group::2: 256 weight rows per instruction, each CTA decoding
+    its 128 rows and copying its half of the tokens; an odd count of row tiles leaves a pair's second CTA without rows):
+    the results of the rounded and the split form are those of the one-CTA kernels bit for bit. It measured slower
+    than one CTA per item (the second half of the activation operand comes from the peer's shared memory) and is
+    reached through the debug switch only."""
+    raw, w, x, ref = _case(rows, k, m, 1.0, 300 + rows)
+    assert torch.equal(_run(8, w, x, rows), _run(6, w, x, rows))
+    assert torch.equal(_run(9, w, x, rows), _run(5, w, x, rows))
+    flag = ctypes.c_int(-1)
+    assert _cabi.lib.gsq_device_error_flag(ctypes.byref(flag)) == 0 and flag.value == 0

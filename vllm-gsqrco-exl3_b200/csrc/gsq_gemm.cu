@@ -884,7 +884,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) gemm_ws_kernel(const GemmArgs g
 static int g_swap_lbo_sbo = 0;
 static int* g_gemm_dump = nullptr;
 static int g_gemm_ksplit = 0;  // experiments: 0 = choose, else 1, 2 or 4
-static int g_gemm_variant = 0;  // behind gsq_linear: 0 = choose by shape, 3 = always a prefill GEMM (gsq_gemm3.cu for repacked IQ3_S, else gsq_gemm2.cu; 5 / 6 / 7: with its split / rounded / integer form forced), 4 = always gsq_gemm2.cu; the kernels of this file: 1 = warp-specialised, 2 = lockstep
+static int g_gemm_variant = 0;  // behind gsq_linear: 0 = choose by shape, 3 = always a prefill GEMM (gsq_gemm3.cu for repacked IQ3_S, else gsq_gemm2.cu; 5 / 6 / 7: with its split / rounded / integer form forced; 9 / 8: split / rounded on pairs of CTAs), 4 = always gsq_gemm2.cu; the kernels of this file: 1 = warp-specialised, 2 = lockstep
 
 int gemm2_error_flag(int* flag);  // gsq_gemm2.cu
 int gemm3_error_flag(int* flag);  // gsq_gemm3.cu
@@ -957,7 +957,7 @@ extern "C" int gsq_debug_swap_descriptor_strides(int on) {
 
 extern "C" int gsq_debug_gemm_variant(int v) {
   const int old = gsq::g_gemm_variant;
-  gsq::g_gemm_variant = (v >= 1 && v <= 7) ? v : 0;
+  gsq::g_gemm_variant = (v >= 1 && v <= 9) ? v : 0;
   return old;
 }
 

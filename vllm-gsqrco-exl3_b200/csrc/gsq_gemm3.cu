@@ -541,7 +541,12 @@ struct SmemAcc {
 };
 static_assert(SmemAcc::A % 128 == 0 && SmemAcc::B % 128 == 0, "operand alignment");
 
-template <int HU, bool PROF>
+// PAIR: two CTAs (a cluster) share an item of 256 weight rows x 256 tokens. Each decodes its own 128 rows and copies
+// only its half of the tokens of every activation unit; the MMAs (M = 256, cta_group::2) are issued by CTA 0 and read
+// both halves, so every CTA moves half the activation bytes from L2 and through its shared memory per result. CTA 0's
+// barriers collect both CTAs' "weight stage decoded" and "sums drained" arrivals; CTA 1 reports each landed unit to
+// CTA 0 (b_peer); MMA completion is signalled to both CTAs at once.
+template <int HU, bool PROF, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
   unsigned long long pw[4] = {0ull, 0ull, 0ull, 0ull};
   auto tick = [&]() -> unsigned long long { return PROF ? (unsigned long long)clock64() : 0ull; };
@@ -549,32 +554,50 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
   using S = SmemAcc;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  // barriers (8 bytes each): a_full[2] a_empty[2] b_full[6] b_empty[6] d_full[2] d_empty[2]
+  constexpr int NB = PAIR ? 2 * ACC_B_SLOTS : ACC_B_SLOTS;      // activation slots (half the bytes each for a pair)
+  constexpr int AHEAD = PAIR ? 2 * ACC_B_AHEAD : ACC_B_AHEAD;
+  constexpr int UBC = PAIR ? UBA / 2 : UBA;                     // bytes of a unit this CTA holds
+  constexpr int PL = PAIR ? HB / 2 : HB;                        // ... of one of its two planes
+  const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = crank == 0u;
+  const int group = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, n_groups = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  // barriers (8 bytes each): a_full[2] a_empty[2] d_full[2] d_empty[2] b_full[NB] b_empty[NB] b_peer[NB]
   const uint32_t bar0 = saddr(smem + S::BAR);
-  const uint32_t a_full = bar0, a_empty = bar0 + 16, b_full = bar0 + 32, b_empty = b_full + 8 * ACC_B_SLOTS,
-                 d_full = b_empty + 8 * ACC_B_SLOTS, d_empty = d_full + 16;
+  const uint32_t a_full = bar0, a_empty = bar0 + 16, d_full = bar0 + 32, d_empty = bar0 + 48, b_full = bar0 + 64,
+                 b_empty = b_full + 8 * NB, b_peer = b_empty + 8 * NB;
+  static_assert(64 + 3 * 8 * 2 * ACC_B_SLOTS <= 256, "barrier area");
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::BAR + 256);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + S::BAR + 260);
   const uint32_t hint = g.wait_hint;
   auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
+    if (PAIR) return mbar_wait_cluster(bar, parity, abort_flag, &g_error);
     return hint ? mbar_wait_hw(bar, parity, hint, abort_flag, &g_error) : mbar_wait(bar, parity, abort_flag, &g_error);
+  };
+  // arrival on a barrier of CTA 0 (the own barrier without a pair)
+  auto arrive_leader = [&](uint32_t bar) {
+    if (PAIR) mbar_arrive_cluster(mapa(bar, 0u));
+    else mbar_arrive(bar);
   };
 
   if (tid == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 2; ++i) {
-      mbar_init(a_full + 8 * i, PROD_THREADS);
+      mbar_init(a_full + 8 * i, PROD_THREADS * (PAIR ? 2 : 1));
       mbar_init(a_empty + 8 * i, 1);          // the MMAs that read the stage have completed
       mbar_init(d_full + 8 * i, 1);
-      mbar_init(d_empty + 8 * i, CONS_WARPS);
+      mbar_init(d_empty + 8 * i, CONS_WARPS * (PAIR ? 2 : 1));
     }
-    for (int i = 0; i < ACC_B_SLOTS; ++i) {
+    for (int i = 0; i < NB; ++i) {
       mbar_init(b_full + 8 * i, 1);
       mbar_init(b_empty + 8 * i, 1);          // the MMAs that read the slot have completed
+      mbar_init(b_peer + 8 * i, 1);           // CTA 1's half of the unit has landed
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == MMA_WARP) tmem_alloc(saddr(tmem_slot), TMEM_COLS);
+  if (warp == MMA_WARP) {
+    if (PAIR) tmem_alloc_pair(saddr(tmem_slot), TMEM_COLS);
+    else tmem_alloc(saddr(tmem_slot), TMEM_COLS);
+  }
   for (int i = tid; i < 512; i += THREADS) {
     const uint32_t gv = g_iq3s_grid3[i];
     const uint32_t pos = gv ^ 0x80808080u, neg = (~gv + 0x01010101u) ^ 0x80808080u;
@@ -583,24 +606,27 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
     for (int r2 = 0; r2 < 4; ++r2) dst[r2] = make_uint4(pos, neg, pos, neg);
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers are initialised before anything arrives on them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   const int nsb = g.k >> 8;
-  const int n_items = g.n_row_tiles * g.n_tok_blocks;
-  auto item_rt = [&](int item) { return item % g.n_row_tiles; };
-  auto item_tb = [&](int item) { return item / g.n_row_tiles; };
+  // items of a CTA (or pair): row tiles (pairs of them) fastest; a pair's second CTA may own a tile past the last row
+  const int n_rt = PAIR ? (g.n_row_tiles + 1) / 2 : g.n_row_tiles;
+  const int n_items = n_rt * g.n_tok_blocks;
+  auto item_rt = [&](int item) { return PAIR ? 2 * (item % n_rt) + (int)crank : item % n_rt; };
+  auto item_tb = [&](int item) { return item / n_rt; };
 
   if (warp < PROD_WARPS) {
     // ------------------------------------------------------------------------------------ producers
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PROD_REGS));
     const int ptid = tid;
-    int f_item = blockIdx.x, f_sb = 0;
+    int f_item = group, f_sb = 0;
     auto fetch_next = [&](uint32_t n_fetch) {
       if (f_item < n_items) {
         fetch_raw(g, item_rt(f_item), f_sb, smem + S::RAW + (n_fetch & 1u) * RAWB, ptid);
-        if (++f_sb == nsb) { f_sb = 0; f_item += gridDim.x; }
+        if (++f_sb == nsb) { f_sb = 0; f_item += n_groups; }
       }
       cp_async_commit();
     };
@@ -609,7 +635,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
     Ring ra = {0u, 0u};
     bool alive = true;
     float* sa = reinterpret_cast<float*>(smem + S::SAX);
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    for (int item = group; item < n_items; item += n_groups) {
       const int rt = item_rt(item);
       for (int sb = 0; sb < nsb; ++sb, ++ns) {
         cp_async_wait<0>();
@@ -629,8 +655,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
             } else {
               decode_half<1>(raw, a, sa, smem + S::GRID, g.nrows - rt * TR, warp, lane);
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(a_full + 8 * ra.i);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> tensor-core reads
+            arrive_leader(a_full + 8 * ra.i);
             pw[1] += tick() - p1;
           }
           ra.next(A_STAGES);
@@ -638,21 +664,21 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
       }
     }
     if (PROF && tid == 0) {
-      g.prof[blockIdx.x * 16 + 0] = pw[0];   // producer: waiting for a free stage
-      g.prof[blockIdx.x * 16 + 1] = pw[1];   // producer: decoding
+      g.prof[(size_t)blockIdx.x * 16 + 0] = pw[0];   // producer: waiting for a free stage
+      g.prof[(size_t)blockIdx.x * 16 + 1] = pw[1];   // producer: decoding
     }
     cp_async_wait<0>();
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------------------------ bulk copies + MMA issue
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PROD_REGS));
     if (lane == 0) {
-      const uint32_t id = idesc();
+      const uint32_t id = PAIR ? (idesc() & ~(0x1Fu << 24)) | ((uint32_t)(2 * TR >> 4) << 24) : idesc();   // M = 256 over the pair
       const uint64_t desc_hi = desc16(0u) & 0xFFFFFFFF00000000ull;
       const uint32_t a_lo0 = (uint32_t)desc16(saddr(smem + S::A)), b_lo0 = (uint32_t)desc16(saddr(smem + S::B));
       auto desc = [&](uint32_t lo) { return desc_hi | (uint64_t)lo; };
       const uint32_t b_smem0 = saddr(smem + S::B);
       // load cursor over the stream of half-units (item, superblock, slice, hi / lo), ACC_B_AHEAD ahead of the MMAs
-      int l_item = blockIdx.x, l_u = 0;
+      int l_item = group, l_u = 0;
       const int units_item = 4 * HU * nsb;
       const uint8_t* l_base = nullptr;
       auto load_item = [&]() {
@@ -668,20 +694,40 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
         alive = wait(b_empty + 8 * rl.i, rl.ph ^ 1u);
         pw[3] += tick() - l0;
         if (!alive) return;
-        mbar_expect_tx(b_full + 8 * rl.i, UBA);
-        bulk_g2s(b_smem0 + rl.i * UBA, l_base + (int64_t)l_u * UBA, UBA, b_full + 8 * rl.i);
-        rl.next(ACC_B_SLOTS);
+        mbar_expect_tx(b_full + 8 * rl.i, UBC);
+        if (PAIR) {
+          // this CTA's tokens of the unit's two planes: 128 of the 256 (the first or second 8 KB of each plane)
+          const uint8_t* src = l_base + (int64_t)l_u * UBA + crank * PL;
+          bulk_g2s(b_smem0 + rl.i * UBC, src, PL, b_full + 8 * rl.i);
+          bulk_g2s(b_smem0 + rl.i * UBC + PL, src + HB, PL, b_full + 8 * rl.i);
+        } else {
+          bulk_g2s(b_smem0 + rl.i * UBC, l_base + (int64_t)l_u * UBA, UBA, b_full + 8 * rl.i);
+        }
+        rl.next(NB);
         ++n_loaded;
         if (++l_u == units_item) {
           l_u = 0;
-          l_item += gridDim.x;
+          l_item += n_groups;
           load_item();
         }
       };
-      for (int i = 0; i < ACC_B_AHEAD; ++i) load_next();
+      for (int i = 0; i < AHEAD; ++i) load_next();
       Ring ra = {0u, 0u}, rb = {0u, 0u}, rd = {0u, 0u};
       uint32_t n_used = 0;
-      for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+      if (PAIR && !leader) {
+        // CTA 1 issues no MMAs: it reports each landed unit to CTA 0 and keeps its own copies going
+        for (int item = group; item < n_items && alive; item += n_groups) {
+          for (int u = 0; u < units_item && alive; ++u) {
+            alive = wait(b_full + 8 * rb.i, rb.ph);
+            if (!alive) break;
+            mbar_arrive_cluster(mapa(b_peer + 8 * rb.i, 0u));
+            rb.next(NB);
+            ++n_used;
+            load_next();
+          }
+        }
+      } else
+      for (int item = group; item < n_items && alive; item += n_groups) {
         for (int st2 = 0; st2 < 2 * nsb && alive; ++st2) {
           const unsigned long long m0 = tick();
           alive = wait(a_full + 8 * ra.i, ra.ph);
@@ -700,42 +746,54 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
           for (int u2 = 0; u2 < 2 * HU && alive; ++u2) {
             const unsigned long long m3 = tick();
             alive = wait(b_full + 8 * rb.i, rb.ph);
+            if (PAIR) alive = alive && wait(b_peer + 8 * rb.i, rb.ph);
             pw[2] += tick() - m3;
             if (!alive) break;
             tc_fence_after();
-            const uint32_t b_lo = b_lo0 + rb.i * (UBA >> 4);
+            const uint32_t b_lo = b_lo0 + rb.i * (UBC >> 4);
             // HU = 1: slices 2 u2, 2 u2 + 1 against the unit's two planes; HU = 2: slice u2 against hi, then lo
             const uint32_t as0 = a_lo + (HU == 1 ? 2 * u2 : u2) * (SL_A >> 4), as1 = HU == 1 ? as0 + (SL_A >> 4) : as0;
-            mma_f16(d_addr, desc(as0), desc(b_lo), id, ((st2 & 1) == 0 && u2 == 0) ? 0u : 1u);
-            mma_f16(d_addr, desc(as0 + (256 >> 4)), desc(b_lo + (256 >> 4)), id, 1u);
-            mma_f16(d_addr, desc(as1), desc(b_lo + (HB >> 4)), id, 1u);
-            mma_f16(d_addr, desc(as1 + (256 >> 4)), desc(b_lo + ((HB + 256) >> 4)), id, 1u);
-            mma_commit(b_empty + 8 * rb.i);
-            rb.next(ACC_B_SLOTS);
+            const uint32_t first = ((st2 & 1) == 0 && u2 == 0) ? 0u : 1u;
+            if (PAIR) {
+              mma_f16_pair(d_addr, desc(as0), desc(b_lo), id, first);
+              mma_f16_pair(d_addr, desc(as0 + (256 >> 4)), desc(b_lo + (256 >> 4)), id, 1u);
+              mma_f16_pair(d_addr, desc(as1), desc(b_lo + (PL >> 4)), id, 1u);
+              mma_f16_pair(d_addr, desc(as1 + (256 >> 4)), desc(b_lo + ((PL + 256) >> 4)), id, 1u);
+              mma_commit_pair(b_empty + 8 * rb.i);
+            } else {
+              mma_f16(d_addr, desc(as0), desc(b_lo), id, first);
+              mma_f16(d_addr, desc(as0 + (256 >> 4)), desc(b_lo + (256 >> 4)), id, 1u);
+              mma_f16(d_addr, desc(as1), desc(b_lo + (PL >> 4)), id, 1u);
+              mma_f16(d_addr, desc(as1 + (256 >> 4)), desc(b_lo + ((PL + 256) >> 4)), id, 1u);
+              mma_commit(b_empty + 8 * rb.i);
+            }
+            rb.next(NB);
             ++n_used;
             load_next();
           }
           if (!alive) break;
-          mma_commit(a_empty + 8 * ra.i);
+          if (PAIR) mma_commit_pair(a_empty + 8 * ra.i);
+          else mma_commit(a_empty + 8 * ra.i);
           ra.next(A_STAGES);
           if (st2 & 1) {
-            mma_commit(d_full + 8 * rd.i);
+            if (PAIR) mma_commit_pair(d_full + 8 * rd.i);
+            else mma_commit(d_full + 8 * rd.i);
             rd.next(2);
           }
         }
       }
       if (PROF) {
-        g.prof[blockIdx.x * 16 + 2] = pw[0];   // MMA thread: waiting for a decoded weight tile
-        g.prof[blockIdx.x * 16 + 3] = pw[1];   // MMA thread: waiting for a drained half of tensor memory
-        g.prof[blockIdx.x * 16 + 4] = pw[2];   // MMA thread: waiting for an activation half-unit to land
-        g.prof[blockIdx.x * 16 + 5] = pw[3];   // MMA thread: waiting for a free activation slot
+        g.prof[(size_t)blockIdx.x * 16 + 2] = pw[0];   // MMA thread: waiting for a decoded weight tile
+        g.prof[(size_t)blockIdx.x * 16 + 3] = pw[1];   // MMA thread: waiting for a drained half of tensor memory
+        g.prof[(size_t)blockIdx.x * 16 + 4] = pw[2];   // MMA thread: waiting for an activation half-unit to land
+        g.prof[(size_t)blockIdx.x * 16 + 5] = pw[3];   // MMA thread: waiting for a free activation slot
 
       }
       if (!alive) {
         // a wait gave up: let the copies already issued land (bounded) before the CTA's shared memory goes away
         for (; n_used < n_loaded; ++n_used) {
           wait(b_full + 8 * rb.i, rb.ph);
-          rb.next(ACC_B_SLOTS);
+          rb.next(NB);
         }
       }
     }
@@ -747,7 +805,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
     const uint32_t t_warp = tmem_base + ((uint32_t)(32 * q4) << 16) + (uint32_t)(64 * cg);
     Ring rd = {0u, 0u};
     bool alive = true;
-    for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+    for (int item = group; item < n_items && alive; item += n_groups) {
       const int rt = item_rt(item), tok0 = item_tb(item) * NT + 64 * cg;
       const int row = rt * TR + r_in;
       const bool row_ok = row < g.nrows;
@@ -788,7 +846,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(d_empty + 8 * rd.i);
+        if (lane == 0) arrive_leader(d_empty + 8 * rd.i);
         pw[3] += tick() - c3t;
         rd.next(2);
       }
@@ -806,26 +864,78 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
   }
   if (PROF && lane == 0 && (warp == CONS_WARP0 || warp == CONS_WARP0 + 3 || warp == CONS_WARP0 + 15)) {
     const int o = warp == CONS_WARP0 ? 6 : warp == CONS_WARP0 + 3 ? 9 : 12;
-    g.prof[blockIdx.x * 16 + o + 1] = pw[2];   // consumer: waiting for a superblock's sums
-    g.prof[blockIdx.x * 16 + o + 2] = pw[3];   // consumer: reading and scaling them
+    g.prof[(size_t)blockIdx.x * 16 + o + 1] = pw[2];   // consumer: waiting for a superblock's sums
+    g.prof[(size_t)blockIdx.x * 16 + o + 2] = pw[3];   // consumer: reading and scaling them
   }
   tc_fence_before();
-  __syncthreads();
-  if (warp == MMA_WARP) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (PAIR) {
+    cluster_sync_all();   // no arrival of a peer is still on its way to this CTA's barriers, no MMA reads its memory
+    if (warp == MMA_WARP) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  } else {
+    __syncthreads();
+    if (warp == MMA_WARP) tmem_dealloc(tmem_base, TMEM_COLS);
+  }
 }
 
-static int launch(const Args& g, int sm_count, int acc, cudaStream_t st) {
+template <int HU, bool PROF, bool PAIR>
+static int launch_acc(const Args& g, int sm_count, cudaStream_t st) {
+  constexpr int smem = SmemAcc::TOTAL;
+  static_assert(smem <= 227 * 1024, "shared memory budget");
+  static bool configured[64];
+  static int max_clusters[64];
+  int dev = 0;
+  GSQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return GSQ_ERR_UNSUPPORTED;
+  auto kern = gemm3_acc_kernel<HU, PROF, PAIR>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = PAIR ? 2 : 1;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (!configured[dev]) {
+    GSQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    max_clusters[dev] = sm_count;
+    if (PAIR) {
+      // how many pairs the device runs at once (an SM without a free neighbour in its GPC stays out)
+      cfg.gridDim = dim3(2u * (unsigned)sm_count);
+      int n = 0;
+      GSQ_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+      if (n < 1) return GSQ_ERR_UNSUPPORTED;
+      max_clusters[dev] = n;
+    }
+    configured[dev] = true;
+  }
+  const int n_items = (PAIR ? (g.n_row_tiles + 1) / 2 : g.n_row_tiles) * g.n_tok_blocks;
+  const int groups = n_items < max_clusters[dev] ? n_items : max_clusters[dev];
+  cfg.gridDim = dim3((unsigned)(PAIR ? 2 * groups : groups));
+  GSQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, g));
+  return GSQ_OK;
+}
+
+// acc: 0 = integer slice sums; 1 / 2 = sums over a superblock on one / two planes of scaled products; pair: two CTAs per item
+static int launch(const Args& g, int sm_count, int acc, int pair, cudaStream_t st) {
+  if (acc) {
+    if (g.dump) return GSQ_ERR_UNSUPPORTED;   // no per-slice integer sums exist in this form
+    if (acc == 1) {
+      if (pair) return g.prof ? launch_acc<1, true, true>(g, sm_count, st) : launch_acc<1, false, true>(g, sm_count, st);
+      return g.prof ? launch_acc<1, true, false>(g, sm_count, st) : launch_acc<1, false, false>(g, sm_count, st);
+    }
+    if (pair) return g.prof ? launch_acc<2, true, true>(g, sm_count, st) : launch_acc<2, false, true>(g, sm_count, st);
+    return g.prof ? launch_acc<2, true, false>(g, sm_count, st) : launch_acc<2, false, false>(g, sm_count, st);
+  }
   static bool configured[64];
   int dev = 0;
   GSQ_CUDA_TRY(cudaGetDevice(&dev));
-  constexpr int smem = Smem::TOTAL, smem_acc = SmemAcc::TOTAL;
-  static_assert(smem <= 227 * 1024 && smem_acc <= 227 * 1024, "shared memory budget");
+  constexpr int smem = Smem::TOTAL;
+  static_assert(smem <= 227 * 1024, "shared memory budget");
   if (dev < 0 || dev >= 64) return GSQ_ERR_UNSUPPORTED;
   if (!configured[dev]) {
-    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm3_acc_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_acc));
-    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm3_acc_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_acc));
-    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm3_acc_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_acc));
-    GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm3_acc_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_acc));
     GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm3_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm3_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     GSQ_CUDA_TRY(cudaFuncSetAttribute(gemm3_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -833,16 +943,7 @@ static int launch(const Args& g, int sm_count, int acc, cudaStream_t st) {
   }
   const int n_items = g.n_row_tiles * g.n_tok_blocks;
   const int grid = n_items < sm_count ? n_items : sm_count;
-  if (acc) {
-    if (g.dump) return GSQ_ERR_UNSUPPORTED;   // no per-slice integer sums exist in this form
-    if (acc == 1) {
-      if (g.prof) gemm3_acc_kernel<1, true><<<grid, THREADS, smem_acc, st>>>(g);
-      else gemm3_acc_kernel<1, false><<<grid, THREADS, smem_acc, st>>>(g);
-    } else {
-      if (g.prof) gemm3_acc_kernel<2, true><<<grid, THREADS, smem_acc, st>>>(g);
-      else gemm3_acc_kernel<2, false><<<grid, THREADS, smem_acc, st>>>(g);
-    }
-  } else if (g.dump) {
+  if (g.dump) {
     gemm3_kernel<1><<<grid, THREADS, smem, st>>>(g);
   } else if (g.prof) {
     gemm3_kernel<2><<<grid, THREADS, smem, st>>>(g);
@@ -878,7 +979,7 @@ bool gemm3_applies(int ggml_type, int packed, int64_t rows) { return ggml_type =
 
 // x_tiles: the output of quantize_tiles_host in the fp16 layout that goes with acc (Q8_TILES_H16, _F16S, _F16S2)
 int gemm3_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_tiles, int64_t m,
-               int64_t k, void* y, int y_dtype, int64_t y_row_stride, int acc, void* stream) {
+               int64_t k, void* y, int y_dtype, int64_t y_row_stride, int acc, int pair, void* stream) {
   if (m == 0 || rows == 0) return GSQ_OK;
   if (m < 0 || rows < 0 || k <= 0 || k % 256 != 0 || !w || !x_tiles || !y) return GSQ_ERR_UNSUPPORTED;
   if (rows > INT32_MAX || k > INT32_MAX || m > INT32_MAX) return GSQ_ERR_TOO_LARGE;
@@ -904,7 +1005,7 @@ int gemm3_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
   g.wait_hint = (uint32_t)g_wait_hint;
   g.inv_scale = acc ? reinterpret_cast<const float*>((const uint8_t*)x_tiles + (size_t)g.n_tok_blocks * (k / 256) * 8 * acc * g3::HB) : nullptr;
   if (acc < 0 || acc > 2) return GSQ_ERR_UNSUPPORTED;
-  return g3::launch(g, di.sm_count, acc, (cudaStream_t)stream);
+  return g3::launch(g, di.sm_count, acc, pair, (cudaStream_t)stream);
 }
 
 }  // namespace gsq

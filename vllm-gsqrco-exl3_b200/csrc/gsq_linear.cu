@@ -21,7 +21,7 @@ int gemm2_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
 bool gemm3_applies(int ggml_type, int packed, int64_t rows);
 size_t gemm3_tile_bytes(int64_t m, int64_t k, int acc);
 int gemm3_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_tiles, int64_t m,
-               int64_t k, void* y, int y_dtype, int64_t y_row_stride, int acc, void* stream);
+               int64_t k, void* y, int y_dtype, int64_t y_row_stride, int acc, int pair, void* stream);
 // gsq_quantize.cu
 int quantize_tiles_host(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride, int layout, void* out, void* stream);
 // gsq_gemm.cu
@@ -81,13 +81,15 @@ extern "C" int gsq_linear(const void* w, int64_t row_bytes, int64_t rows, int gg
     // the form that accumulates over a superblock in tensor memory, on one or two fp16 planes of scaled products, or the
     // one with integer slice sums (also whenever the debug dump of those sums is on); variants 5 / 6 / 7 force one
     int acc = g_prefill_precision == GSQ_PREFILL_ROUNDED ? 1 : g_prefill_precision == GSQ_PREFILL_SPLIT ? 2 : 0;
-    if (variant == 5) acc = 2;
-    if (variant == 6) acc = 1;
+    int pair = 0;
+    if (variant == 5 || variant == 9) acc = 2;
+    if (variant == 6 || variant == 8) acc = 1;
+    if (variant == 8 || variant == 9) pair = 1;
     if (variant == 7 || gemm_dump_pointer()) acc = 0;
     rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, acc == 2 ? Q8_TILES_F16S2 : acc == 1 ? Q8_TILES_F16S : Q8_TILES_H16,
                              scratch, stream);
     if (rc != GSQ_OK) return rc;
-    return gemm3_host(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, acc, stream);
+    return gemm3_host(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, acc, pair, stream);
   }
   if (gemm2_applies(ggml_type, packed, rows) && variant == 4) {
     rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, layout, scratch, stream);
