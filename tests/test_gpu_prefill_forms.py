@@ -128,3 +128,51 @@ def test_two_cta_form_is_bit_identical(rows, k, m):
     assert torch.equal(_run(9, w, x, rows), _run(5, w, x, rows))
     flag = ctypes.c_int(-1)
     assert _cabi.lib.gsq_device_error_flag(ctypes.byref(flag)) == 0 and flag.value == 0
+
+
+IQ4_XS = 23
+
+
+@pytest.mark.parametrize("rows,k,m,scale", [(128, 512, 256, 1.0), (202, 5120, 70, 1e-3), (300, 1024, 700, 3e4), (130, 17408, 300, 1.0)])
+def test_iq4_xs_forms(rows, k, m, scale):
+    """IQ4_XS (GGUF order) on the same kernel: (ls - 32) * table value goes into the fp16 weight operand with one
+    rounding (exact up to 2048; the odd products above, up to 4064, round to even), so the fp16-operand forms stay
+    within the 1e-3 bound but not at 1e-6, and the split and integer settings take the int8 kernel's integer sums."""
+    raw = synth.make_weight(IQ4_XS, rows, k, 40 + rows)
+    w = torch.from_numpy(raw).to(DEV)
+    xa = synth.make_activation(m, k, 41 + m).astype(np.float64) * scale
+    xa[min(3, m - 1), :64] = 0.0
+    if m > 100:
+        xa[100, :] = 0.0
+    x = synth.nudge_ties_torch(torch.from_numpy(xa.astype(np.float32)).to(torch.bfloat16)).float()
+    q, d, _ = q8_1.quantize_mmq(x.numpy(), q8_1.LAYOUT_D4)
+    ref = product.product_q81(blocks.decode(raw, IQ4_XS), q, d)
+
+    def run(form):
+        old = _cabi.lib.gsq_debug_gemm_variant(form)
+        old_mode = _cabi.lib.gsq_debug_mmv_mode(1)
+        try:
+            y = torch.ops._C_gguf.lcpp_mul_mat_q(w, x.to(DEV), IQ4_XS, rows)
+            torch.cuda.synchronize()
+        finally:
+            _cabi.lib.gsq_debug_gemm_variant(old)
+            _cabi.lib.gsq_debug_mmv_mode(old_mode)
+        return y
+
+    errs = {}
+    for name, form, tol in (("rounded", 6, 1e-3), ("split operands", 5, 1e-3), ("int8", 4, 2e-6)):
+        got = run(form).cpu().numpy()
+        assert np.isfinite(got).all(), name
+        errs[name] = product.rel_err(got, ref)
+        assert errs[name] <= tol, (name, errs)
+    print(f"IQ4_XS {rows}x{k} m={m} scale {scale}:", {n: f"{e:.2e}" for n, e in errs.items()})
+    if m >= 256:
+        # the library's own choice: rounded by default; the split and integer settings = the int8 kernel
+        assert torch.equal(run(0), run(6))
+        for mode in (lcpp_ops.PREFILL_SPLIT, lcpp_ops.PREFILL_INTEGER):
+            lcpp_ops.set_prefill_precision(mode)
+            try:
+                y = run(3)
+            finally:
+                lcpp_ops.set_prefill_precision(lcpp_ops.PREFILL_ROUNDED)
+            assert torch.equal(y, run(4))

@@ -530,28 +530,90 @@ constexpr int UBA = 2 * HB;             // one copy and one turn of the MMA thre
 constexpr int ACC_B_SLOTS = 3;
 constexpr int ACC_B_AHEAD = 2;
 
+// weight formats of this kernel: IQ3_S in the fragment-ordered layout (decode_pair above), IQ4_XS in GGUF order
+enum { WK_IQ3S = 0, WK_IQ4XS = 1 };
+constexpr int RAWB_IQ4XS = 128 * 136;   // one superblock of 128 rows
+
+template <int WK>
 struct SmemAcc {
   static constexpr int BAR = 0;
   static constexpr int GRID = 1024;
-  static constexpr int RAW = GRID + GRIDB;
-  static constexpr int A = RAW + RAW_STAGES * RAWB;
+  static constexpr int RAWBK = WK == WK_IQ3S ? RAWB : RAWB_IQ4XS;
+  static constexpr int RAW = GRID + (WK == WK_IQ3S ? GRIDB : 0);   // (IQ4_XS: a 16-entry table, in registers)
+  static constexpr int A = (RAW + RAW_STAGES * RAWBK + 127) / 128 * 128;
   static constexpr int B = A + A_STAGES * STAGE_A;
-  static constexpr int SAX = B + ACC_B_SLOTS * UBA;      // scratch the shared decoder writes its scale planes to (unused here)
+  static constexpr int SAX = B + ACC_B_SLOTS * UBA;      // scratch the shared IQ3_S decoder writes its scale planes to (unused here)
   static constexpr int TOTAL = SAX + SA_STAGE;
 };
-static_assert(SmemAcc::A % 128 == 0 && SmemAcc::B % 128 == 0, "operand alignment");
+static_assert(SmemAcc<0>::B % 128 == 0 && SmemAcc<1>::B % 128 == 0 && RAWB_IQ4XS % 16 == 0, "operand alignment");
+
+__constant__ __align__(16) int8_t c_iq4nl3[16] = GSQ_IQ4NL_VALUES_INIT;
+
+__device__ __forceinline__ void fetch_raw_iq4xs(const Args& g, int rt, int sb, uint8_t* raw, int ptid) {
+  // 128 blocks of 136 bytes, 8-byte aligned in global memory; rows past the last one repeat it (never stored)
+  const uint32_t dst = saddr(raw);
+  for (int i = ptid; i < 128 * 17; i += PROD_THREADS) {
+    const int r = i / 17, c = i - r * 17;
+    const int row = min(rt * TR + r, g.nrows - 1);
+    cp_async8(dst + r * 136 + c * 8, g.w + (int64_t)row * g.row_bytes + (int64_t)sb * 136 + c * 8);
+  }
+}
+
+// 8 nibbles of v -> table bytes: lo = those of the low nibbles of bytes 0..3, hi = of the high nibbles
+__device__ __forceinline__ void iq4_lookup3(uint32_t v, const uint32_t (&tb)[4], uint32_t& lo, uint32_t& hi) {
+  const uint32_t s01 = v & 0x7777u, s23 = (v >> 16) & 0x7777u;
+  const uint32_t pick01 = 0x3210u | ((v & 0x8888u) >> 1), pick23 = 0x3210u | (((v >> 16) & 0x8888u) >> 1);
+  const uint32_t r01 = prmt(prmt(tb[0], tb[1], s01), prmt(tb[2], tb[3], s01), pick01);
+  const uint32_t r23 = prmt(prmt(tb[0], tb[1], s23), prmt(tb[2], tb[3], s23), pick23);
+  lo = prmt(r01, r23, 0x6420u);
+  hi = prmt(r01, r23, 0x7531u);
+}
+
+// IQ4_XS, one (row, slice) of half HF of a superblock: 16 bytes of 4-bit indices (low nibbles = values 0..15 of the
+// slice, high nibbles 16..31) -> 32 fp16 numbers (ls - 32) * table[index], four 16-byte rows of core matrices. `tb`
+// is the table with 128 added to every byte, so that a byte under the high byte 0x64 is the fp16 number 1152 + value
+// and one fused multiply-add gives value * (ls - 32) with a single rounding (exact up to 2048 in magnitude; of the
+// larger products, up to 4064, the odd ones round to even: a relative error of at most 2.4e-4 of that element).
+// item = slice-in-half * 128 + row: a store's 8 threads write one whole 128-byte core matrix.
+template <int HF>
+__device__ __forceinline__ void decode_iq4xs_f16(const uint8_t* raw, uint8_t* a, int item, const uint32_t (&tb)[4]) {
+  const int r = item & 127, s_half = item >> 7, p = 4 * HF + s_half;
+  const uint8_t* b = raw + r * 136;
+  const uint2 hdr = *reinterpret_cast<const uint2*>(b);
+  const uint2 qa = *reinterpret_cast<const uint2*>(b + 8 + 16 * p), qb = *reinterpret_cast<const uint2*>(b + 16 + 16 * p);
+  const uint32_t v[4] = {qa.x, qa.y, qb.x, qb.y};
+  uint32_t lo[4], hi[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) iq4_lookup3(v[e], tb, lo[e], hi[e]);
+  const uint32_t ls = ((hdr.y >> (4 * p)) & 0xFu) | (((hdr.x >> (16 + 2 * p)) & 3u) << 4);
+  const __half subh = __int2half_rn((int)ls - 32);
+  const __half2 sub2 = __half2half2(subh);
+  const __half2 nb2 = __half2half2(__hmul(__float2half_rn(-1152.0f), subh));   // exact: 2^7 * 9 * (ls - 32)
+  uint8_t* dst = a + s_half * SL_A + (r >> 3) * 512 + (r & 7) * 16;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const uint32_t w0 = t < 2 ? lo[2 * t] : hi[2 * t - 4], w1 = t < 2 ? lo[2 * t + 1] : hi[2 * t - 3];
+    uint4 o;
+    o.x = hfma2_bits(prmt(w0, 0x64646464u, 0x4140u), sub2, nb2);
+    o.y = hfma2_bits(prmt(w0, 0x64646464u, 0x4342u), sub2, nb2);
+    o.z = hfma2_bits(prmt(w1, 0x64646464u, 0x4140u), sub2, nb2);
+    o.w = hfma2_bits(prmt(w1, 0x64646464u, 0x4342u), sub2, nb2);
+    *reinterpret_cast<uint4*>(dst + t * 128) = o;
+  }
+}
 
 // PAIR: two CTAs (a cluster) share an item of 256 weight rows x 256 tokens. Each decodes its own 128 rows and copies
 // only its half of the tokens of every activation unit; the MMAs (M = 256, cta_group::2) are issued by CTA 0 and read
 // both halves, so every CTA moves half the activation bytes from L2 and through its shared memory per result. CTA 0's
 // barriers collect both CTAs' "weight stage decoded" and "sums drained" arrivals; CTA 1 reports each landed unit to
 // CTA 0 (b_peer); MMA completion is signalled to both CTAs at once.
-template <int HU, bool PROF, bool PAIR>
+template <int WK, int HU, bool PROF, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
   unsigned long long pw[4] = {0ull, 0ull, 0ull, 0ull};
   auto tick = [&]() -> unsigned long long { return PROF ? (unsigned long long)clock64() : 0ull; };
   extern __shared__ __align__(1024) uint8_t smem[];
-  using S = SmemAcc;
+  using S = SmemAcc<WK>;
+  static_assert(WK == WK_IQ3S || !PAIR, "pairs of CTAs: IQ3_S only");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   constexpr int NB = PAIR ? 2 * ACC_B_SLOTS : ACC_B_SLOTS;      // activation slots (half the bytes each for a pair)
@@ -598,12 +660,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
     if (PAIR) tmem_alloc_pair(saddr(tmem_slot), TMEM_COLS);
     else tmem_alloc(saddr(tmem_slot), TMEM_COLS);
   }
-  for (int i = tid; i < 512; i += THREADS) {
-    const uint32_t gv = g_iq3s_grid3[i];
-    const uint32_t pos = gv ^ 0x80808080u, neg = (~gv + 0x01010101u) ^ 0x80808080u;
-    uint4* dst = reinterpret_cast<uint4*>(smem + S::GRID + i * 64);
+  if (WK == WK_IQ3S) {
+    for (int i = tid; i < 512; i += THREADS) {
+      const uint32_t gv = g_iq3s_grid3[i];
+      const uint32_t pos = gv ^ 0x80808080u, neg = (~gv + 0x01010101u) ^ 0x80808080u;
+      uint4* dst = reinterpret_cast<uint4*>(smem + S::GRID + i * 64);
 #pragma unroll
-    for (int r2 = 0; r2 < 4; ++r2) dst[r2] = make_uint4(pos, neg, pos, neg);
+      for (int r2 = 0; r2 < 4; ++r2) dst[r2] = make_uint4(pos, neg, pos, neg);
+    }
   }
   tc_fence_before();
   if (PAIR) cluster_sync_all();   // the peer's barriers are initialised before anything arrives on them
@@ -625,7 +689,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
     int f_item = group, f_sb = 0;
     auto fetch_next = [&](uint32_t n_fetch) {
       if (f_item < n_items) {
-        fetch_raw(g, item_rt(f_item), f_sb, smem + S::RAW + (n_fetch & 1u) * RAWB, ptid);
+        if (WK == WK_IQ3S) fetch_raw(g, item_rt(f_item), f_sb, smem + S::RAW + (n_fetch & 1u) * S::RAWBK, ptid);
+        else fetch_raw_iq4xs(g, item_rt(f_item), f_sb, smem + S::RAW + (n_fetch & 1u) * S::RAWBK, ptid);
         if (++f_sb == nsb) { f_sb = 0; f_item += n_groups; }
       }
       cp_async_commit();
@@ -635,13 +700,20 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
     Ring ra = {0u, 0u};
     bool alive = true;
     float* sa = reinterpret_cast<float*>(smem + S::SAX);
+    uint32_t tb[4] = {0u, 0u, 0u, 0u};
+    if (WK == WK_IQ4XS) {
+      const uint32_t* tw = reinterpret_cast<const uint32_t*>(c_iq4nl3);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) tb[e] = tw[e] ^ 0x80808080u;
+    }
     for (int item = group; item < n_items; item += n_groups) {
       const int rt = item_rt(item);
       for (int sb = 0; sb < nsb; ++sb, ++ns) {
         cp_async_wait<0>();
         asm volatile("bar.sync 1, %0;" ::"n"(PROD_THREADS) : "memory");
         fetch_next(ns + 1);
-        const uint8_t* raw = smem + S::RAW + (ns & 1u) * RAWB;
+        const uint8_t* raw = smem + S::RAW + (ns & 1u) * S::RAWBK;
+        int it4 = ptid;   // IQ4_XS: this thread's next (slice, row) of the superblock, 1024 of them in half order
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           const unsigned long long p0 = tick();
@@ -650,7 +722,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
           pw[0] += p1 - p0;
           if (alive) {
             uint8_t* a = smem + S::A + ra.i * STAGE_A;
-            if (hf == 0) {
+            if (WK == WK_IQ4XS) {
+              // 512 (slice, row) items per half over 224 threads: the thread carries on where it stopped in the first
+              // half, so the superblock takes 5 rounds, not 2 x 3
+              for (; it4 < 512 * (hf + 1); it4 += PROD_THREADS) {
+                if (hf == 0) decode_iq4xs_f16<0>(raw, a, it4, tb);
+                else decode_iq4xs_f16<1>(raw, a, it4 - 512, tb);
+              }
+            } else if (hf == 0) {
               decode_half<0>(raw, a, sa, smem + S::GRID, g.nrows - rt * TR, warp, lane);
             } else {
               decode_half<1>(raw, a, sa, smem + S::GRID, g.nrows - rt * TR, warp, lane);
@@ -809,10 +888,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
       const int rt = item_rt(item), tok0 = item_tb(item) * NT + 64 * cg;
       const int row = rt * TR + r_in;
       const bool row_ok = row < g.nrows;
-      // fp16 d of this thread's row: halfword (row % 16) / 8 of word row % 8 at byte 1728 of its 16-row record
-      const uint8_t* dwp = g.w + (int64_t)(row & ~15) * g.row_bytes + 1728 + 4 * (row & 7) + 2 * ((row >> 3) & 1);
+      // fp16 d of this thread's row. IQ3_S: halfword (row % 16) / 8 of word row % 8 at byte 1728 of its 16-row record;
+      // IQ4_XS: the first two bytes of the row's block
+      const uint8_t* dwp = WK == WK_IQ3S ? g.w + (int64_t)(row & ~15) * g.row_bytes + 1728 + 4 * (row & 7) + 2 * ((row >> 3) & 1)
+                                         : g.w + (int64_t)row * g.row_bytes;
       auto load_dw = [&](int sb) -> float {
-        return row_ok ? h2f(*reinterpret_cast<const uint16_t*>(dwp + (int64_t)sb * 1760)) : 0.0f;
+        return row_ok ? h2f(*reinterpret_cast<const uint16_t*>(dwp + (int64_t)sb * (WK == WK_IQ3S ? 1760 : 136))) : 0.0f;
       };
       float2 acc[32];
 #pragma unroll
@@ -877,16 +958,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
   }
 }
 
-template <int HU, bool PROF, bool PAIR>
+template <int WK, int HU, bool PROF, bool PAIR>
 static int launch_acc(const Args& g, int sm_count, cudaStream_t st) {
-  constexpr int smem = SmemAcc::TOTAL;
+  constexpr int smem = SmemAcc<WK>::TOTAL;
   static_assert(smem <= 227 * 1024, "shared memory budget");
   static bool configured[64];
   static int max_clusters[64];
   int dev = 0;
   GSQ_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return GSQ_ERR_UNSUPPORTED;
-  auto kern = gemm3_acc_kernel<HU, PROF, PAIR>;
+  auto kern = gemm3_acc_kernel<WK, HU, PROF, PAIR>;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem;
@@ -919,16 +1000,22 @@ static int launch_acc(const Args& g, int sm_count, cudaStream_t st) {
 }
 
 // acc: 0 = integer slice sums; 1 / 2 = sums over a superblock on one / two planes of scaled products; pair: two CTAs per item
-static int launch(const Args& g, int sm_count, int acc, int pair, cudaStream_t st) {
+static int launch(const Args& g, int sm_count, int wk, int acc, int pair, cudaStream_t st) {
   if (acc) {
     if (g.dump) return GSQ_ERR_UNSUPPORTED;   // no per-slice integer sums exist in this form
-    if (acc == 1) {
-      if (pair) return g.prof ? launch_acc<1, true, true>(g, sm_count, st) : launch_acc<1, false, true>(g, sm_count, st);
-      return g.prof ? launch_acc<1, true, false>(g, sm_count, st) : launch_acc<1, false, false>(g, sm_count, st);
+    if (wk == WK_IQ4XS) {
+      if (pair) return GSQ_ERR_UNSUPPORTED;
+      if (acc == 1) return g.prof ? launch_acc<WK_IQ4XS, 1, true, false>(g, sm_count, st) : launch_acc<WK_IQ4XS, 1, false, false>(g, sm_count, st);
+      return g.prof ? launch_acc<WK_IQ4XS, 2, true, false>(g, sm_count, st) : launch_acc<WK_IQ4XS, 2, false, false>(g, sm_count, st);
     }
-    if (pair) return g.prof ? launch_acc<2, true, true>(g, sm_count, st) : launch_acc<2, false, true>(g, sm_count, st);
-    return g.prof ? launch_acc<2, true, false>(g, sm_count, st) : launch_acc<2, false, false>(g, sm_count, st);
+    if (acc == 1) {
+      if (pair) return g.prof ? launch_acc<WK_IQ3S, 1, true, true>(g, sm_count, st) : launch_acc<WK_IQ3S, 1, false, true>(g, sm_count, st);
+      return g.prof ? launch_acc<WK_IQ3S, 1, true, false>(g, sm_count, st) : launch_acc<WK_IQ3S, 1, false, false>(g, sm_count, st);
+    }
+    if (pair) return g.prof ? launch_acc<WK_IQ3S, 2, true, true>(g, sm_count, st) : launch_acc<WK_IQ3S, 2, false, true>(g, sm_count, st);
+    return g.prof ? launch_acc<WK_IQ3S, 2, true, false>(g, sm_count, st) : launch_acc<WK_IQ3S, 2, false, false>(g, sm_count, st);
   }
+  if (wk != WK_IQ3S) return GSQ_ERR_UNSUPPORTED;
   static bool configured[64];
   int dev = 0;
   GSQ_CUDA_TRY(cudaGetDevice(&dev));
@@ -976,6 +1063,10 @@ size_t gemm3_tile_bytes(int64_t m, int64_t k, int acc) {
 }
 
 bool gemm3_applies(int ggml_type, int packed, int64_t rows) { return ggml_type == GSQ_TYPE_IQ3_S && packed && rows % 16 == 0; }
+// the forms that sum over a superblock in tensor memory also serve IQ4_XS (GGUF order)
+bool gemm3_acc_applies(int ggml_type, int packed, int64_t rows) {
+  return gemm3_applies(ggml_type, packed, rows) || (ggml_type == GSQ_TYPE_IQ4_XS && !packed);
+}
 
 // x_tiles: the output of quantize_tiles_host in the fp16 layout that goes with acc (Q8_TILES_H16, _F16S, _F16S2)
 int gemm3_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_tiles, int64_t m,
@@ -983,7 +1074,9 @@ int gemm3_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
   if (m == 0 || rows == 0) return GSQ_OK;
   if (m < 0 || rows < 0 || k <= 0 || k % 256 != 0 || !w || !x_tiles || !y) return GSQ_ERR_UNSUPPORTED;
   if (rows > INT32_MAX || k > INT32_MAX || m > INT32_MAX) return GSQ_ERR_TOO_LARGE;
-  if (!gemm3_applies(ggml_type, packed, rows) || row_bytes != (k / 256) * 110) return GSQ_ERR_UNSUPPORTED;
+  const bool iq4 = ggml_type == GSQ_TYPE_IQ4_XS;
+  if (iq4 ? (!acc || packed || row_bytes != (k / 256) * 136) : (!gemm3_applies(ggml_type, packed, rows) || row_bytes != (k / 256) * 110))
+    return GSQ_ERR_UNSUPPORTED;
   if (y_dtype != GSQ_F32 && y_dtype != GSQ_F16 && y_dtype != GSQ_BF16) return GSQ_ERR_UNSUPPORTED;
   DeviceInfo di;
   const int rc = device_info(&di);
@@ -1005,7 +1098,7 @@ int gemm3_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
   g.wait_hint = (uint32_t)g_wait_hint;
   g.inv_scale = acc ? reinterpret_cast<const float*>((const uint8_t*)x_tiles + (size_t)g.n_tok_blocks * (k / 256) * 8 * acc * g3::HB) : nullptr;
   if (acc < 0 || acc > 2) return GSQ_ERR_UNSUPPORTED;
-  return g3::launch(g, di.sm_count, acc, pair, (cudaStream_t)stream);
+  return g3::launch(g, di.sm_count, iq4 ? g3::WK_IQ4XS : g3::WK_IQ3S, acc, pair, (cudaStream_t)stream);
 }
 
 }  // namespace gsq

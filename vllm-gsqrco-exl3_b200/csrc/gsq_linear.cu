@@ -19,6 +19,7 @@ int gemm2_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
                int64_t k, void* y, int y_dtype, int64_t y_row_stride, void* stream);
 // gsq_gemm3.cu
 bool gemm3_applies(int ggml_type, int packed, int64_t rows);
+bool gemm3_acc_applies(int ggml_type, int packed, int64_t rows);
 size_t gemm3_tile_bytes(int64_t m, int64_t k, int acc);
 int gemm3_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_tiles, int64_t m,
                int64_t k, void* y, int y_dtype, int64_t y_row_stride, int acc, int pair, void* stream);
@@ -43,7 +44,11 @@ extern "C" int gsq_prefill_precision(int mode) {
 extern "C" size_t gsq_linear_scratch_bytes(int64_t rows, int64_t m, int64_t k, int ggml_type, int packed) {
   if (m <= 0 || k <= 0) return 0;
   const size_t mmq = (size_t)(k / 128) * (size_t)m * 144, q81 = (size_t)(k / 32) * (size_t)m * 36;
-  const size_t tiles = gsq::gemm3_applies(ggml_type, packed, rows) ? gsq::gemm3_tile_bytes(m, k, 2) : gsq::gemm2_tile_bytes(m, k, ggml_type);
+  size_t tiles = gsq::gemm3_applies(ggml_type, packed, rows) ? 0 : gsq::gemm2_tile_bytes(m, k, ggml_type);
+  if (gsq::gemm3_acc_applies(ggml_type, packed, rows)) {
+    const size_t t3 = gsq::gemm3_tile_bytes(m, k, 2);
+    tiles = tiles > t3 ? tiles : t3;
+  }
   size_t b = mmq > tiles ? mmq : tiles;
   b = b > q81 ? b : q81;
   return gsq::align256(b);
@@ -76,27 +81,34 @@ extern "C" int gsq_linear(const void* w, int64_t row_bytes, int64_t rows, int gg
   const bool tall = (rows + 127) / 128 >= 74;
   const bool big3 = m >= 256 || (m >= 128 && tall);
   const bool big = m >= 512 || (m >= 192 && tall);
-  // repacked IQ3_S: the kernel with the sub-scales folded into fp16 operands (variant 4 keeps the int8 kernel for it)
-  if (gemm3_applies(ggml_type, packed, rows) && (variant == 3 || variant >= 5 || (variant == 0 && big3))) {
+  // repacked IQ3_S and IQ4_XS: the kernels with the sub-scales folded into fp16 operands (variant 4 keeps the int8
+  // kernel for them)
+  if (gemm3_acc_applies(ggml_type, packed, rows) && (variant == 3 || variant >= 5 || (variant == 0 && big3))) {
     // the form that accumulates over a superblock in tensor memory, on one or two fp16 planes of scaled products, or the
     // one with integer slice sums (also whenever the debug dump of those sums is on); variants 5 / 6 / 7 force one
     int acc = g_prefill_precision == GSQ_PREFILL_ROUNDED ? 1 : g_prefill_precision == GSQ_PREFILL_SPLIT ? 2 : 0;
+    // IQ4_XS: (ls - 32) * value reaches 4064 and is not always exact in fp16, so only the rounded form is offered on
+    // fp16 operands; the split setting takes the int8 kernel's integer sums instead
+    if (ggml_type == GSQ_TYPE_IQ4_XS && acc == 2) acc = 0;
     int pair = 0;
     if (variant == 5 || variant == 9) acc = 2;
     if (variant == 6 || variant == 8) acc = 1;
-    if (variant == 8 || variant == 9) pair = 1;
+    if (variant == 8 || variant == 9) pair = gemm3_applies(ggml_type, packed, rows) ? 1 : 0;
     if (variant == 7 || gemm_dump_pointer()) acc = 0;
-    rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, acc == 2 ? Q8_TILES_F16S2 : acc == 1 ? Q8_TILES_F16S : Q8_TILES_H16,
-                             scratch, stream);
-    if (rc != GSQ_OK) return rc;
-    return gemm3_host(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, acc, pair, stream);
+    if (acc || gemm3_applies(ggml_type, packed, rows)) {
+      rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, acc == 2 ? Q8_TILES_F16S2 : acc == 1 ? Q8_TILES_F16S : Q8_TILES_H16,
+                               scratch, stream);
+      if (rc != GSQ_OK) return rc;
+      return gemm3_host(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, acc, pair, stream);
+    }
+    // (IQ4_XS with integer sums: the int8 kernel below)
   }
   if (gemm2_applies(ggml_type, packed, rows) && variant == 4) {
     rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, layout, scratch, stream);
     if (rc != GSQ_OK) return rc;
     return gemm2_host(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, stream);
   }
-  if (gemm2_applies(ggml_type, packed, rows) && (variant == 3 || (variant == 0 && big))) {
+  if (gemm2_applies(ggml_type, packed, rows) && (variant == 3 || variant >= 5 || (variant == 0 && big))) {
     rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, layout, scratch, stream);
     if (rc != GSQ_OK) return rc;
     return gemm2_host(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, stream);
