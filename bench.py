@@ -695,36 +695,35 @@ def extra_prefill(dev, capture):
             tops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
             row = {"type": tname, "m": m, "n": n, "k": k, "ms": round(ms, 3), "int8_TOPS": round(tops, 1),
                    "frac_nominal": round(tops / NOMINAL_INT8_TOPS, 4),
-                   "frac_measured": round(tops / peak, 4) if peak else None}
-            if packed:
-                # the other two forms of this product (gsq_prefill_precision), and how far the default is from the one
-                # that keeps the reference's exact integer slice sums, relative to the result's norm
-                row["form"] = "rounded (default)"
-                xf = x.float() if m == 2048 else None        # fp32 in, fp32 out: no output rounding in the comparison
-                cmp_fn = lambda: linear.fused_mul_mat_gguf(xf, w, t, None, packed)
-                y0 = cmp_fn() if m == 2048 else None
-                for name, mode in (("split", lcpp_ops.PREFILL_SPLIT), ("integer", lcpp_ops.PREFILL_INTEGER)):
-                    lcpp_ops.set_prefill_precision(mode)
-                    try:
-                        row[name + "_TOPS"] = round(2.0 * m * n * k / (timed(fn) * 1e-3) / 1e12, 1)
-                        if m == 2048:
-                            y1 = cmp_fn()
-                            row["rounded_vs_" + name] = float(((y0 - y1).norm() / y1.norm()).item())
-                            if name == "integer":
-                                yi = y1
-                            else:
-                                ys = y1
-                    finally:
-                        lcpp_ops.set_prefill_precision(lcpp_ops.PREFILL_ROUNDED)
-                if m == 2048:
-                    row["split_vs_integer"] = float(((ys - yi).norm() / yi.norm()).item())
-                    del y1, ys, yi
-                del y0, xf
+                   "frac_measured": round(tops / peak, 4) if peak else None,
+                   "frac_nominal_f16": round(tops / 2250.0, 4)}
+            # the other forms of this product (gsq_prefill_precision), and how far the default is from the one that keeps
+            # the reference's exact integer slice sums, relative to the result's norm (IQ4_XS: split = integer)
+            row["form"] = "rounded (default)"
+            xf = x.float() if m == 2048 else None        # fp32 in, fp32 out: no output rounding in the comparison
+            cmp_fn = lambda: linear.fused_mul_mat_gguf(xf, w, t, None, packed)
+            ys = {"rounded": cmp_fn()} if m == 2048 else {}
+            for name, mode in ((("split", lcpp_ops.PREFILL_SPLIT),) if packed else ()) + (("integer", lcpp_ops.PREFILL_INTEGER),):
+                lcpp_ops.set_prefill_precision(mode)
+                try:
+                    row[name + "_TOPS"] = round(2.0 * m * n * k / (timed(fn) * 1e-3) / 1e12, 1)
+                    if m == 2048:
+                        ys[name] = cmp_fn()
+                finally:
+                    lcpp_ops.set_prefill_precision(lcpp_ops.PREFILL_ROUNDED)
+            if m == 2048:
+                rel = lambda a, b: float(((ys[a] - ys[b]).norm() / ys[b].norm()).item())
+                row["rounded_vs_integer"] = rel("rounded", "integer")
+                if packed:
+                    row["split_vs_integer"] = rel("split", "integer")
+            del ys, xf
             rows.append(row)
             del x
         del w
     return {"int8_peak_nominal_TOPS": NOMINAL_INT8_TOPS, "int8_peak_measured_TOPS": peak,
             "int8_peak_how": "torch._int_mm 8192^3, best of 5", "includes": "activation quantisation + GEMM per call",
+            "operands": "ops = 2 M N K whatever the operand type; the default (rounded) and split forms run on fp16 tensor-core "
+                        "operands (tcgen05 kind::f16, nominal dense peak 2250 TFLOP/s: frac_nominal_f16), IQ4_XS's integer form on int8",
             "cells": rows}
 
 
