@@ -501,7 +501,7 @@ def run_ours(args):
         if world == 1 and not args.no_extras:
             del cells, xs
             torch.cuda.empty_cache()
-            out["prefill"] = extra_prefill(dev, capture)
+            out["prefill"] = extra_prefill(dev, capture, l2, not args.no_ref_kernels)
             out["decode_stack"] = extra_decode_stack(dev, capture)
             out["low_bit_types"] = extra_low_bit(dev, capture, l2)
             out["fused_steps"] = extra_fused_steps(dev, capture)
@@ -659,7 +659,7 @@ def int8_peak(dev):
 NOMINAL_INT8_TOPS = 4500.0
 
 
-def extra_prefill(dev, capture):
+def extra_prefill(dev, capture, l2_bytes, with_ref=True):
     """Prefill GEMM: M tokens x K=5120 -> N=17408 with IQ3_S weights, and M x K=17408 -> N=5120 with IQ4_XS;
     bf16 activations ~ N(0,1) with 0.1 % outliers x20, M in {2048, 8192, 16384}. Algorithmic ops = 2 M N K."""
     import torch
@@ -683,8 +683,10 @@ def extra_prefill(dev, capture):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / 3
 
+    raws, ref_rows = {}, []
     for tname, t, n, k in (("IQ3_S", 21, 17408, 5120), ("IQ4_XS", 23, 5120, 17408)):
-        w = torch.from_numpy(synth.make_weight(t, n, k, 1300)).to(dev)
+        raws[(tname, n, k)] = synth.make_weight(t, n, k, 1300)
+        w = torch.from_numpy(raws[(tname, n, k)]).to(dev)
         packed = t == 21
         if packed:
             iq3_pack.pack_(w, t)
@@ -718,13 +720,22 @@ def extra_prefill(dev, capture):
                     row["split_vs_integer"] = rel("split", "integer")
             del ys, xf
             rows.append(row)
+            if m == 2048:
+                ref_rows.append({"type": tname, "n": n, "k": k, "m": m, "us": round(ms * 1e3, 1)})
             del x
         del w
+    torch.cuda.empty_cache()
+    # the reference's own many-row kernels (its MMQ; for IQ3_S also its packed route) on the 2048-token cells
+    ref = ref_kernels(ref_rows, raws, l2_bytes, {"IQ3_S": 21, "IQ4_XS": 23}) if with_ref else {"skipped": "--no-ref-kernels"}
+    if "cells" in ref:
+        ref["what"] = "reference kernels rebuilt for sm_100a on the 2048-token cells, quantise + product per call, graph replay"
+        for c in ref["cells"]:
+            c["ref_TOPS"] = round(2.0 * c["m"] * c["n"] * c["k"] / c["ref_us"] / 1e6, 1)
     return {"int8_peak_nominal_TOPS": NOMINAL_INT8_TOPS, "int8_peak_measured_TOPS": peak,
             "int8_peak_how": "torch._int_mm 8192^3, best of 5", "includes": "activation quantisation + GEMM per call",
             "operands": "ops = 2 M N K whatever the operand type; the default (rounded) and split forms run on fp16 tensor-core "
                         "operands (tcgen05 kind::f16, nominal dense peak 2250 TFLOP/s: frac_nominal_f16), IQ4_XS's integer form on int8",
-            "cells": rows}
+            "cells": rows, "ref_kernels": ref}
 
 
 LOW_BIT_TYPES = [("Q2_K", 10), ("IQ2_XXS", 16), ("IQ2_XS", 17), ("IQ3_XXS", 18), ("IQ2_S", 22), ("IQ1_M", 29)]
