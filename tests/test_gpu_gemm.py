@@ -66,14 +66,13 @@ def gemm_variant(request):
     tiles (weights decoded once per 256 tokens; for repacked IQ3_S "prefill" is the kernel with fp16 operands in its
     default form -- sub-scales and rounded activation products in the operands, sums over a superblock --,
     "prefill_split" the same with the products as fp16 pairs, "prefill_integer" the form with exact integer slice sums
-    and "prefill_int8" the int8 kernel; IQ4_XS has the first two and the int8 kernel, Q4_K the int8 kernel only), the two older
+    and "prefill_int8" the int8 kernel; IQ4_XS has the first two and the int8 kernel, Q4_K the first and the int8 kernel), the two older
     kernels on 128-value blocks (warp-specialised and all-warps-in-lockstep); and the library's own choice, which up
     to 48 rows is the register-operand kernel."""
     callspec = getattr(request.node, "callspec", None)
     name = callspec.params.get("name", "IQ3_S") if callspec is not None else "IQ3_S"
-    if request.param in ("prefill_int8", "prefill_split", "prefill_integer") and (
-            name == "Q4_K" or (name == "IQ4_XS" and request.param == "prefill_integer")):
-        pytest.skip("the same kernel as 'prefill' (Q4_K) or as 'prefill_int8' (IQ4_XS) for this type")
+    if (request.param == "prefill_integer" and name != "IQ3_S") or (request.param == "prefill_split" and name == "Q4_K"):
+        pytest.skip("the same kernel as 'prefill_int8' for this type")
     variant = {"prefill": 3, "prefill_split": 5, "prefill_integer": 7, "prefill_int8": 4, "specialised": 1, "lockstep": 2,
                "default": 0}[request.param]
     old = _cabi.lib.gsq_debug_gemm_variant(variant)

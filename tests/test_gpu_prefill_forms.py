@@ -130,29 +130,53 @@ def test_two_cta_form_is_bit_identical(rows, k, m):
     assert _cabi.lib.gsq_device_error_flag(ctypes.byref(flag)) == 0 and flag.value == 0
 
 
-IQ4_XS = 23
+IQ4_XS, Q4_K = 23, 12
 
 
+def _reference_q4k(raw, x):
+    """The reference kernels' Q4_K arithmetic in float64: half d and half sum x per block, d * sc and dmin * m rounded
+    to fp16 by its tile loader (mmq-load-tiles.cuh:775-780)."""
+    dec = blocks.decode(raw, Q4_K)
+    q, d, s = q8_1.quantize_mmq(x.numpy(), q8_1.LAYOUT_DS4)
+    dh, sh = d.astype(np.float16).astype(np.float64), s.astype(np.float16).astype(np.float64)
+    gs = (np.repeat(dec.d, 8, axis=1).astype(np.float16) * dec.isc.astype(np.float16)).astype(np.float64)
+    mins = (np.repeat(dec.dmin, 8, axis=1).astype(np.float16) * dec.imin.astype(np.float16)).astype(np.float64)
+    sums = product.block_sums(dec, q).astype(np.float64)
+    return np.einsum("mns,ns,ms->mn", sums, gs, dh, optimize=True) - sh @ mins.T
+
+
+@pytest.mark.parametrize("t", [IQ4_XS, Q4_K])
 @pytest.mark.parametrize("rows,k,m,scale", [(128, 512, 256, 1.0), (202, 5120, 70, 1e-3), (300, 1024, 700, 3e4), (130, 17408, 300, 1.0)])
-def test_iq4_xs_forms(rows, k, m, scale):
-    """IQ4_XS (GGUF order) on the same kernel: (ls - 32) * table value goes into the fp16 weight operand with one
-    rounding (exact up to 2048; the odd products above, up to 4064, round to even), so the fp16-operand forms stay
-    within the 1e-3 bound but not at 1e-6, and the split and integer settings take the int8 kernel's integer sums."""
-    raw = synth.make_weight(IQ4_XS, rows, k, 40 + rows)
+def test_gguf_order_types_on_fp16_operands(t, rows, k, m, scale):
+    """IQ4_XS and Q4_K (GGUF order) on the same kernel, in its rounded form only.
+    IQ4_XS: (ls - 32) * table value goes into the fp16 weight operand with one rounding (exact up to 2048; the odd
+    products above, up to 4064, round to even), which by itself costs ~2e-4 of a row's norm.
+    Q4_K: sc * q is exact; the minimum term rides along as 8 more columns of K per superblock (-(dmin / d) * m against
+    half(sum x)), and 8 more give back what the products' rounding took from each slice in total, since quants of one
+    sign would otherwise add those roundings up. The reference kernels round d * sc and dmin * m to fp16, this does
+    not: about 2e-4 of the difference is theirs.
+    Both stay within the 1e-3 bound; the split and integer settings take the int8 kernel's integer sums."""
+    if t == Q4_K and scale > 100:
+        scale = 30.0          # (the reference keeps Q4_K's sum of 32 activations as a half: it overflows beyond that)
+    raw = synth.make_weight(t, rows, k, 40 + rows)
     w = torch.from_numpy(raw).to(DEV)
     xa = synth.make_activation(m, k, 41 + m).astype(np.float64) * scale
     xa[min(3, m - 1), :64] = 0.0
     if m > 100:
         xa[100, :] = 0.0
+    xa[min(5, m - 1), 7] = 40.0 * scale
     x = synth.nudge_ties_torch(torch.from_numpy(xa.astype(np.float32)).to(torch.bfloat16)).float()
-    q, d, _ = q8_1.quantize_mmq(x.numpy(), q8_1.LAYOUT_D4)
-    ref = product.product_q81(blocks.decode(raw, IQ4_XS), q, d)
+    if t == Q4_K:
+        ref = _reference_q4k(raw, x)
+    else:
+        q, d, _ = q8_1.quantize_mmq(x.numpy(), q8_1.LAYOUT_D4)
+        ref = product.product_q81(blocks.decode(raw, t), q, d)
 
     def run(form):
         old = _cabi.lib.gsq_debug_gemm_variant(form)
         old_mode = _cabi.lib.gsq_debug_mmv_mode(1)
         try:
-            y = torch.ops._C_gguf.lcpp_mul_mat_q(w, x.to(DEV), IQ4_XS, rows)
+            y = torch.ops._C_gguf.lcpp_mul_mat_q(w, x.to(DEV), t, rows)
             torch.cuda.synchronize()
         finally:
             _cabi.lib.gsq_debug_gemm_variant(old)
@@ -160,12 +184,14 @@ def test_iq4_xs_forms(rows, k, m, scale):
         return y
 
     errs = {}
-    for name, form, tol in (("rounded", 6, 1e-3), ("split operands", 5, 1e-3), ("int8", 4, 2e-6)):
+    for name, form, tol in (("rounded", 6, 1e-3), ("int8", 4, 2e-6)) + ((("split operands", 5, 1e-3),) if t == IQ4_XS else ()):
         got = run(form).cpu().numpy()
         assert np.isfinite(got).all(), name
         errs[name] = product.rel_err(got, ref)
         assert errs[name] <= tol, (name, errs)
-    print(f"IQ4_XS {rows}x{k} m={m} scale {scale}:", {n: f"{e:.2e}" for n, e in errs.items()})
+        if m > 100:
+            assert not got[100].any(), name
+    print(f"type {t} {rows}x{k} m={m} scale {scale}:", {n: f"{e:.2e}" for n, e in errs.items()})
     if m >= 256:
         # the library's own choice: rounded by default; the split and integer settings = the int8 kernel
         assert torch.equal(run(0), run(6))
@@ -176,3 +202,25 @@ def test_iq4_xs_forms(rows, k, m, scale):
             finally:
                 lcpp_ops.set_prefill_precision(lcpp_ops.PREFILL_ROUNDED)
             assert torch.equal(y, run(4))
+
+
+def test_q4_k_blocks_whose_minimum_dwarfs_their_scale():
+    """Q4_K superblocks with d = 0, or dmin more than 64 times d: the kernel scales such a block by dmin / 64 instead of
+    d (so that -(dmin / scale) * m stays inside fp16) and the weights then carry one more rounding."""
+    rows, k, m = 128, 1024, 300
+    raw = synth.make_weight(Q4_K, rows, k, 99).copy()
+    blk = raw.reshape(rows, k // 256, 144)
+    d16 = blk[:, :, 0:2].copy().view(np.float16)
+    d16[::3, 0, 0] = 0.0                                   # d = 0 in the first superblock of every third row
+    d16[1::3, 1, 0] = d16[1::3, 1, 0] / np.float16(512.0)  # d tiny against dmin in the second superblock of others
+    blk[:, :, 0:2] = d16.view(np.uint8)
+    w = torch.from_numpy(raw).to(DEV)
+    x = synth.nudge_ties_torch(torch.from_numpy(synth.make_activation(m, k, 98)).to(torch.bfloat16)).float()
+    ref = _reference_q4k(raw, x)
+    old = _cabi.lib.gsq_debug_gemm_variant(6)
+    try:
+        y = torch.ops._C_gguf.lcpp_mul_mat_q(w, x.to(DEV), Q4_K, rows).cpu().numpy()
+    finally:
+        _cabi.lib.gsq_debug_gemm_variant(old)
+    assert np.isfinite(y).all()
+    assert product.rel_err(y, ref) <= 1e-3

@@ -103,7 +103,8 @@ def test_c_route():
     assert r(1, Q4_K, BIG, K, 0) == _cabi.KERNEL_GEMV and r(2, Q4_K, BIG, K, 0) == _cabi.KERNEL_MMV
     assert r(3, IQ4_XS, BIG, K, 0) == _cabi.KERNEL_GEMV and r(4, IQ4_XS, BIG, K, 0) == _cabi.KERNEL_MMV
     assert r(48, Q4_K, BIG, K, 0) == _cabi.KERNEL_MMV and r(49, Q4_K, BIG, K, 0) == _cabi.KERNEL_GEMM
-    assert r(512, Q4_K, BIG, K, 0) == _cabi.KERNEL_GEMM_PREFILL and r(256, Q4_K, 5120, K, 0) == _cabi.KERNEL_GEMM
+    assert r(512, Q4_K, BIG, K, 0) == _cabi.KERNEL_GEMM_PREFILL and r(256, Q4_K, 5120, K, 0) == _cabi.KERNEL_GEMM_PREFILL
+    assert r(255, Q4_K, 5120, K, 0) == _cabi.KERNEL_GEMM and r(128, Q4_K, BIG, K, 0) == _cabi.KERNEL_GEMM_PREFILL
     assert r(256, IQ4_XS, 5120, K, 0) == _cabi.KERNEL_GEMM_PREFILL and r(255, IQ4_XS, 5120, K, 0) == _cabi.KERNEL_GEMM
     assert r(128, IQ3_S, 17408, K, 1) == _cabi.KERNEL_GEMM_PREFILL and r(128, IQ3_S, 5120, K, 1) == _cabi.KERNEL_GEMM
     assert r(8192, Q6_K, 151936, K, 1) == _cabi.KERNEL_MMV     # repacked Q6_K: 48 rows per launch

@@ -174,7 +174,7 @@ extern "C" int gsq_route(int64_t m, int ggml_type, int64_t rows, int64_t k, int 
   if (m <= 8) return GSQ_KERNEL_GEMV;
   if (gsq::gemm2_applies(ggml_type, packed, rows)) {
     const bool tall = (rows + 127) / 128 >= 74;
-    const bool fp16_operands = ggml_type == GSQ_TYPE_IQ3_S || ggml_type == GSQ_TYPE_IQ4_XS;   // gsq_gemm3.cu (IQ3_S: packed, by gemm2_applies)
+    const bool fp16_operands = true;   // gsq_gemm3.cu serves all three types of gemm2_applies in the default precision
     const bool big = fp16_operands ? (m >= 256 || (m >= 128 && tall)) : (m >= 512 || (m >= 192 && tall));
     return big ? GSQ_KERNEL_GEMM_PREFILL : GSQ_KERNEL_GEMM;
   }

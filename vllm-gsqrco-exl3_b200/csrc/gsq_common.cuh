@@ -27,6 +27,9 @@ constexpr int Q8_TILES_H16 = 2;
 // the products d * q themselves as fp16, scaled by a power of two per token: the rounded product alone (16 KB per unit)
 // or with the rounding's remainder as a second fp16 plane (2 x 16 KB per unit); see gemm3_acc_kernel
 constexpr int Q8_TILES_F16S = 3, Q8_TILES_F16S2 = 4;
+// Q8_TILES_F16S with d and the sum of x kept as halves (Q4_K's q8_1 form) and, behind the units, the scaled sums as a
+// tensor-core operand of their own: one 8 KB unit per token block and superblock
+constexpr int Q8_TILES_F16SD = 5;
 
 struct DeviceInfo {
   int sm_count;

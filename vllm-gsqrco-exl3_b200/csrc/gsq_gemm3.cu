@@ -530,22 +530,28 @@ constexpr int UBA = 2 * HB;             // one copy and one turn of the MMA thre
 constexpr int ACC_B_SLOTS = 3;
 constexpr int ACC_B_AHEAD = 2;
 
-// weight formats of this kernel: IQ3_S in the fragment-ordered layout (decode_pair above), IQ4_XS in GGUF order
-enum { WK_IQ3S = 0, WK_IQ4XS = 1 };
+// weight formats of this kernel: IQ3_S in the fragment-ordered layout (decode_pair above), IQ4_XS and Q4_K in GGUF order
+enum { WK_IQ3S = 0, WK_IQ4XS = 1, WK_Q4K = 2 };
 constexpr int RAWB_IQ4XS = 128 * 136;   // one superblock of 128 rows
+constexpr int RAWB_Q4K = 128 * 144;
+constexpr int SUB = 8192;               // Q4_K: one unit of per-slice activation terms (256 tokens x 16 fp16)
+constexpr int AMINB = 4096;             // Q4_K: the per-slice weight terms of a superblock that go with them (128 rows x 16 fp16)
 
 template <int WK>
 struct SmemAcc {
   static constexpr int BAR = 0;
   static constexpr int GRID = 1024;
-  static constexpr int RAWBK = WK == WK_IQ3S ? RAWB : RAWB_IQ4XS;
+  static constexpr int RAWBK = WK == WK_IQ3S ? RAWB : WK == WK_IQ4XS ? RAWB_IQ4XS : RAWB_Q4K;
   static constexpr int RAW = GRID + (WK == WK_IQ3S ? GRIDB : 0);   // (IQ4_XS: a 16-entry table, in registers)
   static constexpr int A = (RAW + RAW_STAGES * RAWBK + 127) / 128 * 128;
   static constexpr int B = A + A_STAGES * STAGE_A;
-  static constexpr int SAX = B + ACC_B_SLOTS * UBA;      // scratch the shared IQ3_S decoder writes its scale planes to (unused here)
-  static constexpr int TOTAL = SAX + SA_STAGE;
+  static constexpr int AMIN = B + ACC_B_SLOTS * UBA;     // Q4_K only: the operand of per-slice weight terms, then one unit of sums
+  static constexpr int BS = AMIN + (WK == WK_Q4K ? AMINB : 0);
+  static constexpr int SAX = BS + (WK == WK_Q4K ? SUB : 0);   // scratch the IQ3_S decoder writes its scale planes to (unused here)
+  static constexpr int TOTAL = SAX + (WK == WK_IQ3S ? SA_STAGE : 0);
 };
-static_assert(SmemAcc<0>::B % 128 == 0 && SmemAcc<1>::B % 128 == 0 && RAWB_IQ4XS % 16 == 0, "operand alignment");
+static_assert(SmemAcc<0>::B % 128 == 0 && SmemAcc<1>::B % 128 == 0 && SmemAcc<2>::B % 128 == 0 && RAWB_IQ4XS % 16 == 0, "operand alignment");
+static_assert(SmemAcc<0>::TOTAL <= 227 * 1024 && SmemAcc<1>::TOTAL <= 227 * 1024 && SmemAcc<2>::TOTAL <= 227 * 1024, "shared memory budget");
 
 __constant__ __align__(16) int8_t c_iq4nl3[16] = GSQ_IQ4NL_VALUES_INIT;
 
@@ -602,6 +608,87 @@ __device__ __forceinline__ void decode_iq4xs_f16(const uint8_t* raw, uint8_t* a,
   }
 }
 
+__device__ __forceinline__ void fetch_raw_q4k(const Args& g, int rt, int sb, uint8_t* raw, int ptid) {
+  const uint32_t dst = saddr(raw);
+  for (int i = ptid; i < 128 * 9; i += PROD_THREADS) {
+    const int r = i / 9, c = i - r * 9;
+    const int row = min(rt * TR + r, g.nrows - 1);
+    cp_async16(dst + r * 144 + c * 16, g.w + (int64_t)row * g.row_bytes + (int64_t)sb * 144 + c * 16);
+  }
+}
+
+// Q4_K: the scale the consumers apply per superblock and row. Normally d itself, so that the weight operand holds the
+// integers sc * q exactly; where dmin is more than 64 times d (or d is zero), dmin / 64, so that the minimum-term
+// operand -(dmin / sigma) * m * 16 stays inside fp16 (at most 64 * 63 * 16).
+__device__ __forceinline__ float q4k_sigma(uint32_t d_dmin) {
+  const float d = h2f(d_dmin), dm = h2f(d_dmin >> 16);
+  float sigma = fabsf(dm) > 64.0f * fabsf(d) ? fabsf(dm) * (1.0f / 64.0f) : d;
+  return sigma == 0.0f ? 1.0f : sigma;
+}
+// 6-bit scales and minimums of slices 2 jj, 2 jj + 1 (low / high byte of the results) from the 12 packed bytes
+__device__ __forceinline__ void q4k_scale_min(const uint4& hdr, int jj, uint32_t& sc, uint32_t& mn) {
+  const uint32_t selh = (jj & 1) ? 0x4432u : 0x4410u;
+  const uint32_t A = prmt(hdr.y, 0u, selh), B = prmt(hdr.z, 0u, selh), C = prmt(hdr.w, 0u, selh);
+  sc = jj < 2 ? (A & 0x3F3Fu) : ((C & 0x0F0Fu) | ((A & 0xC0C0u) >> 2));
+  mn = jj < 2 ? (B & 0x3F3Fu) : (((C >> 4) & 0x0F0Fu) | ((B & 0xC0C0u) >> 2));
+}
+
+// Q4_K, item = (slice pair, 16-byte piece, row) of half HF: 16 bytes of quants (low nibbles: 16 values of slice 2 jj,
+// high nibbles: of slice 2 jj + 1) -> (d / sigma) * sc * q as fp16, two 16-byte core-matrix rows per slice. A nibble
+// under the high byte 0x64 is the fp16 number 1024 + q; (1024 + q) * f - 1024 * f in one fused multiply-add is q * f
+// with one rounding (none whenever sigma = d: f is the integer sc).
+template <int HF>
+__device__ __forceinline__ void decode_q4k_f16(const uint8_t* raw, uint8_t* a, int item) {
+  const int r = item & 127, sub = item >> 7, jj = 2 * HF + (sub >> 1), half = sub & 1;
+  const uint8_t* b = raw + r * 144;
+  const uint4 hdr = *reinterpret_cast<const uint4*>(b);
+  const uint4 v = *reinterpret_cast<const uint4*>(b + 16 + 32 * jj + 16 * half);
+  uint32_t sc, mn;
+  q4k_scale_min(hdr, jj, sc, mn);
+  const float ratio = h2f(hdr.x) / q4k_sigma(hdr.x);    // exactly 1 in the normal case
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int hi = 0; hi < 2; ++hi) {
+    const __half fh = __float2half_rn(ratio * (float)((sc >> (8 * hi)) & 0xFFu));
+    const __half2 f2 = __half2half2(fh);
+    const __half2 nb2 = __half2half2(__hmul(__float2half_rn(-1024.0f), fh));
+    uint8_t* dst = a + (2 * (sub >> 1) + hi) * SL_A + (r >> 3) * 512 + (2 * half) * 128 + (r & 7) * 16;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const uint32_t n0 = (w[2 * c] >> (4 * hi)) & 0x0F0F0F0Fu, n1 = (w[2 * c + 1] >> (4 * hi)) & 0x0F0F0F0Fu;
+      uint4 o;
+      o.x = hfma2_bits(prmt(n0, 0x64646464u, 0x4140u), f2, nb2);
+      o.y = hfma2_bits(prmt(n0, 0x64646464u, 0x4342u), f2, nb2);
+      o.z = hfma2_bits(prmt(n1, 0x64646464u, 0x4140u), f2, nb2);
+      o.w = hfma2_bits(prmt(n1, 0x64646464u, 0x4342u), f2, nb2);
+      *reinterpret_cast<uint4*>(dst + c * 128) = o;
+    }
+  }
+}
+
+// Q4_K, one row of a superblock: the weight terms that multiply per-slice quantities of the activations, as a
+// 16-column operand for the unit the quantiser writes per superblock (layout with sums): K chunk 0 =
+// -(dmin / sigma) * m_s * 16, against half(sum x) * 2^(e - 4): the minimum term; chunk 1 = 8 * (d / sigma) * sc_s * 16
+// (128 sc exactly when sigma = d), against what the fp16 rounding of the slice's products lost in total / 16: the
+// quants 0..15 act on the rounding errors as 8 + (q - 8), and this gives the 8's share back, so that only the
+// centred part of the weights sees them. The consumers scale the superblock's accumulator by sigma.
+__device__ __forceinline__ void q4k_slice_terms(const uint8_t* raw, uint8_t* amin, int r) {
+  const uint4 hdr = *reinterpret_cast<const uint4*>(raw + r * 144);
+  const float sigma = q4k_sigma(hdr.x);
+  const float fm = -16.0f * h2f(hdr.x >> 16) / sigma, fs = 128.0f * (h2f(hdr.x) / sigma);
+  __half2 hm[4], hs[4];
+#pragma unroll
+  for (int jj = 0; jj < 4; ++jj) {
+    uint32_t sc, mn;
+    q4k_scale_min(hdr, jj, sc, mn);
+    hm[jj] = __floats2half2_rn(fm * (float)(mn & 0xFFu), fm * (float)(mn >> 8));
+    hs[jj] = __floats2half2_rn(fs * (float)(sc & 0xFFu), fs * (float)(sc >> 8));
+  }
+  uint8_t* dst = amin + (r >> 3) * 256 + (r & 7) * 16;
+  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(hm);
+  *reinterpret_cast<uint4*>(dst + 128) = *reinterpret_cast<const uint4*>(hs);
+}
+
 // PAIR: two CTAs (a cluster) share an item of 256 weight rows x 256 tokens. Each decodes its own 128 rows and copies
 // only its half of the tokens of every activation unit; the MMAs (M = 256, cta_group::2) are issued by CTA 0 and read
 // both halves, so every CTA moves half the activation bytes from L2 and through its shared memory per result. CTA 0's
@@ -614,6 +701,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
   extern __shared__ __align__(1024) uint8_t smem[];
   using S = SmemAcc<WK>;
   static_assert(WK == WK_IQ3S || !PAIR, "pairs of CTAs: IQ3_S only");
+  static_assert(WK != WK_Q4K || HU == 1, "Q4_K: the rounded form only");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   constexpr int NB = PAIR ? 2 * ACC_B_SLOTS : ACC_B_SLOTS;      // activation slots (half the bytes each for a pair)
@@ -627,7 +715,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
   const uint32_t bar0 = saddr(smem + S::BAR);
   const uint32_t a_full = bar0, a_empty = bar0 + 16, d_full = bar0 + 32, d_empty = bar0 + 48, b_full = bar0 + 64,
                  b_empty = b_full + 8 * NB, b_peer = b_empty + 8 * NB;
-  static_assert(64 + 3 * 8 * 2 * ACC_B_SLOTS <= 256, "barrier area");
+  static_assert(64 + 3 * 8 * 2 * ACC_B_SLOTS + 32 <= 256, "barrier area");
+  const uint32_t s_full = bar0 + 64 + 3 * 8 * 2 * ACC_B_SLOTS, s_empty = s_full + 16;   // Q4_K: units of sums
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + S::BAR + 256);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + S::BAR + 260);
   const uint32_t hint = g.wait_hint;
@@ -648,6 +737,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
       mbar_init(a_empty + 8 * i, 1);          // the MMAs that read the stage have completed
       mbar_init(d_full + 8 * i, 1);
       mbar_init(d_empty + 8 * i, CONS_WARPS * (PAIR ? 2 : 1));
+      mbar_init(s_full + 8 * i, 1);
+      mbar_init(s_empty + 8 * i, 1);
     }
     for (int i = 0; i < NB; ++i) {
       mbar_init(b_full + 8 * i, 1);
@@ -690,7 +781,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
     auto fetch_next = [&](uint32_t n_fetch) {
       if (f_item < n_items) {
         if (WK == WK_IQ3S) fetch_raw(g, item_rt(f_item), f_sb, smem + S::RAW + (n_fetch & 1u) * S::RAWBK, ptid);
-        else fetch_raw_iq4xs(g, item_rt(f_item), f_sb, smem + S::RAW + (n_fetch & 1u) * S::RAWBK, ptid);
+        else if (WK == WK_IQ4XS) fetch_raw_iq4xs(g, item_rt(f_item), f_sb, smem + S::RAW + (n_fetch & 1u) * S::RAWBK, ptid);
+        else fetch_raw_q4k(g, item_rt(f_item), f_sb, smem + S::RAW + (n_fetch & 1u) * S::RAWBK, ptid);
         if (++f_sb == nsb) { f_sb = 0; f_item += n_groups; }
       }
       cp_async_commit();
@@ -713,7 +805,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
         asm volatile("bar.sync 1, %0;" ::"n"(PROD_THREADS) : "memory");
         fetch_next(ns + 1);
         const uint8_t* raw = smem + S::RAW + (ns & 1u) * S::RAWBK;
-        int it4 = ptid;   // IQ4_XS: this thread's next (slice, row) of the superblock, 1024 of them in half order
+        int it4 = ptid;   // IQ4_XS, Q4_K: this thread's next item of the superblock, 1024 of them in half order
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           const unsigned long long p0 = tick();
@@ -722,7 +814,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
           pw[0] += p1 - p0;
           if (alive) {
             uint8_t* a = smem + S::A + ra.i * STAGE_A;
-            if (WK == WK_IQ4XS) {
+            if (WK == WK_Q4K) {
+              // (the minimum-term operand belongs to the first half's stage: the MMA that reads it is issued before
+              // that half's, so the stage's release covers it)
+              if (hf == 0 && ptid < TR) q4k_slice_terms(raw, smem + S::AMIN, ptid);
+              for (; it4 < 512 * (hf + 1); it4 += PROD_THREADS) {
+                if (hf == 0) decode_q4k_f16<0>(raw, a, it4);
+                else decode_q4k_f16<1>(raw, a, it4 - 512);
+              }
+            } else if (WK == WK_IQ4XS) {
               // 512 (slice, row) items per half over 224 threads: the thread carries on where it stopped in the first
               // half, so the superblock takes 5 rounds, not 2 x 3
               for (; it4 < 512 * (hf + 1); it4 += PROD_THREADS) {
@@ -790,6 +890,23 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
           load_item();
         }
       };
+      // Q4_K: the units of sums, one per (item, superblock); one slot, refilled for the next superblock as soon as this
+      // superblock's two instructions on it have completed
+      int s_item = group, s_sb = 0;
+      uint32_t n_sums_loaded = 0, n_sums_used = 0;
+      Ring rsl = {0u, 0u}, rsu = {0u, 0u};
+      const uint8_t* s_region = g.xt + (int64_t)g.n_tok_blocks * units_item * UBA;
+      auto load_sums = [&]() {
+        if (WK != WK_Q4K || s_item >= n_items || !alive) return;
+        alive = wait(s_empty + 8 * rsl.i, rsl.ph ^ 1u);
+        if (!alive) return;
+        mbar_expect_tx(s_full + 8 * rsl.i, SUB);
+        bulk_g2s(saddr(smem + S::BS) + rsl.i * SUB, s_region + ((int64_t)item_tb(s_item) * nsb + s_sb) * SUB, SUB, s_full + 8 * rsl.i);
+        rsl.next(1);
+        ++n_sums_loaded;
+        if (++s_sb == nsb) { s_sb = 0; s_item += n_groups; }
+      };
+      load_sums();
       for (int i = 0; i < AHEAD; ++i) load_next();
       Ring ra = {0u, 0u}, rb = {0u, 0u}, rd = {0u, 0u};
       uint32_t n_used = 0;
@@ -821,6 +938,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
           }
           const uint32_t a_lo = a_lo0 + ra.i * (STAGE_A >> 4);
           const uint32_t d_addr = tmem_base + rd.i * 256;
+          if (WK == WK_Q4K && (st2 & 1) == 0) {
+            // the superblock's sum starts with the terms in per-slice sums (minimums, offset of the centred quants)
+            alive = alive && wait(s_full + 8 * rsu.i, rsu.ph);
+            if (!alive) break;
+            tc_fence_after();
+            mma_f16(d_addr, tc::smem_desc(saddr(smem + S::AMIN), 128, 256), tc::smem_desc(saddr(smem + S::BS) + rsu.i * SUB, 128, 256), id, 0u);
+            mma_commit(s_empty + 8 * rsu.i);
+            rsu.next(1);
+            ++n_sums_used;
+          }
 #pragma unroll 1
           for (int u2 = 0; u2 < 2 * HU && alive; ++u2) {
             const unsigned long long m3 = tick();
@@ -832,7 +959,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
             const uint32_t b_lo = b_lo0 + rb.i * (UBC >> 4);
             // HU = 1: slices 2 u2, 2 u2 + 1 against the unit's two planes; HU = 2: slice u2 against hi, then lo
             const uint32_t as0 = a_lo + (HU == 1 ? 2 * u2 : u2) * (SL_A >> 4), as1 = HU == 1 ? as0 + (SL_A >> 4) : as0;
-            const uint32_t first = ((st2 & 1) == 0 && u2 == 0) ? 0u : 1u;
+            const uint32_t first = (WK != WK_Q4K && (st2 & 1) == 0 && u2 == 0) ? 0u : 1u;
             if (PAIR) {
               mma_f16_pair(d_addr, desc(as0), desc(b_lo), id, first);
               mma_f16_pair(d_addr, desc(as0 + (256 >> 4)), desc(b_lo + (256 >> 4)), id, 1u);
@@ -849,6 +976,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
             rb.next(NB);
             ++n_used;
             load_next();
+            if (WK == WK_Q4K && (st2 & 1) == 0 && u2 == 0) load_sums();   // the next superblock's sums
           }
           if (!alive) break;
           if (PAIR) mma_commit_pair(a_empty + 8 * ra.i);
@@ -874,6 +1002,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
           wait(b_full + 8 * rb.i, rb.ph);
           rb.next(NB);
         }
+        for (; n_sums_used < n_sums_loaded; ++n_sums_used) {
+          wait(s_full + 8 * rsu.i, rsu.ph);
+          rsu.next(1);
+        }
       }
     }
   } else {
@@ -889,11 +1021,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm3_acc_kernel(const Args g) {
       const int row = rt * TR + r_in;
       const bool row_ok = row < g.nrows;
       // fp16 d of this thread's row. IQ3_S: halfword (row % 16) / 8 of word row % 8 at byte 1728 of its 16-row record;
-      // IQ4_XS: the first two bytes of the row's block
+      // IQ4_XS: the first two bytes of the row's block; Q4_K: the scale worked out from its first four (d, dmin)
       const uint8_t* dwp = WK == WK_IQ3S ? g.w + (int64_t)(row & ~15) * g.row_bytes + 1728 + 4 * (row & 7) + 2 * ((row >> 3) & 1)
                                          : g.w + (int64_t)row * g.row_bytes;
       auto load_dw = [&](int sb) -> float {
-        return row_ok ? h2f(*reinterpret_cast<const uint16_t*>(dwp + (int64_t)sb * (WK == WK_IQ3S ? 1760 : 136))) : 0.0f;
+        if (!row_ok) return 0.0f;
+        if (WK == WK_Q4K) return q4k_sigma(*reinterpret_cast<const uint32_t*>(dwp + (int64_t)sb * 144));
+        return h2f(*reinterpret_cast<const uint16_t*>(dwp + (int64_t)sb * (WK == WK_IQ3S ? 1760 : 136)));
       };
       float2 acc[32];
 #pragma unroll
@@ -1003,6 +1137,10 @@ static int launch_acc(const Args& g, int sm_count, cudaStream_t st) {
 static int launch(const Args& g, int sm_count, int wk, int acc, int pair, cudaStream_t st) {
   if (acc) {
     if (g.dump) return GSQ_ERR_UNSUPPORTED;   // no per-slice integer sums exist in this form
+    if (wk == WK_Q4K) {
+      if (pair || acc != 1) return GSQ_ERR_UNSUPPORTED;
+      return g.prof ? launch_acc<WK_Q4K, 1, true, false>(g, sm_count, st) : launch_acc<WK_Q4K, 1, false, false>(g, sm_count, st);
+    }
     if (wk == WK_IQ4XS) {
       if (pair) return GSQ_ERR_UNSUPPORTED;
       if (acc == 1) return g.prof ? launch_acc<WK_IQ4XS, 1, true, false>(g, sm_count, st) : launch_acc<WK_IQ4XS, 1, false, false>(g, sm_count, st);
@@ -1056,16 +1194,17 @@ int gemm3_error_flag(int* flag) {
 
 // bytes of the fp16 activation units of m tokens x k columns (tokens padded to whole blocks of 256). acc: 0 = quants
 // and d per slice, 1 / 2 = scaled products in one / two fp16 planes, then one float per token
-size_t gemm3_tile_bytes(int64_t m, int64_t k, int acc) {
+// (acc = 1 with `sums`: Q4_K's layout, one more 8 KB unit per token block and superblock)
+size_t gemm3_tile_bytes(int64_t m, int64_t k, int acc, int sums) {
   const int64_t tb = (m + g3::NT - 1) / g3::NT;
-  if (acc) return (size_t)(tb * (k / 256) * 8 * acc * g3::HB + tb * g3::NT * 4);
+  if (acc) return (size_t)(tb * (k / 256) * (8 * acc * g3::HB + (sums ? g3::SUB : 0)) + tb * g3::NT * 4);
   return (size_t)(tb * (k / 256) * 8 * g3::UB);
 }
 
 bool gemm3_applies(int ggml_type, int packed, int64_t rows) { return ggml_type == GSQ_TYPE_IQ3_S && packed && rows % 16 == 0; }
 // the forms that sum over a superblock in tensor memory also serve IQ4_XS (GGUF order)
 bool gemm3_acc_applies(int ggml_type, int packed, int64_t rows) {
-  return gemm3_applies(ggml_type, packed, rows) || (ggml_type == GSQ_TYPE_IQ4_XS && !packed);
+  return gemm3_applies(ggml_type, packed, rows) || ((ggml_type == GSQ_TYPE_IQ4_XS || ggml_type == GSQ_TYPE_Q4_K) && !packed);
 }
 
 // x_tiles: the output of quantize_tiles_host in the fp16 layout that goes with acc (Q8_TILES_H16, _F16S, _F16S2)
@@ -1074,8 +1213,8 @@ int gemm3_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
   if (m == 0 || rows == 0) return GSQ_OK;
   if (m < 0 || rows < 0 || k <= 0 || k % 256 != 0 || !w || !x_tiles || !y) return GSQ_ERR_UNSUPPORTED;
   if (rows > INT32_MAX || k > INT32_MAX || m > INT32_MAX) return GSQ_ERR_TOO_LARGE;
-  const bool iq4 = ggml_type == GSQ_TYPE_IQ4_XS;
-  if (iq4 ? (!acc || packed || row_bytes != (k / 256) * 136) : (!gemm3_applies(ggml_type, packed, rows) || row_bytes != (k / 256) * 110))
+  const bool iq4 = ggml_type == GSQ_TYPE_IQ4_XS, q4k = ggml_type == GSQ_TYPE_Q4_K;
+  if (iq4 || q4k ? (!acc || packed || row_bytes != (k / 256) * (iq4 ? 136 : 144)) : (!gemm3_applies(ggml_type, packed, rows) || row_bytes != (k / 256) * 110))
     return GSQ_ERR_UNSUPPORTED;
   if (y_dtype != GSQ_F32 && y_dtype != GSQ_F16 && y_dtype != GSQ_BF16) return GSQ_ERR_UNSUPPORTED;
   DeviceInfo di;
@@ -1096,9 +1235,9 @@ int gemm3_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
   g.dump = gemm_dump_pointer();
   g.prof = gemm_profile_pointer();
   g.wait_hint = (uint32_t)g_wait_hint;
-  g.inv_scale = acc ? reinterpret_cast<const float*>((const uint8_t*)x_tiles + (size_t)g.n_tok_blocks * (k / 256) * 8 * acc * g3::HB) : nullptr;
+  g.inv_scale = acc ? reinterpret_cast<const float*>((const uint8_t*)x_tiles + (size_t)g.n_tok_blocks * (k / 256) * (8 * acc * g3::HB + (q4k ? g3::SUB : 0))) : nullptr;
   if (acc < 0 || acc > 2) return GSQ_ERR_UNSUPPORTED;
-  return g3::launch(g, di.sm_count, iq4 ? g3::WK_IQ4XS : g3::WK_IQ3S, acc, pair, (cudaStream_t)stream);
+  return g3::launch(g, di.sm_count, iq4 ? g3::WK_IQ4XS : q4k ? g3::WK_Q4K : g3::WK_IQ3S, acc, pair, (cudaStream_t)stream);
 }
 
 }  // namespace gsq

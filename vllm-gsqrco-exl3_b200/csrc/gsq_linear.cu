@@ -20,7 +20,7 @@ int gemm2_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
 // gsq_gemm3.cu
 bool gemm3_applies(int ggml_type, int packed, int64_t rows);
 bool gemm3_acc_applies(int ggml_type, int packed, int64_t rows);
-size_t gemm3_tile_bytes(int64_t m, int64_t k, int acc);
+size_t gemm3_tile_bytes(int64_t m, int64_t k, int acc, int sums);
 int gemm3_host(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, int packed, const void* x_tiles, int64_t m,
                int64_t k, void* y, int y_dtype, int64_t y_row_stride, int acc, int pair, void* stream);
 // gsq_quantize.cu
@@ -46,7 +46,7 @@ extern "C" size_t gsq_linear_scratch_bytes(int64_t rows, int64_t m, int64_t k, i
   const size_t mmq = (size_t)(k / 128) * (size_t)m * 144, q81 = (size_t)(k / 32) * (size_t)m * 36;
   size_t tiles = gsq::gemm3_applies(ggml_type, packed, rows) ? 0 : gsq::gemm2_tile_bytes(m, k, ggml_type);
   if (gsq::gemm3_acc_applies(ggml_type, packed, rows)) {
-    const size_t t3 = gsq::gemm3_tile_bytes(m, k, 2);
+    const size_t t3 = gsq::gemm3_tile_bytes(m, k, 2, 1);
     tiles = tiles > t3 ? tiles : t3;
   }
   size_t b = mmq > tiles ? mmq : tiles;
@@ -89,14 +89,16 @@ extern "C" int gsq_linear(const void* w, int64_t row_bytes, int64_t rows, int gg
     int acc = g_prefill_precision == GSQ_PREFILL_ROUNDED ? 1 : g_prefill_precision == GSQ_PREFILL_SPLIT ? 2 : 0;
     // IQ4_XS: (ls - 32) * value reaches 4064 and is not always exact in fp16, so only the rounded form is offered on
     // fp16 operands; the split setting takes the int8 kernel's integer sums instead
-    if (ggml_type == GSQ_TYPE_IQ4_XS && acc == 2) acc = 0;
+    // (and Q4_K, whose minimum term is folded in with one rounding of dmin / d * m)
+    if ((ggml_type == GSQ_TYPE_IQ4_XS || ggml_type == GSQ_TYPE_Q4_K) && acc == 2) acc = 0;
     int pair = 0;
     if (variant == 5 || variant == 9) acc = 2;
     if (variant == 6 || variant == 8) acc = 1;
     if (variant == 8 || variant == 9) pair = gemm3_applies(ggml_type, packed, rows) ? 1 : 0;
     if (variant == 7 || gemm_dump_pointer()) acc = 0;
     if (acc || gemm3_applies(ggml_type, packed, rows)) {
-      rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride, acc == 2 ? Q8_TILES_F16S2 : acc == 1 ? Q8_TILES_F16S : Q8_TILES_H16,
+      rc = quantize_tiles_host(x, x_dtype, m, k, x_row_stride,
+                               acc == 2 ? Q8_TILES_F16S2 : acc == 1 ? (ggml_type == GSQ_TYPE_Q4_K ? Q8_TILES_F16SD : Q8_TILES_F16S) : Q8_TILES_H16,
                                scratch, stream);
       if (rc != GSQ_OK) return rc;
       return gemm3_host(w, row_bytes, rows, ggml_type, packed, scratch, m, k, y, y_dtype, y_row_stride, acc, pair, stream);

@@ -218,6 +218,13 @@ __global__ void __launch_bounds__(256) row_scale_kernel(const T* __restrict__ x,
 //                   bytes) and, for _F16S2, lo = fp16(d * q * 2^e - hi) (16384 more); after the last unit one float
 //                   per token of the padded range, 2^-e[token] (row_scale_kernel: 2^e brings the token's largest
 //                   magnitude to [2^13, 2^14), so no product overflows fp16 and hi + lo carries 22 bits of each)
+//   ... with sums (LAYOUT = Q8_TILES_F16SD, for Q4_K): d and sum x rounded to halves as the reference's DS4 blocks
+//                   keep them; between the last unit and the per-token floats one 8 KB unit per token block and
+//                   superblock, [32 token groups][2 K chunks of 8][8 tokens][8 fp16], for the 8 slices:
+//                   chunk 0 = half(sum x) * 2^(e - 4) (exact, below 2^15: the minimum term's activations);
+//                   chunk 1 = (sum of the slice's exact products - sum of the rounded ones) * 2^-4, what the rounding
+//                   took from the slice in total. Q4_K's quants are all of one sign (0..15), so the roundings would
+//                   add up along a slice as 8 sc * (sum of the errors); the kernel adds that amount back.
 // Tokens past m (up to the end of the last block) are written as zeros. One CUDA block = 64 tokens x one slice:
 // warp w holds token group w of the 64, lane = (token % 8) * 4 + 8-value piece, so a warp writes whole core matrices.
 template <typename T, bool VEC, int LAYOUT>
@@ -225,8 +232,9 @@ __global__ void __launch_bounds__(256) quantize_q8_1_tiles_kernel(const T* __res
                                                                  int64_t m, int64_t k, int64_t stride) {
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  constexpr bool DS = LAYOUT == GSQ_Q8_LAYOUT_DS4, H16 = LAYOUT == Q8_TILES_H16;
-  constexpr bool F16S = LAYOUT == Q8_TILES_F16S || LAYOUT == Q8_TILES_F16S2, LO = LAYOUT == Q8_TILES_F16S2;
+  constexpr bool SD = LAYOUT == Q8_TILES_F16SD;
+  constexpr bool DS = LAYOUT == GSQ_Q8_LAYOUT_DS4 || SD, H16 = LAYOUT == Q8_TILES_H16;
+  constexpr bool F16S = LAYOUT == Q8_TILES_F16S || LAYOUT == Q8_TILES_F16S2 || SD, LO = LAYOUT == Q8_TILES_F16S2;
   constexpr int UB = F16S ? (LO ? 32768 : 16384) : H16 ? 16384 + 1024 : 8192 + (DS ? 2048 : 1024);
   const int slice = blockIdx.x;              // 32-value slice along k
   const int64_t tt = blockIdx.y;             // token tile
@@ -265,16 +273,35 @@ __global__ void __launch_bounds__(256) quantize_q8_1_tiles_kernel(const T* __res
   const int rb = (int)(tt & 3) * 64 + r;   // token within its block of 256
   uint8_t* unit = out + (((tt >> 2) * (k >> 8) + sb) * 8 + s) * UB;
   if constexpr (F16S) {
-    const float* inv_scale = reinterpret_cast<const float*>(out + (int64_t)gridDim.y / 4 * (k >> 8) * 8 * UB);
-    const float ds = live ? d * (1.0f / inv_scale[row]) : 0.0f;   // a power of two: exact
+    uint8_t* behind = out + (int64_t)gridDim.y / 4 * (k >> 8) * 8 * UB;     // what follows the last unit
+    const float* inv_scale = reinterpret_cast<const float*>(behind + (SD ? (int64_t)gridDim.y / 4 * (k >> 8) * 8192 : 0));
+    const float up = live ? 1.0f / inv_scale[row] : 0.0f;         // 2^e, a power of two: the products below are exact
+    float sum_half = 0.0f;
+    if constexpr (SD) {
+      const float2 dsum = __half22float2(__floats2half2_rn(d, sum));   // the reference keeps half2(d, sum)
+      d = dsum.x;
+      sum_half = dsum.y;
+    }
+    const float ds = d * up;
     uint8_t* dst = unit + (rb >> 3) * 512 + piece * 128 + (rb & 7) * 16;
     __half2 hi[4], lo[4];
+    float lost = 0.0f;   // exact products minus rounded ones, this lane's 8 values
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float p0 = ds * q[2 * e], p1 = ds * q[2 * e + 1];
       hi[e] = __floats2half2_rn(p0, p1);
       const float2 back = __half22float2(hi[e]);
       lo[e] = __floats2half2_rn(p0 - back.x, p1 - back.y);
+      lost += (p0 - back.x) + (p1 - back.y);
+    }
+    if constexpr (SD) {
+      lost += __shfl_xor_sync(0xFFFFFFFFu, lost, 2);
+      lost += __shfl_xor_sync(0xFFFFFFFFu, lost, 1);
+      if (piece == 0) {
+        uint8_t* su = behind + ((tt >> 2) * (k >> 8) + sb) * 8192 + (rb >> 3) * 256 + (rb & 7) * 16;
+        reinterpret_cast<__half*>(su)[s] = __float2half_rn(sum_half * up * 0.0625f);
+        reinterpret_cast<__half*>(su + 128)[s] = __float2half_rn(lost * 0.0625f);
+      }
     }
     *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(hi);
     if constexpr (LO) *reinterpret_cast<uint4*>(dst + 16384) = *reinterpret_cast<const uint4*>(lo);
@@ -455,10 +482,12 @@ template <typename T, int LAYOUT>
 static int launch_q8_1_tiles(const void* x, int64_t m, int64_t k, int64_t stride, void* out, cudaStream_t st) {
   if (m == 0) return GSQ_OK;
   const bool vec = ((uintptr_t)x % 16 == 0) && ((stride * (int64_t)sizeof(T)) % 16 == 0);
-  if constexpr (LAYOUT == Q8_TILES_F16S || LAYOUT == Q8_TILES_F16S2) {
-    // first the per-token scales, behind the last unit
+  if constexpr (LAYOUT == Q8_TILES_F16S || LAYOUT == Q8_TILES_F16S2 || LAYOUT == Q8_TILES_F16SD) {
+    // first the per-token scales, behind the last unit (and the units of sums)
     const int64_t mpad = (m + 255) / 256 * 256;
-    float* inv_scale = reinterpret_cast<float*>((uint8_t*)out + mpad / 256 * (k >> 8) * 8 * (LAYOUT == Q8_TILES_F16S2 ? 32768 : 16384));
+    float* inv_scale = reinterpret_cast<float*>((uint8_t*)out + mpad / 256 * (k >> 8) *
+                                                                    (8 * (LAYOUT == Q8_TILES_F16S2 ? 32768 : 16384) +
+                                                                     (LAYOUT == Q8_TILES_F16SD ? 8192 : 0)));
     const unsigned grid = (unsigned)(mpad / 8);
     const int rc = vec ? launch_pdl(row_scale_kernel<T, true>, grid, st, (const T*)x, inv_scale, m, mpad, k, stride)
                        : launch_pdl(row_scale_kernel<T, false>, grid, st, (const T*)x, inv_scale, m, mpad, k, stride);
@@ -489,6 +518,7 @@ int quantize_tiles_host(const void* x, int x_dtype, int64_t m, int64_t k, int64_
   return layout == Q8_TILES_H16      ? launch_q8_1_tiles<T, Q8_TILES_H16>(x, m, k, stride, out, st)     \
          : layout == Q8_TILES_F16S   ? launch_q8_1_tiles<T, Q8_TILES_F16S>(x, m, k, stride, out, st)    \
          : layout == Q8_TILES_F16S2  ? launch_q8_1_tiles<T, Q8_TILES_F16S2>(x, m, k, stride, out, st)   \
+         : layout == Q8_TILES_F16SD  ? launch_q8_1_tiles<T, Q8_TILES_F16SD>(x, m, k, stride, out, st)   \
          : layout == GSQ_Q8_LAYOUT_D4 ? launch_q8_1_tiles<T, GSQ_Q8_LAYOUT_D4>(x, m, k, stride, out, st) \
                                       : launch_q8_1_tiles<T, GSQ_Q8_LAYOUT_DS4>(x, m, k, stride, out, st)
   switch (x_dtype) {
