@@ -660,7 +660,8 @@ NOMINAL_INT8_TOPS = 4500.0
 
 
 def extra_prefill(dev, capture, l2_bytes, with_ref=True):
-    """Prefill GEMM: M tokens x K=5120 -> N=17408 with IQ3_S weights, and M x K=17408 -> N=5120 with IQ4_XS;
+    """Prefill GEMM: M tokens x K=5120 -> N=17408 with IQ3_S weights, M x K=17408 -> N=5120 with IQ4_XS (the two products
+    of the prefill configuration), and M x K=5120 -> N=17408 with Q4_K;
     bf16 activations ~ N(0,1) with 0.1 % outliers x20, M in {2048, 8192, 16384}. Algorithmic ops = 2 M N K."""
     import torch
 
@@ -684,7 +685,7 @@ def extra_prefill(dev, capture, l2_bytes, with_ref=True):
         return e0.elapsed_time(e1) / 3
 
     raws, ref_rows = {}, []
-    for tname, t, n, k in (("IQ3_S", 21, 17408, 5120), ("IQ4_XS", 23, 5120, 17408)):
+    for tname, t, n, k in (("IQ3_S", 21, 17408, 5120), ("IQ4_XS", 23, 5120, 17408), ("Q4_K", 12, 17408, 5120)):
         raws[(tname, n, k)] = synth.make_weight(t, n, k, 1300)
         w = torch.from_numpy(raws[(tname, n, k)]).to(dev)
         packed = t == 21
@@ -700,7 +701,7 @@ def extra_prefill(dev, capture, l2_bytes, with_ref=True):
                    "frac_measured": round(tops / peak, 4) if peak else None,
                    "frac_nominal_f16": round(tops / 2250.0, 4)}
             # the other forms of this product (gsq_prefill_precision), and how far the default is from the one that keeps
-            # the reference's exact integer slice sums, relative to the result's norm (IQ4_XS: split = integer)
+            # the reference's exact integer slice sums, relative to the result's norm (IQ4_XS, Q4_K: split = integer)
             row["form"] = "rounded (default)"
             xf = x.float() if m == 2048 else None        # fp32 in, fp32 out: no output rounding in the comparison
             cmp_fn = lambda: linear.fused_mul_mat_gguf(xf, w, t, None, packed)
@@ -726,7 +727,7 @@ def extra_prefill(dev, capture, l2_bytes, with_ref=True):
         del w
     torch.cuda.empty_cache()
     # the reference's own many-row kernels (its MMQ; for IQ3_S also its packed route) on the 2048-token cells
-    ref = ref_kernels(ref_rows, raws, l2_bytes, {"IQ3_S": 21, "IQ4_XS": 23}) if with_ref else {"skipped": "--no-ref-kernels"}
+    ref = ref_kernels(ref_rows, raws, l2_bytes, {"IQ3_S": 21, "IQ4_XS": 23, "Q4_K": 12}) if with_ref else {"skipped": "--no-ref-kernels"}
     if "cells" in ref:
         ref["what"] = "reference kernels rebuilt for sm_100a on the 2048-token cells, quantise + product per call, graph replay"
         for c in ref["cells"]:
@@ -734,7 +735,7 @@ def extra_prefill(dev, capture, l2_bytes, with_ref=True):
     return {"int8_peak_nominal_TOPS": NOMINAL_INT8_TOPS, "int8_peak_measured_TOPS": peak,
             "int8_peak_how": "torch._int_mm 8192^3, best of 5", "includes": "activation quantisation + GEMM per call",
             "operands": "ops = 2 M N K whatever the operand type; the default (rounded) and split forms run on fp16 tensor-core "
-                        "operands (tcgen05 kind::f16, nominal dense peak 2250 TFLOP/s: frac_nominal_f16), IQ4_XS's integer form on int8",
+                        "operands (tcgen05 kind::f16, nominal dense peak 2250 TFLOP/s: frac_nominal_f16), the integer form of IQ4_XS and Q4_K on int8",
             "cells": rows, "ref_kernels": ref}
 
 

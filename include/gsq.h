@@ -234,15 +234,15 @@ int gsq_linear(const void* w, int64_t row_bytes, int64_t rows, int ggml_type, in
                size_t scratch_bytes, void* stream);
 
 /*
- * How gsq_linear forms the prefill product of repacked IQ3_S and of IQ4_XS (256 tokens and up; the other routes are
- * not affected).
+ * How gsq_linear forms the prefill product of repacked IQ3_S, of IQ4_XS and of Q4_K (256 tokens and up; the other
+ * routes are not affected).
  * The reference's kernels keep an exact int32 sum per 32-value slice and scale it in fp32
  * (lcpp_owned_iq3_mma.cu:768-970, mmq.cuh:961-1385). Sets the mode, returns the previous one:
  *   GSQ_PREFILL_ROUNDED (default)  d_x * q goes into the tensor-core operand as one fp16 number and tensor memory
  *                                  accumulates over a superblock: a result differs from the reference kernels' by
- *                                  about 3e-4 of its row's norm (bound of the parity tests: 1e-3); fastest
- *   GSQ_PREFILL_SPLIT              d_x * q as a pair of fp16 numbers (22 bits): differs by about 1e-6 (IQ4_XS, whose
- *                                  weights times sub-scales do not all fit fp16: as GSQ_PREFILL_INTEGER)
+ *                                  2e-4 .. 4e-4 of its row's norm (bound of the parity tests: 1e-3); fastest
+ *   GSQ_PREFILL_SPLIT              d_x * q as a pair of fp16 numbers (22 bits): differs by about 1e-6 (IQ4_XS and Q4_K,
+ *                                  whose weight operands carry a rounding of their own: as GSQ_PREFILL_INTEGER)
  *   GSQ_PREFILL_INTEGER            exact integer slice sums, scaled per slice as the reference does
  * A process-wide setting; not to be changed while products are in flight on another thread.
  */
