@@ -1278,6 +1278,9 @@ def run_cell(args):
     tname, n, k = args.cell[0], int(args.cell[1]), int(args.cell[2])
     ms = [int(v) for v in args.cell[3].split(",")]
     dev = "cuda:0"
+    from gsq_b200 import lcpp_ops
+    lcpp_ops.set_prefill_precision({"rounded": lcpp_ops.PREFILL_ROUNDED, "split": lcpp_ops.PREFILL_SPLIT,
+                                    "integer": lcpp_ops.PREFILL_INTEGER}[args.precision])
     t = {**synth.TYPE_IDS, **synth.LOW_BIT_TYPE_IDS}[tname]
     w0 = torch.from_numpy(synth.make_weight(t, n, k, 1)).to(dev)
     packed = tname in ("IQ3_S", "Q6_K") and not args.unpacked and n % 16 == 0
@@ -1338,6 +1341,8 @@ def main():
     ap.add_argument("--kernel", default="default", choices=["default", "tcgen05", "both"],
                     help="--cell: 'tcgen05' switches the register-operand small-batch kernel off, so that 9..48 rows run on "
                          "the tcgen05 GEMM instead; 'both' times one after the other")
+    ap.add_argument("--precision", default="rounded", choices=["rounded", "split", "integer"],
+                    help="--cell: form of the prefill product from 256 rows on (gsq_prefill_precision)")
     ap.add_argument("--graph", action="store_true", help="--cell: time a CUDA graph of the calls (no launch overhead), best of 3 replays")
     args = ap.parse_args()
     if args.cell:
