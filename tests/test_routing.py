@@ -124,3 +124,25 @@ def test_route_switch_keys_the_compile_cache():
     keep = reg["VLLM_GGUF_LCPP"]
     linear.register_compile_factor(reg)                # a second registration keeps the first entry
     assert reg["VLLM_GGUF_LCPP"] is keep
+
+
+def test_prefill_precision_setting():
+    """gsq_prefill_precision: a process-wide mode, returns the previous one, ignores values it does not know; the
+    scratch gsq_linear asks for covers every form's activation units."""
+    from gsq_b200 import _cabi, lcpp_ops
+
+    lib = _cabi.lib
+    assert lcpp_ops.set_prefill_precision(lcpp_ops.PREFILL_SPLIT) == lcpp_ops.PREFILL_ROUNDED      # rounded is the default
+    try:
+        assert lib.gsq_prefill_precision(99) == lcpp_ops.PREFILL_SPLIT and lib.gsq_prefill_precision(-1) == lcpp_ops.PREFILL_SPLIT
+        assert lcpp_ops.set_prefill_precision(lcpp_ops.PREFILL_INTEGER) == lcpp_ops.PREFILL_SPLIT
+    finally:
+        assert lcpp_ops.set_prefill_precision(lcpp_ops.PREFILL_ROUNDED) == lcpp_ops.PREFILL_INTEGER
+    m, k = 300, 5120
+    blocks = (m + 255) // 256 * (k // 256)
+    sb = lib.gsq_linear_scratch_bytes
+    # two fp16 planes per slice (split form) + Q4_K's unit of sums + one float per token of the padded range
+    need = blocks * (8 * 2 * 16384 + 8192) + (m + 255) // 256 * 256 * 4
+    for t, packed in ((IQ3_S, 1), (IQ4_XS, 0), (Q4_K, 0)):
+        assert sb(BIG, m, k, t, packed) >= need, (t, sb(BIG, m, k, t, packed), need)
+    assert sb(BIG, m, k, Q6_K, 1) < need            # a type without a prefill GEMM: q8_1 blocks only

@@ -1,5 +1,8 @@
-// Prefill GEMM for repacked IQ3_S with the sub-scales folded into the tensor-core operand (sm_100a: tcgen05
-// kind::f16 with fp32 accumulators in tensor memory), warp-specialised.
+// Prefill GEMMs with the sub-scales folded into the tensor-core operand (sm_100a: tcgen05 kind::f16 with fp32
+// accumulators in tensor memory), warp-specialised. Two kernels:
+//   gemm3_kernel      repacked IQ3_S; exact integer slice sums, scaled per 32-value slice (described next);
+//   gemm3_acc_kernel  repacked IQ3_S, IQ4_XS, Q4_K; the activation scale in the operand too, sums over a superblock
+//                     in tensor memory, one FMA per result and superblock (described further down, at the kernel).
 //
 // Serves gsq_linear above the small-batch row counts for IQ3_S in the fragment-ordered layout: the reference's
 // iq3_packed_mmq (plugin/vllm_gguf_plugin/csrc/lcpp_owned_iq3_mma.cu:768-970) and, behind it, MMQ (csrc/lcpp/ggml/src/
