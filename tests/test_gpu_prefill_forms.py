@@ -224,3 +224,34 @@ def test_q4_k_blocks_whose_minimum_dwarfs_their_scale():
         _cabi.lib.gsq_debug_gemm_variant(old)
     assert np.isfinite(y).all()
     assert product.rel_err(y, ref) <= 1e-3
+
+
+@pytest.mark.parametrize("t,form,split", [(IQ3_S, 6, False), (IQ3_S, 5, True), (IQ4_XS, 6, False), (IQ4_XS, 5, True), (Q4_K, 6, False)])
+@pytest.mark.parametrize("rows,k,m,scale", [(144, 1024, 300, 1.0), (128, 5120, 70, 1e-3), (272, 512, 513, 30.0)])
+def test_kernels_follow_the_model_of_their_own_arithmetic(t, form, split, rows, k, m, scale):
+    """The 1e-3 bound above is the distance to the reference's arithmetic. Against the CPU model of what these forms
+    compute themselves (oracle/prefill_forms.py: the same roundings to fp16, sums in float64) the kernels agree at
+    fp32 accuracy, which pins the operand layouts, the per-token scaling and Q4_K's extra columns exactly."""
+    from oracle import prefill_forms
+
+    raw = synth.make_weight(t, rows, k, 500 + rows)
+    w = torch.from_numpy(raw).to(DEV)
+    if t == IQ3_S:
+        iq3_pack.pack_(w, IQ3_S)
+    xa = synth.make_activation(m, k, 501 + m).astype(np.float64) * scale
+    xa[3, :64] = 0.0
+    xa[min(40, m - 1), :] = 0.0
+    xa[5, 7] = 40.0 * scale
+    x = synth.nudge_ties_torch(torch.from_numpy(xa.astype(np.float32)).to(torch.bfloat16)).float()
+    want = prefill_forms.product(raw, t, x.numpy(), split=split)
+    old = _cabi.lib.gsq_debug_gemm_variant(form)
+    old_mode = _cabi.lib.gsq_debug_mmv_mode(1)
+    try:
+        op = torch.ops._C_gguf.lcpp_mul_mat_iq3_packed if t == IQ3_S else torch.ops._C_gguf.lcpp_mul_mat_q
+        y = op(w, x.to(DEV), t, rows).cpu().numpy()
+    finally:
+        _cabi.lib.gsq_debug_gemm_variant(old)
+        _cabi.lib.gsq_debug_mmv_mode(old_mode)
+    err = product.rel_err(y, want)
+    print(f"type {t} form {form} {rows}x{k} m={m} scale {scale}: {err:.2e}")
+    assert err <= 3e-6, err
