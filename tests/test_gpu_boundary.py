@@ -83,6 +83,8 @@ _CAPTURE_FIRST = textwrap.dedent("""
     ("IQ4_XS", IQ4_XS, "lcpp_mul_mat_q", 200, False),
     ("IQ3_S", IQ3_S, "lcpp_mul_mat_iq3_packed", 130, True),
     ("IQ3_S", IQ3_S, "lcpp_mul_mat_iq3_packed", 512, True),
+    ("IQ4_XS", IQ4_XS, "lcpp_mul_mat_q", 600, False),
+    ("Q4_K", Q4_K, "lcpp_mul_mat_q", 600, False),
     ("Q6_K", Q6_K, "lcpp_mul_mat_vec_q", 3, False),
     ("Q6_K", Q6_K, "gsq_mul_mat_q6k_packed", 20, True),
 ])
