@@ -141,8 +141,17 @@ def test_prefill_precision_setting():
     m, k = 300, 5120
     blocks = (m + 255) // 256 * (k // 256)
     sb = lib.gsq_linear_scratch_bytes
-    # two fp16 planes per slice (split form) + Q4_K's unit of sums + one float per token of the padded range
-    need = blocks * (8 * 2 * 16384 + 8192) + (m + 255) // 256 * 256 * 4
+    per_token = (m + 255) // 256 * 256 * 4
+
+    def need(planes, sums):
+        return blocks * (8 * planes * 16384 + (8192 if sums else 0)) + per_token
+
+    # one fp16 plane of scaled products per slice in the default form (+ Q4_K's unit of sums), two in the split form
     for t, packed in ((IQ3_S, 1), (IQ4_XS, 0), (Q4_K, 0)):
-        assert sb(BIG, m, k, t, packed) >= need, (t, sb(BIG, m, k, t, packed), need)
-    assert sb(BIG, m, k, Q6_K, 1) < need            # a type without a prefill GEMM: q8_1 blocks only
+        assert need(1, t == Q4_K) <= sb(BIG, m, k, t, packed) < need(2, False), t
+    lcpp_ops.set_prefill_precision(lcpp_ops.PREFILL_SPLIT)
+    try:
+        assert sb(BIG, m, k, IQ3_S, 1) >= need(2, False)
+    finally:
+        lcpp_ops.set_prefill_precision(lcpp_ops.PREFILL_ROUNDED)
+    assert sb(BIG, m, k, Q6_K, 1) < need(1, False)            # a type without a prefill GEMM: q8_1 blocks only

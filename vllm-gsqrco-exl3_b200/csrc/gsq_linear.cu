@@ -46,8 +46,13 @@ extern "C" size_t gsq_linear_scratch_bytes(int64_t rows, int64_t m, int64_t k, i
   const size_t mmq = (size_t)(k / 128) * (size_t)m * 144, q81 = (size_t)(k / 32) * (size_t)m * 36;
   size_t tiles = gsq::gemm3_applies(ggml_type, packed, rows) ? 0 : gsq::gemm2_tile_bytes(m, k, ggml_type);
   if (gsq::gemm3_acc_applies(ggml_type, packed, rows)) {
-    const size_t t3 = gsq::gemm3_tile_bytes(m, k, 2, 1);
+    // the fp16-operand forms: one plane of scaled products per slice, two where the split form is selected (or forced
+    // through the debug switch); and the integer-sum form's units, which the dump of those sums selects
+    const int v = gsq::gemm_variant();
+    const int planes = (gsq::g_prefill_precision == GSQ_PREFILL_SPLIT || v == 5 || v == 9) ? 2 : 1;
+    const size_t t3 = gsq::gemm3_tile_bytes(m, k, planes, ggml_type == GSQ_TYPE_Q4_K), t0 = gsq::gemm3_tile_bytes(m, k, 0, 0);
     tiles = tiles > t3 ? tiles : t3;
+    tiles = tiles > t0 ? tiles : t0;
   }
   size_t b = mmq > tiles ? mmq : tiles;
   b = b > q81 ? b : q81;
