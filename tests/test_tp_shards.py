@@ -32,7 +32,7 @@ def test_plans_cover_exactly(world, n, k):
         assert max(counts) - min(counts) <= 1
 
 
-def test_uneven_k_shards_of_the_survey():
+def test_uneven_k_shards_of_the_two_k_sharded_layers():
     assert [tp.shard_plan(5120, 17408, 8, r).count for r in range(8)] == [9, 9, 9, 9, 8, 8, 8, 8]
     assert [tp.shard_plan(5120, 5120, 8, r, "K").count for r in range(8)] == [3, 3, 3, 3, 2, 2, 2, 2]
 
