@@ -73,3 +73,20 @@ def test_load_fused_layer_and_apply(gguf_file, m):
     assert product.rel_err(yh.float().cpu().numpy(), ref) <= 2e-3
     back = iq3_pack.unpack(head.weight.data, 14) if head.weight.iq3_packed else head.weight.data
     assert np.array_equal(back.cpu().numpy(), raws["output.weight"])
+
+
+def test_parallel_staging_copy():
+    """The loader's host-side copy into its staging buffer: rows split over threads, byte for byte; small matrices
+    take the plain copy."""
+    from gsq_b200 import gguf_load
+
+    rng = np.random.default_rng(5)
+    for rows, rb in ((7, 110), (1000, 2200), (17408, 2200), (4099, 3997)):
+        src = rng.integers(0, 256, size=(rows, rb), dtype=np.uint8)
+        dst = np.zeros_like(src)
+        gguf_load._parallel_copy(dst, src)
+        assert np.array_equal(dst, src)
+    big = rng.integers(0, 256, size=(20000, 1100), dtype=np.uint8)
+    view = np.zeros((20000, 1100), dtype=np.uint8)
+    gguf_load._parallel_copy(view, big[:, :1100])
+    assert np.array_equal(view, big)

@@ -22,6 +22,25 @@ from . import ops
 from .quantization import linear
 
 _CHUNK = 64 << 20
+_COPY_THREADS = 8
+_pool = None
+
+
+def _parallel_copy(dst: np.ndarray, src: np.ndarray) -> None:
+    """dst[...] = src for row matrices, the rows split over a few threads: one thread copying out of the page cache
+    reaches a fraction of what the staging buffer's transfer to the device can take (numpy's copy releases the GIL)."""
+    global _pool
+    rows = src.shape[0]
+    if src.nbytes < (8 << 20) or rows < 2 * _COPY_THREADS:
+        dst[...] = src
+        return
+    if _pool is None:
+        from concurrent.futures import ThreadPoolExecutor
+
+        _pool = ThreadPoolExecutor(max_workers=_COPY_THREADS, thread_name_prefix="gguf-stage")
+    step = -(-rows // _COPY_THREADS)
+    for f in [_pool.submit(np.copyto, dst[i:i + step], src[i:i + step]) for i in range(0, rows, step)]:
+        f.result()
 
 
 def tensors(path: str):
@@ -60,7 +79,7 @@ class _Stager:
             self.turn ^= 1
             self.events[h].synchronize()                       # the previous use of this half has been copied out
             stage = self.pin[h * _CHUNK: h * _CHUNK + c * rb].view(c, rb)
-            stage.numpy()[...] = src[i:i + c]
+            _parallel_copy(stage.numpy(), src[i:i + c])
             dst[i:i + c, :rb].copy_(stage, non_blocking=True)
             self.events[h].record()
             self.bytes += c * rb
